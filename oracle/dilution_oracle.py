@@ -1,0 +1,190 @@
+"""CPU oracle for dilution attention.  TEST INFRASTRUCTURE ONLY.
+
+This module is a plain restatement, on the CPU, of the reference operator in
+`src/dilution/kernels.py:40-68` (the fp32 spec `dilution_attention_reference`)
+and of the eager cached-decode step in `src/dilution/model.py:242-257`.  Only
+the test-suite, the smoke check and the CPU-baseline leg of the benchmark may
+import it; the product path never does, and it raises when the CUDA library is
+missing rather than falling back to anything here.
+
+Pinning: `tests/golden/make_golden.py` imports the unmodified reference and
+stores its outputs and autograd gradients for seeded inputs;
+`tests/test_oracle.py` checks every function below against those fixtures, so
+parity of this oracle is pinned to the reference itself.
+
+All functions take and return torch CPU tensors.  Arithmetic is fp32 unless the
+caller passes fp64 tensors to `dilution_dense`, which is used to measure the
+fp32 reference's own rounding error.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+EPS = 1e-9  # hard-coded twice in the reference: kernels.py:66 and :67
+
+
+def dilution_dense(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """The operator, densely, line for line as kernels.py:59-68.
+
+    q/k/v: (..., T, D).  Returns (..., T, D) in fp32 (fp64 if the inputs are
+    fp64).  Differentiable by autograd.
+    """
+    wide = torch.float64 if q.dtype == torch.float64 else torch.float32
+    seq, head_dim = q.shape[-2], q.shape[-1]
+    aff = (q.to(wide) @ k.to(wide).transpose(-2, -1)) / math.sqrt(head_dim)   # :60
+    mask = torch.tril(torch.ones(seq, seq, dtype=torch.bool))                 # :61
+    aff = aff.masked_fill(~mask, torch.finfo(torch.float32).min)              # :62
+    p = aff.softmax(dim=-1)                                                   # :64
+    committed = p.cumsum(dim=-2) - p                                          # :65
+    share = p / (committed + p + EPS)                                         # :66
+    attn = share / (share.sum(dim=-1, keepdim=True) + EPS)                    # :67
+    return attn @ v.to(wide)                                                  # :68
+
+
+def bids(q: torch.Tensor, k: torch.Tensor, q_offset: int = 0) -> torch.Tensor:
+    """Causal-softmax bids p (kernels.py:60-64) for queries at absolute
+    positions q_offset.. against keys 0..Tk-1; (..., Tq, Tk) fp32."""
+    tq, tk, head_dim = q.shape[-2], k.shape[-2], q.shape[-1]
+    aff = (q.float() @ k.float().transpose(-2, -1)) / math.sqrt(head_dim)
+    rows = torch.arange(tq)[:, None] + q_offset
+    cols = torch.arange(tk)[None, :]
+    aff = aff.masked_fill(cols > rows, torch.finfo(torch.float32).min)
+    return aff.softmax(dim=-1)
+
+
+def dilution_chunked(q, k, v, chunk: int = 1024, return_demand: bool = False):
+    """Same four lines as kernels.py:64-68, evaluated in query-row chunks with a
+    running per-key column sum, so memory is O(chunk * T) instead of O(T^2).
+
+    Returns out (..., T, D) fp32 and, with return_demand, the inclusive column
+    totals of p (..., T) — the decode accumulator after this prefix
+    (kernels.py:451-453).
+    """
+    seq = q.shape[-2]
+    lead = q.shape[:-2]
+    out = torch.empty(*lead, seq, v.shape[-1], dtype=torch.float32)
+    demand = torch.zeros(*lead, seq, dtype=torch.float32)
+    for a in range(0, seq, chunk):
+        b = min(a + chunk, seq)
+        p = bids(q[..., a:b, :], k[..., :b, :], q_offset=a)          # (..., b-a, b)
+        committed = demand[..., None, :b] + p.cumsum(dim=-2) - p      # :65 with carry
+        share = p / (committed + p + EPS)                             # :66
+        attn = share / (share.sum(dim=-1, keepdim=True) + EPS)        # :67
+        out[..., a:b, :] = attn @ v[..., :b, :].float()               # :68
+        demand[..., :b] += p.sum(dim=-2)
+    return (out, demand) if return_demand else out
+
+
+def demand_totals(q, k) -> torch.Tensor:
+    """Inclusive column totals of p over all rows, `p.sum(-2)`: what the
+    reference's tests compare `aux["committed_total"]` with
+    (tests/test_kernels.py:142)."""
+    return bids(q, k).sum(dim=-2)
+
+
+def block_carry(q, k, block: int) -> torch.Tensor:
+    """Exclusive demand at the start of every `block`-row query block:
+    carry[..., rb, j] = sum_{i < rb*block} p_ij  (tests/test_kernels.py:145-149)."""
+    p = bids(q, k)
+    seq = p.shape[-1]
+    nb = (seq + block - 1) // block
+    inclusive = p.cumsum(dim=-2)
+    rows = [torch.zeros_like(inclusive[..., 0, :])]
+    for rb in range(1, nb):
+        rows.append(inclusive[..., rb * block - 1, :])
+    return torch.stack(rows, dim=-2)
+
+
+def row_stats(q, k):
+    """(rmax, rden) of the causal softmax in the log2 domain, as K1 stores them
+    (kernels.py:159-184): rmax = max_j aff*log2(e), rden = sum_j 2^(aff*log2e - rmax)."""
+    seq, head_dim = q.shape[-2], q.shape[-1]
+    z = (q.float() @ k.float().transpose(-2, -1)) * (1.4426950408889634 / math.sqrt(head_dim))
+    mask = torch.tril(torch.ones(seq, seq, dtype=torch.bool))
+    z = z.masked_fill(~mask, float("-inf"))
+    rmax = z.max(dim=-1).values
+    rden = torch.exp2(z - rmax[..., None]).sum(dim=-1)
+    return rmax, rden
+
+
+def query_correction(q, k) -> torch.Tensor:
+    """pk = (p @ k) / sqrt(D), the saved softmax-Jacobian term for dq
+    (tests/test_kernels.py:55-59)."""
+    return (bids(q, k) @ k.float()) / math.sqrt(q.shape[-1])
+
+
+def dilution_backward(q, k, v, dout):
+    """out, dq, dk, dv by autograd through `dilution_dense`, exactly how the
+    reference's gradient tests obtain them (tests/test_kernels.py:116-120)."""
+    qs, ks, vs = (t.detach().clone().float().requires_grad_(True) for t in (q, k, v))
+    out = dilution_dense(qs, ks, vs)
+    out.backward(dout.float())
+    return out.detach(), qs.grad, ks.grad, vs.grad
+
+
+def dilution_backward_analytic(q, k, v, dout):
+    """The closed-form gradient the fused backward evaluates (the maths of
+    kernels.py:460-465, 677-826 written densely): used to pin the formulas the
+    CUDA kernels implement against autograd, independently of any kernel.
+
+    Returns dq, dk, dv and the intermediates (ghat, pk, dbar) the kernels store.
+    """
+    q, k, v, dout = (t.float() for t in (q, k, v, dout))
+    scale = 1.0 / math.sqrt(q.shape[-1])
+    p = bids(q, k)
+    c = p.cumsum(dim=-2) - p
+    inv = 1.0 / (c + p + EPS)
+    share = p * inv
+    ssum = share.sum(dim=-1, keepdim=True)
+    sinv = 1.0 / (ssum + EPS)
+    attn = share * sinv
+    out = attn @ v
+    dbar = (dout * out).sum(dim=-1, keepdim=True)
+    ds = (dout @ v.transpose(-2, -1) - dbar) * sinv            # kernels.py:463-464
+    ds = ds * (p > 0)                                          # causal mask (:465)
+    g = -ds * p * inv * inv                                    # dk_share (:761)
+    suffix = g.flip(-2).cumsum(dim=-2).flip(-2) - g            # later queries only (:763)
+    pdp = p * (ds * (c + EPS) * inv * inv + suffix)            # (:765)
+    ghat = pdp.sum(dim=-1, keepdim=True)                       # (:766)
+    dz = pdp - p * ghat
+    dq = scale * (dz @ k)
+    dk = scale * (dz.transpose(-2, -1) @ q)
+    dv = attn.transpose(-2, -1) @ dout                         # (:758)
+    pk = scale * (p @ k)
+    return dq, dk, dv, dict(ghat=ghat.squeeze(-1), pk=pk, dbar=dbar.squeeze(-1), out=out)
+
+
+def decode_step(q1, k_cache, v_cache, committed, length: int) -> torch.Tensor:
+    """One cached decode step, the eager maths of model.py:242-257 with the
+    softmax bid (kernels_bid.py bids_from_affinity, 'softmax' branch).
+
+    q1 (B,H,1,D); caches (B,H,cap,D) with the new token already at length-1;
+    committed (B,H,cap) fp32, advanced IN PLACE on [..., :length].  Returns
+    (B,H,1,D) fp32.
+    """
+    head_dim = q1.shape[-1]
+    k = k_cache[:, :, :length].float()
+    v = v_cache[:, :, :length].float()
+    c = committed[:, :, :length]
+    aff = (q1.float() @ k.transpose(-2, -1)).squeeze(2) / math.sqrt(head_dim)   # :246
+    p = aff.softmax(dim=-1)
+    share = p / (c + p + EPS)                                                   # :250-251
+    attn = share / (share.sum(dim=-1, keepdim=True) + EPS)                      # :252
+    y = attn.unsqueeze(2) @ v                                                   # :255
+    c += p                                                                      # :256
+    return y
+
+
+def equal_area_bounds(seq: int, ranks: int, tile: int = 128) -> list[int]:
+    """Contiguous query-chunk boundaries with (nearly) equal causal area per
+    rank: a_r = seq*sqrt(r/R) rounded to the tile size.  Mirrors the host-side
+    partition used by the sequence-parallel prefill so tests can cross-check it."""
+    bounds = [0]
+    for r in range(1, ranks):
+        a = int(round(seq * math.sqrt(r / ranks) / tile)) * tile
+        bounds.append(min(max(a, bounds[-1]), seq))
+    bounds.append(seq)
+    return bounds

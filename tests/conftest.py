@@ -1,0 +1,64 @@
+"""Shared test plumbing: the `gpu` marker, import paths, seeded inputs."""
+
+from __future__ import annotations
+
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def load_package():
+    """The package directory carries a hyphen, so it is imported by name."""
+    return importlib.import_module("dilution-attention_b200")
+
+
+@pytest.fixture(scope="session")
+def pkg():
+    return load_package()
+
+
+@pytest.fixture(scope="session")
+def kernels(pkg):
+    return pkg.kernels
+
+
+def seeded(shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g, dtype=torch.float32) * scale).to(dtype)
+
+
+def make_inputs(b, h, t, d, seed, scales=(1.0, 1.0, 1.0, 1.0)):
+    """q, k, v, dout from consecutive CPU seeds (same recipe as make_golden.py)."""
+    return tuple(seeded((b, h, t, d), seed + i, scales[i]) for i in range(4))
+
+
+def golden(name):
+    return np.load(os.path.join(GOLDEN, name))
+
+
+def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
+    """max-abs error over max-abs reference: the reference's own gradient metric
+    (tests/test_kernels.py:125-126 of the reference)."""
+    return (got.double() - ref.double()).abs().max().item() / (ref.double().abs().max().item() + 1e-12)

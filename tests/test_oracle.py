@@ -1,0 +1,119 @@
+"""The CPU oracle against the reference's golden outputs (no GPU needed)."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden, make_inputs, rel_err
+from oracle import dilution_oracle as O
+
+SMALL = [(1, (1, 2, 32)), (8, (2, 2, 64)), (65, (1, 2, 32)), (257, (1, 2, 64))]
+
+
+def _small(t):
+    g = golden("small_cases.npz")
+    return {k[len(f"t{t}_"):]: torch.from_numpy(g[k]) for k in g.files if k.startswith(f"t{t}_")}
+
+
+def test_config1_inputs_regenerate_bit_exact():
+    g = golden("c1_b1h4t512d64.npz")
+    q, k, v, dout = make_inputs(1, 4, 512, 64, int(g["seed"]))
+    fp = np.array([float(x.double().sum()) for x in (q, k, v, dout)] +
+                  [float(x.flatten()[0]) for x in (q, k, v, dout)])
+    assert np.array_equal(fp, g["fingerprint"])
+
+
+def test_config1_dense_forward_and_autograd_match_reference():
+    g = golden("c1_b1h4t512d64.npz")
+    q, k, v, dout = make_inputs(1, 4, 512, 64, int(g["seed"]))
+    out, dq, dk, dv = O.dilution_backward(q, k, v, dout)
+    for name, got in dict(out=out, dq=dq, dk=dk, dv=dv).items():
+        assert rel_err(got, torch.from_numpy(g[name])) < 1e-6, name
+
+
+def test_config1_analytic_backward_matches_reference():
+    g = golden("c1_b1h4t512d64.npz")
+    q, k, v, dout = make_inputs(1, 4, 512, 64, int(g["seed"]))
+    dq, dk, dv, aux = O.dilution_backward_analytic(q, k, v, dout)
+    assert rel_err(aux["out"], torch.from_numpy(g["out"])) < 1e-5
+    for name, got in dict(dq=dq, dk=dk, dv=dv).items():
+        assert rel_err(got, torch.from_numpy(g[name])) < 1e-4, name
+
+
+@pytest.mark.parametrize("t,shape", SMALL)
+def test_small_cases_all_quantities(t, shape):
+    c = _small(t)
+    out, dq, dk, dv = O.dilution_backward(c["q"], c["k"], c["v"], c["dout"])
+    assert rel_err(out, c["out"]) < 1e-6
+    for name, got in dict(dq=dq, dk=dk, dv=dv).items():
+        assert rel_err(got, c[name]) < 1e-5, name
+    assert rel_err(O.demand_totals(c["q"], c["k"]), c["demand"]) < 1e-6
+    assert rel_err(O.query_correction(c["q"], c["k"]), c["pk"]) < 1e-6
+    adq, adk, adv, _ = O.dilution_backward_analytic(c["q"], c["k"], c["v"], c["dout"])
+    for name, got in dict(dq=adq, dk=adk, dv=adv).items():
+        assert rel_err(got, c[name]) < 2e-4, name
+
+
+@pytest.mark.parametrize("t,shape", SMALL)
+@pytest.mark.parametrize("chunk", [1, 7, 64, 1024])
+def test_chunked_equals_dense(t, shape, chunk):
+    c = _small(t)
+    out, demand = O.dilution_chunked(c["q"], c["k"], c["v"], chunk=chunk, return_demand=True)
+    assert rel_err(out, c["out"]) < 2e-5
+    assert rel_err(demand, c["demand"]) < 2e-6
+
+
+def test_row_stats_rebuild_bids():
+    c = _small(257)
+    rmax, rden = O.row_stats(c["q"], c["k"])
+    d = c["q"].shape[-1]
+    z = (c["q"] @ c["k"].transpose(-2, -1)) * (1.4426950408889634 / math.sqrt(d))
+    p = torch.exp2(z - rmax[..., None]) / rden[..., None]
+    p = p * torch.ones(257, 257).tril()
+    assert rel_err(p, O.bids(c["q"], c["k"])) < 1e-5
+
+
+def test_block_carry_is_exclusive_prefix():
+    c = _small(257)
+    carry = O.block_carry(c["q"], c["k"], 64)
+    p = O.bids(c["q"], c["k"])
+    assert carry.shape[-2] == 5
+    assert torch.equal(carry[..., 0, :], torch.zeros_like(carry[..., 0, :]))
+    assert rel_err(carry[..., 3, :], p[..., :192, :].sum(-2)) < 1e-6
+
+
+def test_decode_steps_match_reference_rows():
+    g = golden("decode_b2h4d32.npz")
+    q, k, v, rows = (torch.from_numpy(g[n]) for n in ("q", "k", "v", "rows"))
+    prefix = int(g["prefix"])
+    total = q.shape[2]
+    cap = total + 3
+    kc = torch.zeros(2, 4, cap, 32)
+    vc = torch.zeros(2, 4, cap, 32)
+    kc[:, :, :prefix], vc[:, :, :prefix] = k[:, :, :prefix], v[:, :, :prefix]
+    committed = torch.zeros(2, 4, cap)
+    committed[:, :, :prefix] = torch.from_numpy(g["demand_prefix"])
+    for t in range(prefix, total):
+        kc[:, :, t], vc[:, :, t] = k[:, :, t], v[:, :, t]
+        y = O.decode_step(q[:, :, t:t + 1], kc, vc, committed, t + 1)
+        assert (y[:, :, 0] - rows[:, :, t]).abs().max().item() < 1e-5
+    assert rel_err(committed[:, :, :total], torch.from_numpy(g["demand_final"])) < 1e-5
+    assert committed[:, :, total:].abs().max().item() == 0
+
+
+def test_fp32_reference_rounding_is_far_inside_tolerance():
+    """fp64 restatement: the fp32 reference's own error, the floor for the 1e-4 bound."""
+    c = _small(257)
+    hi = O.dilution_dense(c["q"].double(), c["k"].double(), c["v"].double())
+    assert rel_err(c["out"], hi) < 1e-5
+
+
+def test_equal_area_bounds():
+    b = O.equal_area_bounds(131072, 8)
+    assert b[0] == 0 and b[-1] == 131072 and all(x % 128 == 0 for x in b)
+    areas = [b[i + 1] ** 2 - b[i] ** 2 for i in range(8)]
+    assert max(areas) / min(areas) < 1.05
