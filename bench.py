@@ -1,0 +1,383 @@
+"""Benchmark of the dilution-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline (the JSON line's metric/value): forward + backward of the training-shape
+operator, B=4 H=16 T=16384 d=64, bf16 inputs (q,k = 0.5*N(0,1), v = N(0,1),
+dout = 1e-2*N(0,1)), fp32 accumulation, as TFLOP/s by the 7-matmul causal count
+7 * N * T*(T+1) * D.  One step = one forward + one backward of that batch.
+With N GPUs every rank runs its own batch*head slab (weak scaling, no collective).
+
+Also on the line:
+  roofline      the dominant kernel (backward main pass) against the measured
+                dense-bf16 peak; per-kernel CUDA-event times in `kernels_ms`;
+  e2e           the same step through the public op with pinned HOST buffers:
+                H2D of q,k,v,dout and D2H of out,dq,dk,dv inside the timed region;
+  decode        cached decode tok/s at a 128K KV cache (batch 64 x 16 heads),
+                against the measured HBM copy bandwidth;
+  cpu_baseline  the CPU oracle timed on this box's host cores on a bounded sample.
+
+--impl reference times the reference's CPU implementation (restated in oracle/)
+on the host cores for the same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TRAIN = dict(B=4, H=16, T=16384, D=64)
+DECODE = dict(batch=64, H=16, D=64, L=131072, steps=64)
+METRIC = "fwd+bwd TFLOP/s @T=16K,d=64"
+
+
+def causal_flops(n_rows, t, d, matmuls):
+    return matmuls * n_rows * t * (t + 1) * d
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return dict(hbm=m["hbm_gbs"], tensor=m["bf16_tflops_sustained"], burst=m["bf16_tflops"],
+                    source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, burst=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while a region runs."""
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                bits = get(self.h)
+                for bit, name in names.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_sample(t, reps):
+    """The CPU oracle, forward + autograd backward, one (b,h) row at length t."""
+    from oracle import dilution_oracle as O
+    g = torch.Generator().manual_seed(1339)
+    q, k = (torch.randn(1, 1, t, 64, generator=g) * 0.5 for _ in range(2))
+    v = torch.randn(1, 1, t, 64, generator=g)
+    dout = torch.randn(1, 1, t, 64, generator=g) * 1e-2
+    O.dilution_backward(q[:, :, :256], k[:, :, :256], v[:, :, :256], dout[:, :, :256])   # warm
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.dilution_backward(q, k, v, dout)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times)
+
+
+def cpu_baseline_block(t=8192, reps=5):
+    sec = cpu_sample(t, reps)
+    return {"value": causal_flops(1, t, 64, 7) / sec / 1e12, "unit": "TFLOP/s",
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 (batch,head) row at T={t}, d=64, fp32 forward + autograd backward, "
+                      f"median of {reps}; {os.cpu_count()} logical CPUs"}
+
+
+def run_reference(args, rank):
+    """The reference's CPU path (oracle port of kernels.py:40-68) on the host cores."""
+    if rank != 0:
+        return
+    t = 8192
+    for _ in range(args.warmup):
+        cpu_sample(t, 1)
+    times = [cpu_sample(t, 1) for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    value = causal_flops(1, t, 64, 7) / sec / 1e12
+    sample = (f"each step = 1 (batch,head) row at T={t} of the B4 H16 T16384 workload, fp32 forward + "
+              f"autograd backward on {torch.get_num_threads()} host threads")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "train_fwd_bwd_B4_H16_T16384_d64", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                             "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def make_train_inputs(dev, rank):
+    """Seeded synthetic inputs of the training shape; pinned host copies kept for e2e."""
+    B, H, T, D = (TRAIN[x] for x in "BHTD")
+    g = torch.Generator().manual_seed(1339 + rank)
+    host = {}
+    for name, scale, dt in (("q", 0.5, torch.bfloat16), ("k", 0.5, torch.bfloat16),
+                            ("v", 1.0, torch.bfloat16), ("dout", 1e-2, torch.float32)):
+        x = torch.empty(B, H, T, D, dtype=torch.float32).normal_(generator=g).mul_(scale).to(dt)
+        host[name] = x.pin_memory()
+    return host, {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+
+
+def train_step(K, q, k, v, dout):
+    q.grad = k.grad = v.grad = None
+    out = K.dilution_attention(q, k, v, dot_precision="bf16")
+    out.backward(dout)
+    return out
+
+
+def run_ours(args, rank, world):
+    pkg = importlib.import_module("dilution-attention_b200")
+    K, L = pkg.kernels, pkg._lib
+    L.load()
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    B, H, T, D = (TRAIN[x] for x in "BHTD")
+    n_rows = B * H
+
+    host, devt = make_train_inputs(dev, rank)
+    q, k, v = (devt[x].requires_grad_(True) for x in "qkv")
+    dout = devt["dout"]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        train_step(K, q, k, v, dout)
+    barrier()
+
+    # --- timed region: K steps, device-resident inputs, CUDA events, per-kernel events on
+    launches0 = L.launch_count()
+    L.profile(True)
+    L.profile_collect()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            train_step(K, q, k, v, dout)
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+    prof = L.profile_collect()
+    L.profile(False)
+    launches = L.launch_count() - launches0
+    if distributed:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = tms.item()
+    ms_per_step = ms / args.steps
+    total_flops = causal_flops(n_rows, T, D, 7) * world
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # dominant kernel and its roofline (5 of the 7 matmuls live in the backward main pass)
+    kernels_ms = {name: tot / cnt for name, (cnt, tot) in prof.items()}
+    share = {"backward_main": 5, "forward_main": 1, "rowstats": 1, "colsum_scan": 1, "backward_dk_correction": 2}
+    dom = max(kernels_ms, key=kernels_ms.get) if kernels_ms else None
+    roofline = None
+    if dom is not None:
+        mm = next((m for key, m in share.items() if key in dom), 1)
+        achieved = causal_flops(n_rows, T, D, mm) / (kernels_ms[dom] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": None,
+                    "peak_source": f"{peaks['source']} sustained bf16", "matmuls_in_kernel": mm,
+                    "step_frac_of_peak": value / world / peaks["tensor"]}
+
+    # --- e2e: host buffers in, host buffers out, copies inside the timed region
+    outs = {n: torch.empty_like(host[n if n != "out" else "dout"]).pin_memory() for n in ("out",)}
+    for n in "qkv":
+        outs["d" + n] = torch.empty_like(host[n]).pin_memory()
+    dbuf = {n: torch.empty_like(devt[n]) for n in ("q", "k", "v", "dout")}
+
+    def e2e_step():
+        for n in ("q", "k", "v", "dout"):
+            dbuf[n].copy_(host[n], non_blocking=True)
+        qq, kk, vv = (dbuf[x].detach().requires_grad_(True) for x in "qkv")
+        o = train_step(K, qq, kk, vv, dbuf["dout"])
+        outs["out"].copy_(o.detach(), non_blocking=True)
+        outs["dq"].copy_(qq.grad, non_blocking=True)
+        outs["dk"].copy_(kk.grad, non_blocking=True)
+        outs["dv"].copy_(vv.grad, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 3))
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop) / e2e_steps
+    if distributed:
+        tms = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        e2e_ms = tms.item()
+    h2d = sum(host[n].numel() * host[n].element_size() for n in ("q", "k", "v", "dout"))
+    d2h = sum(x.numel() * x.element_size() for x in outs.values())
+    e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    del dbuf, devt, q, k, v, dout
+    torch.cuda.empty_cache()
+
+    # --- cached decode at a 128K cache (heads sharded across ranks)
+    decode = None
+    if not args.no_decode:
+        decode = run_decode(K, L, dev, rank, world, peaks, barrier, distributed)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "train_fwd_bwd_B4_H16_T16384_d64", "rows_per_gpu": n_rows,
+                           "global_rows": n_rows * world, "seq_len": T, "head_dim": D,
+                           "parallelism": f"batch*head slab per GPU x{world}, no collective",
+                           "l2": "inputs exceed L2 (q,k,v 134 MB each, dout/out 268 MB)",
+                           "flop_count": "7*N*T*(T+1)*D"},
+                "roofline": roofline, "kernels_ms": kernels_ms, "e2e": e2e, "gpu_launches": launches,
+                "clocks": clocks.summary(), "decode": decode}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_block()
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
+    import torch.distributed as dist
+    cfg = DECODE
+    rows = cfg["batch"] * cfg["H"] // world          # heads sharded across ranks
+    d, L0, steps = cfg["D"], cfg["L"], cfg["steps"]
+    warm = 3
+    cap = L0 + steps + warm
+    gen = torch.Generator(device=dev).manual_seed(4 + rank)
+    kc = torch.empty(rows, cap, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    vc = torch.empty(rows, cap, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    committed = torch.zeros(rows, cap, device=dev)
+    # demand after a 128K prefix: running a T=128K prefill for 1024 rows is minutes of work, so
+    # the accumulator is filled with the mean-field value of column sums, sum_{i>=j} 1/i ~ ln(L0/j)
+    j = torch.arange(1, L0 + 1, device=dev, dtype=torch.float32)
+    committed[:, :L0] = (math.log(L0) - torch.log(j) + 1.0 / j)[None, :]
+    scratch = K.decode_scratch(rows, cap, d, dev)
+    newq = torch.empty(steps + warm, rows, 1, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    kc4, vc4, c3 = kc.view(1, rows, cap, d), vc.view(1, rows, cap, d), committed.view(1, rows, cap)
+
+    def step(i, length):
+        return K.dilution_decode_step(newq[i].view(1, rows, 1, d), kc4, vc4, c3, length, scratch=scratch)
+
+    for i in range(warm):
+        step(i, L0 + i + 1)
+    barrier()
+    L.profile(True)
+    L.profile_collect()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step(warm + i, L0 + warm + i + 1)
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop) / steps
+    prof = L.profile_collect()
+    L.profile(False)
+    if distributed:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = tms.item()
+    mean_len = L0 + warm + (steps + 1) / 2
+    algo_bytes = rows * mean_len * (2 * d * 2 + 4 + 4)
+    kernel_ms = sum(tot / cnt for cnt, tot in prof.values())
+    achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+    del kc, vc, committed, scratch
+    torch.cuda.empty_cache()
+    return {"metric": "decode tok/s @128K KV", "value": cfg["batch"] / (ms * 1e-3), "unit": "tok/s",
+            "ms_per_step": ms, "rows_per_gpu": rows, "cache_len": L0, "steps": steps,
+            "config": "batch 64 x 16 heads, d=64, bf16 KV, fp32 demand; heads sharded across GPUs; "
+                      "demand initialised analytically (ln(L/j)), KV N(0,1) generated on device",
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm"], "traffic": None,
+                         "algorithmic_bytes_per_key": 2 * d * 2 + 8,
+                         "peak_source": f"{peaks['source']} copy bandwidth"},
+            "kernels_ms": {n: tot / cnt for n, (cnt, tot) in prof.items()}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

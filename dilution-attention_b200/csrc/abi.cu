@@ -1,0 +1,438 @@
+// extern "C" entry points of libdilution_b200.so: argument validation, kernel
+// selection and launches.  Declarations and the reference interface each entry
+// point replaces are in include/dilution_b200.h.
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/dilution_b200.h"
+#include "decode_kernels.cuh"
+#include "simt_kernels.cuh"
+#if __has_include("tc_kernels.cuh")
+#include "tc_kernels.cuh"
+#define DILUTION_TENSOR_PATH 1
+#endif
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DILUTION_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return DILUTION_OK;
+}
+
+// Launch accounting: a global count of kernel launches and, when enabled, a pair
+// of CUDA events around every launch on the launching stream.
+struct ProfRecord {
+  const char* name;
+  cudaEvent_t a, b;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof;
+unsigned long long g_launches = 0;
+
+struct Prof {
+  cudaStream_t st;
+  ProfRecord rec;
+  bool on;
+  Prof(const char* name, cudaStream_t s) : st(s), on(false) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    ++g_launches;
+    if (!g_prof_on) return;
+    rec.name = name;
+    if (cudaEventCreate(&rec.a) != cudaSuccess) return;
+    if (cudaEventCreate(&rec.b) != cudaSuccess) { cudaEventDestroy(rec.a); return; }
+    on = true;
+    cudaEventRecord(rec.a, st);
+  }
+  ~Prof() {
+    if (!on) return;
+    cudaEventRecord(rec.b, st);
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof.push_back(rec);
+  }
+};
+
+template <typename K>
+int set_smem(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return DILUTION_OK;
+  const cudaError_t e =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess)
+    return fail(DILUTION_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", bytes, cudaGetErrorString(e));
+  return DILUTION_OK;
+}
+
+bool valid_d(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+
+int check_common(const char* fn, int dtype, int precision, int64_t n, int64_t tq, int64_t tk,
+                 int64_t q_offset, int d) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "%s: dtype must be DILUTION_F32 or DILUTION_BF16", fn);
+  if (precision < DILUTION_PREC_IEEE || precision > DILUTION_PREC_BF16)
+    return fail(DILUTION_ERR_ARG, "%s: precision must be one of ieee, tf32, bf16", fn);
+  if (!valid_d(d))
+    return fail(DILUTION_ERR_UNSUPPORTED, "%s: head_dim %d not in {16, 32, 64, 128}", fn, d);
+  if (n < 1 || tq < 1 || tk < 1 || q_offset < 0)
+    return fail(DILUTION_ERR_ARG, "%s: sizes must be positive (n=%lld tq=%lld tk=%lld q_offset=%lld)",
+                fn, (long long)n, (long long)tq, (long long)tk, (long long)q_offset);
+  if (tq > (1 << 30) || tk > (1 << 30) || q_offset > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "%s: sequence length beyond 2^30", fn);
+  const int64_t blocks = (tq > tk ? tq : tk) / 64 + 1;
+  if (n * blocks >= (int64_t)1 << 31)
+    return fail(DILUTION_ERR_ARG, "%s: n * blocks exceeds the grid limit", fn);
+  return DILUTION_OK;
+}
+
+dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps) {
+  dil::Geom g;
+  g.n = n;
+  g.tq = (int)tq;
+  g.tk = (int)tk;
+  g.q_off = (int)q_offset;
+  g.scale = scale;
+  g.zscale = scale * dil::kLog2e;
+  g.eps = eps;
+  return g;
+}
+
+#define DIL_DISPATCH_D(d, ...)                         \
+  switch (d) {                                         \
+    case 16: { constexpr int D = 16; __VA_ARGS__; break; }   \
+    case 32: { constexpr int D = 32; __VA_ARGS__; break; }   \
+    case 64: { constexpr int D = 64; __VA_ARGS__; break; }   \
+    default: { constexpr int D = 128; __VA_ARGS__; break; }  \
+  }
+
+#define DIL_DISPATCH(dtype, d, ...)                                        \
+  if ((dtype) == DILUTION_F32) { using T = float; DIL_DISPATCH_D(d, __VA_ARGS__) } \
+  else { using T = __nv_bfloat16; DIL_DISPATCH_D(d, __VA_ARGS__) }
+
+// ---- exact-fp32 launches ---------------------------------------------------
+template <typename T, int D>
+int launch_rowstats(const void* q, const void* k, const dil::Geom& g, float* rmax, float* rden,
+                    cudaStream_t st) {
+  using namespace dil::simt;
+  auto kern = rowstats_kernel<T, D>;
+  if (int rc = set_smem(kern, smem_rowstats<D>())) return rc;
+  const int nqb = (g.tq + TS - 1) / TS;
+  {
+    Prof prof("simt_rowstats", st);
+    kern<<<(unsigned)(g.n * nqb), NT, smem_rowstats<D>(), st>>>((const T*)q, (const T*)k, g, rmax, rden);
+  }
+  return check_launch("rowstats");
+}
+
+template <typename T, int D>
+int launch_colsum(const void* q, const void* k, const dil::Geom& g, const float* rmax,
+                  const float* rden, const float* base, float* carry, float* total,
+                  cudaStream_t st) {
+  using namespace dil::simt;
+  auto kern = colsum_scan_kernel<T, D>;
+  if (int rc = set_smem(kern, smem_colsum<D>())) return rc;
+  const int nkb = (g.tk + TS - 1) / TS;
+  {
+    Prof prof("simt_colsum_scan", st);
+    kern<<<(unsigned)(g.n * nkb), NT, smem_colsum<D>(), st>>>((const T*)q, (const T*)k, g, rmax, rden,
+                                                               base, carry, total);
+  }
+  return check_launch("colsum_scan");
+}
+
+template <typename T, int D>
+int launch_main(const void* q, const void* k, const void* v, const dil::Geom& g, const float* rmax,
+                const float* rden, const float* carry, const float* base, float* out, float* ssum,
+                float* pk, cudaStream_t st) {
+  using namespace dil::simt;
+  const int nqb = (g.tq + TS - 1) / TS;
+  const unsigned grid = (unsigned)(g.n * nqb);
+  Prof prof("simt_forward_main", st);
+  if (pk) {
+    auto kern = main_kernel<T, D, true>;
+    if (int rc = set_smem(kern, smem_main<D>())) return rc;
+    kern<<<grid, NT, smem_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, rmax, rden,
+                                            carry, base, out, ssum, pk);
+  } else {
+    auto kern = main_kernel<T, D, false>;
+    if (int rc = set_smem(kern, smem_main<D>())) return rc;
+    kern<<<grid, NT, smem_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, rmax, rden,
+                                            carry, base, out, ssum, nullptr);
+  }
+  return check_launch("forward_main");
+}
+
+struct BwdScratch {
+  float *dq_main, *dk_main, *ghat, *dbar;
+};
+BwdScratch carve_bwd(void* scratch, int64_t n, int64_t t, int d) {
+  BwdScratch s;
+  s.dq_main = (float*)scratch;
+  s.dk_main = s.dq_main + n * t * d;
+  s.ghat = s.dk_main + n * t * d;
+  s.dbar = s.ghat + n * t;
+  return s;
+}
+
+template <typename T, int D>
+int launch_backward(const void* q, const void* k, const void* v, const dil::Geom& g,
+                    const float* dout, const float* out, const float* rmax, const float* rden,
+                    const float* carry, const float* ssum, const float* pk, const BwdScratch& s,
+                    void* dq, void* dk, void* dv, cudaStream_t st) {
+  using namespace dil::simt;
+  const int64_t rows = g.n * g.tq;
+  {
+    Prof prof("dbar", st);
+    dbar_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dout, out, rows, s.dbar, s.ghat, s.dq_main);
+  }
+  if (int rc = check_launch("dbar")) return rc;
+  const int nkb = (g.tk + TS - 1) / TS;
+  const unsigned grid = (unsigned)(g.n * nkb);
+  {
+    auto kern = backward_main_kernel<T, D>;
+    if (int rc = set_smem(kern, smem_bwd_main<D>())) return rc;
+    {
+      Prof prof("simt_backward_main", st);
+      kern<<<grid, NT, smem_bwd_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, dout, s.dbar,
+                                                  ssum, rmax, rden, carry, s.dq_main, s.dk_main,
+                                                  (T*)dv, s.ghat);
+    }
+    if (int rc = check_launch("backward_main")) return rc;
+  }
+  {
+    auto kern = backward_dk_correction_kernel<T, D>;
+    if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
+    {
+      Prof prof("simt_backward_dk_correction", st);
+      kern<<<grid, NT, smem_bwd_dk<D>(), st>>>((const T*)q, (const T*)k, g, rmax, rden, s.ghat,
+                                                s.dk_main, (T*)dk);
+    }
+    if (int rc = check_launch("backward_dk_correction")) return rc;
+  }
+  const int64_t total = rows * D;
+  {
+    Prof prof("dq_epilogue", st);
+    dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(s.dq_main, s.ghat, pk, total, D,
+                                                                          (T*)dq);
+  }
+  return check_launch("dq_epilogue");
+}
+
+// ---- decode ----------------------------------------------------------------
+int decode_chunk(int64_t n, int64_t len) {
+  int64_t chunk = 2048;
+  while (chunk > dil::decode::ROUND && n * ((len + chunk - 1) / chunk) < 148 * 8) chunk /= 2;
+  while ((len + chunk - 1) / chunk > dil::decode::MAX_CHUNKS) chunk *= 2;
+  return (int)chunk;
+}
+int64_t decode_stride(int64_t len) { return (len + 31) / 32 * 32; }
+
+dil::decode::Scratch carve_decode(void* scratch, int64_t n, int64_t len, int d) {
+  dil::decode::Scratch s;
+  char* p = (char*)scratch;
+  s.aff = (float*)p;
+  p += sizeof(float) * n * decode_stride(len);
+  s.part = (float2*)p;
+  p += sizeof(float2) * n * dil::decode::MAX_CHUNKS;
+  s.pout = (float*)p;
+  p += sizeof(float) * n * dil::decode::MAX_CHUNKS * d;
+  s.psum = (float*)p;
+  return s;
+}
+
+template <typename T, int D>
+int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
+                  int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
+                  cudaStream_t st) {
+  using namespace dil::decode;
+  const int chunk = decode_chunk(n, len);
+  const int nch = (int)((len + chunk - 1) / chunk);
+  const Scratch s = carve_decode(scratch, n, len, D);
+  const int64_t stride = decode_stride(len);
+  const dim3 grid((unsigned)nch, (unsigned)n);
+  {
+    Prof prof("decode_scores", st);
+    scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
+                                             scale * dil::kLog2e, stride, s.aff, s.part);
+  }
+  if (int rc = check_launch("decode scores")) return rc;
+  {
+    Prof prof("decode_sweep", st);
+    sweep_kernel<T, D><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
+                                            committed, s.pout, s.psum);
+  }
+  if (int rc = check_launch("decode sweep")) return rc;
+  {
+    Prof prof("decode_finalize", st);
+    finalize_kernel<T, D><<<(unsigned)n, D, 0, st>>>(s.pout, s.psum, nch, eps, (T*)out);
+  }
+  return check_launch("decode finalize");
+}
+
+}  // namespace
+
+extern "C" {
+
+int dilution_version(void) { return DILUTION_ABI_VERSION; }
+
+const char* dilution_last_error(void) { return g_err; }
+
+unsigned long long dilution_launch_count(void) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  return g_launches;
+}
+
+int dilution_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_on = on != 0;
+  return DILUTION_OK;
+}
+
+int dilution_profile_collect(char* buf, size_t cap) {
+  std::vector<ProfRecord> recs;
+  {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    recs.swap(g_prof);
+  }
+  struct Acc { std::string name; int count; double ms; };
+  std::vector<Acc> accs;
+  for (auto& r : recs) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.b) == cudaSuccess) cudaEventElapsedTime(&ms, r.a, r.b);
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+    bool found = false;
+    for (auto& a : accs)
+      if (a.name == r.name) { a.count++; a.ms += ms; found = true; break; }
+    if (!found) accs.push_back({r.name, 1, (double)ms});
+  }
+  std::string text;
+  char line[160];
+  for (auto& a : accs) {
+    snprintf(line, sizeof(line), "%s %d %.6f\n", a.name.c_str(), a.count, a.ms);
+    text += line;
+  }
+  if (!buf || cap == 0) return fail(DILUTION_ERR_ARG, "dilution_profile_collect: no buffer");
+  if (text.size() + 1 > cap) return fail(DILUTION_ERR_ARG, "dilution_profile_collect: buffer too small");
+  memcpy(buf, text.c_str(), text.size() + 1);
+  return DILUTION_OK;
+}
+
+int dilution_rowstats(const void* q, const void* k, int dtype, int precision, int64_t n, int64_t tq,
+                      int64_t tk, int64_t q_offset, int d, float scale, float* rmax, float* rden,
+                      void* stream) {
+  if (int rc = check_common("dilution_rowstats", dtype, precision, n, tq, tk, q_offset, d)) return rc;
+  if (!q || !k || !rmax || !rden) return fail(DILUTION_ERR_ARG, "dilution_rowstats: null pointer");
+  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
+  cudaStream_t st = (cudaStream_t)stream;
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, q_offset))
+    return dil::tc::rowstats(q, k, g, rmax, rden, st, g_err, sizeof(g_err));
+#endif
+  DIL_DISPATCH(dtype, d, return (launch_rowstats<T, D>(q, k, g, rmax, rden, st)))
+  return DILUTION_OK;
+}
+
+int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision, int64_t n,
+                         int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
+                         const float* rmax, const float* rden, const float* carry_base,
+                         float* carry, float* total, void* stream) {
+  if (int rc = check_common("dilution_colsum_scan", dtype, precision, n, tq, tk, q_offset, d)) return rc;
+  if (!q || !k || !rmax || !rden || !carry || !total)
+    return fail(DILUTION_ERR_ARG, "dilution_colsum_scan: null pointer");
+  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
+  cudaStream_t st = (cudaStream_t)stream;
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, q_offset))
+    return dil::tc::colsum_scan(q, k, g, rmax, rden, carry_base, carry, total, st, g_err, sizeof(g_err));
+#endif
+  DIL_DISPATCH(dtype, d, return (launch_colsum<T, D>(q, k, g, rmax, rden, carry_base, carry, total, st)))
+  return DILUTION_OK;
+}
+
+int dilution_forward_main(const void* q, const void* k, const void* v, int dtype, int precision,
+                          int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
+                          float eps, const float* rmax, const float* rden, const float* carry,
+                          const float* carry_base, float* out, float* ssum, float* pk,
+                          void* stream) {
+  if (int rc = check_common("dilution_forward_main", dtype, precision, n, tq, tk, q_offset, d)) return rc;
+  if (!q || !k || !v || !rmax || !rden || !carry || !out || !ssum)
+    return fail(DILUTION_ERR_ARG, "dilution_forward_main: null pointer");
+  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, eps);
+  cudaStream_t st = (cudaStream_t)stream;
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, q_offset))
+    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st, g_err, sizeof(g_err));
+#endif
+  DIL_DISPATCH(dtype, d, return (launch_main<T, D>(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st)))
+  return DILUTION_OK;
+}
+
+size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d) {
+  if (n < 1 || t < 1 || d < 1) return 0;
+  return sizeof(float) * (size_t)(2 * n * t * d + 2 * n * t);
+}
+
+int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
+                      int64_t n, int64_t t, int d, float scale, float eps, const float* dout,
+                      const float* out, const float* rmax, const float* rden, const float* carry,
+                      const float* ssum, const float* pk, void* scratch, void* dq, void* dk,
+                      void* dv, void* stream) {
+  if (int rc = check_common("dilution_backward", dtype, precision, n, t, t, 0, d)) return rc;
+  if (!q || !k || !v || !dout || !out || !rmax || !rden || !carry || !ssum || !pk || !scratch ||
+      !dq || !dk || !dv)
+    return fail(DILUTION_ERR_ARG, "dilution_backward: null pointer");
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps);
+  const BwdScratch s = carve_bwd(scratch, n, t, d);
+  cudaStream_t st = (cudaStream_t)stream;
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, 0))
+    return dil::tc::backward(q, k, v, g, dout, out, rmax, rden, carry, ssum, pk, s.dq_main, s.dk_main,
+                             s.ghat, s.dbar, dq, dk, dv, st, g_err, sizeof(g_err));
+#endif
+  DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, dout, out, rmax, rden, carry, ssum,
+                                                       pk, s, dq, dk, dv, st)))
+  return DILUTION_OK;
+}
+
+size_t dilution_decode_scratch_bytes(int64_t n, int64_t length, int d) {
+  if (n < 1 || length < 1 || d < 1) return 0;
+  return sizeof(float) * (size_t)(n * decode_stride(length)) +
+         sizeof(float) * (size_t)(n * dil::decode::MAX_CHUNKS) * (size_t)(2 + d + 1);
+}
+
+int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, int dtype, int64_t n,
+                    int64_t capacity, int64_t length, int d, float scale, float eps,
+                    float* committed, void* out, void* scratch, void* stream) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_decode: dtype must be DILUTION_F32 or DILUTION_BF16");
+  if (!valid_d(d)) return fail(DILUTION_ERR_UNSUPPORTED, "dilution_decode: head_dim %d not in {16, 32, 64, 128}", d);
+  if (n < 1 || n > 65535) return fail(DILUTION_ERR_ARG, "dilution_decode: n must be in [1, 65535] rows per call");
+  if (capacity < 1 || length < 1 || length > capacity || capacity > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "dilution_decode: length %lld outside cache capacity %lld",
+                (long long)length, (long long)capacity);
+  if (!q1 || !k_cache || !v_cache || !committed || !out || !scratch)
+    return fail(DILUTION_ERR_ARG, "dilution_decode: null pointer");
+  if (((uintptr_t)q1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+    return fail(DILUTION_ERR_ARG, "dilution_decode: q1 / caches must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
+                                                     committed, out, scratch, st)))
+  return DILUTION_OK;
+}
+
+}  // extern "C"

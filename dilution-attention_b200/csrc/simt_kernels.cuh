@@ -1,0 +1,535 @@
+// Exact-fp32 kernels for every pass of dilution attention (forward and backward).
+//
+// These serve dot_precision "ieee"/"tf32" (fp32 products, as the reference's
+// tl.dot(input_precision="ieee"), kernels.py:81-92) and every head_dim the
+// tensor-core path is not built for.  Products are plain FFMA on 64x64 tiles
+// staged in shared memory; all softmax / cumsum / share arithmetic is fp32.
+//
+// Layout of one CTA: 256 threads, one 64x64 (query x key) tile at a time.
+//   thread (ty = tid/16, tx = tid%16) owns tile rows ty+16r, columns tx+16c.
+// Shared tiles of operands are [64][D+4] fp32 (float4-aligned, conflict-free
+// for the access patterns below); score tiles are [64][65].
+#pragma once
+
+#include "common.cuh"
+
+namespace dil {
+namespace simt {
+
+constexpr int TS = 64;    // tile side
+constexpr int NT = 256;   // threads per CTA
+constexpr int SL = 65;    // leading dimension of score tiles
+
+template <int D> __host__ __device__ constexpr int ld() { return D + 4; }
+
+// Rows [row0, row0+64) of a (rows_total, D) row-major matrix -> fp32 smem tile.
+// Rows past the end are zero.
+template <typename T, int D>
+__device__ __forceinline__ void load_tile(float* s, const T* __restrict__ g, int row0,
+                                          int rows_total) {
+  constexpr int LD = ld<D>();
+  for (int idx = threadIdx.x; idx < TS * D; idx += NT) {
+    const int r = idx / D, c = idx % D;
+    const int gr = row0 + r;
+    s[r * LD + c] = (gr < rows_total) ? to_f32(g[(int64_t)gr * D + c]) : 0.f;
+  }
+}
+
+// C[i][j] = sum_d A[i][d] * B[j][d]   (A, B: [64][D+4]; C: [64][65])
+template <int D>
+__device__ __forceinline__ void score_tile(const float* A, const float* B, float* C) {
+  constexpr int LD = ld<D>();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+#pragma unroll 4
+  for (int d = 0; d < D; d += 4) {
+    float4 a[4], b[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4*>(&A[(ty + 16 * r) * LD + d]);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const float4*>(&B[(tx + 16 * c) * LD + d]);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc[r][c] = fmaf(a[r].x, b[c].x, acc[r][c]);
+        acc[r][c] = fmaf(a[r].y, b[c].y, acc[r][c]);
+        acc[r][c] = fmaf(a[r].z, b[c].z, acc[r][c]);
+        acc[r][c] = fmaf(a[r].w, b[c].w, acc[r][c]);
+      }
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) C[(ty + 16 * r) * SL + tx + 16 * c] = acc[r][c];
+}
+
+// acc[r][c] += sum_j A(i,j) * B[j][tx+16c],  i = ty+16r.
+// A is a [64][65] score tile, read transposed when TRANS_A (A(i,j) = A[j][i]).
+template <int D, bool TRANS_A>
+__device__ __forceinline__ void accum_tile(const float* A, const float* B, float (&acc)[4][D / 16]) {
+  constexpr int LD = ld<D>();
+  constexpr int DC = D / 16;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll 4
+  for (int j = 0; j < TS; ++j) {
+    float a[4], b[DC];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) a[r] = TRANS_A ? A[j * SL + ty + 16 * r] : A[(ty + 16 * r) * SL + j];
+#pragma unroll
+    for (int c = 0; c < DC; ++c) b[c] = B[j * LD + tx + 16 * c];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < DC; ++c) acc[r][c] = fmaf(a[r], b[c], acc[r][c]);
+  }
+}
+
+// Row statistics of local rows [ib*64, ib*64+64) into shared arrays (rinv = 1/rden;
+// both zero for rows past tq so that their p is exactly zero).
+__device__ __forceinline__ void load_stats(float* sM, float* sRinv, const float* rmax,
+                                           const float* rden, int64_t n, int ib, int tq) {
+  if (threadIdx.x < TS) {
+    const int i = ib * TS + threadIdx.x;
+    const bool ok = i < tq;
+    sM[threadIdx.x] = ok ? rmax[n * tq + i] : 0.f;
+    sRinv[threadIdx.x] = ok ? 1.f / rden[n * tq + i] : 0.f;
+  }
+}
+
+// Raw scores in S -> bids p in place (zero outside the causal/bounds mask).
+__device__ __forceinline__ void scores_to_bids(float* S, const float* sM, const float* sRinv,
+                                               const Geom& g, int ib, int jb) {
+  for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
+    const int i = idx >> 6, j = idx & 63;
+    const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
+    const float z = S[i * SL + j] * g.zscale;
+    S[i * SL + j] = (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] : 0.f;
+  }
+}
+
+__device__ __forceinline__ int first_query_block(int jb, int q_off) {
+  const int k0 = jb * TS;
+  return k0 > q_off ? (k0 - q_off) / TS : 0;
+}
+
+// ---------------------------------------------------------------- pass 1
+// grid = n * ceil(tq/64), longest rows first.
+template <typename T, int D>
+__global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
+                                                      const T* __restrict__ k, Geom g,
+                                                      float* __restrict__ rmax,
+                                                      float* __restrict__ rden) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int LD = ld<D>();
+  float* sQ = smem;
+  float* sK = sQ + TS * LD;
+  float* sS = sK + TS * LD;
+  const int nqb = (g.tq + TS - 1) / TS;
+  const int64_t n = blockIdx.x % g.n;
+  const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
+  load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+
+  const int r = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int ia = g.q_off + ib * TS + r;
+  float m = -INFINITY, s = 0.f;
+  const int last_key = min(g.tk - 1, g.q_off + ib * TS + TS - 1);
+  const int njb = last_key / TS + 1;
+  for (int jb = 0; jb < njb; ++jb) {
+    __syncthreads();
+    load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+    __syncthreads();
+    score_tile<D>(sQ, sK, sS);
+    __syncthreads();
+    float z[16];
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const int ja = jb * TS + part * 16 + c;
+      float val = sS[r * SL + part * 16 + c] * g.zscale;
+      if (ja > ia || ja >= g.tk) val = -INFINITY;
+      z[c] = val;
+      tmax = fmaxf(tmax, val);
+    }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const float nm = fmaxf(m, tmax);
+    float ps = 0.f;
+    if (nm > -INFINITY) {
+#pragma unroll
+      for (int c = 0; c < 16; ++c) ps += exp2f(z[c] - nm);
+    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+    if (nm > -INFINITY) {
+      s = s * exp2f(m - nm) + ps;
+      m = nm;
+    }
+  }
+  const int i = ib * TS + r;
+  if (part == 0 && i < g.tq) {
+    rmax[n * g.tq + i] = m;
+    rden[n * g.tq + i] = s;
+  }
+}
+
+// ---------------------------------------------------------------- pass 2
+// Key-stationary: one CTA per (row n, 64-key block), query blocks in causal
+// order; the running per-key demand is the exclusive scan, written as a
+// checkpoint before each query block.  grid = n * ceil(tk/64).
+template <typename T, int D>
+__global__ void __launch_bounds__(NT) colsum_scan_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
+    const float* __restrict__ rden, const float* __restrict__ carry_base,
+    float* __restrict__ carry, float* __restrict__ total) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int LD = ld<D>();
+  float* sK = smem;
+  float* sQ = sK + TS * LD;
+  float* sS = sQ + TS * LD;
+  float* sM = sS + TS * SL;
+  float* sRinv = sM + TS;
+  float* sPart = sRinv + TS;  // [4][64]
+  const int nqb = (g.tq + TS - 1) / TS;
+  const int64_t n = blockIdx.x % g.n;
+  const int jb = (int)(blockIdx.x / g.n);
+  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+
+  const int col = threadIdx.x & 63, seg = threadIdx.x >> 6;
+  const int ja = jb * TS + col;
+  const float base = (seg == 0 && carry_base != nullptr && ja < g.tk) ? carry_base[n * g.tk + ja] : 0.f;
+  float local = 0.f;
+  for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
+    __syncthreads();
+    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    __syncthreads();
+    score_tile<D>(sQ, sK, sS);
+    __syncthreads();
+    float part = 0.f;
+#pragma unroll 4
+    for (int rr = 0; rr < 16; ++rr) {
+      const int i = seg * 16 + rr;
+      const int ia = g.q_off + ib * TS + i;
+      const float z = sS[i * SL + col] * g.zscale;
+      part += (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] : 0.f;
+    }
+    sPart[seg * TS + col] = part;
+    __syncthreads();
+    if (seg == 0) {
+      if (ja < g.tk) carry[(n * nqb + ib) * (int64_t)g.tk + ja] = base + local;
+      local += (sPart[col] + sPart[TS + col]) + (sPart[2 * TS + col] + sPart[3 * TS + col]);
+    }
+  }
+  if (seg == 0 && ja < g.tk) total[n * g.tk + ja] = local;
+}
+
+// ---------------------------------------------------------------- pass 3
+// Query-stationary main pass.  grid = n * ceil(tq/64), longest rows first.
+template <typename T, int D, bool PK>
+__global__ void __launch_bounds__(NT) main_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, Geom g,
+    const float* __restrict__ rmax, const float* __restrict__ rden,
+    const float* __restrict__ carry, const float* __restrict__ carry_base,
+    float* __restrict__ out, float* __restrict__ ssum, float* __restrict__ pk) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int LD = ld<D>();
+  constexpr int DC = D / 16;
+  float* sQ = smem;
+  float* sK = sQ + TS * LD;
+  float* sV = sK + TS * LD;
+  float* sP = sV + TS * LD;
+  float* sSh = sP + TS * SL;
+  float* sM = sSh + TS * SL;
+  float* sRinv = sM + TS;
+  float* sRow = sRinv + TS;
+  const int nqb = (g.tq + TS - 1) / TS;
+  const int64_t n = blockIdx.x % g.n;
+  const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
+  load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+  load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+
+  float acc_o[4][DC], acc_pk[4][DC];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < DC; ++c) acc_o[r][c] = acc_pk[r][c] = 0.f;
+  float my_ssum = 0.f;
+  const int row = threadIdx.x >> 2, part = threadIdx.x & 3;
+
+  const int last_key = min(g.tk - 1, g.q_off + ib * TS + TS - 1);
+  const int njb = last_key / TS + 1;
+  const float* carry_row = carry + (n * nqb + ib) * (int64_t)g.tk;
+  for (int jb = 0; jb < njb; ++jb) {
+    __syncthreads();
+    load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+    load_tile<T, D>(sV, v + n * g.tk * D, jb * TS, g.tk);
+    __syncthreads();
+    score_tile<D>(sQ, sK, sP);
+    __syncthreads();
+    scores_to_bids(sP, sM, sRinv, g, ib, jb);
+    __syncthreads();
+    if (threadIdx.x < TS) {
+      const int col = threadIdx.x, ja = jb * TS + col;
+      float c = (ja < g.tk) ? carry_row[ja] : 0.f;
+      if (carry_base != nullptr && ja < g.tk) c += carry_base[n * g.tk + ja];
+      for (int i = 0; i < TS; ++i) {
+        const float p = sP[i * SL + col];
+        sSh[i * SL + col] = p / (c + p + g.eps);
+        c += p;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 16; ++c) my_ssum += sSh[row * SL + part * 16 + c];
+    accum_tile<D, false>(sSh, sV, acc_o);
+    if (PK) accum_tile<D, false>(sP, sK, acc_pk);
+  }
+  my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 1);
+  my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 2);
+  __syncthreads();
+  if (part == 0) {
+    sRow[row] = my_ssum;
+    const int i = ib * TS + row;
+    if (i < g.tq) ssum[n * g.tq + i] = my_ssum;
+  }
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int il = ty + 16 * r, i = ib * TS + il;
+    if (i >= g.tq) continue;
+    const float den = sRow[il] + g.eps;
+#pragma unroll
+    for (int c = 0; c < DC; ++c) {
+      const int64_t o = (n * g.tq + i) * D + tx + 16 * c;
+      out[o] = acc_o[r][c] / den;
+      if (PK) pk[o] = acc_pk[r][c] * g.scale;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- backward
+// dbar_i = dout_i . out_i ; one warp per row.  Also zeroes the atomics targets.
+template <int D>
+__global__ void dbar_kernel(const float* __restrict__ dout, const float* __restrict__ out,
+                            int64_t rows, float* __restrict__ dbar, float* __restrict__ ghat,
+                            float* __restrict__ dq_main) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int c = lane; c < D; c += 32) {
+    s += dout[row * D + c] * out[row * D + c];
+    dq_main[row * D + c] = 0.f;
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    dbar[row] = s;
+    ghat[row] = 0.f;
+  }
+}
+
+// Heavy reverse pass (the reference's BA, kernels.py:677-775): key-stationary,
+// query blocks from last to first so the per-key suffix of dk_share is a
+// running sum.  grid = n * ceil(t/64).
+template <typename T, int D>
+__global__ void __launch_bounds__(NT) backward_main_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, Geom g,
+    const float* __restrict__ dout, const float* __restrict__ dbar,
+    const float* __restrict__ ssum, const float* __restrict__ rmax,
+    const float* __restrict__ rden, const float* __restrict__ carry,
+    float* __restrict__ dq_main, float* __restrict__ dk_main, T* __restrict__ dv,
+    float* __restrict__ ghat) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int LD = ld<D>();
+  constexpr int DC = D / 16;
+  float* sK = smem;
+  float* sV = sK + TS * LD;
+  float* sQ = sV + TS * LD;
+  float* sDO = sQ + TS * LD;
+  float* sP = sDO + TS * LD;
+  float* sDS = sP + TS * SL;
+  float* sC = sDS + TS * SL;
+  float* sM = sC + TS * SL;
+  float* sRinv = sM + TS;
+  float* sDbar = sRinv + TS;
+  float* sSinv = sDbar + TS;
+  const int nqb = (g.tq + TS - 1) / TS;
+  const int64_t n = blockIdx.x % g.n;
+  const int jb = (int)(blockIdx.x / g.n);
+  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+  load_tile<T, D>(sV, v + n * g.tk * D, jb * TS, g.tk);
+
+  float acc_dk[4][DC], acc_dv[4][DC];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < DC; ++c) acc_dk[r][c] = acc_dv[r][c] = 0.f;
+  float sufk = 0.f;
+  const int row = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+  for (int ib = nqb - 1; ib >= first_query_block(jb, g.q_off); --ib) {
+    __syncthreads();
+    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_tile<float, D>(sDO, dout + n * g.tq * D, ib * TS, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    if (threadIdx.x < TS) {
+      const int i = ib * TS + threadIdx.x;
+      const bool ok = i < g.tq;
+      sDbar[threadIdx.x] = ok ? dbar[n * g.tq + i] : 0.f;
+      sSinv[threadIdx.x] = ok ? 1.f / (ssum[n * g.tq + i] + g.eps) : 0.f;
+    }
+    __syncthreads();
+    score_tile<D>(sQ, sK, sP);
+    score_tile<D>(sDO, sV, sDS);
+    __syncthreads();
+    scores_to_bids(sP, sM, sRinv, g, ib, jb);
+    for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
+      const int i = idx >> 6, j = idx & 63;
+      const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
+      const float ds = (sDS[i * SL + j] - sDbar[i]) * sSinv[i];   // kernels.py:463-464
+      sDS[i * SL + j] = (ja <= ia && ja < g.tk) ? ds : 0.f;
+    }
+    __syncthreads();
+    if (threadIdx.x < TS) {
+      const int col = threadIdx.x, ja = jb * TS + col;
+      float c = (ja < g.tk) ? carry[(n * nqb + ib) * (int64_t)g.tk + ja] : 0.f;
+      for (int i = 0; i < TS; ++i) {          // forward: exclusive demand
+        sC[i * SL + col] = c;
+        c += sP[i * SL + col];
+      }
+      float r = sufk;                          // reverse: suffix of dk_share
+      for (int i = TS - 1; i >= 0; --i) {
+        const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
+        const float inv = 1.f / (cc + p + g.eps);
+        const float inv2 = inv * inv;
+        const float dk_share = -ds * p * inv2;                       // :761
+        sDS[i * SL + col] = p * (ds * (cc + g.eps) * inv2 + r);      // pdp, :765
+        sP[i * SL + col] = p * inv * sSinv[i];                       // attn, :757
+        r += dk_share;
+      }
+      sufk = r;
+    }
+    __syncthreads();
+    {
+      float gs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) gs += sDS[row * SL + part * 16 + c];
+      gs += __shfl_xor_sync(0xffffffffu, gs, 1);
+      gs += __shfl_xor_sync(0xffffffffu, gs, 2);
+      const int i = ib * TS + row;
+      if (part == 0 && i < g.tq) atomicAdd(&ghat[n * g.tq + i], gs);
+    }
+    accum_tile<D, true>(sP, sDO, acc_dv);
+    accum_tile<D, true>(sDS, sQ, acc_dk);
+    float dqp[4][DC];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < DC; ++c) dqp[r][c] = 0.f;
+    accum_tile<D, false>(sDS, sK, dqp);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = ib * TS + ty + 16 * r;
+      if (i >= g.tq) continue;
+#pragma unroll
+      for (int c = 0; c < DC; ++c)
+        atomicAdd(&dq_main[(n * g.tq + i) * D + tx + 16 * c], dqp[r][c] * g.scale);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = jb * TS + ty + 16 * r;
+    if (j >= g.tk) continue;
+#pragma unroll
+    for (int c = 0; c < DC; ++c) {
+      const int64_t o = (n * g.tk + j) * D + tx + 16 * c;
+      dk_main[o] = acc_dk[r][c] * g.scale;
+      dv[o] = from_f32<T>(acc_dv[r][c]);
+    }
+  }
+}
+
+// Softmax-Jacobian correction for dk (the reference's BC, kernels.py:777-809):
+// dk = dk_main - scale * p^T (ghat q).  grid = n * ceil(t/64).
+template <typename T, int D>
+__global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
+    const float* __restrict__ rden, const float* __restrict__ ghat,
+    const float* __restrict__ dk_main, T* __restrict__ dk) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int LD = ld<D>();
+  constexpr int DC = D / 16;
+  float* sK = smem;
+  float* sQ = sK + TS * LD;
+  float* sP = sQ + TS * LD;
+  float* sM = sP + TS * SL;
+  float* sRinv = sM + TS;
+  float* sG = sRinv + TS;
+  const int nqb = (g.tq + TS - 1) / TS;
+  const int64_t n = blockIdx.x % g.n;
+  const int jb = (int)(blockIdx.x / g.n);
+  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+  float acc[4][DC];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < DC; ++c) acc[r][c] = 0.f;
+  for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
+    __syncthreads();
+    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    if (threadIdx.x < TS) {
+      const int i = ib * TS + threadIdx.x;
+      sG[threadIdx.x] = i < g.tq ? ghat[n * g.tq + i] : 0.f;
+    }
+    __syncthreads();
+    score_tile<D>(sQ, sK, sP);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
+      const int i = idx >> 6, j = idx & 63;
+      const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
+      const float z = sP[i * SL + j] * g.zscale;
+      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] * sG[i] : 0.f;
+    }
+    __syncthreads();
+    accum_tile<D, true>(sP, sQ, acc);
+  }
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = jb * TS + ty + 16 * r;
+    if (j >= g.tk) continue;
+#pragma unroll
+    for (int c = 0; c < DC; ++c) {
+      const int64_t o = (n * g.tk + j) * D + tx + 16 * c;
+      dk[o] = from_f32<T>(dk_main[o] - acc[r][c] * g.scale);
+    }
+  }
+}
+
+// dq = dq_main - ghat * pk  (kernels.py:814-826), stored in the input dtype.
+template <typename T>
+__global__ void dq_epilogue_kernel(const float* __restrict__ dq_main,
+                                   const float* __restrict__ ghat, const float* __restrict__ pk,
+                                   int64_t total, int d, T* __restrict__ dq) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  dq[idx] = from_f32<T>(dq_main[idx] - ghat[idx / d] * pk[idx]);
+}
+
+// Shared-memory sizes (bytes) of the kernels above.
+template <int D> constexpr size_t smem_rowstats() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL); }
+template <int D> constexpr size_t smem_colsum() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 2 * TS + 4 * TS); }
+template <int D> constexpr size_t smem_main() { return sizeof(float) * (3 * TS * ld<D>() + 2 * TS * SL + 3 * TS); }
+template <int D> constexpr size_t smem_bwd_main() { return sizeof(float) * (4 * TS * ld<D>() + 3 * TS * SL + 4 * TS); }
+template <int D> constexpr size_t smem_bwd_dk() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 3 * TS); }
+
+}  // namespace simt
+}  // namespace dil

@@ -1,0 +1,306 @@
+"""Dilution attention on B200: the `dilution.kernels` entry points, unchanged.
+
+Same names, arguments, return values and errors as the reference module
+(src/dilution/kernels.py), backed by hand-written sm_100a CUDA kernels in
+libdilution_b200.so instead of Triton:
+
+    dilution_attention_reference(q, k, v)                      kernels.py:40-68
+    dilution_attention_forward(q, k, v, dot_precision=...,     kernels.py:328-455
+                               return_aux=..., _save_pk=...)
+    dilution_attention(q, k, v, dot_precision=...)             kernels.py:906-930
+    dilution_decode_step(q1, k_cache, v_cache, committed, t)   kernels.py:994-1038
+
+The operator (docs/operator.md of the reference):
+
+    p         = causal_softmax(q k^T / sqrt(D))
+    committed = exclusive cumsum of p down the query axis, per key
+    share     = p / (committed + p + 1e-9)
+    out       = (share / (rowsum(share) + 1e-9)) @ v            fp32
+
+Forward = three passes (row statistics; per-key column sums with their
+exclusive scan over query blocks; main pass), backward = a reverse key-stationary
+pass plus the softmax-Jacobian corrections, decode = a bandwidth-bound streaming
+kernel.  All tensors must live on a CUDA device; there is no CPU, Triton or
+eager fallback — a missing library raises RuntimeError.
+
+Triton tuning keywords of the reference (block_m, block_n, num_warps, num_stages,
+bwd_*, b3_*, b4_*) are accepted and ignored.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+EPS = 1e-9                      # kernels.py:66-67 of the reference, twice
+CARRY_ROWS = _lib.CARRY_ROWS    # query rows per demand checkpoint
+KEY_FORWARD_MIN_SEQ = 256       # read by the reference's scripts; no meaning here
+HAS_TRITON = False              # this backend never uses Triton
+HAS_CUDA_LIB = _lib.available()
+
+
+def _resolve_precision(dot_precision: str) -> tuple[int, str]:
+    """"ieee" / "tf32": fp32 products; "bf16": bf16 tensor-core operands
+    (kernels.py:318-325, same return values and error)."""
+    if dot_precision == "bf16":
+        return 1, "tf32"
+    if dot_precision in ("ieee", "tf32"):
+        return 0, dot_precision
+    raise ValueError("dot_precision must be one of ieee, tf32, bf16")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _prepare(q, k, v, dot_precision):
+    """Contiguous (n, t, d) operands in the dtype the kernels take
+    (kernels.py:362-364), the dtype code and the precision code."""
+    lowp, _ = _resolve_precision(dot_precision)
+    if not q.is_cuda:
+        raise RuntimeError("dilution attention needs CUDA tensors (no CPU fallback in this backend)")
+    batch, heads, seq, head_dim = q.shape
+    n = batch * heads
+    want = torch.bfloat16 if (lowp or q.dtype == torch.bfloat16) else torch.float32
+    ops = []
+    for x in (q, k, v):
+        if x is None:
+            ops.append(None)
+            continue
+        x = x.reshape(n, x.shape[2], head_dim)
+        if x.dtype != want:
+            x = x.to(want)
+        ops.append(x.contiguous())
+    code = _lib.BF16 if want == torch.bfloat16 else _lib.F32
+    return ops, code, _lib.PREC[dot_precision], n
+
+
+def _forward_rows(lib, qf, kf, vf, code, prec, scale, out, ssum, rmax, rden, carry, total, pk,
+                  q_offset=0, carry_base=None):
+    """Passes 1-3 on a slab of (batch*head) rows."""
+    n, tq, d = qf.shape
+    tk = kf.shape[1]
+    st = _stream(qf.device)
+    _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
+                                     d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
+    _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
+                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None,
+                                        carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
+    _lib.check(lib.dilution_forward_main(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec,
+                                         n, tq, tk, q_offset, d, scale, EPS,
+                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
+                                         _ptr(carry_base), out.data_ptr(), ssum.data_ptr(), _ptr(pk), st),
+               "dilution_forward_main")
+
+
+def dilution_attention_forward(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    dot_precision: str = "ieee",
+    block_m: int = 64,
+    block_n: int = 64,
+    return_aux: bool = False,
+    num_warps: int = 4,
+    num_stages: int = 2,
+    _save_pk: bool = False,
+    scratch_budget_gib: float = 16.0,
+):
+    """Fused forward; returns fp32 (B, H, T, D)  (kernels.py:328-455).
+
+    With return_aux=True also returns the aux dict of the reference: pk (or
+    None), rmax, rden, carry, ssum, bwd_block_m, block_m, block_n,
+    dot_precision, num_warps and committed_total (B, H, T) fp32 — the inclusive
+    column totals of p, i.e. the decode accumulator after this prefix.
+    `carry` holds one per-key demand checkpoint every aux["bwd_block_m"] query
+    rows; entries for keys a row block cannot see are unwritten.
+
+    Without return_aux the (batch*head) rows are processed in slabs so that the
+    quadratic carry scratch stays under scratch_budget_gib; rows are independent,
+    so this changes nothing numerically.
+    """
+    lib = _lib.load()
+    (qf, kf, vf), code, prec, n = _prepare(q, k, v, dot_precision)
+    batch, heads, seq, head_dim = q.shape
+    dev = q.device
+    scale = 1.0 / math.sqrt(head_dim)
+    ncb = (seq + CARRY_ROWS - 1) // CARRY_ROWS
+
+    f32 = dict(device=dev, dtype=torch.float32)
+    out = torch.empty(n, seq, head_dim, **f32)
+    pk = torch.empty(n, seq, head_dim, **f32) if _save_pk else None
+    rmax = torch.empty(n, seq, **f32)
+    rden = torch.empty(n, seq, **f32)
+    ssum = torch.empty(n, seq, **f32)
+    total = torch.empty(n, seq, **f32)
+
+    rows = n
+    if not return_aux:
+        per_row = ncb * seq * 4
+        rows = max(1, min(n, int(scratch_budget_gib * 2**30) // max(per_row, 1)))
+    carry = torch.empty(rows, ncb, seq, **f32)
+    for a in range(0, n, rows):
+        b = min(a + rows, n)
+        _forward_rows(lib, qf[a:b], kf[a:b], vf[a:b], code, prec, scale, out[a:b], ssum[a:b],
+                      rmax[a:b], rden[a:b], carry[: b - a], total[a:b],
+                      None if pk is None else pk[a:b])
+
+    result = out.reshape(batch, heads, seq, head_dim)
+    if return_aux:
+        aux = dict(pk=pk, rmax=rmax, rden=rden, carry=carry, ssum=ssum, bwd_block_m=CARRY_ROWS,
+                   block_m=block_m, block_n=block_n, dot_precision=dot_precision,
+                   num_warps=num_warps,
+                   committed_total=total.reshape(batch, heads, seq))
+        return result, aux
+    return result
+
+
+class _DilutionAttentionFn(torch.autograd.Function):
+    """Autograd op (kernels.py:829-903): fp32 output; dq, dk, dv in the input dtypes."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, dot_precision):
+        out, aux = dilution_attention_forward(
+            q, k, v, dot_precision=dot_precision, return_aux=True,
+            _save_pk=any(ctx.needs_input_grad[:3]))
+        ctx.save_for_backward(q, k, v, out, aux["rmax"], aux["rden"], aux["carry"], aux["ssum"], aux["pk"])
+        ctx.dot_precision = dot_precision
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, rmax, rden, carry, ssum, pk = ctx.saved_tensors
+        lib = _lib.load()
+        batch, heads, seq, head_dim = q.shape
+        (qf, kf, vf), code, prec, n = _prepare(q, k, v, ctx.dot_precision)
+        dev = q.device
+        dof = dout.reshape(n, seq, head_dim).float().contiguous()
+        of = out.reshape(n, seq, head_dim)
+        gdt = qf.dtype
+        dq = torch.empty(n, seq, head_dim, device=dev, dtype=gdt)
+        dk = torch.empty_like(dq)
+        dv = torch.empty_like(dq)
+        nbytes = lib.dilution_backward_scratch_bytes(n, seq, head_dim)
+        scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+        _lib.check(lib.dilution_backward(
+            qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim,
+            1.0 / math.sqrt(head_dim), EPS, dof.data_ptr(), of.data_ptr(),
+            rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), ssum.data_ptr(), pk.data_ptr(),
+            scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _stream(dev)),
+            "dilution_backward")
+        shape4 = (batch, heads, seq, head_dim)
+        return (dq.reshape(shape4).to(q.dtype), dk.reshape(shape4).to(k.dtype),
+                dv.reshape(shape4).to(v.dtype), None)
+
+
+def dilution_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    dot_precision: str = "bf16",
+    block_m: int = 64,
+    block_n: int = 64,
+    num_warps: int = 4,
+    bwd_num_warps: int = 4,
+    bwd_num_stages: int = 1,
+    b3_block_n: int | None = None,
+    b3_num_warps: int | None = None,
+    b4_num_warps: int | None = 4,
+) -> torch.Tensor:
+    """Differentiable fused dilution attention (kernels.py:906-930).
+
+    "bf16" (default): bf16 tensor-core operands, fp32 accumulation and fp32
+    cumsum/share maths; "tf32"/"ieee": fp32 products.
+    """
+    _resolve_precision(dot_precision)
+    return _DilutionAttentionFn.apply(q, k, v, dot_precision)
+
+
+def dilution_attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """The operator in fp32 with the reference's signature (kernels.py:40-68):
+    q/k/v (B, H, T, D) -> (B, H, T, D) fp32, differentiable.
+
+    Inputs are cast to fp32 and every product is an fp32 FMA on the GPU; unlike
+    the reference's dense PyTorch version nothing (T x T)-shaped is materialised.
+    """
+    return _DilutionAttentionFn.apply(q.float(), k.float(), v.float(), "ieee")
+
+
+def decode_scratch(n: int, capacity: int, head_dim: int, device) -> torch.Tensor:
+    """Scratch buffer for dilution_decode_step, big enough for any length up to
+    `capacity`.  Reuse it across steps to keep allocation out of the token loop."""
+    nbytes = _lib.load().dilution_decode_scratch_bytes(n, capacity, head_dim)
+    return torch.empty(nbytes, device=device, dtype=torch.uint8)
+
+
+def dilution_decode_step(
+    q1: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    committed: torch.Tensor,
+    length: int,
+    block_n: int = 512,
+    num_warps: int = 8,
+    scratch: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Fused decode step (kernels.py:994-1038).  Returns (B, H, 1, D) in q1.dtype.
+
+    q1: (B, H, 1, D).  k_cache / v_cache: contiguous (B, H, capacity, D) buffers
+    whose first `length` positions are valid, the new token already written at
+    length-1.  committed: contiguous (B, H, capacity) fp32 accumulator, advanced
+    IN PLACE to include this row; positions >= length are never touched.
+    `scratch` (optional, from decode_scratch) avoids a per-call allocation.
+    """
+    lib = _lib.load()
+    batch, heads, one, head_dim = q1.shape
+    if one != 1:
+        raise ValueError("decode step takes exactly one query row per (batch, head)")
+    if head_dim & (head_dim - 1):
+        raise ValueError("head_dim must be a power of two")
+    capacity = k_cache.shape[2]
+    if not 1 <= length <= capacity:
+        raise ValueError(f"length {length} outside cache capacity {capacity}")
+    if not q1.is_cuda:
+        raise RuntimeError("dilution decode needs CUDA tensors (no CPU fallback in this backend)")
+    if q1.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("decode supports float32 and bfloat16 caches")
+    if k_cache.dtype != q1.dtype or v_cache.dtype != q1.dtype or committed.dtype != torch.float32:
+        raise ValueError("caches must have q1's dtype and committed must be float32")
+    n = batch * heads
+    qf = q1.reshape(n, head_dim)
+    if not qf.is_contiguous():
+        qf = qf.contiguous()
+    kf = k_cache.view(n, capacity, head_dim)      # .view: the caches must be contiguous
+    vf = v_cache.view(n, capacity, head_dim)
+    cf = committed.view(n, capacity)
+    out = torch.empty(n, head_dim, device=q1.device, dtype=q1.dtype)
+    need = lib.dilution_decode_scratch_bytes(n, length, head_dim)
+    if scratch is None or scratch.numel() * scratch.element_size() < need:
+        scratch = torch.empty(need, device=q1.device, dtype=torch.uint8)
+    code = _lib.BF16 if q1.dtype == torch.bfloat16 else _lib.F32
+    _lib.check(lib.dilution_decode(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, n, capacity,
+                                   length, head_dim, 1.0 / math.sqrt(head_dim), EPS,
+                                   cf.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                   _stream(q1.device)), "dilution_decode")
+    return out.view(batch, heads, 1, head_dim)
+
+
+def install(target=None):
+    """Plug this backend into the reference package: assign the fused entry
+    points onto `dilution.kernels` (or `target`), the same way the reference's
+    scripts/train_kernel_variant.py:39 swaps implementations.  The model looks
+    the functions up at call time (model.py:145-150), so DilutionLM then runs on
+    these kernels after enable_dilution_kernel()."""
+    if target is None:
+        import dilution.kernels as target  # the reference package, if importable
+    for name in ("dilution_attention_forward", "dilution_attention", "dilution_decode_step"):
+        setattr(target, name, globals()[name])
+    target.HAS_TRITON = True   # the reference gates its kernel path on this flag
+    return target

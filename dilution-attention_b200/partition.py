@@ -1,0 +1,168 @@
+"""Partitioning of dilution attention over the GPUs of one box.
+
+Two ways, both one process per GPU (`torch.distributed`, NCCL on GPUs, gloo in
+the CPU tests):
+
+* batch x head rows are independent (every kernel indexes by the row n = b*H+h
+  only), so training and decode shard the rows with no collective at all:
+  `row_shard`.
+
+* long-context prefill is sequence-parallel: rank r owns the contiguous query
+  rows [a_r, a_{r+1}) — boundaries chosen for equal causal AREA, since with equal
+  lengths the last rank would own (2R-1)/R^2 of the work — all-gathers K/V into
+  its own memory, runs the three forward passes on its chunk, and needs exactly
+  one exchange: the exclusive prefix over ranks of the per-key column sums of p
+  (`exclusive_demand_prefix`).  NCCL has no scan collective, so the prefix is an
+  all-gather of the (rows, T) sums followed by a local masked sum.
+
+Nothing here touches device memory of a peer directly: remote data always lands
+in local memory through the collective first.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from . import kernels as K
+
+TILE = 128  # chunk boundaries are multiples of the largest kernel tile
+
+
+def row_shard(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous [begin, end) slice of the batch*head rows owned by `rank`."""
+    base, extra = divmod(n_rows, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def equal_area_bounds(seq: int, world: int, tile: int = TILE) -> list[int]:
+    """Query-chunk boundaries a_0=0 <= ... <= a_R=seq with near-equal causal
+    area a_{r+1}^2 - a_r^2, rounded to `tile`."""
+    bounds = [0]
+    for r in range(1, world):
+        a = int(round(seq * math.sqrt(r / world) / tile)) * tile
+        bounds.append(min(max(a, bounds[-1]), seq))
+    bounds.append(seq)
+    return bounds
+
+
+def exclusive_demand_prefix(local_total: torch.Tensor, seq: int, group=None):
+    """Cross-rank exclusive scan of per-key demand.
+
+    local_total: (rows, tk_r) column sums of p over THIS rank's query rows (keys
+    beyond tk_r are implicitly zero).  Returns (base, demand):
+      base   (rows, tk_r): demand committed by ranks before this one,
+      demand (rows, seq) : demand of all ranks, the decode accumulator.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    rows, tk = local_total.shape
+    padded = local_total.new_zeros(rows, seq)
+    padded[:, :tk] = local_total
+    gathered = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(gathered, padded, group=group)
+    base = padded.new_zeros(rows, seq)
+    for s in range(rank):
+        base += gathered[s]
+    demand = base.clone()
+    for s in range(rank, world):
+        demand += gathered[s]
+    return base[:, :tk].contiguous(), demand
+
+
+def gather_keys(k_local: torch.Tensor, v_local: torch.Tensor, bounds: list[int], group=None):
+    """All-gather the K/V chunks of every rank into local memory and return the
+    prefix [0, a_{rank+1}) this rank's queries can see.  k_local/v_local:
+    (rows, a_{r+1}-a_r, d)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    rows, _, d = k_local.shape
+    longest = max(bounds[r + 1] - bounds[r] for r in range(world))
+    pad = k_local.new_zeros(2, rows, longest, d)
+    pad[0, :, : k_local.shape[1]] = k_local
+    pad[1, :, : v_local.shape[1]] = v_local
+    parts = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(parts, pad, group=group)
+    end = bounds[rank + 1]
+    k = k_local.new_empty(rows, end, d)
+    v = v_local.new_empty(rows, end, d)
+    for s in range(rank + 1):
+        a, b = bounds[s], bounds[s + 1]
+        k[:, a:b] = parts[s][0, :, : b - a]
+        v[:, a:b] = parts[s][1, :, : b - a]
+    return k, v
+
+
+def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "bf16",
+                  demand_prefix=None, exchange=None):
+    """Forward of one contiguous query chunk against the keys it can see.
+
+    q_local (rows, tq, d) at absolute positions q_offset..; k_seen/v_seen
+    (rows, q_offset+tq, d).  `exchange(local_total)` -> base is called between
+    pass 2 and pass 3 and returns the demand committed by earlier chunks (the
+    cross-rank exscan, or a cached prefix); `demand_prefix` supplies it directly.
+    Returns out (rows, tq, d) fp32 and local_total (rows, tk) fp32.
+    """
+    lib = _lib.load()
+    rows, tq, d = q_local.shape
+    tk = k_seen.shape[1]
+    dev = q_local.device
+    lowp, _ = K._resolve_precision(dot_precision)
+    want = torch.bfloat16 if (lowp or q_local.dtype == torch.bfloat16) else torch.float32
+    qf, kf, vf = (x.to(want).contiguous() for x in (q_local, k_seen, v_seen))
+    code = _lib.BF16 if want == torch.bfloat16 else _lib.F32
+    prec = _lib.PREC[dot_precision]
+    scale = 1.0 / math.sqrt(d)
+    f32 = dict(device=dev, dtype=torch.float32)
+    ncb = (tq + K.CARRY_ROWS - 1) // K.CARRY_ROWS
+    rmax, rden, ssum = (torch.empty(rows, tq, **f32) for _ in range(3))
+    carry = torch.empty(rows, ncb, tk, **f32)
+    total = torch.empty(rows, tk, **f32)
+    out = torch.empty(rows, tq, d, **f32)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, rows, tq, tk, q_offset,
+                                     d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
+    _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, rows, tq, tk, q_offset,
+                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None,
+                                        carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
+    base = demand_prefix
+    if exchange is not None:
+        base = exchange(total)
+    if base is not None:
+        base = base.to(torch.float32).contiguous()
+    _lib.check(lib.dilution_forward_main(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec,
+                                         rows, tq, tk, q_offset, d, scale, K.EPS,
+                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
+                                         None if base is None else base.data_ptr(),
+                                         out.data_ptr(), ssum.data_ptr(), None, st),
+               "dilution_forward_main")
+    return out, total
+
+
+def sequence_parallel_prefill(q_local, k_local, v_local, seq: int, bounds: list[int] | None = None,
+                              dot_precision: str = "bf16", group=None):
+    """Sequence-parallel prefill of a (rows, seq, d) problem.
+
+    Every rank passes ITS chunk of q, k, v (rows, a_{r+1}-a_r, d) for the
+    boundaries `bounds` (default: equal_area_bounds).  Returns
+      out    (rows, a_{r+1}-a_r, d) fp32 for the local query rows,
+      demand (rows, seq) fp32: the decode accumulator, identical on all ranks.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if bounds is None:
+        bounds = equal_area_bounds(seq, world)
+    k_seen, v_seen = gather_keys(k_local, v_local, bounds, group)
+    result = {}
+
+    def exchange(local_total):
+        base, demand = exclusive_demand_prefix(local_total, seq, group)
+        result["demand"] = demand
+        return base
+
+    out, _ = prefill_chunk(q_local, k_seen, v_seen, bounds[rank], dot_precision, exchange=exchange)
+    return out, result["demand"]

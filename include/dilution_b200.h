@@ -1,0 +1,142 @@
+/*
+ * dilution_b200.h — C ABI of libdilution_b200.so (sm_100a).
+ *
+ * Drop-in boundary for ONE path of Royer-Research-Labs/Dilution-Attention: the
+ * entry points of its `dilution.kernels` module (src/dilution/kernels.py).  The
+ * reference launches Triton kernels from Python; a host that wants this library
+ * instead binds the functions below (ctypes from Python) and
+ * keeps the Python-level signatures unchanged.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer owned by the caller; nothing here
+ *    allocates, frees or synchronises; every launch goes to `stream`
+ *    (a cudaStream_t passed as void*);
+ *  - q/k/v/… are contiguous (n, t, d) row-major, n = batch*heads, exactly what
+ *    the reference builds with reshape(n, seq, d).contiguous() (kernels.py:362-364);
+ *  - `dtype` is the element type of q/k/v (and of the decode caches);
+ *  - `precision` mirrors the reference's dot_precision (kernels.py:318-325):
+ *    IEEE/TF32 keep fp32 products (exact fp32 FMA here, which satisfies both),
+ *    BF16 uses bf16 tensor-core operands with fp32 accumulation;
+ *  - row statistics are in the log2 domain as in kernels.py:159-184:
+ *    rmax = max_j z_ij, rden = sum_j 2^(z_ij - rmax), z = q.k * scale * log2(e);
+ *  - `q_offset`: absolute position of local query row 0 (0 for a whole sequence;
+ *    a multiple of 128 for a sequence-parallel rank that owns a query chunk).
+ *    Query i (local) sees keys j <= i + q_offset, j < tk;
+ *  - carry rows are checkpoints of per-key cumulative demand every
+ *    DILUTION_CARRY_ROWS query rows: carry[n][rb][j] = (carry_base[n][j]) +
+ *    sum over local rows i < rb*DILUTION_CARRY_ROWS of p_ij.  Entries for keys
+ *    a row block cannot see are left unwritten (as kernels.py:353-354);
+ *  - return value 0 = ok; otherwise an error code, with a message available
+ *    from dilution_last_error() (thread-local).
+ */
+#ifndef DILUTION_B200_H
+#define DILUTION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DILUTION_ABI_VERSION 1
+#define DILUTION_CARRY_ROWS 64      /* query rows per carry checkpoint (aux["bwd_block_m"]) */
+
+enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
+enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */
+enum {
+  DILUTION_OK = 0,
+  DILUTION_ERR_ARG = 1,        /* bad size / dtype / null pointer / alignment */
+  DILUTION_ERR_UNSUPPORTED = 2,/* head_dim or dtype combination not built */
+  DILUTION_ERR_CUDA = 3,       /* a CUDA runtime call or launch failed */
+  DILUTION_ERR_DEVICE = 4      /* a kernel reported a bounded wait that ran out */
+};
+
+/* ABI version of the loaded library. No reference counterpart (the reference's
+ * availability flag is HAS_TRITON, kernels.py:31-37). */
+int dilution_version(void);
+
+/* Message of the last failing call on this host thread ("" if none). */
+const char* dilution_last_error(void);
+
+/* Kernel launches issued by this library so far in this process.
+ * No reference counterpart. */
+unsigned long long dilution_launch_count(void);
+
+/* Per-kernel timing with CUDA events on the launching stream (off by default).
+ * The reference profiles the same way from Python, with torch.profiler and CUDA
+ * events (scripts/step_profile.py:29-47, scripts/profile_kernels.py:115-124).
+ * dilution_profile_collect waits for the recorded events, writes one line
+ * "<kernel> <launches> <total_ms>" per kernel into buf and clears the records. */
+int dilution_profile_enable(int on);
+int dilution_profile_collect(char* buf, size_t cap);
+
+/* Pass 1 — causal-softmax row statistics for every query.
+ * Replaces _dilution_k1's sweep 1 (kernels.py:158-185).
+ * rmax, rden: (n, tq) fp32 out. */
+int dilution_rowstats(const void* q, const void* k, int dtype, int precision,
+                      int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
+                      float* rmax, float* rden, void* stream);
+
+/* Pass 2 — per-(query-block, key-block) column sums of p and their exclusive
+ * scan over query blocks, in one key-stationary sweep.
+ * Replaces _dilution_k1's sweep 2 (kernels.py:190-198) + _dilution_scan (:250-264).
+ * carry_base: optional (n, tk) fp32 demand already committed by earlier query
+ *   chunks (sequence-parallel ranks), or NULL.
+ * carry: (n, ceil(tq/DILUTION_CARRY_ROWS), tk) fp32 out.
+ * total: (n, tk) fp32 out, column sums of p over the LOCAL rows (the decode
+ *   accumulator `committed_total`, kernels.py:451-453, when tq covers the sequence). */
+int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
+                         int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
+                         const float* rmax, const float* rden, const float* carry_base,
+                         float* carry, float* total, void* stream);
+
+/* Pass 3 — main forward pass: rebuild p, committed = carry + in-tile exclusive
+ * column cumsum, share = p/(committed+p+eps), out = (share@v)/(rowsum(share)+eps).
+ * Replaces _dilution_k2 (kernels.py:266-315); with pk != NULL it also emits
+ * pk = scale * p@k (n, tq, d) fp32, which the reference's K1 saves for the
+ * backward (kernels.py:161-188).
+ * carry_base: optional (n, tk) fp32 added to every carry row on the fly (demand
+ *   committed by earlier query chunks, known only after pass 2 ran), or NULL.
+ * out: (n, tq, d) fp32.  ssum: (n, tq) fp32 row sums of share. */
+int dilution_forward_main(const void* q, const void* k, const void* v, int dtype, int precision,
+                          int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d,
+                          float scale, float eps,
+                          const float* rmax, const float* rden, const float* carry,
+                          const float* carry_base,
+                          float* out, float* ssum, float* pk, void* stream);
+
+/* Bytes of fp32 scratch dilution_backward needs (dq_main, dk_main, ghat, dbar). */
+size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
+
+/* Pass 4 — backward of the whole operator.
+ * Replaces torch dbar (kernels.py:866), _dilution_ba (:677-775), _dilution_bc
+ * (:777-809) and _dilution_dq_epilogue (:814-826).
+ * dout, out: (n, t, d) fp32.  rmax, rden, ssum: (n, t).  carry as written by
+ * dilution_colsum_scan with tq == tk == t, q_offset == 0, carry_base == NULL.
+ * pk as written by dilution_forward_main.  scratch: dilution_backward_scratch_bytes.
+ * dq, dk, dv: (n, t, d) in `dtype` (the input dtype, as kernels.py:873-875). */
+int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
+                      int64_t n, int64_t t, int d, float scale, float eps,
+                      const float* dout, const float* out,
+                      const float* rmax, const float* rden, const float* carry,
+                      const float* ssum, const float* pk,
+                      void* scratch, void* dq, void* dk, void* dv, void* stream);
+
+/* Bytes of scratch dilution_decode needs for n rows at this `length`. */
+size_t dilution_decode_scratch_bytes(int64_t n, int64_t length, int d);
+
+/* Pass 5 — one cached decode step for every (batch, head) row.
+ * Replaces dilution_decode_step / _dilution_decode (kernels.py:936-1038).
+ * q1: (n, d).  k_cache, v_cache: contiguous (n, capacity, d) in `dtype` with the
+ * new token already at length-1.  committed: (n, capacity) fp32, advanced IN
+ * PLACE on [0, length) (+= p); rows >= length of every buffer are never touched.
+ * out: (n, d) in `dtype`. */
+int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, int dtype,
+                    int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
+                    float* committed, void* out, void* scratch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DILUTION_B200_H */

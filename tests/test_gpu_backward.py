@@ -1,0 +1,90 @@
+"""Gradient parity of the autograd op against autograd through the reference
+(stored goldens) and the CPU oracle.  Mirrors tests/test_kernels.py:109-202."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import golden, make_inputs, rel_err
+from oracle import dilution_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("seq", [8, 64, 257, 1024, 2049])
+def test_backward_matches_oracle_autograd_fp32(kernels, seq):
+    q, k, v, dout = make_inputs(2, 4, seq, 64, seq)
+    _, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    kernels.dilution_attention(qs, ks, vs, dot_precision="ieee").backward(dout.to(DEV))
+    for name, ref, got in (("dq", rdq, qs.grad), ("dk", rdk, ks.grad), ("dv", rdv, vs.grad)):
+        err = rel_err(got.cpu(), ref)
+        assert err < 2e-3, f"{name} {err}"            # the reference's bound
+        assert err < 1e-4, f"{name} {err}"            # fp32 kernels: 1e-4 relative
+
+
+@pytest.mark.parametrize("t", [1, 8, 65, 257])
+def test_backward_small_goldens(kernels, t):
+    g = golden("small_cases.npz")
+    c = {k[len(f"t{t}_"):]: torch.from_numpy(g[k]) for k in g.files if k.startswith(f"t{t}_")}
+    qs, ks, vs = (c[n].to(DEV).requires_grad_(True) for n in "qkv")
+    kernels.dilution_attention(qs, ks, vs, dot_precision="ieee").backward(c["dout"].to(DEV))
+    for name, got in (("dq", qs.grad), ("dk", ks.grad), ("dv", vs.grad)):
+        assert rel_err(got.cpu(), c[name]) < 1e-4, name
+
+
+@pytest.mark.parametrize("head_dim", [16, 32, 128])
+def test_backward_other_head_dims(kernels, head_dim):
+    q, k, v, dout = make_inputs(1, 2, 130, head_dim, 500 + head_dim)
+    _, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    kernels.dilution_attention(qs, ks, vs, dot_precision="tf32").backward(dout.to(DEV))
+    for name, ref, got in (("dq", rdq, qs.grad), ("dk", rdk, ks.grad), ("dv", rdv, vs.grad)):
+        assert rel_err(got.cpu(), ref) < 1e-4, name
+
+
+def test_backward_finite_grads(kernels):
+    q, k, v, _ = make_inputs(1, 2, 96, 64, 1)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    kernels.dilution_attention(qs, ks, vs, dot_precision="ieee").sum().backward()
+    for t in (qs, ks, vs):
+        assert t.grad is not None and torch.isfinite(t.grad).all()
+
+
+@pytest.mark.parametrize("seq", [257, 1100])
+def test_bf16_mode_forward_and_backward(kernels, seq):
+    """dot_precision="bf16": bf16 tensor-core operands, fp32 cumsum/share maths."""
+    q, k, v, dout = make_inputs(2, 4, seq, 64, 5)
+    ref, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
+    qb, kb, vb = (x.to(DEV).bfloat16().requires_grad_(True) for x in (q, k, v))
+    out = kernels.dilution_attention(qb, kb, vb, dot_precision="bf16")
+    out.backward(dout.to(DEV).bfloat16())
+    assert torch.isfinite(out).all() and out.dtype == torch.float32
+    assert (out.detach().cpu() - ref).abs().max().item() < 5e-2
+    for name, gr, t in (("dq", rdq, qb), ("dk", rdk, kb), ("dv", rdv, vb)):
+        assert t.grad.dtype == torch.bfloat16
+        err = rel_err(t.grad.float().cpu(), gr)
+        assert torch.isfinite(t.grad).all() and err < 1e-1, f"{name} {err}"   # reference bound
+    # same bf16-rounded inputs: 2e-2 max-abs on outputs and gradients
+    r2 = O.dilution_backward(qb.detach().float().cpu(), kb.detach().float().cpu(), vb.detach().float().cpu(),
+                             dout.bfloat16().float())
+    assert (out.detach().cpu() - r2[0]).abs().max().item() < 2e-2
+    for name, gr, t in (("dq", r2[1], qb), ("dk", r2[2], kb), ("dv", r2[3], vb)):
+        assert (t.grad.float().cpu() - gr).abs().max().item() < 2e-2, name
+        assert rel_err(t.grad.float().cpu(), gr) < 3e-2, name
+
+
+def test_training_shape_inputs_bf16_small_t(kernels):
+    """The benchmark's value distribution (q,k ~ 0.5 N, dout ~ 1e-2 N) at T=2048."""
+    q, k, v, dout = make_inputs(1, 2, 2048, 64, 1339, scales=(0.5, 0.5, 1.0, 1e-2))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref = O.dilution_backward(qb.float(), kb.float(), vb.float(), dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+    out.backward(dout.to(DEV))
+    assert (out.detach().cpu() - ref[0]).abs().max().item() < 2e-2
+    for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
+        assert (t.grad.float().cpu() - gr).abs().max().item() < 2e-2, name
+        assert rel_err(t.grad.float().cpu(), gr) < 5e-2, name

@@ -1,0 +1,89 @@
+"""Cached decode parity.  Mirrors tests/test_kernels.py:205-241 of the reference."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import golden, make_inputs, rel_err
+from oracle import dilution_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_matches_reference_rows(kernels, dtype):
+    g = golden("decode_b2h4d32.npz")
+    q, k, v, rows = (torch.from_numpy(g[n]) for n in ("q", "k", "v", "rows"))
+    prefix, total = int(g["prefix"]), q.shape[2]
+    prec = "bf16" if dtype == torch.bfloat16 else "ieee"
+    _, aux = kernels.dilution_attention_forward(
+        q[:, :, :prefix].to(DEV, dtype), k[:, :, :prefix].to(DEV, dtype), v[:, :, :prefix].to(DEV, dtype),
+        dot_precision=prec, return_aux=True)
+    capacity = total + 3          # spare rows: the kernel must never touch them
+    kc = torch.zeros(2, 4, capacity, 32, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kc[:, :, :prefix] = k[:, :, :prefix].to(DEV, dtype)
+    vc[:, :, :prefix] = v[:, :, :prefix].to(DEV, dtype)
+    committed = torch.zeros(2, 4, capacity, device=DEV)
+    committed[:, :, :prefix] = aux["committed_total"]
+    tol = 1e-3 if dtype == torch.float32 else 5e-2
+    for t in range(prefix, total):
+        kc[:, :, t] = k[:, :, t].to(DEV, dtype)
+        vc[:, :, t] = v[:, :, t].to(DEV, dtype)
+        out = kernels.dilution_decode_step(q[:, :, t:t + 1].to(DEV, dtype), kc, vc, committed, t + 1)
+        assert out.dtype == dtype and out.shape == (2, 4, 1, 32)
+        assert torch.isfinite(out).all()
+        err = (out[:, :, 0].float().cpu() - rows[:, :, t]).abs().max().item()
+        assert err < tol, f"t={t} max abs err {err}"
+    assert committed[:, :, total - 1].abs().max().item() > 0
+    assert committed[:, :, total:].abs().max().item() == 0
+    if dtype == torch.float32:
+        assert rel_err(committed[:, :, :total].cpu(), torch.from_numpy(g["demand_final"])) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,d,length", [(torch.bfloat16, 64, 5000), (torch.float32, 128, 700),
+                                            (torch.bfloat16, 16, 1), (torch.float32, 16, 33),
+                                            (torch.bfloat16, 128, 4097)])
+def test_decode_long_rows_many_chunks(kernels, dtype, d, length):
+    """Lengths that span several key chunks, every head_dim/dtype layout, random demand."""
+    b, h, cap = 2, 3, length + 5
+    g = torch.Generator().manual_seed(length)
+    kc = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    vc = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    q1 = torch.randn(b, h, 1, d, generator=g).to(dtype)
+    committed = torch.rand(b, h, cap, generator=g)
+    committed[:, :, length - 1:] = 0
+    ref_c = committed.clone()
+    ref = O.decode_step(q1, kc, vc, ref_c, length)
+    dc = committed.to(DEV)
+    dk, dv = kc.to(DEV), vc.to(DEV)
+    scratch = kernels.decode_scratch(b * h, cap, d, DEV)
+    out = kernels.dilution_decode_step(q1.to(DEV), dk, dv, dc, length, scratch=scratch)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert (out.float().cpu() - ref).abs().max().item() < tol
+    assert rel_err(dc.cpu(), ref_c) < 1e-5
+    assert torch.equal(dc[:, :, length:].cpu(), committed[:, :, length:])
+    assert torch.equal(dk.cpu(), kc) and torch.equal(dv.cpu(), vc)
+
+
+def test_decode_sequence_of_steps_bf16_d64(kernels):
+    """Prefill with the bf16 tensor path, then 16 steps, against the dense oracle rows."""
+    b, h, d, prefix, steps = 1, 4, 64, 300, 16
+    total = prefix + steps
+    q, k, v, _ = make_inputs(b, h, total, d, 31)
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    rows = O.dilution_dense(qb.float(), kb.float(), vb.float())
+    _, aux = kernels.dilution_attention_forward(qb[:, :, :prefix].to(DEV), kb[:, :, :prefix].to(DEV),
+                                                vb[:, :, :prefix].to(DEV), dot_precision="bf16", return_aux=True)
+    kc = torch.zeros(b, h, total, d, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc[:, :, :prefix], vc[:, :, :prefix] = kb[:, :, :prefix].to(DEV), vb[:, :, :prefix].to(DEV)
+    committed = torch.zeros(b, h, total, device=DEV)
+    committed[:, :, :prefix] = aux["committed_total"]
+    for t in range(prefix, total):
+        kc[:, :, t], vc[:, :, t] = kb[:, :, t].to(DEV), vb[:, :, t].to(DEV)
+        out = kernels.dilution_decode_step(qb[:, :, t:t + 1].to(DEV), kc, vc, committed, t + 1)
+        assert (out[:, :, 0].float().cpu() - rows[:, :, t]).abs().max().item() < 2e-2
+    assert rel_err(committed.cpu(), O.demand_totals(qb.float(), kb.float())) < 2e-2
