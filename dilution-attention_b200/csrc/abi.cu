@@ -50,10 +50,10 @@ struct Prof {
   cudaStream_t st;
   ProfRecord rec;
   bool on;
-  Prof(const char* name, cudaStream_t s) : st(s), on(false) {
+  Prof(const char* name, cudaStream_t s, bool timing = true) : st(s), on(false) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
     ++g_launches;
-    if (!g_prof_on) return;
+    if (!g_prof_on || !timing) return;
     rec.name = name;
     if (cudaEventCreate(&rec.a) != cudaSuccess) return;
     if (cudaEventCreate(&rec.b) != cudaSuccess) { cudaEventDestroy(rec.a); return; }
@@ -257,7 +257,7 @@ dil::decode::Scratch carve_decode(void* scratch, int64_t n, int64_t len, int d) 
 template <typename T, int D>
 int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool timing = true) {
   using namespace dil::decode;
   const int chunk = decode_chunk(n, len);
   const int nch = (int)((len + chunk - 1) / chunk);
@@ -265,22 +265,57 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
   const int64_t stride = decode_stride(len);
   const dim3 grid((unsigned)nch, (unsigned)n);
   {
-    Prof prof("decode_scores", st);
+    Prof prof("decode_scores", st, timing);
     scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
                                              scale * dil::kLog2e, stride, s.aff, s.part);
   }
   if (int rc = check_launch("decode scores")) return rc;
   {
-    Prof prof("decode_sweep", st);
+    Prof prof("decode_sweep", st, timing);
     sweep_kernel<T, D><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
                                             committed, s.pout, s.psum);
   }
   if (int rc = check_launch("decode sweep")) return rc;
   {
-    Prof prof("decode_finalize", st);
+    Prof prof("decode_finalize", st, timing);
     finalize_kernel<T, D><<<(unsigned)n, D, 0, st>>>(s.pout, s.psum, nch, eps, (T*)out);
   }
   return check_launch("decode finalize");
+}
+
+// ---- decode without caller-provided scratch ----------------------------------
+// Scratch of dilution_decode_static: one array in device global memory, part of
+// the library image, so every GPU that loads the library holds it until exit.
+constexpr int64_t kStaticMaxRows = DILUTION_DECODE_STATIC_MAX_ROWS;
+constexpr int64_t kStaticMaxKeys = DILUTION_DECODE_STATIC_MAX_KEYS;
+constexpr size_t kStaticBytes =
+    sizeof(float) * (size_t)kStaticMaxKeys +
+    sizeof(float) * (size_t)kStaticMaxRows * dil::decode::MAX_CHUNKS * (2 + 128 + 1);
+static __device__ __align__(256) unsigned char g_decode_static[kStaticBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of g_decode_static on the CURRENT device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device and cached.
+int static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(DILUTION_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_decode_static: device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(DILUTION_ERR_CUDA, "cudaGetSymbolAddress(static decode scratch): %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return DILUTION_OK;
 }
 
 }  // namespace
@@ -432,6 +467,34 @@ int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, in
   cudaStream_t st = (cudaStream_t)stream;
   DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
                                                      committed, out, scratch, st)))
+  return DILUTION_OK;
+}
+
+int dilution_decode_static(const void* q1, const void* k_cache, const void* v_cache, int dtype,
+                           int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
+                           float* committed, void* out, void* stream) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_static: dtype must be DILUTION_F32 or DILUTION_BF16");
+  if (!valid_d(d))
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_decode_static: head_dim %d not in {16, 32, 64, 128}", d);
+  if (n < 1 || capacity < 1 || length < 1 || length > capacity || capacity > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "dilution_decode_static: length %lld outside cache capacity %lld",
+                (long long)length, (long long)capacity);
+  if (n > kStaticMaxRows || n * decode_stride(length) > kStaticMaxKeys)
+    return fail(DILUTION_ERR_ARG,
+                "dilution_decode_static: %lld rows x %lld keys exceeds the built-in scratch "
+                "(at most %lld rows and rows * round_up(length, 32) <= %lld); use dilution_decode "
+                "with caller-provided scratch",
+                (long long)n, (long long)length, (long long)kStaticMaxRows, (long long)kStaticMaxKeys);
+  if (!q1 || !k_cache || !v_cache || !committed || !out)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_static: null pointer");
+  if (((uintptr_t)q1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_static: q1 / caches must be 16-byte aligned");
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
+                                                     committed, out, scratch, st, /*timing=*/false)))
   return DILUTION_OK;
 }
 

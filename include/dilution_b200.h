@@ -136,6 +136,40 @@ int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, in
                     int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
                     float* committed, void* out, void* scratch, void* stream);
 
+/* The same decode step for callers that cannot hand over scratch memory.
+ * No counterpart in the reference (its decode allocates out and scratch with
+ * torch on every call, kernels.py:1029-1030).
+ *
+ * Who needs this: a serving process that gave the whole device heap to its own
+ * KV-cache pool at start-up, so a later cudaMalloc fails or fragments the pool;
+ * a token loop in which an allocation would stall the device; a host that binds
+ * this C ABI from a language without a device allocator at hand.  For them the
+ * step's scratch (the per-key scores and the per-chunk partial results) lives
+ * in one array inside the library image, DILUTION_DECODE_STATIC_BYTES (~17 MB)
+ * of device memory on every GPU that loads the library, held until exit.  The
+ * call allocates nothing: no cudaMalloc/cudaFree, no library allocator.
+ *
+ * Limits: n <= DILUTION_DECODE_STATIC_MAX_ROWS and
+ * n * round_up(length, 32) <= DILUTION_DECODE_STATIC_MAX_KEYS (e.g. 128 rows at
+ * 16K keys, or 16 rows at 128K keys); anything larger is refused with
+ * DILUTION_ERR_ARG and a message.  Arguments are those of dilution_decode
+ * without `scratch`; results are identical to it.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and caches it; make that
+ * first call before starting any stream capture.  All calls on a device share
+ * the one array: it keeps the previous call's contents (nothing in it needs to
+ * start at zero — every entry read in a step was written earlier in that step),
+ * and two calls that overlap on the GPU (different streams, no ordering) race
+ * on it.  Serialise them, or use dilution_decode with separate scratch. */
+#define DILUTION_DECODE_STATIC_MAX_ROWS 128
+#define DILUTION_DECODE_STATIC_MAX_KEYS (1 << 21)
+#define DILUTION_DECODE_STATIC_BYTES \
+  (4u * DILUTION_DECODE_STATIC_MAX_KEYS + 4u * DILUTION_DECODE_STATIC_MAX_ROWS * 128u * (2u + 128u + 1u))
+int dilution_decode_static(const void* q1, const void* k_cache, const void* v_cache, int dtype,
+                           int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
+                           float* committed, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
