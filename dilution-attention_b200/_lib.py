@@ -21,6 +21,7 @@ _P, _I, _L, _F, _Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_flo
 SIGNATURES = {
     "dilution_version": (ctypes.c_int, []),
     "dilution_last_error": (ctypes.c_char_p, []),
+    "dilution_device_status": (_I, []),
     "dilution_launch_count": (ctypes.c_ulonglong, []),
     "dilution_profile_enable": (_I, [_I]),
     "dilution_profile_collect": (_I, [ctypes.c_char_p, _Z]),

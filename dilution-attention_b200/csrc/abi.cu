@@ -326,6 +326,15 @@ int dilution_version(void) { return DILUTION_ABI_VERSION; }
 
 const char* dilution_last_error(void) { return g_err; }
 
+int dilution_device_status(void) {
+#ifdef DILUTION_TENSOR_PATH
+  int v = 0;
+  if (dil::tc::read_status(&v) != 0) return fail(DILUTION_ERR_CUDA, "dilution_device_status: could not read the status word");
+  if (v != 0) return fail(DILUTION_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", v);
+#endif
+  return DILUTION_OK;
+}
+
 unsigned long long dilution_launch_count(void) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
   return g_launches;
@@ -375,8 +384,10 @@ int dilution_rowstats(const void* q, const void* k, int dtype, int precision, in
   const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
-  if (dil::tc::supported(dtype, precision, d, q_offset))
+  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+    Prof prof("tc_rowstats", st);
     return dil::tc::rowstats(q, k, g, rmax, rden, st, g_err, sizeof(g_err));
+  }
 #endif
   DIL_DISPATCH(dtype, d, return (launch_rowstats<T, D>(q, k, g, rmax, rden, st)))
   return DILUTION_OK;
@@ -392,8 +403,10 @@ int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
   const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
-  if (dil::tc::supported(dtype, precision, d, q_offset))
+  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+    Prof prof("tc_colsum_scan", st);
     return dil::tc::colsum_scan(q, k, g, rmax, rden, carry_base, carry, total, st, g_err, sizeof(g_err));
+  }
 #endif
   DIL_DISPATCH(dtype, d, return (launch_colsum<T, D>(q, k, g, rmax, rden, carry_base, carry, total, st)))
   return DILUTION_OK;
@@ -410,8 +423,13 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
   const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, eps);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
-  if (dil::tc::supported(dtype, precision, d, q_offset))
-    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st, g_err, sizeof(g_err));
+#if DILUTION_TC_HAS_MAIN
+  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+    Prof prof("tc_forward_main", st);
+    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st, g_err,
+                                 sizeof(g_err));
+  }
+#endif
 #endif
   DIL_DISPATCH(dtype, d, return (launch_main<T, D>(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st)))
   return DILUTION_OK;
@@ -435,9 +453,11 @@ int dilution_backward(const void* q, const void* k, const void* v, int dtype, in
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
+#if DILUTION_TC_HAS_BACKWARD
   if (dil::tc::supported(dtype, precision, d, 0))
     return dil::tc::backward(q, k, v, g, dout, out, rmax, rden, carry, ssum, pk, s.dq_main, s.dk_main,
                              s.ghat, s.dbar, dq, dk, dv, st, g_err, sizeof(g_err));
+#endif
 #endif
   DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, dout, out, rmax, rden, carry, ssum,
                                                        pk, s, dq, dk, dv, st)))

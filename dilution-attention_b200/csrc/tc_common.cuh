@@ -1,0 +1,195 @@
+// Blackwell (sm_100a) building blocks for the bf16 tensor-core path: mbarriers
+// with bounded waits, TMA tile loads, TMEM allocation, tcgen05.mma issue/commit
+// and tcgen05.ld, plus the shared-memory and instruction descriptors they take.
+//
+// Conventions used by every kernel built on these:
+//  * operand tiles are [128 rows][64 bf16] = 16 KB, written by TMA with the
+//    128-byte swizzle; row pitch 128 B, 8-row groups 1024 B apart, tile base
+//    1024-byte aligned.  Read as a K-major operand the rows are the M/N index
+//    and the 64 elements the contraction index; read as an MN-major operand the
+//    64 elements are the M/N index and the rows the contraction index;
+//  * accumulators live in TMEM with M = 128: row r of D is TMEM lane r, column
+//    c of D is TMEM column base+c (fp32);
+//  * every wait on an mbarrier gives up after kWaitCycles, records a code in the
+//    device status word and raises the CTA's abort flag; later waits return at
+//    once, the CTA drains, frees its TMEM and exits.  Loop bounds and addresses
+//    never depend on data, so an aborted CTA stays in bounds.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace dil {
+namespace tc {
+
+constexpr int kTileRows = 128;
+constexpr int kHeadDim = 64;
+constexpr uint32_t kTileBytes = kTileRows * kHeadDim * 2;   // 16 KB
+constexpr long long kWaitCycles = 4000000000LL;             // ~2 s: a live wait is microseconds
+
+enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- mbarrier ---------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Per-CTA control block in shared memory.
+struct Ctl {
+  volatile int abort;   // raised by the first wait that ran out
+  uint32_t tmem;        // written by tcgen05.alloc
+};
+
+// Bounded wait.  Returns false (at once, if the CTA is already aborting) when
+// the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, int* status,
+                                          int code) {
+  if (ctl->abort) return false;
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) {
+      ctl->abort = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+// ---- fences -------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- TMA ----------------------------------------------------------------------
+// One [box rows][64 bf16] tile of a (n, t, 64) tensor: coordinates (0, row, n).
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, int row, int n,
+                                              uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(row), "r"(n)
+      : "memory");
+}
+
+// ---- TMEM -----------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {   // whole warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t taddr, uint32_t cols) {         // whole warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31},"
+      " [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- descriptors ------------------------------------------------------------------
+// Shared-memory matrix descriptor, 128-byte swizzle, for the 16 KB tile layout above.
+//   K-major view : 8-row groups 1024 B apart (SBO); LBO unused.
+//   MN-major view: the 64 contiguous elements are one MN group (LBO = distance to the
+//                  next group of 64, for tiles wider than 64); 8 contraction rows per
+//                  1024 B (SBO).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;   // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, M x N, operand majors (0 = K-major, 1 = MN-major).
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, int a_mn, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; one instruction covers 16 contraction elements.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0),
+        "r"(0)
+      : "memory");
+}
+// Arrive on an mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// S[128 x 128] = A[128 x 64] * B[128 x 64]^T, both K-major tiles: 4 instructions.
+__device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, int n_cols) {
+  const uint32_t idesc = instr_desc(128, n_cols, 0, 0);
+  const uint64_t a = smem_desc(a_smem, 16, 1024), b = smem_desc(b_smem, 16, 1024);
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) mma_ss(d_tmem, a + 2 * kk, b + 2 * kk, idesc, kk > 0);
+}
+
+// Dynamic shared memory base rounded up to 1024 bytes.
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return p + ((1024u - (smem_u32(p) & 1023u)) & 1023u);
+}
+
+}  // namespace tc
+}  // namespace dil

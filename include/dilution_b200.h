@@ -59,6 +59,13 @@ int dilution_version(void);
 /* Message of the last failing call on this host thread ("" if none). */
 const char* dilution_last_error(void);
 
+/* Every wait inside a kernel (on a TMA copy or a tensor-core batch) is bounded; a
+ * wait that runs out records a code in a device status word and the kernel
+ * drains and returns instead of hanging.  This call SYNCHRONISES the device,
+ * returns DILUTION_ERR_DEVICE if a code was recorded since the last call (and
+ * clears it), else DILUTION_OK.  No reference counterpart. */
+int dilution_device_status(void);
+
 /* Kernel launches issued by this library so far in this process.
  * No reference counterpart. */
 unsigned long long dilution_launch_count(void);

@@ -62,3 +62,13 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
     """max-abs error over max-abs reference: the reference's own gradient metric
     (tests/test_kernels.py:125-126 of the reference)."""
     return (got.double() - ref.double()).abs().max().item() / (ref.double().abs().max().item() + 1e-12)
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel may have given up a bounded wait."""
+    yield
+    if "gpu" in request.keywords and torch.cuda.is_available():
+        lib = load_package()._lib.load()
+        rc = lib.dilution_device_status()
+        assert rc == 0, lib.dilution_last_error().decode()
