@@ -424,9 +424,10 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
 #if DILUTION_TC_HAS_MAIN
-  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+  // pk is produced by the fp32 kernel only: the tensor-core backward does not need it
+  if (pk == nullptr && dil::tc::supported(dtype, precision, d, q_offset)) {
     Prof prof("tc_forward_main", st);
-    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st, g_err,
+    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, st, g_err,
                                  sizeof(g_err));
   }
 #endif
