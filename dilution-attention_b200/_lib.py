@@ -31,7 +31,7 @@ SIGNATURES = {
                                    _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_backward_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F,
-                               _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+                               _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_decode_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_decode": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
     "dilution_decode_static": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P]),
@@ -84,3 +84,8 @@ def profile_collect() -> dict:
         name, count, ms = line.split()
         out[name] = (int(count), float(ms))
     return out
+
+
+def tensor_core_path(dtype_code: int, precision_code: int, head_dim: int) -> bool:
+    """True when a call with these parameters runs on the tcgen05 kernels."""
+    return dtype_code == BF16 and precision_code == PREC["bf16"] and head_dim == 64

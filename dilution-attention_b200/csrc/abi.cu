@@ -178,6 +178,7 @@ int launch_main(const void* q, const void* k, const void* v, const dil::Geom& g,
 
 struct BwdScratch {
   float *dq_main, *dk_main, *ghat, *dbar;
+  void* dop;   // (n, t, d) bf16: dout pre-scaled by 1/(ssum+eps), tensor-core path only
 };
 BwdScratch carve_bwd(void* scratch, int64_t n, int64_t t, int d) {
   BwdScratch s;
@@ -185,7 +186,19 @@ BwdScratch carve_bwd(void* scratch, int64_t n, int64_t t, int d) {
   s.dk_main = s.dq_main + n * t * d;
   s.ghat = s.dk_main + n * t * d;
   s.dbar = s.ghat + n * t;
+  s.dop = s.dbar + n * t;
   return s;
+}
+
+// Start/stop a named timing scope from code that cannot see Prof.
+thread_local Prof* g_mark = nullptr;
+void mark_scope(const char* name, cudaStream_t st, int phase) {
+  if (phase == 0) {
+    g_mark = new Prof(name, st);
+  } else if (g_mark != nullptr) {
+    delete g_mark;
+    g_mark = nullptr;
+  }
 }
 
 template <typename T, int D>
@@ -438,16 +451,16 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
 
 size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d) {
   if (n < 1 || t < 1 || d < 1) return 0;
-  return sizeof(float) * (size_t)(2 * n * t * d + 2 * n * t);
+  return sizeof(float) * (size_t)(2 * n * t * d + 2 * n * t) + 2 * (size_t)(n * t * d);
 }
 
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
                       int64_t n, int64_t t, int d, float scale, float eps, const float* dout,
                       const float* out, const float* rmax, const float* rden, const float* carry,
-                      const float* ssum, const float* pk, void* scratch, void* dq, void* dk,
-                      void* dv, void* stream) {
+                      const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
+                      void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_backward", dtype, precision, n, t, t, 0, d)) return rc;
-  if (!q || !k || !v || !dout || !out || !rmax || !rden || !carry || !ssum || !pk || !scratch ||
+  if (!q || !k || !v || !dout || !out || !rmax || !rden || !carry || !total || !ssum || !scratch ||
       !dq || !dk || !dv)
     return fail(DILUTION_ERR_ARG, "dilution_backward: null pointer");
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps);
@@ -456,9 +469,10 @@ int dilution_backward(const void* q, const void* k, const void* v, int dtype, in
 #ifdef DILUTION_TENSOR_PATH
 #if DILUTION_TC_HAS_BACKWARD
   if (dil::tc::supported(dtype, precision, d, 0))
-    return dil::tc::backward(q, k, v, g, dout, out, rmax, rden, carry, ssum, pk, s.dq_main, s.dk_main,
-                             s.ghat, s.dbar, dq, dk, dv, st, g_err, sizeof(g_err));
+    return dil::tc::backward(q, k, v, g, dout, out, rmax, rden, carry, total, ssum, s.dq_main, s.dk_main,
+                             s.ghat, s.dbar, s.dop, dq, dk, dv, st, g_err, sizeof(g_err), mark_scope);
 #endif
+  if (!pk) return fail(DILUTION_ERR_ARG, "dilution_backward: the fp32 path needs pk from dilution_forward_main");
 #endif
   DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, dout, out, rmax, rden, carry, ssum,
                                                        pk, s, dq, dk, dv, st)))

@@ -487,9 +487,462 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
   if (warp == 0) tmem_free(tmem, 256);
 }
 
+// ---------------------------------------------------------------- pass 4: backward
+// Pre-pass, one warp per query row: sinv = 1/(ssum+eps); dbar' = sinv * (dout . out);
+// do' = bf16(sinv * dout); zeroes the dq / ghat accumulators.  Folding sinv into dO
+// turns  ds = (do.v - dbar) * sinv  into  do'.v - dbar'  and  dv = attn^T do  into
+// share^T do', so the main pass never multiplies by sinv per element.
+__global__ void backward_prep_kernel(const float* __restrict__ dout, const float* __restrict__ out,
+                                     const float* __restrict__ ssum, float eps, int64_t rows,
+                                     float* __restrict__ dbarp, __nv_bfloat16* __restrict__ dop,
+                                     float* __restrict__ ghat, float* __restrict__ dq_main) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float2 a = reinterpret_cast<const float2*>(dout + row * kHeadDim)[lane];
+  const float2 b = reinterpret_cast<const float2*>(out + row * kHeadDim)[lane];
+  const float sinv = 1.f / (ssum[row] + eps);
+  const float dot = warp_sum(a.x * b.x + a.y * b.y);
+  reinterpret_cast<uint32_t*>(dop + row * kHeadDim)[lane] = pack_bf16(a.x * sinv, a.y * sinv);
+  reinterpret_cast<float2*>(dq_main + row * kHeadDim)[lane] = make_float2(0.f, 0.f);
+  if (lane == 0) {
+    dbarp[row] = dot * sinv;
+    ghat[row] = 0.f;
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+// Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
+// key blocks with the most query blocks first; one CTA per SM (464 TMEM columns).
+// S^T = K Q^T and (dO' V^T)^T = V dO'^T, lane = key.  The thread walks the queries
+// of a tile from last to first:
+//   incl   : demand of its key including the current query.  It restarts from the
+//            stored checkpoint at each 64-row boundary and is walked backwards by
+//            subtracting p, so committed + p + eps = incl + eps needs no forward sweep;
+//   suffix : running sum of dk_share over later queries (kernels.py:763-764).
+// Per tile it writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
+// K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q);
+// pdp read as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).
+constexpr int kBwdSmem = 6 * kTileBytes + 4 * kTileBytes + 2048 + 2048 + 1024 + 256;
+
+__global__ void __launch_bounds__(128) backward_main_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, Geom g,
+    const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
+    const float* __restrict__ carry, const float* __restrict__ total, float* __restrict__ dq_main,
+    float* __restrict__ dk_main, __nv_bfloat16* __restrict__ dv, float* __restrict__ ghat) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  const uint32_t sK = smem_u32(smem), sV = sK + kTileBytes;
+  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 4 * kTileBytes;     // [2] each
+  const uint32_t sSh = sK + 6 * kTileBytes, sPd = sK + 8 * kTileBytes;      // 32 KB each
+  const uint32_t sOnes = sK + 10 * kTileBytes;
+  uint8_t* ones_ptr = smem + 10 * kTileBytes;
+  float2* sStat = reinterpret_cast<float2*>(smem + 10 * kTileBytes + 2048);   // [2][128] (lse, dbar')
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * kTileBytes + 4096);
+  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
+  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);         // qfull[2]
+  const uint32_t sdone = smem_u32(bars + 3), dqdone = smem_u32(bars + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
+  const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
+  const int n = (int)(blockIdx.x % g.n);
+  const int jb = (int)(blockIdx.x / g.n);
+  const int k0 = jb * kTileRows;
+  const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
+  const int64_t row_base = (int64_t)n * g.tq;
+
+  auto stage_stats = [&](int buf, int ib) {
+    const int i = ib * kTileRows + tid;
+    float2 st = make_float2(INFINITY, 0.f);
+    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
+    sStat[buf * 128 + tid] = st;
+  };
+
+  if (tid == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < 5; ++i) mbar_init(kvfull + 8 * i, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
+  stage_stats(0, nqb - 1);
+  reinterpret_cast<uint4*>(ones_ptr)[tid] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem;
+  const uint32_t tS = tmem, tDOV = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
+                 tG = tmem + 448;
+
+  if (tid == 0) {
+    mbar_expect_tx(kvfull, 2 * kTileBytes);
+    tma_load_tile(sK, &map_k, k0, n, kvfull);
+    tma_load_tile(sV, &map_v, k0, n, kvfull);
+    mbar_expect_tx(qfull, 2 * kTileBytes);
+    tma_load_tile(sQ0, &map_q, (nqb - 1) * kTileRows, n, qfull);
+    tma_load_tile(sD0, &map_do, (nqb - 1) * kTileRows, n, qfull);
+    mbar_wait(kvfull, 0, ctl, &g_status, kErrWaitTma);
+    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
+    tc_fence_after();
+    mma_scores(tS, sK, sQ0, 128);
+    mma_scores(tDOV, sV, sD0, 128);
+    mma_commit(sdone);
+  }
+  __syncwarp();
+
+  const int ja = k0 + tid;
+  const bool dead = ja >= g.tk;
+  float suffix = 0.f;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  for (int t = 0; t < nsteps; ++t) {
+    const int ib = nqb - 1 - t, b = t & 1;
+    mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    if (tid == 0 && t + 1 < nsteps) {               // buffers of step t-1 are free
+      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+      tma_load_tile(sD0 + kTileBytes * (b ^ 1), &map_do, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+    }
+    __syncwarp();
+    if (t + 1 < nsteps) stage_stats(b ^ 1, ib - 1);
+    const int i0 = ib * kTileRows;                   // first query of the tile (q_off == 0 here)
+    const bool diag = i0 < k0 + kTileRows - 1;
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+#pragma unroll 1
+    for (int h = 1; h >= 0; --h) {
+      const int rb = 2 * ib + h;
+      float incl = 0.f;                              // demand through the last query of this half
+      if (!dead) incl = (rb + 1 < ncb) ? carry[((int64_t)n * ncb + rb + 1) * g.tk + ja]
+                                       : total[(int64_t)n * g.tk + ja];
+#pragma unroll 1
+      for (int c = 1; c >= 0; --c) {
+        float vs[32], vd[32];
+        tmem_ld32(tS + lane_base + 64 * h + 32 * c, vs);
+        tmem_ld32(tDOV + lane_base + 64 * h + 32 * c, vd);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e8 = 3; e8 >= 0; --e8) {
+          float sh[8], pd[8];
+#pragma unroll
+          for (int u2 = 3; u2 >= 0; --u2) {
+            const float4 st = St4[(h * 64 + c * 32 + e8 * 8) / 2 + u2];   // two queries: (lse, dbar') x2
+            const float lse[2] = {st.x, st.z}, dbr[2] = {st.y, st.w};
+#pragma unroll
+            for (int w = 1; w >= 0; --w) {
+              const int u = u2 * 2 + w, e = e8 * 8 + u;
+              float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
+              const bool masked = dead || (diag && ja > i0 + h * 64 + c * 32 + e);
+              if (masked) p = 0.f;
+              const float den = fmaxf(incl + g.eps, g.eps);
+              const float inv = fast_rcp(den);
+              const float ds = vd[e] - dbr[w];
+              const float a = ds * inv * inv;
+              const float gneg = a * p;                        // -dk_share
+              const float dp = fmaf(a, den - p, suffix);       // ds (committed+eps) inv^2 + suffix
+              pd[u] = masked ? 0.f : p * dp;
+              sh[u] = p * inv;
+              if (!masked) {
+                suffix -= gneg;
+                incl -= p;
+              }
+            }
+          }
+          const uint32_t off = share_chunk_offset(tid, h * 64 + c * 32 + e8 * 8);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sSh + off),
+                       "r"(pack_bf16(sh[0], sh[1])), "r"(pack_bf16(sh[2], sh[3])),
+                       "r"(pack_bf16(sh[4], sh[5])), "r"(pack_bf16(sh[6], sh[7]))
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off),
+                       "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
+                       "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
+                       : "memory");
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t id_kd = instr_desc(128, 64, 0, 1);   // A K-major (M = keys), B MN-major
+      const uint32_t id_qd = instr_desc(128, 64, 1, 1);   // A MN-major (M = queries)
+      const uint32_t id_g = instr_desc(128, 16, 1, 0);
+      const uint32_t sQ = sQ0 + kTileBytes * b, sD = sD0 + kTileBytes * b;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {                    // contraction over the 128 keys
+        const uint64_t a = smem_desc(sPd + 2048 * kk, kTileBytes, 1024);
+        mma_ss(tDQ, a, smem_desc(sK + 2048 * kk, kTileBytes, 1024), id_qd, kk > 0);
+        mma_ss(tG, a, smem_desc(sOnes + 32 * (kk & 3), 16, 1024), id_g, kk > 0);
+      }
+      mma_commit(dqdone);
+#pragma unroll
+      for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
+        const uint32_t aoff = (kq >> 2) * kTileBytes + (kq & 3) * 32;
+        mma_ss(tDV, smem_desc(sSh + aoff, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
+               (t > 0 || kq > 0));
+        mma_ss(tDK, smem_desc(sPd + aoff, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
+               (t > 0 || kq > 0));
+      }
+      if (t + 1 < nsteps) {
+        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+        tc_fence_after();
+        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
+        mma_scores(tDOV, sV, sD0 + kTileBytes * (b ^ 1), 128);
+      }
+      mma_commit(sdone);
+    }
+    __syncwarp();
+    // dQ and ghat of this tile: lane = query.  Runs under the remaining MMAs.
+    mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    {
+      float dq[64], gh[32];
+      tmem_ld32(tDQ + lane_base, dq);
+      tmem_ld32(tDQ + lane_base + 32, dq + 32);
+      tmem_ld32(tG + lane_base, gh);
+      tmem_ld_wait();
+      const int i = i0 + tid;
+      if (i < g.tq) {
+        float* dst = dq_main + (row_base + i) * kHeadDim;
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          red_add_v4(dst + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale, dq[4 * c4 + 2] * g.scale,
+                     dq[4 * c4 + 3] * g.scale);
+        atomicAdd(ghat + row_base + i, gh[0]);
+      }
+    }
+    tc_fence_before();
+  }
+  mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
+  tc_fence_after();
+  {
+    float a[32];
+    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      tmem_ld32(tDK + lane_base + 32 * c, a);
+      tmem_ld_wait();
+      if (!dead) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 4)
+          *reinterpret_cast<float4*>(dk_main + o + 32 * c + e) =
+              make_float4(a[e] * g.scale, a[e + 1] * g.scale, a[e + 2] * g.scale, a[e + 3] * g.scale);
+      }
+      tmem_ld32(tDV + lane_base + 32 * c, a);
+      tmem_ld_wait();
+      if (!dead) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 8)
+          *reinterpret_cast<uint4*>(dv + o + 32 * c + e) =
+              make_uint4(pack_bf16(a[e], a[e + 1]), pack_bf16(a[e + 2], a[e + 3]),
+                         pack_bf16(a[e + 4], a[e + 5]), pack_bf16(a[e + 6], a[e + 7]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 512);
+}
+
+// Softmax-Jacobian corrections (the reference's BC + dq epilogue, kernels.py:777-826):
+//   dk = dk_main - scale * P^T (ghat * Q)        (accumulated here per key block)
+//   dq = dq_main - scale * ghat * (P K)          (added to dq_main with vector reductions;
+//                                                 the reference reads a saved pk instead)
+// One bf16 tile W[key][query] = p * ghat serves both products: K-major it is the A
+// operand with M = keys, MN-major the A operand with M = queries.
+// grid = n * ceil(t/128); TMEM: S^T 128, dKc 64, dQc 64 (256; two CTAs per SM).
+constexpr int kCorrSmem = 3 * kTileBytes + 2 * kTileBytes + 2048 + 1024 + 256;
+
+__global__ void __launch_bounds__(128) backward_correction_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
+    const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ ghat,
+    const float* __restrict__ dk_main, float* __restrict__ dq_main, __nv_bfloat16* __restrict__ dk) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes, sW = sK + 3 * kTileBytes;
+  float2* sStat = reinterpret_cast<float2*>(smem + 5 * kTileBytes);           // [2][128] (lse, ghat)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * kTileBytes + 2048);
+  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
+  const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2), dqdone = smem_u32(bars + 3);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
+  const int n = (int)(blockIdx.x % g.n);
+  const int jb = (int)(blockIdx.x / g.n);
+  const int k0 = jb * kTileRows;
+  const int nsteps = nqb - jb;
+  const int64_t row_base = (int64_t)n * g.tq;
+
+  auto stage_stats = [&](int buf, int ib) {
+    const int i = ib * kTileRows + tid;
+    float2 st = make_float2(INFINITY, 0.f);
+    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), ghat[row_base + i]);
+    sStat[buf * 128 + tid] = st;
+  };
+
+  if (tid == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(qfull + 8 * i, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
+  stage_stats(0, jb);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem;
+  const uint32_t tS = tmem, tDK = tmem + 128, tDQ = tmem + 192;
+
+  if (tid == 0) {
+    mbar_expect_tx(qfull, 2 * kTileBytes);
+    tma_load_tile(sK, &map_k, k0, n, qfull);
+    tma_load_tile(sQ0, &map_q, jb * kTileRows, n, qfull);
+    if (nsteps > 1) {
+      mbar_expect_tx(qfull + 8, kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes, &map_q, (jb + 1) * kTileRows, n, qfull + 8);
+    }
+    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
+    tc_fence_after();
+    mma_scores(tS, sK, sQ0, 128);
+    mma_commit(sdone);
+  }
+  __syncwarp();
+
+  const int ja = k0 + tid;
+  const bool dead = ja >= g.tk;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  for (int t = 0; t < nsteps; ++t) {
+    const int ib = jb + t, b = t & 1;
+    mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    if (tid == 0 && t >= 1 && t + 1 < nsteps) {      // the Q stage of step t-1 is free
+      mbar_expect_tx(qfull + 8 * (b ^ 1), kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+    }
+    __syncwarp();
+    if (t + 1 < nsteps) stage_stats(b ^ 1, ib + 1);
+    const int i0 = ib * kTileRows;
+    const bool diag = t == 0;
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float vs[32];
+      tmem_ld32(tS + lane_base + 32 * c, vs);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e8 = 0; e8 < 4; ++e8) {
+        float w8[8];
+#pragma unroll
+        for (int u2 = 0; u2 < 4; ++u2) {
+          const float4 st = St4[(c * 32 + e8 * 8) / 2 + u2];
+          const float lse[2] = {st.x, st.z}, gh[2] = {st.y, st.w};
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            const int u = u2 * 2 + w, e = e8 * 8 + u;
+            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
+            if (dead || (diag && ja > i0 + c * 32 + e)) p = 0.f;
+            w8[u] = p * gh[w];
+          }
+        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sW + share_chunk_offset(tid, c * 32 + e8 * 8)),
+                     "r"(pack_bf16(w8[0], w8[1])), "r"(pack_bf16(w8[2], w8[3])),
+                     "r"(pack_bf16(w8[4], w8[5])), "r"(pack_bf16(w8[6], w8[7]))
+                     : "memory");
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t id_kd = instr_desc(128, 64, 0, 1), id_qd = instr_desc(128, 64, 1, 1);
+      const uint32_t sQ = sQ0 + kTileBytes * b;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        mma_ss(tDQ, smem_desc(sW + 2048 * kk, kTileBytes, 1024), smem_desc(sK + 2048 * kk, kTileBytes, 1024),
+               id_qd, kk > 0);
+      mma_commit(dqdone);
+#pragma unroll
+      for (int kq = 0; kq < 8; ++kq)
+        mma_ss(tDK, smem_desc(sW + (kq >> 2) * kTileBytes + (kq & 3) * 32, 16, 1024),
+               smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
+      if (t + 1 < nsteps) {
+        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+        tc_fence_after();
+        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
+      }
+      mma_commit(sdone);
+    }
+    __syncwarp();
+    mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    {
+      float dq[64];
+      tmem_ld32(tDQ + lane_base, dq);
+      tmem_ld32(tDQ + lane_base + 32, dq + 32);
+      tmem_ld_wait();
+      const int i = i0 + tid;
+      if (i < g.tq) {
+        float* dst = dq_main + (row_base + i) * kHeadDim;
+        const float ns = -g.scale;
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          red_add_v4(dst + 4 * c4, dq[4 * c4] * ns, dq[4 * c4 + 1] * ns, dq[4 * c4 + 2] * ns, dq[4 * c4 + 3] * ns);
+      }
+    }
+    tc_fence_before();
+  }
+  mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
+  tc_fence_after();
+  {
+    float a[32];
+    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      tmem_ld32(tDK + lane_base + 32 * c, a);
+      tmem_ld_wait();
+      if (!dead) {
+        float m[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(dk_main + o + 32 * c + e);
+          m[e] = x.x - g.scale * a[e];
+          m[e + 1] = x.y - g.scale * a[e + 1];
+          m[e + 2] = x.z - g.scale * a[e + 2];
+          m[e + 3] = x.w - g.scale * a[e + 3];
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 8)
+          *reinterpret_cast<uint4*>(dk + o + 32 * c + e) =
+              make_uint4(pack_bf16(m[e], m[e + 1]), pack_bf16(m[e + 2], m[e + 3]),
+                         pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 256);
+}
+
+// dq = bf16(dq_main)
+__global__ void cast_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n4) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 x = reinterpret_cast<const float4*>(src)[i];
+  reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w));
+}
+
 // ---------------------------------------------------------------- host launchers
 #define DILUTION_TC_HAS_MAIN 1
-#define DILUTION_TC_HAS_BACKWARD 0
+#define DILUTION_TC_HAS_BACKWARD 1
 
 inline int set_smem_attr(const void* fn, int bytes, char* err, size_t errlen) {
   const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -553,6 +1006,44 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   forward_main_kernel<<<(unsigned)(g.n * nqb), 128, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
                                                               out, ssum);
   return launch_status("tc forward_main", err, errlen);
+}
+
+// dop: (n, t, 64) bf16 scratch for the pre-scaled dout.
+inline int backward(const void* q, const void* k, const void* v, const Geom& g, const float* dout,
+                    const float* out, const float* rmax, const float* rden, const float* carry,
+                    const float* total, const float* ssum, float* dq_main, float* dk_main, float* ghat,
+                    float* dbarp, void* dop, void* dq, void* dk, void* dv, cudaStream_t st, char* err,
+                    size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
+  CUtensorMap mq, mk, mv, md;
+  if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
+  if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
+  if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
+  if (int rc = make_map(&md, dop, g.n, g.tq, err, errlen)) return rc;
+  const int64_t rows = g.n * g.tq;
+  const int nkb = (g.tk + kTileRows - 1) / kTileRows;
+  mark("tc_backward_prep", st, 0);
+  backward_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dout, out, ssum, g.eps, rows, dbarp,
+                                                                  (__nv_bfloat16*)dop, ghat, dq_main);
+  mark("tc_backward_prep", st, 1);
+  if (int rc = launch_status("tc backward_prep", err, errlen)) return rc;
+  if (int rc = set_smem_attr((const void*)backward_main_kernel, kBwdSmem, err, errlen)) return rc;
+  mark("tc_backward_main", st, 0);
+  backward_main_kernel<<<(unsigned)(g.n * nkb), 128, kBwdSmem, st>>>(
+      mq, mk, mv, md, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
+  mark("tc_backward_main", st, 1);
+  if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
+  constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
+  if (int rc = set_smem_attr((const void*)backward_correction_kernel, smem, err, errlen)) return rc;
+  mark("tc_backward_correction", st, 0);
+  backward_correction_kernel<<<(unsigned)(g.n * nkb), 128, smem, st>>>(mq, mk, g, rmax, rden, ghat, dk_main,
+                                                                     dq_main, (__nv_bfloat16*)dk);
+  mark("tc_backward_correction", st, 1);
+  if (int rc = launch_status("tc backward_correction", err, errlen)) return rc;
+  const int64_t n4 = rows * kHeadDim / 4;
+  mark("tc_cast_dq", st, 0);
+  cast_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_main, (__nv_bfloat16*)dq, n4);
+  mark("tc_cast_dq", st, 1);
+  return launch_status("tc cast_dq", err, errlen);
 }
 
 // Reads (and clears) the device status word; synchronises the device.

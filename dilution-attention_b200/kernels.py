@@ -167,16 +167,21 @@ class _DilutionAttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, dot_precision):
+        # the tensor-core backward applies the dq correction itself and needs no saved pk
+        lowp, _ = _resolve_precision(dot_precision)
+        on_tc = _lib.tensor_core_path(_lib.BF16 if (lowp or q.dtype == torch.bfloat16) else _lib.F32,
+                                      _lib.PREC[dot_precision], q.shape[-1])
         out, aux = dilution_attention_forward(
             q, k, v, dot_precision=dot_precision, return_aux=True,
-            _save_pk=any(ctx.needs_input_grad[:3]))
-        ctx.save_for_backward(q, k, v, out, aux["rmax"], aux["rden"], aux["carry"], aux["ssum"], aux["pk"])
+            _save_pk=any(ctx.needs_input_grad[:3]) and not on_tc)
+        ctx.save_for_backward(q, k, v, out, aux["rmax"], aux["rden"], aux["carry"], aux["ssum"], aux["pk"],
+                              aux["committed_total"])
         ctx.dot_precision = dot_precision
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, rmax, rden, carry, ssum, pk = ctx.saved_tensors
+        q, k, v, out, rmax, rden, carry, ssum, pk, total = ctx.saved_tensors
         lib = _lib.load()
         batch, heads, seq, head_dim = q.shape
         (qf, kf, vf), code, prec, n = _prepare(q, k, v, ctx.dot_precision)
@@ -192,8 +197,8 @@ class _DilutionAttentionFn(torch.autograd.Function):
         _lib.check(lib.dilution_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim,
             1.0 / math.sqrt(head_dim), EPS, dof.data_ptr(), of.data_ptr(),
-            rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), ssum.data_ptr(), pk.data_ptr(),
-            scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _stream(dev)),
+            rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), total.data_ptr(), ssum.data_ptr(),
+            _ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _stream(dev)),
             "dilution_backward")
         shape4 = (batch, heads, seq, head_dim)
         return (dq.reshape(shape4).to(q.dtype), dk.reshape(shape4).to(k.dtype),

@@ -113,20 +113,23 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
                           const float* carry_base,
                           float* out, float* ssum, float* pk, void* stream);
 
-/* Bytes of fp32 scratch dilution_backward needs (dq_main, dk_main, ghat, dbar). */
+/* Bytes of scratch dilution_backward needs (fp32 dq_main, dk_main, ghat, dbar and a
+ * bf16 copy of dout). */
 size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
 
 /* Pass 4 — backward of the whole operator.
  * Replaces torch dbar (kernels.py:866), _dilution_ba (:677-775), _dilution_bc
  * (:777-809) and _dilution_dq_epilogue (:814-826).
- * dout, out: (n, t, d) fp32.  rmax, rden, ssum: (n, t).  carry as written by
- * dilution_colsum_scan with tq == tk == t, q_offset == 0, carry_base == NULL.
- * pk as written by dilution_forward_main.  scratch: dilution_backward_scratch_bytes.
+ * dout, out: (n, t, d) fp32.  rmax, rden, ssum: (n, t).  carry and total as written
+ * by dilution_colsum_scan with tq == tk == t, q_offset == 0, carry_base == NULL.
+ * pk as written by dilution_forward_main; it may be NULL for bf16 inputs with
+ * BF16 precision and d == 64 (the tensor-core backward applies the dq correction
+ * itself).  scratch: dilution_backward_scratch_bytes.
  * dq, dk, dv: (n, t, d) in `dtype` (the input dtype, as kernels.py:873-875). */
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
                       int64_t n, int64_t t, int d, float scale, float eps,
                       const float* dout, const float* out,
-                      const float* rmax, const float* rden, const float* carry,
+                      const float* rmax, const float* rden, const float* carry, const float* total,
                       const float* ssum, const float* pk,
                       void* scratch, void* dq, void* dk, void* dv, void* stream);
 

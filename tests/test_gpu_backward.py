@@ -88,3 +88,21 @@ def test_training_shape_inputs_bf16_small_t(kernels):
     for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
         assert (t.grad.float().cpu() - gr).abs().max().item() < 2e-2, name
         assert rel_err(t.grad.float().cpu(), gr) < 5e-2, name
+
+
+def test_bf16_training_step_runs_on_the_tensor_core_kernels(pkg, kernels):
+    """Forward and backward of the bf16 op launch tcgen05 kernels only (plus the
+    small elementwise pre/post kernels): no fp32-FMA kernel on the training path."""
+    q, k, v, dout = make_inputs(1, 2, 900, 64, 77, scales=(0.5, 0.5, 1.0, 1e-2))
+    qs, ks, vs = (x.bfloat16().to(DEV).requires_grad_(True) for x in (q, k, v))
+    pkg._lib.profile(True)
+    pkg._lib.profile_collect()
+    kernels.dilution_attention(qs, ks, vs, dot_precision="bf16").backward(dout.to(DEV))
+    torch.cuda.synchronize()
+    names = set(pkg._lib.profile_collect())
+    pkg._lib.profile(False)
+    assert names == {"tc_rowstats", "tc_colsum_scan", "tc_forward_main", "tc_backward_prep",
+                     "tc_backward_main", "tc_backward_correction", "tc_cast_dq"}, names
+    ref = O.dilution_backward(qs.detach().float().cpu(), ks.detach().float().cpu(), vs.detach().float().cpu(), dout)
+    for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
+        assert rel_err(t.grad.float().cpu(), gr) < 3e-2, name

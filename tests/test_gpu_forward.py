@@ -108,6 +108,23 @@ def test_bf16_tensor_path_ragged_lengths(kernels, seq):
     assert rel_err(aux["pk"].reshape(1, 3, seq, 64).cpu(), O.query_correction(qb.float(), kb.float())) < 2e-2
 
 
+def test_bf16_forward_runs_on_the_tensor_core_kernels(pkg, kernels):
+    """dot_precision="bf16" with bf16 inputs and head_dim 64 must launch the tcgen05
+    kernels for all three passes (not the fp32-FMA ones), and match the oracle."""
+    q, k, v, _ = make_inputs(2, 2, 700, 64, 21, scales=(0.5, 0.5, 1.0, 1.0))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    pkg._lib.profile(True)
+    pkg._lib.profile_collect()
+    out, aux = kernels.dilution_attention_forward(*_cuda(qb, kb, vb), dot_precision="bf16", return_aux=True)
+    torch.cuda.synchronize()
+    names = set(pkg._lib.profile_collect())
+    pkg._lib.profile(False)
+    assert {"tc_rowstats", "tc_colsum_scan", "tc_forward_main"} <= names, names
+    ref, demand = O.dilution_chunked(qb.float(), kb.float(), vb.float(), chunk=256, return_demand=True)
+    assert (out.cpu() - ref).abs().max().item() < 2e-2
+    assert rel_err(aux["committed_total"].cpu(), demand) < 2e-2
+
+
 def test_slabbed_forward_equals_single_launch(kernels):
     q, k, v, _ = make_inputs(2, 3, 200, 64, 5)
     whole = kernels.dilution_attention_forward(*_cuda(q, k, v))
