@@ -233,18 +233,53 @@ def run_ours(args, rank, world):
 
     # dominant kernel and its roofline (5 of the 7 matmuls live in the backward main pass)
     kernels_ms = {name: tot / cnt for name, (cnt, tot) in prof.items()}
-    share = {"backward_main": 5, "forward_main": 1, "rowstats": 1, "colsum_scan": 1, "backward_dk_correction": 2}
+    # algorithmic matmuls per kernel: the backward main pass carries all five backward products,
+    # the forward main pass QK^T and share@V; the other passes are recomputation overhead
+    share = {"backward_main": 5, "forward_main": 2}
     dom = max(kernels_ms, key=kernels_ms.get) if kernels_ms else None
     roofline = None
     if dom is not None:
-        mm = next((m for key, m in share.items() if key in dom), 1)
+        mm = next((m for key, m in share.items() if key in dom), 0)
         achieved = causal_flops(n_rows, T, D, mm) / (kernels_ms[dom] * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": None,
                     "peak_source": f"{peaks['source']} sustained bf16", "matmuls_in_kernel": mm,
                     "step_frac_of_peak": value / world / peaks["tensor"]}
 
-    # --- e2e: host buffers in, host buffers out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, K, host, devt, dev, barrier, distributed, total_flops)
+    del devt, q, k, v, dout
+    torch.cuda.empty_cache()
+
+    # --- cached decode at a 128K cache (heads sharded across ranks)
+    decode = None
+    if not args.no_decode:
+        decode = run_decode(K, L, dev, rank, world, peaks, barrier, distributed)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"train_fwd_bwd_B{B}_H{H}_T{T}_d{D}", "rows_per_gpu": n_rows,
+                           "global_rows": n_rows * world, "seq_len": T, "head_dim": D,
+                           "parallelism": f"batch*head slab per GPU x{world}, no collective",
+                           "l2": "inputs exceed L2 (q,k,v 134 MB each, dout/out 268 MB at T=16384)",
+                           "flop_count": "7*N*T*(T+1)*D"},
+                "roofline": roofline, "kernels_ms": kernels_ms, "e2e": e2e, "gpu_launches": launches,
+                "clocks": clocks.summary(), "decode": decode}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_block()
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, K, host, devt, dev, barrier, distributed, total_flops):
+    """The step through the public op with pinned HOST buffers: H2D of q, k, v, dout and
+    D2H of out, dq, dk, dv inside the timed region."""
+    import torch.distributed as dist
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     outs = {n: torch.empty_like(host[n if n != "out" else "dout"]).pin_memory() for n in ("out",)}
     for n in "qkv":
         outs["d" + n] = torch.empty_like(host[n]).pin_memory()
@@ -277,30 +312,8 @@ def run_ours(args, rank, world):
     d2h = sum(x.numel() * x.element_size() for x in outs.values())
     e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
-    del dbuf, devt, q, k, v, dout
-    torch.cuda.empty_cache()
-
-    # --- cached decode at a 128K cache (heads sharded across ranks)
-    decode = None
-    if not args.no_decode:
-        decode = run_decode(K, L, dev, rank, world, peaks, barrier, distributed)
-
-    if rank == 0:
-        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": "train_fwd_bwd_B4_H16_T16384_d64", "rows_per_gpu": n_rows,
-                           "global_rows": n_rows * world, "seq_len": T, "head_dim": D,
-                           "parallelism": f"batch*head slab per GPU x{world}, no collective",
-                           "l2": "inputs exceed L2 (q,k,v 134 MB each, dout/out 268 MB)",
-                           "flop_count": "7*N*T*(T+1)*D"},
-                "roofline": roofline, "kernels_ms": kernels_ms, "e2e": e2e, "gpu_launches": launches,
-                "clocks": clocks.summary(), "decode": decode}
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline_block()
-        print(json.dumps(line), flush=True)
-    if distributed:
-        dist.destroy_process_group()
+    del dbuf
+    return e2e
 
 
 def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
@@ -368,9 +381,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--seq", type=int, default=TRAIN["T"],
+                    help="sequence length of the training-shape operator (profiling captures use a smaller one)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    TRAIN["T"] = args.seq
     if args.impl == "reference":
         run_reference(args, rank)
         return

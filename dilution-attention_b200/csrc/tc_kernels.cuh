@@ -71,37 +71,64 @@ inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, ch
   return 0;
 }
 
-// ---------------------------------------------------------------- pass 1: row statistics
-// grid = n * ceil(tq/128), longest rows first.  S = Q K^T, lane = query.
-// Shared: Q tile, two K stages.  TMEM: two 128-column S buffers, so the MMA of
-// key tile jb+1 runs while the threads reduce tile jb.
-constexpr int kRowstatsSmem = 3 * kTileBytes + 1024 + 256;
+// ---------------------------------------------------------------- forward kernels
+// Common shape of passes 1-3: 256 threads = two warpgroups.  Warp w reads TMEM
+// lanes 32*(w%4).., so both warpgroups see all 128 lanes of a 128x128 score tile
+// and split its COLUMNS: warpgroup 0 takes columns 0-63, warpgroup 1 columns 64-127.
+// Thread 0 issues TMA and MMA.  One score buffer in TMEM per CTA; several CTAs per
+// SM overlap each other's MMA/TMA latency.
 
-__global__ void __launch_bounds__(128) rowstats_kernel(const __grid_constant__ CUtensorMap map_q,
-                                                       const __grid_constant__ CUtensorMap map_k,
-                                                       Geom g, float* __restrict__ rmax,
-                                                       float* __restrict__ rden) {
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Byte offset of the 16-byte chunk holding queries [q, q+8) of `key` in an
+// MN-major [128 keys][128 queries] bf16 tile (q a multiple of 8): two 64-query
+// sub-tiles of 16 KB, rows of 128 B, 16-byte chunks XOR-swizzled by the row.
+__device__ __forceinline__ uint32_t share_chunk_offset(int key, int q) {
+  return (uint32_t)((q >> 6) * (int)kTileBytes + key * 128 + ((((q & 63) >> 3) ^ (key & 7)) << 4));
+}
+
+// log2-domain log-sum-exp of query i (+inf past the end, so that its p is 0)
+__device__ __forceinline__ float load_lse(const float* __restrict__ rmax, const float* __restrict__ rden,
+                                          int64_t row_base, int i, int tq) {
+  return i < tq ? rmax[row_base + i] + log2f(rden[row_base + i]) : INFINITY;
+}
+
+// ---------------------------------------------------------------- pass 1: row statistics
+// grid = n * ceil(tq/128), longest rows first.  S = Q K^T, lane = query: each
+// thread reduces its 64 key columns of the tile with an online max / sum; the two
+// halves of a row are merged once at the end.  TMEM: 128 columns; 4 CTAs per SM.
+constexpr int kRowstatsSmem = 3 * kTileBytes + 1024 + 1024 + 256;
+
+__global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                          const __grid_constant__ CUtensorMap map_k,
+                                                          Geom g, float* __restrict__ rmax,
+                                                          float* __restrict__ rden) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sQ = smem_u32(smem), sK0 = sQ + kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes);
+  float2* sMerge = reinterpret_cast<float2*>(smem + 3 * kTileBytes);          // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 1024);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kfull = smem_u32(bars), sdone = smem_u32(bars + 2);   // [2] each
+  const uint32_t kfull = smem_u32(bars), sdone = smem_u32(bars + 2);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int n = (int)(blockIdx.x % g.n);
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
-  const int q0 = g.q_off + ib * kTileRows;                   // absolute position of row 0
+  const int q0 = g.q_off + ib * kTileRows;
   const int njb = min(g.tk - 1, q0 + kTileRows - 1) / kTileRows + 1;
 
   if (tid == 0) {
     ctl->abort = 0;
-    for (int i = 0; i < 4; ++i) mbar_init(kfull + 8 * i, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(kfull + 8 * i, 1);
     fence_barrier_init();
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 128);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -115,25 +142,20 @@ __global__ void __launch_bounds__(128) rowstats_kernel(const __grid_constant__ C
       mbar_expect_tx(kfull + 8, kTileBytes);
       tma_load_tile(sK0 + kTileBytes, &map_k, kTileRows, n, kfull + 8);
     }
-    mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    mma_scores(tmem, sQ, sK0, 128);
-    mma_commit(sdone);
   }
-  __syncwarp();
-
   float m = -INFINITY, s = 0.f;
-  const int ia = q0 + tid;
+  const int ia = q0 + row;
+  const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
   for (int jb = 0; jb < njb; ++jb) {
     const int b = jb & 1;
-    if (tid == 0 && jb + 1 < njb) {     // MMA of the next tile into the other S buffer
-      mbar_wait(kfull + 8 * (b ^ 1), ((jb + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+    if (tid == 0) {
+      mbar_wait(kfull + 8 * b, (jb >> 1) & 1, ctl, &g_status, kErrWaitTma);
       tc_fence_after();
-      mma_scores(tmem + 128 * (b ^ 1), sQ, sK0 + kTileBytes * (b ^ 1), 128);
-      mma_commit(sdone + 8 * (b ^ 1));
+      mma_scores(tmem, sQ, sK0 + kTileBytes * b, 128);
+      mma_commit(sdone);
     }
     __syncwarp();
-    mbar_wait(sdone + 8 * b, (jb >> 1) & 1, ctl, &g_status, kErrWaitMma);
+    mbar_wait(sdone, jb & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && jb + 2 < njb) {     // this K stage is free again
       mbar_expect_tx(kfull + 8 * b, kTileBytes);
@@ -141,18 +163,17 @@ __global__ void __launch_bounds__(128) rowstats_kernel(const __grid_constant__ C
     }
     __syncwarp();
     const bool edge = (jb * kTileRows + kTileRows - 1 > q0) || ((jb + 1) * kTileRows > g.tk);
-    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + 128 * b;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       float v[32];
       tmem_ld32(taddr + 32 * c, v);
-      tmem_ld_wait();
+      tmem_ld_wait(v);
       float cmax = -INFINITY;
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         float z = v[e] * g.zscale;
         if (edge) {
-          const int ja = jb * kTileRows + c * 32 + e;
+          const int ja = jb * kTileRows + wg * 64 + c * 32 + e;
           if (ja > ia || ja >= g.tk) z = -INFINITY;
         }
         v[e] = z;
@@ -170,43 +191,43 @@ __global__ void __launch_bounds__(128) rowstats_kernel(const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
   }
-  const int i = ib * kTileRows + tid;
-  if (i < g.tq) {
-    rmax[(int64_t)n * g.tq + i] = m;
-    rden[(int64_t)n * g.tq + i] = s;
+  if (wg == 1) sMerge[row] = make_float2(m, s);
+  __syncthreads();
+  const int i = ib * kTileRows + row;
+  if (wg == 0 && i < g.tq) {
+    const float2 o = sMerge[row];
+    const float nm = fmaxf(m, o.x);          // finite: the first tile always holds key 0
+    const float tot = s * fast_exp2(m - nm) + o.y * fast_exp2(o.x - nm);
+    rmax[(int64_t)n * g.tq + i] = nm;
+    rden[(int64_t)n * g.tq + i] = tot;
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
+  if (warp == 0) tmem_free(tmem, 128);
 }
 
 // ---------------------------------------------------------------- pass 2: column sums + scan
 // grid = n * ceil(tk/128), key blocks with the most query blocks first.
 // S^T = K Q^T, lane = key.  The CTA keeps its K tile and walks the query blocks
-// in causal order; each thread's running sum of p over the queries seen so far
-// is the exclusive scan, stored as a checkpoint every 64 query rows.
-constexpr int kColsumSmem = 3 * kTileBytes + 2 * 128 * 4 + 1024 + 256;
+// in causal order.  Each warpgroup sums p over its 64 queries of the tile; the
+// thread of warpgroup 0 owns the key's running sum — the exclusive scan — and
+// stores one checkpoint per 64 query rows, one tile behind the sums.
+constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 1024 + 1024 + 256;
 
-__device__ __forceinline__ void stage_lse(float* dst, const float* __restrict__ rmax,
-                                          const float* __restrict__ rden, int64_t row_base, int i,
-                                          int tq) {
-  // log2-domain log-sum-exp of one query; +inf for rows past the end so their p is 0
-  dst[threadIdx.x] = i < tq ? rmax[row_base + i] + log2f(rden[row_base + i]) : INFINITY;
-}
-
-__global__ void __launch_bounds__(128) colsum_scan_kernel(
+__global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden,
     const float* __restrict__ carry_base, float* __restrict__ carry, float* __restrict__ total) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes;
-  float* sL = reinterpret_cast<float*>(smem + 3 * kTileBytes);            // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 1024);
+  float* sL = reinterpret_cast<float*>(smem + 3 * kTileBytes);                 // [2][128]
+  float* sCs = reinterpret_cast<float*>(smem + 3 * kTileBytes + 1024);         // [2][128] sums of warpgroup 1
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 2048);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int n = (int)(blockIdx.x % g.n);
@@ -218,12 +239,12 @@ __global__ void __launch_bounds__(128) colsum_scan_kernel(
 
   if (tid == 0) {
     ctl->abort = 0;
-    for (int i = 0; i < 4; ++i) mbar_init(qfull + 8 * i, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(qfull + 8 * i, 1);
     fence_barrier_init();
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  if (nib > 0) stage_lse(sL, rmax, rden, row_base, ib0 * kTileRows + tid, g.tq);
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 128);
+  if (nib > 0 && wg == 0) sL[row] = load_lse(rmax, rden, row_base, ib0 * kTileRows + row, g.tq);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -237,96 +258,93 @@ __global__ void __launch_bounds__(128) colsum_scan_kernel(
       mbar_expect_tx(qfull + 8, kTileBytes);
       tma_load_tile(sQ0 + kTileBytes, &map_q, (ib0 + 1) * kTileRows, n, qfull + 8);
     }
-    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    mma_scores(tmem, sK, sQ0, 128);
-    mma_commit(sdone);
   }
-  __syncwarp();
-
-  const int ja = k0 + tid;
-  const float base = (carry_base != nullptr && ja < g.tk) ? carry_base[(int64_t)n * g.tk + ja] : 0.f;
-  float local = 0.f;
+  const int ja = k0 + row;
+  const bool live = ja < g.tk;
+  const float base = (carry_base != nullptr && live) ? carry_base[(int64_t)n * g.tk + ja] : 0.f;
+  float local = 0.f, prev = 0.f;      // warpgroup 0: scan state and its own sum of the previous tile
+  const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
   for (int it = 0; it < nib; ++it) {
     const int ib = ib0 + it, b = it & 1;
-    if (tid == 0 && it + 1 < nib) {
-      mbar_wait(qfull + 8 * (b ^ 1), ((it + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+    if (tid == 0) {
+      mbar_wait(qfull + 8 * b, (it >> 1) & 1, ctl, &g_status, kErrWaitTma);
       tc_fence_after();
-      mma_scores(tmem + 128 * (b ^ 1), sK, sQ0 + kTileBytes * (b ^ 1), 128);
-      mma_commit(sdone + 8 * (b ^ 1));
+      mma_scores(tmem, sK, sQ0 + kTileBytes * b, 128);
+      mma_commit(sdone);
     }
     __syncwarp();
-    if (it + 1 < nib) stage_lse(sL + 128 * (b ^ 1), rmax, rden, row_base, (ib + 1) * kTileRows + tid, g.tq);
-    mbar_wait(sdone + 8 * b, (it >> 1) & 1, ctl, &g_status, kErrWaitMma);
+    // while the MMA runs: next tile's statistics, and the checkpoints of the previous tile
+    float lse_next = 0.f;
+    if (wg == 1 && it + 1 < nib) lse_next = load_lse(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq);
+    if (wg == 0 && it > 0) {
+      const int rb = (ib - 1) * 2;
+      if (live) {
+        if (rb < ncb) carry[((int64_t)n * ncb + rb) * g.tk + ja] = base + local;
+        if (rb + 1 < ncb) carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] = base + local + prev;
+      }
+      local += prev + sCs[((it - 1) & 1) * 128 + row];
+    }
+    mbar_wait(sdone, it & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && it + 2 < nib) {
       mbar_expect_tx(qfull + 8 * b, kTileBytes);
       tma_load_tile(sQ0 + kTileBytes * b, &map_q, (ib + 2) * kTileRows, n, qfull + 8 * b);
     }
     __syncwarp();
-    const int i0 = g.q_off + ib * kTileRows;          // absolute position of the tile's first query
-    const bool edge = i0 < k0 + kTileRows - 1;         // the diagonal tile
-    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + 128 * b;
-    const float4* L4 = reinterpret_cast<const float4*>(sL + 128 * b);
+    const int i0 = g.q_off + ib * kTileRows + 64 * wg;   // absolute position of this half's first query
+    const bool edge = i0 < k0 + kTileRows - 1;            // part of the diagonal tile
+    const float4* L4 = reinterpret_cast<const float4*>(sL + 128 * b + 64 * wg);
+    float colsum = 0.f;
 #pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-      float colsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_ld32(taddr + 64 * h + 32 * c, v);
-        tmem_ld_wait();
+    for (int c = 0; c < 2; ++c) {
+      float v[32];
+      tmem_ld32(taddr + 32 * c, v);
+      tmem_ld_wait(v);
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 l = L4[h * 16 + c * 8 + e4];
-          const float ls[4] = {l.x, l.y, l.z, l.w};
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 l = L4[c * 8 + e4];
+        const float ls[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
-            if (edge && ja > i0 + h * 64 + c * 32 + e4 * 4 + u) p = 0.f;
-            colsum += p;
-          }
+        for (int u = 0; u < 4; ++u) {
+          float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
+          if (edge && ja > i0 + c * 32 + e4 * 4 + u) p = 0.f;
+          colsum += p;
         }
       }
-      const int rb = ib * 2 + h;
-      if (rb < ncb && ja < g.tk) carry[((int64_t)n * ncb + rb) * g.tk + ja] = base + local;
-      local += colsum;
     }
+    if (wg == 0) prev = colsum; else sCs[b * 128 + row] = colsum;
+    if (wg == 1 && it + 1 < nib) sL[128 * (b ^ 1) + row] = lse_next;
     tc_fence_before();
     __syncthreads();
   }
-  if (ja < g.tk) total[(int64_t)n * g.tk + ja] = local;
+  if (wg == 0 && live) {
+    if (nib > 0) {
+      const int rb = (nqb - 1) * 2;
+      if (rb < ncb) carry[((int64_t)n * ncb + rb) * g.tk + ja] = base + local;
+      if (rb + 1 < ncb) carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] = base + local + prev;
+      local += prev + sCs[((nib - 1) & 1) * 128 + row];
+    }
+    total[(int64_t)n * g.tk + ja] = local;
+  }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
+  if (warp == 0) tmem_free(tmem, 128);
 }
 
 // ---------------------------------------------------------------- pass 3: main pass
 // grid = n * ceil(tq/128), longest rows first.  S^T = K Q^T, lane = key.
-// Each thread walks the 128 queries of the tile in order with its key's demand
-// in one register:  den += p;  share = p / den  (den = committed + p + eps),
-// and writes the bf16 share tile to shared memory as an MN-major operand
-// ([key][query], 128-byte swizzle, two 64-query sub-tiles).  Two MMAs consume it:
-//   O   [query x d ] += share   * V      (A = share MN-major, B = V MN-major)
-//   rs  [query x 16] += share   * ones   (row sums of the SAME bf16 shares)
+// Each thread walks 64 queries of the tile in order (warpgroup 1 starts from the
+// mid-block checkpoint) with its key's demand in one register:
+//     den += p;  share = p / den          (den = committed + p + eps)
+// and writes its half of the bf16 share tile to shared memory as an MN-major
+// operand ([key][query]).  Two MMAs consume the tile:
+//   O   [query x d ] += share * V      (A = share MN-major, B = V MN-major)
+//   rs  [query x 16] += share * ones   (row sums of the SAME bf16 shares)
 // so the final divide out = O / (rs + eps) normalises exactly what was summed.
 // TMEM: S^T 128 columns, O 64, rs 16 (256 allocated; two CTAs per SM).
-constexpr int kMainTiles = 4;   // Q, K x2, V
-constexpr int kMainSmem = kMainTiles * kTileBytes + 2 * kTileBytes + 2048 + 512 + 1024 + 256;
+constexpr int kMainSmem = 4 * kTileBytes + 2 * kTileBytes + 2048 + 512 + 1024 + 256;
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
-// Byte offset of the 16-byte chunk holding queries [q, q+8) of `key` in an
-// MN-major [128 keys][128 queries] bf16 tile (q a multiple of 8).
-__device__ __forceinline__ uint32_t share_chunk_offset(int key, int q) {
-  return (uint32_t)((q >> 6) * (int)kTileBytes + key * 128 + ((((q & 63) >> 3) ^ (key & 7)) << 4));
-}
-
-__global__ void __launch_bounds__(128) forward_main_kernel(
+__global__ void __launch_bounds__(256, 2) forward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, Geom g, const float* __restrict__ rmax,
     const float* __restrict__ rden, const float* __restrict__ carry,
@@ -341,7 +359,7 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t kfull = smem_u32(bars), vfull = smem_u32(bars + 2), sdone = smem_u32(bars + 3);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int n = (int)(blockIdx.x % g.n);
@@ -356,8 +374,8 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  stage_lse(sL, rmax, rden, (int64_t)n * g.tq, ib * kTileRows + tid, g.tq);
-  reinterpret_cast<uint4*>(ones_ptr)[tid] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  if (wg == 0) sL[row] = load_lse(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
+  else reinterpret_cast<uint4*>(ones_ptr)[row] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -382,17 +400,27 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
   }
   __syncwarp();
 
-  const float4* L4 = reinterpret_cast<const float4*>(sL);
-  const int64_t carry_row = ((int64_t)n * ncb + 2 * ib) * g.tk;
+  // the checkpoint row this warpgroup starts from: rows 2*ib (queries 0-63) and 2*ib+1 (64-127)
+  const int rb = 2 * ib + wg;
+  const bool have_rows = rb < ncb;                 // false only for a ragged last half block
+  const int64_t carry_row = ((int64_t)n * ncb + (have_rows ? rb : 0)) * g.tk;
+  const float4* L4 = reinterpret_cast<const float4*>(sL + 64 * wg);
+  const uint32_t taddr = tS + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
+  const int qh = q0 + 64 * wg;                     // absolute position of this half's first query
+  auto load_den = [&](int jbx) {
+    const int jx = jbx * kTileRows + row;
+    float d = g.eps;
+    if (jx < g.tk && have_rows) {
+      d += carry[carry_row + jx];
+      if (carry_base != nullptr) d += carry_base[(int64_t)n * g.tk + jx];
+    }
+    return d;
+  };
+  float den_next = load_den(0);
   for (int jb = 0; jb < njb; ++jb) {
     const int b = jb & 1;
-    const int ja = jb * kTileRows + tid;
-    // demand committed before this tile's first query, plus eps once
-    float den = g.eps;
-    if (ja < g.tk) {
-      den += carry[carry_row + ja];
-      if (carry_base != nullptr) den += carry_base[(int64_t)n * g.tk + ja];
-    }
+    const int ja = jb * kTileRows + row;
+    float den = den_next;
     mbar_wait(sdone, jb & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0) {
@@ -406,14 +434,14 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
       }
     }
     __syncwarp();
-    const bool diag = jb * kTileRows + kTileRows - 1 > q0;
+    if (jb + 1 < njb) den_next = load_den(jb + 1);   // lands while this tile is processed
+    const bool diag = jb * kTileRows + kTileRows - 1 > qh;
     const bool dead = ja >= g.tk;
-    const uint32_t taddr = tS + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       float v[32];
       tmem_ld32(taddr + 32 * c, v);
-      tmem_ld_wait();
+      tmem_ld_wait(v);
 #pragma unroll
       for (int e8 = 0; e8 < 4; ++e8) {
         uint32_t packed[4];
@@ -426,14 +454,14 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
           for (int u = 0; u < 4; ++u) {
             const int e = e8 * 8 + h * 4 + u;
             float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
-            if (dead || (diag && ja > q0 + c * 32 + e)) p = 0.f;
+            if (dead || (diag && ja > qh + c * 32 + e)) p = 0.f;
             den += p;
             sh[u] = p * fast_rcp(den);
           }
           packed[h * 2 + 0] = pack_bf16(sh[0], sh[1]);
           packed[h * 2 + 1] = pack_bf16(sh[2], sh[3]);
         }
-        const uint32_t dst = sSh + share_chunk_offset(tid, c * 32 + e8 * 8);
+        const uint32_t dst = sSh + share_chunk_offset(row, wg * 64 + c * 32 + e8 * 8);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]),
                      "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
                      : "memory");
@@ -465,21 +493,21 @@ __global__ void __launch_bounds__(128) forward_main_kernel(
   mbar_wait(sdone, njb & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
   {
-    // lane = query now: row tid of O and of the row sums
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float o[64], r[32];
-    tmem_ld32(tO + lane_base, o);
-    tmem_ld32(tO + lane_base + 32, o + 32);
+    // lane = query now: each warpgroup stores 32 of the 64 output columns of row `row`
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    float o[32], r[32];
+    tmem_ld32(tO + lane_base + 32 * wg, o);
     tmem_ld32(tR + lane_base, r);
-    tmem_ld_wait();
-    const int i = ib * kTileRows + tid;
+    tmem_ld_wait(o);
+    tmem_ld_wait(r);
+    const int i = ib * kTileRows + row;
     if (i < g.tq) {
       const float inv = 1.f / (r[0] + g.eps);
-      float4* dst = reinterpret_cast<float4*>(out + ((int64_t)n * g.tq + i) * kHeadDim);
+      float4* dst = reinterpret_cast<float4*>(out + ((int64_t)n * g.tq + i) * kHeadDim + 32 * wg);
 #pragma unroll
-      for (int c = 0; c < 16; ++c)
+      for (int c = 0; c < 8; ++c)
         dst[c] = make_float4(o[4 * c] * inv, o[4 * c + 1] * inv, o[4 * c + 2] * inv, o[4 * c + 3] * inv);
-      ssum[(int64_t)n * g.tq + i] = r[0];
+      if (wg == 0) ssum[(int64_t)n * g.tq + i] = r[0];
     }
   }
   tc_fence_before();
@@ -962,19 +990,21 @@ inline int launch_status(const char* what, char* err, size_t errlen) {
   return 0;
 }
 
-// Shared memory is padded so that at most two CTAs share an SM: each holds 256
-// TMEM columns and an SM has 512.
+// Shared memory of the 256-column kernels is padded so that at most two CTAs share
+// an SM (an SM has 512 TMEM columns); the 128-column kernels fit four by themselves.
 constexpr int kTwoPerSm = 100 * 1024;
+static_assert(5 * (kRowstatsSmem + 1024) > 233472 && 5 * (kColsumSmem + 1024) > 233472,
+              "at most four CTAs of a 128-column kernel may share an SM");
 
 inline int rowstats(const void* q, const void* k, const Geom& g, float* rmax, float* rden,
                     cudaStream_t st, char* err, size_t errlen) {
   CUtensorMap mq, mk;
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
-  constexpr int smem = kRowstatsSmem > kTwoPerSm ? kRowstatsSmem : kTwoPerSm;
+  constexpr int smem = kRowstatsSmem;
   if (int rc = set_smem_attr((const void*)rowstats_kernel, smem, err, errlen)) return rc;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  rowstats_kernel<<<(unsigned)(g.n * nqb), 128, smem, st>>>(mq, mk, g, rmax, rden);
+  rowstats_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, g, rmax, rden);
   return launch_status("tc rowstats", err, errlen);
 }
 
@@ -984,10 +1014,10 @@ inline int colsum_scan(const void* q, const void* k, const Geom& g, const float*
   CUtensorMap mq, mk;
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
-  constexpr int smem = kColsumSmem > kTwoPerSm ? kColsumSmem : kTwoPerSm;
+  constexpr int smem = kColsumSmem;
   if (int rc = set_smem_attr((const void*)colsum_scan_kernel, smem, err, errlen)) return rc;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
-  colsum_scan_kernel<<<(unsigned)(g.n * nkb), 128, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
+  colsum_scan_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
                                                              total);
   return launch_status("tc colsum_scan", err, errlen);
 }
@@ -1003,7 +1033,7 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   static_assert(2 * (smem + 1024) <= 233472, "two CTAs of the main pass must fit one SM");
   if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  forward_main_kernel<<<(unsigned)(g.n * nqb), 128, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
+  forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
                                                               out, ssum);
   return launch_status("tc forward_main", err, errlen);
 }
