@@ -16,6 +16,8 @@
 // other's arithmetic.
 #pragma once
 
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 namespace dil {
@@ -555,9 +557,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // Per tile it writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
 // K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q);
 // pdp read as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).
+// Everything a tile needs from global memory (checkpoints, row statistics) is
+// fetched one tile ahead, and TMEM chunks are loaded one chunk ahead, so the single
+// warp per scheduler does not stall on either.
 constexpr int kBwdSmem = 6 * kTileBytes + 4 * kTileBytes + 2048 + 2048 + 1024 + 256;
 
-__global__ void __launch_bounds__(128) backward_main_kernel(
+__global__ void __launch_bounds__(128, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
@@ -584,12 +589,20 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
   const int k0 = jb * kTileRows;
   const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
   const int64_t row_base = (int64_t)n * g.tq;
+  const int ja = k0 + tid;
+  const bool dead = ja >= g.tk;
 
-  auto stage_stats = [&](int buf, int ib) {
+  auto load_stats = [&](int ib) {
     const int i = ib * kTileRows + tid;
     float2 st = make_float2(INFINITY, 0.f);
     if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
-    sStat[buf * 128 + tid] = st;
+    return st;
+  };
+  // demand of this thread's key through the last query of half h of block ib
+  auto load_incl = [&](int ib, int h) {
+    const int rb = 2 * ib + h + 1;
+    if (dead) return 0.f;
+    return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
   };
 
   if (tid == 0) {
@@ -599,7 +612,7 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
-  stage_stats(0, nqb - 1);
+  sStat[tid] = load_stats(nqb - 1);
   reinterpret_cast<uint4*>(ones_ptr)[tid] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   fence_async_smem();
   tc_fence_before();
@@ -625,12 +638,19 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
   }
   __syncwarp();
 
-  const int ja = k0 + tid;
-  const bool dead = ja >= g.tk;
   float suffix = 0.f;
+  float incl_hi = load_incl(nqb - 1, 1), incl_lo = load_incl(nqb - 1, 0);
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   for (int t = 0; t < nsteps; ++t) {
     const int ib = nqb - 1 - t, b = t & 1;
+    // fetch what the next tile needs before waiting for this one
+    float2 stat_next = make_float2(INFINITY, 0.f);
+    float incl_hi_next = 0.f, incl_lo_next = 0.f;
+    if (t + 1 < nsteps) {
+      stat_next = load_stats(ib - 1);
+      incl_hi_next = load_incl(ib - 1, 1);
+      incl_lo_next = load_incl(ib - 1, 0);
+    }
     mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && t + 1 < nsteps) {               // buffers of step t-1 are free
@@ -639,61 +659,78 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
       tma_load_tile(sD0 + kTileBytes * (b ^ 1), &map_do, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
-    if (t + 1 < nsteps) stage_stats(b ^ 1, ib - 1);
     const int i0 = ib * kTileRows;                   // first query of the tile (q_off == 0 here)
-    const bool diag = i0 < k0 + kTileRows - 1;
+    const bool masked_tile = dead || (i0 < k0 + kTileRows - 1);
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
-#pragma unroll 1
-    for (int h = 1; h >= 0; --h) {
-      const int rb = 2 * ib + h;
-      float incl = 0.f;                              // demand through the last query of this half
-      if (!dead) incl = (rb + 1 < ncb) ? carry[((int64_t)n * ncb + rb + 1) * g.tk + ja]
-                                       : total[(int64_t)n * g.tk + ja];
-#pragma unroll 1
-      for (int c = 1; c >= 0; --c) {
-        float vs[32], vd[32];
-        tmem_ld32(tS + lane_base + 64 * h + 32 * c, vs);
-        tmem_ld32(tDOV + lane_base + 64 * h + 32 * c, vd);
-        tmem_ld_wait();
+
+    // one chunk = 32 queries, visited from the last to the first
+    auto chunk = [&](auto mask_tag, const float* vs, const float* vd, int qc, float& incl) {
+      constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
-        for (int e8 = 3; e8 >= 0; --e8) {
-          float sh[8], pd[8];
+      for (int e8 = 3; e8 >= 0; --e8) {
+        float sh[8], pd[8];
 #pragma unroll
-          for (int u2 = 3; u2 >= 0; --u2) {
-            const float4 st = St4[(h * 64 + c * 32 + e8 * 8) / 2 + u2];   // two queries: (lse, dbar') x2
-            const float lse[2] = {st.x, st.z}, dbr[2] = {st.y, st.w};
+        for (int u2 = 3; u2 >= 0; --u2) {
+          const float4 st = St4[(qc + e8 * 8) / 2 + u2];       // two queries: (lse, dbar') x2
+          const float lse[2] = {st.x, st.z}, dbr[2] = {st.y, st.w};
 #pragma unroll
-            for (int w = 1; w >= 0; --w) {
-              const int u = u2 * 2 + w, e = e8 * 8 + u;
-              float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
-              const bool masked = dead || (diag && ja > i0 + h * 64 + c * 32 + e);
-              if (masked) p = 0.f;
-              const float den = fmaxf(incl + g.eps, g.eps);
-              const float inv = fast_rcp(den);
-              const float ds = vd[e] - dbr[w];
-              const float a = ds * inv * inv;
-              const float gneg = a * p;                        // -dk_share
-              const float dp = fmaf(a, den - p, suffix);       // ds (committed+eps) inv^2 + suffix
-              pd[u] = masked ? 0.f : p * dp;
-              sh[u] = p * inv;
-              if (!masked) {
-                suffix -= gneg;
-                incl -= p;
-              }
+          for (int w = 1; w >= 0; --w) {
+            const int u = u2 * 2 + w, e = e8 * 8 + u;
+            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
+            bool off = false;
+            if (MASK) {
+              off = dead || ja > i0 + qc + e;
+              if (off) p = 0.f;
+            }
+            const float den = fmaxf(incl + g.eps, g.eps);
+            const float inv = fast_rcp(den);
+            const float a = (vd[e] - dbr[w]) * inv * inv;
+            const float dp = fmaf(a, den - p, suffix);         // ds (committed+eps) inv^2 + suffix
+            pd[u] = p * dp;
+            sh[u] = p * inv;
+            if (!MASK || !off) {
+              suffix -= a * p;                                 // += dk_share
+              incl -= p;
             }
           }
-          const uint32_t off = share_chunk_offset(tid, h * 64 + c * 32 + e8 * 8);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sSh + off),
-                       "r"(pack_bf16(sh[0], sh[1])), "r"(pack_bf16(sh[2], sh[3])),
-                       "r"(pack_bf16(sh[4], sh[5])), "r"(pack_bf16(sh[6], sh[7]))
-                       : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off),
-                       "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
-                       "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
-                       : "memory");
         }
+        const uint32_t off8 = share_chunk_offset(tid, qc + e8 * 8);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sSh + off8),
+                     "r"(pack_bf16(sh[0], sh[1])), "r"(pack_bf16(sh[2], sh[3])),
+                     "r"(pack_bf16(sh[4], sh[5])), "r"(pack_bf16(sh[6], sh[7]))
+                     : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off8),
+                     "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
+                     "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
+                     : "memory");
       }
+    };
+    {
+      float sa[32], da[32], sb[32], db[32];
+      tmem_ld32(tS + lane_base + 96, sa);
+      tmem_ld32(tDOV + lane_base + 96, da);
+      tmem_ld_wait(sa);
+      tmem_ld_wait(da);
+      tmem_ld32(tS + lane_base + 64, sb);
+      tmem_ld32(tDOV + lane_base + 64, db);
+      if (masked_tile) chunk(std::true_type{}, sa, da, 96, incl_hi); else chunk(std::false_type{}, sa, da, 96, incl_hi);
+      tmem_ld_wait(sb);
+      tmem_ld_wait(db);
+      tmem_ld32(tS + lane_base + 32, sa);
+      tmem_ld32(tDOV + lane_base + 32, da);
+      if (masked_tile) chunk(std::true_type{}, sb, db, 64, incl_hi); else chunk(std::false_type{}, sb, db, 64, incl_hi);
+      tmem_ld_wait(sa);
+      tmem_ld_wait(da);
+      tmem_ld32(tS + lane_base, sb);
+      tmem_ld32(tDOV + lane_base, db);
+      if (masked_tile) chunk(std::true_type{}, sa, da, 32, incl_lo); else chunk(std::false_type{}, sa, da, 32, incl_lo);
+      tmem_ld_wait(sb);
+      tmem_ld_wait(db);
+      if (masked_tile) chunk(std::true_type{}, sb, db, 0, incl_lo); else chunk(std::false_type{}, sb, db, 0, incl_lo);
     }
+    sStat[(b ^ 1) * 128 + tid] = stat_next;
+    incl_hi = incl_hi_next;
+    incl_lo = incl_lo_next;
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -731,20 +768,23 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
     mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     {
-      float dq[64], gh[32];
-      tmem_ld32(tDQ + lane_base, dq);
-      tmem_ld32(tDQ + lane_base + 32, dq + 32);
+      float dq[32], gh[32];
       tmem_ld32(tG + lane_base, gh);
-      tmem_ld_wait();
       const int i = i0 + tid;
-      if (i < g.tq) {
-        float* dst = dq_main + (row_base + i) * kHeadDim;
+      float* dst = dq_main + (row_base + i) * kHeadDim;
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4)
-          red_add_v4(dst + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale, dq[4 * c4 + 2] * g.scale,
-                     dq[4 * c4 + 3] * g.scale);
-        atomicAdd(ghat + row_base + i, gh[0]);
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tDQ + lane_base + 32 * c, dq);
+        tmem_ld_wait(dq);
+        if (i < g.tq) {
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4)
+            red_add_v4(dst + 32 * c + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale,
+                       dq[4 * c4 + 2] * g.scale, dq[4 * c4 + 3] * g.scale);
+        }
       }
+      tmem_ld_wait(gh);
+      if (i < g.tq) atomicAdd(ghat + row_base + i, gh[0]);
     }
     tc_fence_before();
   }
@@ -756,7 +796,7 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
       tmem_ld32(tDK + lane_base + 32 * c, a);
-      tmem_ld_wait();
+      tmem_ld_wait(a);
       if (!dead) {
 #pragma unroll
         for (int e = 0; e < 32; e += 4)
@@ -764,7 +804,7 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
               make_float4(a[e] * g.scale, a[e + 1] * g.scale, a[e + 2] * g.scale, a[e + 3] * g.scale);
       }
       tmem_ld32(tDV + lane_base + 32 * c, a);
-      tmem_ld_wait();
+      tmem_ld_wait(a);
       if (!dead) {
 #pragma unroll
         for (int e = 0; e < 32; e += 8)
@@ -785,10 +825,11 @@ __global__ void __launch_bounds__(128) backward_main_kernel(
 //                                                 the reference reads a saved pk instead)
 // One bf16 tile W[key][query] = p * ghat serves both products: K-major it is the A
 // operand with M = keys, MN-major the A operand with M = queries.
-// grid = n * ceil(t/128); TMEM: S^T 128, dKc 64, dQc 64 (256; two CTAs per SM).
+// grid = n * ceil(t/128); 256 threads, the two warpgroups split the tile's query
+// columns; TMEM: S^T 128, dKc 64, dQc 64 (256; two CTAs per SM).
 constexpr int kCorrSmem = 3 * kTileBytes + 2 * kTileBytes + 2048 + 1024 + 256;
 
-__global__ void __launch_bounds__(128) backward_correction_kernel(
+__global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ ghat,
     const float* __restrict__ dk_main, float* __restrict__ dq_main, __nv_bfloat16* __restrict__ dk) {
@@ -800,7 +841,7 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2), dqdone = smem_u32(bars + 3);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int n = (int)(blockIdx.x % g.n);
   const int jb = (int)(blockIdx.x / g.n);
@@ -808,11 +849,11 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
   const int nsteps = nqb - jb;
   const int64_t row_base = (int64_t)n * g.tq;
 
-  auto stage_stats = [&](int buf, int ib) {
-    const int i = ib * kTileRows + tid;
+  auto load_stats = [&](int ib) {
+    const int i = ib * kTileRows + row;
     float2 st = make_float2(INFINITY, 0.f);
     if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), ghat[row_base + i]);
-    sStat[buf * 128 + tid] = st;
+    return st;
   };
 
   if (tid == 0) {
@@ -822,7 +863,7 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  stage_stats(0, jb);
+  if (wg == 1) sStat[row] = load_stats(jb);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -844,11 +885,13 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
   }
   __syncwarp();
 
-  const int ja = k0 + tid;
+  const int ja = k0 + row;
   const bool dead = ja >= g.tk;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   for (int t = 0; t < nsteps; ++t) {
     const int ib = jb + t, b = t & 1;
+    float2 stat_next = make_float2(INFINITY, 0.f);
+    if (wg == 1 && t + 1 < nsteps) stat_next = load_stats(ib + 1);
     mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && t >= 1 && t + 1 < nsteps) {      // the Q stage of step t-1 is free
@@ -856,15 +899,14 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
       tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
-    if (t + 1 < nsteps) stage_stats(b ^ 1, ib + 1);
-    const int i0 = ib * kTileRows;
-    const bool diag = t == 0;
-    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+    const int i0 = ib * kTileRows + 64 * wg;
+    const bool masked_tile = dead || t == 0;
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       float vs[32];
-      tmem_ld32(tS + lane_base + 32 * c, vs);
-      tmem_ld_wait();
+      tmem_ld32(tS + lane_base + 64 * wg + 32 * c, vs);
+      tmem_ld_wait(vs);
 #pragma unroll
       for (int e8 = 0; e8 < 4; ++e8) {
         float w8[8];
@@ -876,16 +918,17 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
           for (int w = 0; w < 2; ++w) {
             const int u = u2 * 2 + w, e = e8 * 8 + u;
             float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
-            if (dead || (diag && ja > i0 + c * 32 + e)) p = 0.f;
+            if (masked_tile && (dead || ja > i0 + c * 32 + e)) p = 0.f;
             w8[u] = p * gh[w];
           }
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sW + share_chunk_offset(tid, c * 32 + e8 * 8)),
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sW + share_chunk_offset(row, wg * 64 + c * 32 + e8 * 8)),
                      "r"(pack_bf16(w8[0], w8[1])), "r"(pack_bf16(w8[2], w8[3])),
                      "r"(pack_bf16(w8[4], w8[5])), "r"(pack_bf16(w8[6], w8[7]))
                      : "memory");
       }
     }
+    if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -913,16 +956,16 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
     mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     {
-      float dq[64];
-      tmem_ld32(tDQ + lane_base, dq);
-      tmem_ld32(tDQ + lane_base + 32, dq + 32);
-      tmem_ld_wait();
-      const int i = i0 + tid;
+      // lane = query: each warpgroup adds 32 of the 64 columns of row `row`
+      float dq[32];
+      tmem_ld32(tDQ + lane_base + 32 * wg, dq);
+      tmem_ld_wait(dq);
+      const int i = ib * kTileRows + row;
       if (i < g.tq) {
-        float* dst = dq_main + (row_base + i) * kHeadDim;
+        float* dst = dq_main + (row_base + i) * kHeadDim + 32 * wg;
         const float ns = -g.scale;
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4)
+        for (int c4 = 0; c4 < 8; ++c4)
           red_add_v4(dst + 4 * c4, dq[4 * c4] * ns, dq[4 * c4 + 1] * ns, dq[4 * c4 + 2] * ns, dq[4 * c4 + 3] * ns);
       }
     }
@@ -931,28 +974,26 @@ __global__ void __launch_bounds__(128) backward_correction_kernel(
   mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
   {
+    // lane = key: each warpgroup finishes 32 of the 64 columns of dk
     float a[32];
-    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tDK + lane_base + 32 * c, a);
-      tmem_ld_wait();
-      if (!dead) {
-        float m[32];
+    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
+    tmem_ld32(tDK + lane_base + 32 * wg, a);
+    tmem_ld_wait(a);
+    if (!dead) {
+      float m[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 x = *reinterpret_cast<const float4*>(dk_main + o + 32 * c + e);
-          m[e] = x.x - g.scale * a[e];
-          m[e + 1] = x.y - g.scale * a[e + 1];
-          m[e + 2] = x.z - g.scale * a[e + 2];
-          m[e + 3] = x.w - g.scale * a[e + 3];
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 8)
-          *reinterpret_cast<uint4*>(dk + o + 32 * c + e) =
-              make_uint4(pack_bf16(m[e], m[e + 1]), pack_bf16(m[e + 2], m[e + 3]),
-                         pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
+      for (int e = 0; e < 32; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(dk_main + o + e);
+        m[e] = x.x - g.scale * a[e];
+        m[e + 1] = x.y - g.scale * a[e + 1];
+        m[e + 2] = x.z - g.scale * a[e + 2];
+        m[e + 3] = x.w - g.scale * a[e + 3];
       }
+#pragma unroll
+      for (int e = 0; e < 32; e += 8)
+        *reinterpret_cast<uint4*>(dk + o + e) =
+            make_uint4(pack_bf16(m[e], m[e + 1]), pack_bf16(m[e + 2], m[e + 3]),
+                       pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
     }
   }
   tc_fence_before();
@@ -1065,7 +1106,7 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
   if (int rc = set_smem_attr((const void*)backward_correction_kernel, smem, err, errlen)) return rc;
   mark("tc_backward_correction", st, 0);
-  backward_correction_kernel<<<(unsigned)(g.n * nkb), 128, smem, st>>>(mq, mk, g, rmax, rden, ghat, dk_main,
+  backward_correction_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, ghat, dk_main,
                                                                      dq_main, (__nv_bfloat16*)dk);
   mark("tc_backward_correction", st, 1);
   if (int rc = launch_status("tc backward_correction", err, errlen)) return rc;
