@@ -49,7 +49,8 @@ inline EncodeTiledFn encode_fn() {
 
 // (n, t, 64) bf16 row-major -> 3-D map {64, t, n}, box {64, 128, 1}, 128-byte swizzle.
 // Rows past t read as zero, and a box never crosses into the next (batch, head) row.
-inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen) {
+inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen,
+                    int box_rows = kTileRows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
@@ -61,7 +62,7 @@ inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, ch
   }
   const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)t, (cuuint64_t)n};
   const cuuint64_t strides[2] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)t * kHeadDim * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)kHeadDim, (cuuint32_t)kTileRows, 1};
+  const cuuint32_t box[3] = {(cuuint32_t)kHeadDim, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -444,13 +445,20 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
       float v[32];
       tmem_ld32(taddr + 32 * c, v);
       tmem_ld_wait(v);
+      // the statistics of group e8+1 are read before group e8 is stored: shared-memory
+      // loads cannot be hoisted above the stores by the compiler
+      float4 lnext[2] = {L4[c * 8], L4[c * 8 + 1]};
 #pragma unroll
       for (int e8 = 0; e8 < 4; ++e8) {
         uint32_t packed[4];
+        const float4 lcur[2] = {lnext[0], lnext[1]};
+        if (e8 < 3) {
+          lnext[0] = L4[c * 8 + e8 * 2 + 2];
+          lnext[1] = L4[c * 8 + e8 * 2 + 3];
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const float4 l = L4[c * 8 + e8 * 2 + h];
-          const float ls[4] = {l.x, l.y, l.z, l.w};
+          const float ls[4] = {lcur[h].x, lcur[h].y, lcur[h].z, lcur[h].w};
           float sh[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -542,27 +550,35 @@ __global__ void backward_prep_kernel(const float* __restrict__ dout, const float
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+#ifdef DIL_EXP_NO_RED
+  return;
+#endif
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
 
 // Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
-// key blocks with the most query blocks first; one CTA per SM (464 TMEM columns).
-// S^T = K Q^T and (dO' V^T)^T = V dO'^T, lane = key.  The thread walks the queries
-// of a tile from last to first:
-//   incl   : demand of its key including the current query.  It restarts from the
-//            stored checkpoint at each 64-row boundary and is walked backwards by
+// key blocks with the most query blocks first; 128 threads, two CTAs per SM.
+// The CTA keeps the K and V tiles of 128 keys and walks the 64-row query blocks from
+// last to first.  S^T = K Q^T and (dO' V^T)^T = V dO'^T are [128 keys x 64 queries]
+// tiles, lane = key.  The thread walks the 64 queries backwards with two registers:
+//   incl   : demand of its key including the current query.  It starts from the
+//            stored checkpoint of the next 64-row block and is walked backwards by
 //            subtracting p, so committed + p + eps = incl + eps needs no forward sweep;
 //   suffix : running sum of dk_share over later queries (kernels.py:763-764).
-// Per tile it writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
-// K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q);
-// pdp read as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).
-// Everything a tile needs from global memory (checkpoints, row statistics) is
-// fetched one tile ahead, and TMEM chunks are loaded one chunk ahead, so the single
-// warp per scheduler does not stall on either.
-constexpr int kBwdSmem = 6 * kTileBytes + 4 * kTileBytes + 2048 + 2048 + 1024 + 256;
+// Per step it writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
+// K-major they are A operands with M = 128 keys (dV += share^T dO', dK += pdp^T Q);
+// pdp read as MN-major is the A operand with M = 64 queries (dQ = pdp K, ghat = pdp 1).
+// TMEM (256 columns): S^T 64 | dOV^T 64 | dV 64 | dK 64.  The dQ and ghat results of a
+// step reuse the S^T / dOV^T columns, which are dead once the threads have consumed
+// them; the next step's score MMAs are issued after dQ has been read out.
+// An M = 64 accumulator sits on lanes 0-15 of each 32-lane quarter: row r of D is lane
+// 32*(r/16) + r%16, so threads with (tid & 31) < 16 own one query row each.
+constexpr int kHalfRows = 64;
+constexpr uint32_t kHalfBytes = kHalfRows * kHeadDim * 2;     // 8 KB
+constexpr int kBwdSmem = 2 * kTileBytes + 4 * kHalfBytes + 2 * kTileBytes + 2048 + 1024 + 1024 + 256;
 
-__global__ void __launch_bounds__(128, 1) backward_main_kernel(
+__global__ void __launch_bounds__(128, 2) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
@@ -571,38 +587,39 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sK = smem_u32(smem), sV = sK + kTileBytes;
-  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 4 * kTileBytes;     // [2] each
-  const uint32_t sSh = sK + 6 * kTileBytes, sPd = sK + 8 * kTileBytes;      // 32 KB each
-  const uint32_t sOnes = sK + 10 * kTileBytes;
-  uint8_t* ones_ptr = smem + 10 * kTileBytes;
-  float2* sStat = reinterpret_cast<float2*>(smem + 10 * kTileBytes + 2048);   // [2][128] (lse, dbar')
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * kTileBytes + 4096);
+  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sQ0 + 2 * kHalfBytes;        // [2] each, 64 rows
+  const uint32_t sSh = sD0 + 2 * kHalfBytes, sPd = sSh + kTileBytes;            // [128 keys][64 q]
+  const uint32_t sOnes = sPd + kTileBytes;
+  constexpr int kOff = 2 * kTileBytes + 4 * kHalfBytes + 2 * kTileBytes;
+  uint8_t* ones_ptr = smem + kOff;
+  float2* sStat = reinterpret_cast<float2*>(smem + kOff + 2048);                // [2][64] (lse, dbar')
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOff + 2048 + 1024);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);         // qfull[2]
+  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);           // qfull[2]
   const uint32_t sdone = smem_u32(bars + 3), dqdone = smem_u32(bars + 4);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int n = (int)(blockIdx.x % g.n);
   const int jb = (int)(blockIdx.x / g.n);
   const int k0 = jb * kTileRows;
-  const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
+  const int rb_first = 2 * jb;                       // first 64-row block that sees these keys
+  const int nsteps = ncb - rb_first;                 // >= 1
   const int64_t row_base = (int64_t)n * g.tq;
   const int ja = k0 + tid;
   const bool dead = ja >= g.tk;
 
-  auto load_stats = [&](int ib) {
-    const int i = ib * kTileRows + tid;
+  auto load_stats = [&](int rb) {
+    const int i = rb * kHalfRows + tid;
     float2 st = make_float2(INFINITY, 0.f);
-    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
+    if (tid < kHalfRows && i < g.tq)
+      st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
     return st;
   };
-  // demand of this thread's key through the last query of half h of block ib
-  auto load_incl = [&](int ib, int h) {
-    const int rb = 2 * ib + h + 1;
+  // demand of this thread's key through the last query of block rb
+  auto load_incl = [&](int rb) {
     if (dead) return 0.f;
-    return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
+    return rb + 1 < ncb ? carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
   };
 
   if (tid == 0) {
@@ -611,60 +628,62 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
     fence_barrier_init();
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
-  sStat[tid] = load_stats(nqb - 1);
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
+  {
+    const float2 st = load_stats(ncb - 1);
+    if (tid < kHalfRows) sStat[tid] = st;
+  }
   reinterpret_cast<uint4*>(ones_ptr)[tid] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tDOV = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
-                 tG = tmem + 448;
+  const uint32_t tS = tmem, tDOV = tmem + 64, tDV = tmem + 128, tDK = tmem + 192;
+  const uint32_t tDQ = tS, tG = tDOV;                // reuse, see above
 
   if (tid == 0) {
     mbar_expect_tx(kvfull, 2 * kTileBytes);
     tma_load_tile(sK, &map_k, k0, n, kvfull);
     tma_load_tile(sV, &map_v, k0, n, kvfull);
-    mbar_expect_tx(qfull, 2 * kTileBytes);
-    tma_load_tile(sQ0, &map_q, (nqb - 1) * kTileRows, n, qfull);
-    tma_load_tile(sD0, &map_do, (nqb - 1) * kTileRows, n, qfull);
+    mbar_expect_tx(qfull, 2 * kHalfBytes);
+    tma_load_tile(sQ0, &map_q, (ncb - 1) * kHalfRows, n, qfull);
+    tma_load_tile(sD0, &map_do, (ncb - 1) * kHalfRows, n, qfull);
     mbar_wait(kvfull, 0, ctl, &g_status, kErrWaitTma);
     mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
     tc_fence_after();
-    mma_scores(tS, sK, sQ0, 128);
-    mma_scores(tDOV, sV, sD0, 128);
+    mma_scores(tS, sK, sQ0, 64);
+    mma_scores(tDOV, sV, sD0, 64);
     mma_commit(sdone);
   }
   __syncwarp();
 
   float suffix = 0.f;
-  float incl_hi = load_incl(nqb - 1, 1), incl_lo = load_incl(nqb - 1, 0);
+  float incl = load_incl(ncb - 1);
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   for (int t = 0; t < nsteps; ++t) {
-    const int ib = nqb - 1 - t, b = t & 1;
-    // fetch what the next tile needs before waiting for this one
+    const int rb = ncb - 1 - t, b = t & 1;
+    // fetch what the next step needs before waiting for this one
     float2 stat_next = make_float2(INFINITY, 0.f);
-    float incl_hi_next = 0.f, incl_lo_next = 0.f;
+    float incl_next = 0.f;
     if (t + 1 < nsteps) {
-      stat_next = load_stats(ib - 1);
-      incl_hi_next = load_incl(ib - 1, 1);
-      incl_lo_next = load_incl(ib - 1, 0);
+      stat_next = load_stats(rb - 1);
+      incl_next = load_incl(rb - 1);
     }
     mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
-    if (tid == 0 && t + 1 < nsteps) {               // buffers of step t-1 are free
-      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kTileBytes);
-      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
-      tma_load_tile(sD0 + kTileBytes * (b ^ 1), &map_do, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+    if (tid == 0 && t + 1 < nsteps) {               // the stage of step t-1 is free
+      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kHalfBytes);
+      tma_load_tile(sQ0 + kHalfBytes * (b ^ 1), &map_q, (rb - 1) * kHalfRows, n, qfull + 8 * (b ^ 1));
+      tma_load_tile(sD0 + kHalfBytes * (b ^ 1), &map_do, (rb - 1) * kHalfRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
-    const int i0 = ib * kTileRows;                   // first query of the tile (q_off == 0 here)
+    const int i0 = rb * kHalfRows;                   // first query of the block (q_off == 0 here)
     const bool masked_tile = dead || (i0 < k0 + kTileRows - 1);
-    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * kHalfRows);
 
     // one chunk = 32 queries, visited from the last to the first
-    auto chunk = [&](auto mask_tag, const float* vs, const float* vd, int qc, float& incl) {
+    auto chunk = [&](auto mask_tag, const float* vs, const float* vd, int qc) {
       constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
       for (int e8 = 3; e8 >= 0; --e8) {
@@ -705,41 +724,26 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
                      : "memory");
       }
     };
-    {
-      float sa[32], da[32], sb[32], db[32];
-      tmem_ld32(tS + lane_base + 96, sa);
-      tmem_ld32(tDOV + lane_base + 96, da);
-      tmem_ld_wait(sa);
-      tmem_ld_wait(da);
-      tmem_ld32(tS + lane_base + 64, sb);
-      tmem_ld32(tDOV + lane_base + 64, db);
-      if (masked_tile) chunk(std::true_type{}, sa, da, 96, incl_hi); else chunk(std::false_type{}, sa, da, 96, incl_hi);
-      tmem_ld_wait(sb);
-      tmem_ld_wait(db);
-      tmem_ld32(tS + lane_base + 32, sa);
-      tmem_ld32(tDOV + lane_base + 32, da);
-      if (masked_tile) chunk(std::true_type{}, sb, db, 64, incl_hi); else chunk(std::false_type{}, sb, db, 64, incl_hi);
-      tmem_ld_wait(sa);
-      tmem_ld_wait(da);
-      tmem_ld32(tS + lane_base, sb);
-      tmem_ld32(tDOV + lane_base, db);
-      if (masked_tile) chunk(std::true_type{}, sa, da, 32, incl_lo); else chunk(std::false_type{}, sa, da, 32, incl_lo);
-      tmem_ld_wait(sb);
-      tmem_ld_wait(db);
-      if (masked_tile) chunk(std::true_type{}, sb, db, 0, incl_lo); else chunk(std::false_type{}, sb, db, 0, incl_lo);
+#pragma unroll 1
+    for (int c = 1; c >= 0; --c) {
+      float vs[32], vd[32];
+      tmem_ld32(tS + lane_base + 32 * c, vs);
+      tmem_ld32(tDOV + lane_base + 32 * c, vd);
+      tmem_ld_wait(vs);
+      tmem_ld_wait(vd);
+      if (masked_tile) chunk(std::true_type{}, vs, vd, 32 * c); else chunk(std::false_type{}, vs, vd, 32 * c);
     }
-    sStat[(b ^ 1) * 128 + tid] = stat_next;
-    incl_hi = incl_hi_next;
-    incl_lo = incl_lo_next;
+    if (tid < kHalfRows) sStat[(b ^ 1) * kHalfRows + tid] = stat_next;
+    incl = incl_next;
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
       const uint32_t id_kd = instr_desc(128, 64, 0, 1);   // A K-major (M = keys), B MN-major
-      const uint32_t id_qd = instr_desc(128, 64, 1, 1);   // A MN-major (M = queries)
-      const uint32_t id_g = instr_desc(128, 16, 1, 0);
-      const uint32_t sQ = sQ0 + kTileBytes * b, sD = sD0 + kTileBytes * b;
+      const uint32_t id_qd = instr_desc(64, 64, 1, 1);    // A MN-major (M = 64 queries)
+      const uint32_t id_g = instr_desc(64, 16, 1, 0);
+      const uint32_t sQ = sQ0 + kHalfBytes * b, sD = sD0 + kHalfBytes * b;
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {                    // contraction over the 128 keys
         const uint64_t a = smem_desc(sPd + 2048 * kk, kTileBytes, 1024);
@@ -748,35 +752,28 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
       }
       mma_commit(dqdone);
 #pragma unroll
-      for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
-        const uint32_t aoff = (kq >> 2) * kTileBytes + (kq & 3) * 32;
-        mma_ss(tDV, smem_desc(sSh + aoff, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
+      for (int kq = 0; kq < 4; ++kq) {                    // contraction over the 64 queries
+        mma_ss(tDV, smem_desc(sSh + 32 * kq, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
                (t > 0 || kq > 0));
-        mma_ss(tDK, smem_desc(sPd + aoff, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
+        mma_ss(tDK, smem_desc(sPd + 32 * kq, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
                (t > 0 || kq > 0));
       }
-      if (t + 1 < nsteps) {
-        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
-        tc_fence_after();
-        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
-        mma_scores(tDOV, sV, sD0 + kTileBytes * (b ^ 1), 128);
-      }
-      mma_commit(sdone);
     }
     __syncwarp();
-    // dQ and ghat of this tile: lane = query.  Runs under the remaining MMAs.
+    // dQ and ghat of this step.  Runs under the dV / dK MMAs.
     mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     {
       float dq[32], gh[32];
       tmem_ld32(tG + lane_base, gh);
-      const int i = i0 + tid;
+      const int i = i0 + 16 * warp + lane;             // valid for lane < 16
+      const bool mine = lane < 16 && i < g.tq;
       float* dst = dq_main + (row_base + i) * kHeadDim;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         tmem_ld32(tDQ + lane_base + 32 * c, dq);
         tmem_ld_wait(dq);
-        if (i < g.tq) {
+        if (mine) {
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4)
             red_add_v4(dst + 32 * c + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale,
@@ -784,9 +781,21 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
         }
       }
       tmem_ld_wait(gh);
-      if (i < g.tq) atomicAdd(ghat + row_base + i, gh[0]);
+      if (mine) atomicAdd(ghat + row_base + i, gh[0]);
     }
     tc_fence_before();
+    __syncthreads();                                     // S^T / dOV^T columns are free again
+    if (tid == 0) {
+      tc_fence_after();
+      if (t + 1 < nsteps) {
+        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+        tc_fence_after();
+        mma_scores(tS, sK, sQ0 + kHalfBytes * (b ^ 1), 64);
+        mma_scores(tDOV, sV, sD0 + kHalfBytes * (b ^ 1), 64);
+      }
+      mma_commit(sdone);
+    }
+    __syncwarp();
   }
   mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
@@ -816,7 +825,7 @@ __global__ void __launch_bounds__(128, 1) backward_main_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, 512);
+  if (warp == 0) tmem_free(tmem, 256);
 }
 
 // Softmax-Jacobian corrections (the reference's BC + dq epilogue, kernels.py:777-826):
@@ -907,12 +916,22 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       float vs[32];
       tmem_ld32(tS + lane_base + 64 * wg + 32 * c, vs);
       tmem_ld_wait(vs);
+      float4 snext[4];
+#pragma unroll
+      for (int u2 = 0; u2 < 4; ++u2) snext[u2] = St4[(c * 32) / 2 + u2];
 #pragma unroll
       for (int e8 = 0; e8 < 4; ++e8) {
         float w8[8];
+        float4 scur[4];
+#pragma unroll
+        for (int u2 = 0; u2 < 4; ++u2) scur[u2] = snext[u2];
+        if (e8 < 3) {      // next group's statistics, read before this group's store
+#pragma unroll
+          for (int u2 = 0; u2 < 4; ++u2) snext[u2] = St4[(c * 32 + (e8 + 1) * 8) / 2 + u2];
+        }
 #pragma unroll
         for (int u2 = 0; u2 < 4; ++u2) {
-          const float4 st = St4[(c * 32 + e8 * 8) / 2 + u2];
+          const float4 st = scur[u2];
           const float lse[2] = {st.x, st.z}, gh[2] = {st.y, st.w};
 #pragma unroll
           for (int w = 0; w < 2; ++w) {
@@ -1085,11 +1104,13 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
                     const float* total, const float* ssum, float* dq_main, float* dk_main, float* ghat,
                     float* dbarp, void* dop, void* dq, void* dk, void* dv, cudaStream_t st, char* err,
                     size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
-  CUtensorMap mq, mk, mv, md;
+  CUtensorMap mq, mk, mv;
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
-  if (int rc = make_map(&md, dop, g.n, g.tq, err, errlen)) return rc;
+  CUtensorMap mq64, md64;
+  if (int rc = make_map(&mq64, q, g.n, g.tq, err, errlen, kHalfRows)) return rc;
+  if (int rc = make_map(&md64, dop, g.n, g.tq, err, errlen, kHalfRows)) return rc;
   const int64_t rows = g.n * g.tq;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
   mark("tc_backward_prep", st, 0);
@@ -1097,10 +1118,12 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
                                                                   (__nv_bfloat16*)dop, ghat, dq_main);
   mark("tc_backward_prep", st, 1);
   if (int rc = launch_status("tc backward_prep", err, errlen)) return rc;
-  if (int rc = set_smem_attr((const void*)backward_main_kernel, kBwdSmem, err, errlen)) return rc;
+  constexpr int smem_bwd = kBwdSmem > kTwoPerSm ? kBwdSmem : kTwoPerSm;
+  static_assert(2 * (smem_bwd + 1024) <= 233472, "two CTAs of the backward main pass must fit one SM");
+  if (int rc = set_smem_attr((const void*)backward_main_kernel, smem_bwd, err, errlen)) return rc;
   mark("tc_backward_main", st, 0);
-  backward_main_kernel<<<(unsigned)(g.n * nkb), 128, kBwdSmem, st>>>(
-      mq, mk, mv, md, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
+  backward_main_kernel<<<(unsigned)(g.n * nkb), 128, smem_bwd, st>>>(
+      mq64, mk, mv, md64, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
