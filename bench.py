@@ -373,12 +373,71 @@ def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
             "kernels_ms": {n: tot / cnt for n, (cnt, tot) in prof.items()}}
 
 
+PREFILL = dict(H=16, T=131072, D=64)
+
+
+def run_prefill(args, rank, world):
+    """Long-context prefill (forward + demand vector), B=1 H=16 T=131072 d=64 bf16, sequence-parallel:
+    rank r owns a contiguous, equal-causal-area query chunk, all-gathers K/V, exchanges per-key
+    demand once.  Strong scaling: the problem is fixed, value = 2*H*T*(T+1)*D / time."""
+    import torch.distributed as dist
+    pkg = importlib.import_module("dilution-attention_b200")
+    P = pkg.partition
+    pkg._lib.load()
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    H, T, D = (PREFILL[x] for x in "HTD")
+    T = args.seq if args.seq != TRAIN["T"] else T
+    bounds = P.equal_area_bounds(T, world)
+    a, b = bounds[rank], bounds[rank + 1]
+    gen = torch.Generator(device=dev).manual_seed(1340 + rank)
+    ql, kl, vl = (torch.empty(H, b - a, D, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+                  for _ in range(3))
+
+    def step():
+        return P.sequence_parallel_prefill(ql, kl, vl, T, bounds, dot_precision="bf16")
+
+    for _ in range(args.warmup):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            out, demand = step()
+        stop.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+    tms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = tms.item()
+    status = pkg._lib.load().dilution_device_status()
+    if rank == 0:
+        flops = causal_flops(H, T, D, 2)
+        print(json.dumps({"metric": "prefill TFLOP/s @T=128K (B1 H16 d64, forward + demand)",
+                          "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic", "device_status": status,
+                          "config": {"workload": f"prefill_B1_H{H}_T{T}_d{D}", "query_chunk_bounds": bounds,
+                                     "parallelism": f"sequence-parallel x{world}: K/V all-gather + "
+                                                    "all-gather/masked-sum exscan of per-key demand",
+                                     "flop_count": "2*H*T*(T+1)*D"},
+                          "clocks": clocks.summary()}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="train", choices=["train", "prefill"],
+                    help="train: the headline fwd+bwd step (default); prefill: 128K sequence-parallel forward")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -393,6 +452,13 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    if args.workload == "prefill":
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        run_prefill(args, rank, world)
+        return
     run_ours(args, rank, world)
 
 

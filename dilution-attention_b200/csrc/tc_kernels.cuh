@@ -166,31 +166,34 @@ __global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant_
     }
     __syncwarp();
     const bool edge = (jb * kTileRows + kTileRows - 1 > q0) || ((jb + 1) * kTileRows > g.tk);
+    // the mask arithmetic exists only in the instantiation used for edge tiles
+    auto tile = [&](auto edge_tag) {
+      constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      float v[32];
-      tmem_ld32(taddr + 32 * c, v);
-      tmem_ld_wait(v);
-      float cmax = -INFINITY;
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(taddr + 32 * c, v);
+        tmem_ld_wait(v);
+        float cmax = -INFINITY;          // max of the raw scores (zscale > 0 keeps the order)
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float z = v[e] * g.zscale;
-        if (edge) {
-          const int ja = jb * kTileRows + wg * 64 + c * 32 + e;
-          if (ja > ia || ja >= g.tk) z = -INFINITY;
+        for (int e = 0; e < 32; ++e) {
+          if (EDGE) {
+            const int ja = jb * kTileRows + wg * 64 + c * 32 + e;
+            if (ja > ia || ja >= g.tk) v[e] = -INFINITY;
+          }
+          cmax = fmaxf(cmax, v[e]);
         }
-        v[e] = z;
-        cmax = fmaxf(cmax, z);
-      }
-      const float nm = fmaxf(m, cmax);
-      if (nm > -INFINITY) {
-        float ps = 0.f;
+        const float nm = fmaxf(m, cmax * g.zscale);
+        if (nm > -INFINITY) {
+          float ps = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) ps += fast_exp2(v[e] - nm);
-        s = s * fast_exp2(m - nm) + ps;
-        m = nm;
+          for (int e = 0; e < 32; ++e) ps += fast_exp2(fmaf(v[e], g.zscale, -nm));
+          s = s * fast_exp2(m - nm) + ps;
+          m = nm;
+        }
       }
-    }
+    };
+    if (edge) tile(std::true_type{}); else tile(std::false_type{});
     tc_fence_before();
     __syncthreads();
   }
@@ -298,23 +301,29 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
     const bool edge = i0 < k0 + kTileRows - 1;            // part of the diagonal tile
     const float4* L4 = reinterpret_cast<const float4*>(sL + 128 * b + 64 * wg);
     float colsum = 0.f;
+    auto tile = [&](auto edge_tag) {
+      constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      float v[32];
-      tmem_ld32(taddr + 32 * c, v);
-      tmem_ld_wait(v);
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(taddr + 32 * c, v);
+        tmem_ld_wait(v);
+        float part[4] = {0.f, 0.f, 0.f, 0.f};     // four independent sums
 #pragma unroll
-      for (int e4 = 0; e4 < 8; ++e4) {
-        const float4 l = L4[c * 8 + e4];
-        const float ls[4] = {l.x, l.y, l.z, l.w};
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l = L4[c * 8 + e4];
+          const float ls[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
-          if (edge && ja > i0 + c * 32 + e4 * 4 + u) p = 0.f;
-          colsum += p;
+          for (int u = 0; u < 4; ++u) {
+            float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
+            if (EDGE && ja > i0 + c * 32 + e4 * 4 + u) p = 0.f;
+            part[u] += p;
+          }
         }
+        colsum += (part[0] + part[1]) + (part[2] + part[3]);
       }
-    }
+    };
+    if (edge) tile(std::true_type{}); else tile(std::false_type{});
     if (wg == 0) prev = colsum; else sCs[b * 128 + row] = colsum;
     if (wg == 1 && it + 1 < nib) sL[128 * (b ^ 1) + row] = lse_next;
     tc_fence_before();
@@ -440,6 +449,8 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
     if (jb + 1 < njb) den_next = load_den(jb + 1);   // lands while this tile is processed
     const bool diag = jb * kTileRows + kTileRows - 1 > qh;
     const bool dead = ja >= g.tk;
+    auto tile = [&](auto mask_tag) {
+    constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
       float v[32];
@@ -464,7 +475,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
           for (int u = 0; u < 4; ++u) {
             const int e = e8 * 8 + h * 4 + u;
             float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
-            if (dead || (diag && ja > qh + c * 32 + e)) p = 0.f;
+            if (MASK && (dead || ja > qh + c * 32 + e)) p = 0.f;
             den += p;
             sh[u] = p * fast_rcp(den);
           }
@@ -477,6 +488,8 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
                      : "memory");
       }
     }
+    };
+    if (diag || dead) tile(std::true_type{}); else tile(std::false_type{});
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -701,14 +714,17 @@ __global__ void __launch_bounds__(128, 2) backward_main_kernel(
               off = dead || ja > i0 + qc + e;
               if (off) p = 0.f;
             }
-            const float den = fmaxf(incl + g.eps, g.eps);
+            // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
+            //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share
+            const float den = MASK ? fmaxf(incl + g.eps, g.eps) : incl + g.eps;
             const float inv = fast_rcp(den);
-            const float a = (vd[e] - dbr[w]) * inv * inv;
-            const float dp = fmaf(a, den - p, suffix);         // ds (committed+eps) inv^2 + suffix
-            pd[u] = p * dp;
-            sh[u] = p * inv;
+            const float wv = (vd[e] - dbr[w]) * inv;
+            const float share = p * inv;
+            const float gneg = wv * share;                     // -dk_share
+            pd[u] = p * ((wv - gneg) + suffix);                // p * dp
+            sh[u] = share;
             if (!MASK || !off) {
-              suffix -= a * p;                                 // += dk_share
+              suffix -= gneg;
               incl -= p;
             }
           }
@@ -911,6 +927,8 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     const int i0 = ib * kTileRows + 64 * wg;
     const bool masked_tile = dead || t == 0;
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
+    auto tile = [&](auto mask_tag) {
+    constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
       float vs[32];
@@ -937,7 +955,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
           for (int w = 0; w < 2; ++w) {
             const int u = u2 * 2 + w, e = e8 * 8 + u;
             float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
-            if (masked_tile && (dead || ja > i0 + c * 32 + e)) p = 0.f;
+            if (MASK && (dead || ja > i0 + c * 32 + e)) p = 0.f;
             w8[u] = p * gh[w];
           }
         }
@@ -947,6 +965,8 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
                      : "memory");
       }
     }
+    };
+    if (masked_tile) tile(std::true_type{}); else tile(std::false_type{});
     if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
     fence_async_smem();
     tc_fence_before();
