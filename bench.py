@@ -190,6 +190,17 @@ def run_ours(args, rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
+    if args.no_train:
+        def sync_only():
+            if distributed:
+                dist.barrier()
+            torch.cuda.synchronize()
+        decode = run_decode(K, L, dev, rank, world, peaks, sync_only, distributed)
+        if rank == 0:
+            print(json.dumps({"decode": decode}), flush=True)
+        if distributed:
+            dist.destroy_process_group()
+        return
     B, H, T, D = (TRAIN[x] for x in "BHTD")
     n_rows = B * H
 
@@ -319,7 +330,7 @@ def run_e2e(args, K, host, devt, dev, barrier, distributed, total_flops):
 def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
     import torch.distributed as dist
     cfg = DECODE
-    rows = cfg["batch"] * cfg["H"] // world          # heads sharded across ranks
+    rows = cfg["rows"] // world                       # heads sharded across ranks
     d, L0, steps = cfg["D"], cfg["L"], cfg["steps"]
     warm = 3
     cap = L0 + steps + warm
@@ -362,7 +373,7 @@ def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
     achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
     del kc, vc, committed, scratch
     torch.cuda.empty_cache()
-    return {"metric": "decode tok/s @128K KV", "value": cfg["batch"] / (ms * 1e-3), "unit": "tok/s",
+    return {"metric": "decode tok/s @128K KV", "value": cfg["rows"] / cfg["H"] / (ms * 1e-3), "unit": "tok/s",
             "ms_per_step": ms, "rows_per_gpu": rows, "cache_len": L0, "steps": steps,
             "config": "batch 64 x 16 heads, d=64, bf16 KV, fp32 demand; heads sharded across GPUs; "
                       "demand initialised analytically (ln(L/j)), KV N(0,1) generated on device",
@@ -439,6 +450,10 @@ def main():
     ap.add_argument("--workload", default="train", choices=["train", "prefill"],
                     help="train: the headline fwd+bwd step (default); prefill: 128K sequence-parallel forward")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-train", action="store_true", help="skip the training-shape step (decode only)")
+    ap.add_argument("--decode-rows", type=int, default=DECODE["batch"] * DECODE["H"],
+                    help="(batch*head) rows of the decode workload (profiling captures use fewer)")
+    ap.add_argument("--decode-steps", type=int, default=DECODE["steps"])
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seq", type=int, default=TRAIN["T"],
@@ -447,6 +462,8 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     TRAIN["T"] = args.seq
+    DECODE["rows"] = args.decode_rows
+    DECODE["steps"] = args.decode_steps
     if args.impl == "reference":
         run_reference(args, rank)
         return
