@@ -19,6 +19,7 @@ from . import _lib, kernels, partition  # noqa: F401
 from .kernels import (  # noqa: F401
     dilution_attention,
     dilution_attention_forward,
+    dilution_attention_host,
     dilution_attention_reference,
     dilution_decode_step,
     install,
@@ -28,5 +29,5 @@ _sys.modules.setdefault("dilution_attention_b200", _sys.modules[__name__])
 
 __all__ = [
     "kernels", "partition", "dilution_attention", "dilution_attention_forward",
-    "dilution_attention_reference", "dilution_decode_step", "install",
+    "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step", "install",
 ]

@@ -297,6 +297,82 @@ def dilution_decode_step(
     return out.view(batch, heads, 1, head_dim)
 
 
+def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", device=None, slabs: int = 8,
+                            out=None, grads=None):
+    """The operator for tensors that live in HOST memory (ideally pinned).
+
+    q, k, v: (B, H, T, D) CPU tensors; dout: optional (B, H, T, D) upstream gradient.
+    Returns out (fp32, CPU) and, when dout is given, (out, dq, dk, dv) with the
+    gradients in the input dtypes.  `out` / `grads` may be preallocated (pinned)
+    result buffers.
+
+    The (batch*head) rows are independent, so the call is cut into `slabs` row
+    slabs that flow through three CUDA streams: host->device copy of slab i+1,
+    forward+backward of slab i and device->host copy of slab i-1 run at the same
+    time.  End-to-end time approaches max(compute, one copy direction) instead of
+    their sum.  The maths and kernels are those of `dilution_attention`.
+    """
+    lib_device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    batch, heads, seq, head_dim = q.shape
+    n = batch * heads
+    slabs = max(1, min(slabs, n))
+    bounds = [n * i // slabs for i in range(slabs + 1)]
+    qh, kh, vh = (x.reshape(n, 1, seq, head_dim) for x in (q, k, v))
+    doh = None if dout is None else dout.reshape(n, 1, seq, head_dim)
+    if out is None:
+        out = torch.empty(batch, heads, seq, head_dim, dtype=torch.float32, pin_memory=True)
+    oh = out.reshape(n, 1, seq, head_dim)
+    if dout is not None and grads is None:
+        grads = tuple(torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in (q, k, v))
+    gh = None if dout is None else tuple(x.reshape(n, 1, seq, head_dim) for x in grads)
+
+    main = torch.cuda.current_stream(lib_device)
+    s_in, s_out = torch.cuda.Stream(lib_device), torch.cuda.Stream(lib_device)
+    s_in.wait_stream(main)
+    staged, done = [], []
+
+    def stage(i):
+        a, b = bounds[i], bounds[i + 1]
+        with torch.cuda.stream(s_in):
+            bufs = [x[a:b].to(lib_device, non_blocking=True) for x in (qh, kh, vh)]
+            bufs.append(None if doh is None else doh[a:b].to(lib_device, non_blocking=True))
+            ev = torch.cuda.Event()
+            ev.record(s_in)
+        return bufs, ev
+
+    staged.append(stage(0))
+    for i in range(slabs):
+        a, b = bounds[i], bounds[i + 1]
+        if i + 1 < slabs:
+            staged.append(stage(i + 1))
+        (qd, kd, vd, dd), ev = staged[i]
+        main.wait_event(ev)
+        if dd is None:
+            od = dilution_attention_forward(qd, kd, vd, dot_precision=dot_precision)
+            res = (od,)
+        else:
+            qd, kd, vd = (x.requires_grad_(True) for x in (qd, kd, vd))
+            od = dilution_attention(qd, kd, vd, dot_precision=dot_precision)
+            od.backward(dd)
+            res = (od.detach(), qd.grad, kd.grad, vd.grad)
+        for x in (qd, kd, vd, dd) + res:
+            if x is not None:
+                x.record_stream(main)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ready)
+            oh[a:b].copy_(res[0], non_blocking=True)
+            if dd is not None:
+                for dst, src in zip(gh, res[1:]):
+                    dst[a:b].copy_(src, non_blocking=True)
+            for x in res:
+                x.record_stream(s_out)
+        staged[i] = None
+    main.wait_stream(s_out)
+    return out if dout is None else (out, *grads)
+
+
 def install(target=None):
     """Plug this backend into the reference package: assign the fused entry
     points onto `dilution.kernels` (or `target`), the same way the reference's

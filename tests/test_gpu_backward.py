@@ -106,3 +106,23 @@ def test_bf16_training_step_runs_on_the_tensor_core_kernels(pkg, kernels):
     ref = O.dilution_backward(qs.detach().float().cpu(), ks.detach().float().cpu(), vs.detach().float().cpu(), dout)
     for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
         assert rel_err(t.grad.float().cpu(), gr) < 3e-2, name
+
+
+def test_host_buffer_entry_point_matches_device_op(kernels):
+    """dilution_attention_host (pinned host tensors in and out, slabs pipelined over
+    streams) returns what the device op returns."""
+    q, k, v, dout = make_inputs(2, 3, 300, 64, 901, scales=(0.5, 0.5, 1.0, 1e-2))
+    qb, kb, vb = (x.bfloat16().pin_memory() for x in (q, k, v))
+    dout = dout.pin_memory()
+    out, dq, dk, dv = kernels.dilution_attention_host(qb, kb, vb, dout, dot_precision="bf16", slabs=4)
+    torch.cuda.synchronize()
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    ref = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+    ref.backward(dout.to(DEV))
+    assert torch.equal(out, ref.detach().cpu())
+    assert torch.equal(dv, vs.grad.cpu()) and torch.equal(dk, ks.grad.cpu())
+    # dq is accumulated with floating-point reductions whose order varies between runs
+    assert rel_err(dq.float(), qs.grad.float().cpu()) < 2e-2
+    fwd_only = kernels.dilution_attention_host(qb, kb, vb, dot_precision="bf16", slabs=3)
+    torch.cuda.synchronize()
+    assert torch.equal(fwd_only, out)
