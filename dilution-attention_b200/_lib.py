@@ -22,6 +22,7 @@ SIGNATURES = {
     "dilution_version": (ctypes.c_int, []),
     "dilution_last_error": (ctypes.c_char_p, []),
     "dilution_device_status": (_I, []),
+    "dilution_selftest_bounded_wait": (_I, [_P, _P]),
     "dilution_launch_count": (ctypes.c_ulonglong, []),
     "dilution_profile_enable": (_I, [_I]),
     "dilution_profile_collect": (_I, [ctypes.c_char_p, _Z]),

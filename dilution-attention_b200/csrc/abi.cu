@@ -348,6 +348,15 @@ int dilution_device_status(void) {
   return DILUTION_OK;
 }
 
+int dilution_selftest_bounded_wait(int* gave_up, void* stream) {
+#ifdef DILUTION_TENSOR_PATH
+  if (!gave_up) return fail(DILUTION_ERR_ARG, "dilution_selftest_bounded_wait: null pointer");
+  return dil::tc::selftest_wait(gave_up, (cudaStream_t)stream, g_err, sizeof(g_err));
+#else
+  return fail(DILUTION_ERR_UNSUPPORTED, "built without the tensor-core path");
+#endif
+}
+
 unsigned long long dilution_launch_count(void) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
   return g_launches;

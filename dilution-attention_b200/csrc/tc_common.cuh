@@ -28,7 +28,7 @@ constexpr int kHeadDim = 64;
 constexpr uint32_t kTileBytes = kTileRows * kHeadDim * 2;   // 16 KB
 constexpr long long kWaitCycles = 4000000000LL;             // ~2 s: a live wait is microseconds
 
-enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103 };
+enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103, kErrSelfTest = 199 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -69,12 +69,12 @@ struct Ctl {
 // Bounded wait.  Returns false (at once, if the CTA is already aborting) when
 // the phase did not complete in time.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, int* status,
-                                          int code) {
+                                          int code, long long limit = kWaitCycles) {
   if (ctl->abort) return false;
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       ctl->abort = 1;
       atomicCAS(status, 0, code);
       return false;

@@ -1160,6 +1160,28 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   return launch_status("tc cast_dq", err, errlen);
 }
 
+// Self-test of the bounded wait: one CTA waits on an mbarrier phase that nothing will
+// ever complete, with a short limit (about a millisecond).  The wait must give up,
+// record kErrSelfTest and let the kernel return normally; nothing faults or hangs.
+__global__ void selftest_wait_kernel(long long limit_cycles, int* __restrict__ gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ Ctl ctl;
+  if (threadIdx.x == 0) {
+    ctl.abort = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait(smem_u32(&bar), 0, &ctl, &g_status, kErrSelfTest, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+
+inline int selftest_wait(int* gave_up_dev, cudaStream_t st, char* err, size_t errlen) {
+  selftest_wait_kernel<<<1, 64, 0, st>>>(2000000LL, gave_up_dev);
+  return launch_status("selftest_wait", err, errlen);
+}
+
 // Reads (and clears) the device status word; synchronises the device.
 inline int read_status(int* out) {
   int v = 0;

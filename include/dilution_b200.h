@@ -66,6 +66,13 @@ const char* dilution_last_error(void);
  * clears it), else DILUTION_OK.  No reference counterpart. */
 int dilution_device_status(void);
 
+/* Exercises the bounded wait without faulting anything: launches one tiny kernel
+ * that waits (about a millisecond) on a barrier nothing will complete.  The wait
+ * gives up, the kernel writes 1 to *gave_up (device int) and returns normally, and
+ * the next dilution_device_status() reports DILUTION_ERR_DEVICE once.  The context
+ * stays usable.  No reference counterpart. */
+int dilution_selftest_bounded_wait(int* gave_up, void* stream);
+
 /* Kernel launches issued by this library so far in this process.
  * No reference counterpart. */
 unsigned long long dilution_launch_count(void);
