@@ -571,27 +571,28 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 
 // Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
-// key blocks with the most query blocks first; 128 threads, two CTAs per SM.
-// The CTA keeps the K and V tiles of 128 keys and walks the 64-row query blocks from
-// last to first.  S^T = K Q^T and (dO' V^T)^T = V dO'^T are [128 keys x 64 queries]
-// tiles, lane = key.  The thread walks the 64 queries backwards with two registers:
-//   incl   : demand of its key including the current query.  It starts from the
-//            stored checkpoint of the next 64-row block and is walked backwards by
-//            subtracting p, so committed + p + eps = incl + eps needs no forward sweep;
-//   suffix : running sum of dk_share over later queries (kernels.py:763-764).
-// Per step it writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
-// K-major they are A operands with M = 128 keys (dV += share^T dO', dK += pdp^T Q);
-// pdp read as MN-major is the A operand with M = 64 queries (dQ = pdp K, ghat = pdp 1).
-// TMEM (256 columns): S^T 64 | dOV^T 64 | dV 64 | dK 64.  The dQ and ghat results of a
-// step reuse the S^T / dOV^T columns, which are dead once the threads have consumed
-// them; the next step's score MMAs are issued after dQ has been read out.
-// An M = 64 accumulator sits on lanes 0-15 of each 32-lane quarter: row r of D is lane
-// 32*(r/16) + r%16, so threads with (tid & 31) < 16 own one query row each.
-constexpr int kHalfRows = 64;
-constexpr uint32_t kHalfBytes = kHalfRows * kHeadDim * 2;     // 8 KB
-constexpr int kBwdSmem = 2 * kTileBytes + 4 * kHalfBytes + 2 * kTileBytes + 2048 + 1024 + 1024 + 256;
+// key blocks with the most query blocks first; 256 threads, one CTA per SM (464 TMEM
+// columns: S^T 128 | dOV^T 128 | dV 64 | dK 64 | dQ 64 | ghat 16).
+// The CTA keeps the K and V tiles of 128 keys and walks the 128-row query blocks from
+// last to first.  S^T = K Q^T and (dO' V^T)^T = V dO'^T are [128 keys x 128 queries],
+// lane = key.  Two threads share a key: warpgroup 0 walks queries 127..64 of the tile,
+// warpgroup 1 queries 63..0, both backwards, each with two registers:
+//   incl   : demand of the key including the current query.  It starts from the stored
+//            checkpoint of the next 64-row block and is walked backwards by subtracting
+//            p, so committed + p + eps = incl + eps needs no forward sweep and the two
+//            halves are independent;
+//   suffix : running sum of dk_share over later queries (kernels.py:763-764).  Warpgroup
+//            1 does not yet know the sum G0 of warpgroup 0's half; dp is linear in the
+//            suffix, so it keeps pdp (fp32) and p (bf16) in registers, and after one
+//            block-wide barrier adds p * G0 before it stores its half of the pdp tile.
+// Per step the CTA writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
+// K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q); pdp read
+// as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).  dQ has its
+// own columns, so the next step's score MMAs are issued right behind this step's and
+// the dQ read-out runs under them.
+constexpr int kBwdSmem = 6 * kTileBytes + 4 * kTileBytes + 2048 + 2048 + 1024 + 1024 + 256;
 
-__global__ void __launch_bounds__(128, 2) backward_main_kernel(
+__global__ void __launch_bounds__(256, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
@@ -600,39 +601,40 @@ __global__ void __launch_bounds__(128, 2) backward_main_kernel(
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sK = smem_u32(smem), sV = sK + kTileBytes;
-  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sQ0 + 2 * kHalfBytes;        // [2] each, 64 rows
-  const uint32_t sSh = sD0 + 2 * kHalfBytes, sPd = sSh + kTileBytes;            // [128 keys][64 q]
-  const uint32_t sOnes = sPd + kTileBytes;
-  constexpr int kOff = 2 * kTileBytes + 4 * kHalfBytes + 2 * kTileBytes;
-  uint8_t* ones_ptr = smem + kOff;
-  float2* sStat = reinterpret_cast<float2*>(smem + kOff + 2048);                // [2][64] (lse, dbar')
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOff + 2048 + 1024);
+  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 4 * kTileBytes;     // [2] each
+  const uint32_t sSh = sK + 6 * kTileBytes, sPd = sK + 8 * kTileBytes;      // 32 KB each
+  const uint32_t sOnes = sK + 10 * kTileBytes;
+  uint8_t* ones_ptr = smem + 10 * kTileBytes;
+  float2* sStat = reinterpret_cast<float2*>(smem + 10 * kTileBytes + 2048);   // [2][128] (lse, dbar')
+  float* sG = reinterpret_cast<float*>(smem + 10 * kTileBytes + 4096);        // [2][128] half sums of dk_share
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * kTileBytes + 5120);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);           // qfull[2]
+  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);         // qfull[2]
   const uint32_t sdone = smem_u32(bars + 3), dqdone = smem_u32(bars + 4);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
+  const int half = 1 - wg;                          // warpgroup 0 owns the later 64 queries
+  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int n = (int)(blockIdx.x % g.n);
   const int jb = (int)(blockIdx.x / g.n);
   const int k0 = jb * kTileRows;
-  const int rb_first = 2 * jb;                       // first 64-row block that sees these keys
-  const int nsteps = ncb - rb_first;                 // >= 1
+  const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
   const int64_t row_base = (int64_t)n * g.tq;
-  const int ja = k0 + tid;
+  const int ja = k0 + row;
   const bool dead = ja >= g.tk;
 
-  auto load_stats = [&](int rb) {
-    const int i = rb * kHalfRows + tid;
+  auto load_stats = [&](int ib) {
+    const int i = ib * kTileRows + row;
     float2 st = make_float2(INFINITY, 0.f);
-    if (tid < kHalfRows && i < g.tq)
-      st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
+    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
     return st;
   };
-  // demand of this thread's key through the last query of block rb
-  auto load_incl = [&](int rb) {
+  // demand of this thread's key through the last query of its half of block ib
+  auto load_incl = [&](int ib) {
+    const int rb = 2 * ib + half + 1;
     if (dead) return 0.f;
-    return rb + 1 < ncb ? carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
+    return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
   };
 
   if (tid == 0) {
@@ -641,66 +643,68 @@ __global__ void __launch_bounds__(128, 2) backward_main_kernel(
     fence_barrier_init();
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  {
-    const float2 st = load_stats(ncb - 1);
-    if (tid < kHalfRows) sStat[tid] = st;
-  }
-  reinterpret_cast<uint4*>(ones_ptr)[tid] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
+  if (wg == 0) sStat[row] = load_stats(nqb - 1);
+  else reinterpret_cast<uint4*>(ones_ptr)[row] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tDOV = tmem + 64, tDV = tmem + 128, tDK = tmem + 192;
-  const uint32_t tDQ = tS, tG = tDOV;                // reuse, see above
+  const uint32_t tS = tmem, tDOV = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
+                 tG = tmem + 448;
 
   if (tid == 0) {
     mbar_expect_tx(kvfull, 2 * kTileBytes);
     tma_load_tile(sK, &map_k, k0, n, kvfull);
     tma_load_tile(sV, &map_v, k0, n, kvfull);
-    mbar_expect_tx(qfull, 2 * kHalfBytes);
-    tma_load_tile(sQ0, &map_q, (ncb - 1) * kHalfRows, n, qfull);
-    tma_load_tile(sD0, &map_do, (ncb - 1) * kHalfRows, n, qfull);
+    mbar_expect_tx(qfull, 2 * kTileBytes);
+    tma_load_tile(sQ0, &map_q, (nqb - 1) * kTileRows, n, qfull);
+    tma_load_tile(sD0, &map_do, (nqb - 1) * kTileRows, n, qfull);
     mbar_wait(kvfull, 0, ctl, &g_status, kErrWaitTma);
     mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
     tc_fence_after();
-    mma_scores(tS, sK, sQ0, 64);
-    mma_scores(tDOV, sV, sD0, 64);
+    mma_scores(tS, sK, sQ0, 128);
+    mma_scores(tDOV, sV, sD0, 128);
     mma_commit(sdone);
   }
   __syncwarp();
 
-  float suffix = 0.f;
-  float incl = load_incl(ncb - 1);
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  float suffix_in = 0.f;                            // suffix entering the tile (same in both warpgroups)
+  float incl = load_incl(nqb - 1);
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const int qbase = 64 * half;                      // first query column of this warpgroup
   for (int t = 0; t < nsteps; ++t) {
-    const int rb = ncb - 1 - t, b = t & 1;
-    // fetch what the next step needs before waiting for this one
+    const int ib = nqb - 1 - t, b = t & 1;
+    // fetch what the next tile needs before waiting for this one
     float2 stat_next = make_float2(INFINITY, 0.f);
     float incl_next = 0.f;
     if (t + 1 < nsteps) {
-      stat_next = load_stats(rb - 1);
-      incl_next = load_incl(rb - 1);
+      if (wg == 0) stat_next = load_stats(ib - 1);
+      incl_next = load_incl(ib - 1);
     }
     mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
-    if (tid == 0 && t + 1 < nsteps) {               // the stage of step t-1 is free
-      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kHalfBytes);
-      tma_load_tile(sQ0 + kHalfBytes * (b ^ 1), &map_q, (rb - 1) * kHalfRows, n, qfull + 8 * (b ^ 1));
-      tma_load_tile(sD0 + kHalfBytes * (b ^ 1), &map_do, (rb - 1) * kHalfRows, n, qfull + 8 * (b ^ 1));
+    if (tid == 0 && t + 1 < nsteps) {               // buffers of step t-1 are free
+      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+      tma_load_tile(sD0 + kTileBytes * (b ^ 1), &map_do, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
-    const int i0 = rb * kHalfRows;                   // first query of the block (q_off == 0 here)
+    const int i0 = ib * kTileRows;                   // first query of the tile (q_off == 0 here)
     const bool masked_tile = dead || (i0 < k0 + kTileRows - 1);
-    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * kHalfRows);
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+    float suffix = suffix_in;
+    float pdk[64];                                   // warpgroup 1: pdp without warpgroup 0's half sum
+    uint32_t pk2[32];                                // warpgroup 1: p as bf16 pairs
 
-    // one chunk = 32 queries, visited from the last to the first
-    auto chunk = [&](auto mask_tag, const float* vs, const float* vd, int qc) {
+    // one chunk = 32 queries [qc, qc+32) of the tile, visited from the last to the first
+    auto chunk = [&](auto mask_tag, auto keep_tag, const float* vs, const float* vd, int qc, int slot) {
       constexpr bool MASK = decltype(mask_tag)::value;
+      constexpr bool KEEP = decltype(keep_tag)::value;
 #pragma unroll
       for (int e8 = 3; e8 >= 0; --e8) {
-        float sh[8], pd[8];
+        float sh[8], pd[8], pp[8];
 #pragma unroll
         for (int u2 = 3; u2 >= 0; --u2) {
           const float4 st = St4[(qc + e8 * 8) / 2 + u2];       // two queries: (lse, dbar') x2
@@ -723,43 +727,81 @@ __global__ void __launch_bounds__(128, 2) backward_main_kernel(
             const float gneg = wv * share;                     // -dk_share
             pd[u] = p * ((wv - gneg) + suffix);                // p * dp
             sh[u] = share;
+            pp[u] = p;
             if (!MASK || !off) {
               suffix -= gneg;
               incl -= p;
             }
           }
         }
-        const uint32_t off8 = share_chunk_offset(tid, qc + e8 * 8);
+        const uint32_t off8 = share_chunk_offset(row, qc + e8 * 8);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sSh + off8),
                      "r"(pack_bf16(sh[0], sh[1])), "r"(pack_bf16(sh[2], sh[3])),
                      "r"(pack_bf16(sh[4], sh[5])), "r"(pack_bf16(sh[6], sh[7]))
                      : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off8),
-                     "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
-                     "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
-                     : "memory");
+        if (KEEP) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) pdk[slot * 32 + e8 * 8 + u] = pd[u];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) pk2[slot * 16 + e8 * 4 + u] = pack_bf16(pp[2 * u], pp[2 * u + 1]);
+        } else {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off8),
+                       "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
+                       "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
+                       : "memory");
+        }
       }
     };
-#pragma unroll 1
-    for (int c = 1; c >= 0; --c) {
-      float vs[32], vd[32];
-      tmem_ld32(tS + lane_base + 32 * c, vs);
-      tmem_ld32(tDOV + lane_base + 32 * c, vd);
-      tmem_ld_wait(vs);
-      tmem_ld_wait(vd);
-      if (masked_tile) chunk(std::true_type{}, vs, vd, 32 * c); else chunk(std::false_type{}, vs, vd, 32 * c);
+    auto run = [&](auto keep_tag) {
+#pragma unroll
+      for (int c = 1; c >= 0; --c) {
+        float vs[32], vd[32];
+        tmem_ld32(tS + lane_base + qbase + 32 * c, vs);
+        tmem_ld32(tDOV + lane_base + qbase + 32 * c, vd);
+        tmem_ld_wait(vs);
+        tmem_ld_wait(vd);
+        if (masked_tile) chunk(std::true_type{}, keep_tag, vs, vd, qbase + 32 * c, c);
+        else chunk(std::false_type{}, keep_tag, vs, vd, qbase + 32 * c, c);
+      }
+    };
+    if (wg == 0) run(std::false_type{}); else run(std::true_type{});
+    const float gsum = suffix - suffix_in;           // this half's sum of dk_share
+    if (wg == 0) sG[row] = gsum;
+    __syncthreads();                                 // warpgroup 0's half sums are visible
+    float g0 = gsum, g1 = gsum;
+    if (wg == 1) {
+      g0 = sG[row];
+      sG[128 + row] = gsum;
+#pragma unroll
+      for (int c = 1; c >= 0; --c)
+#pragma unroll
+        for (int e8 = 3; e8 >= 0; --e8) {
+          uint32_t o[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t pr = pk2[c * 16 + e8 * 4 + u];
+            const float plo = __uint_as_float(pr << 16), phi = __uint_as_float(pr & 0xffff0000u);
+            o[u] = pack_bf16(fmaf(plo, g0, pdk[c * 32 + e8 * 8 + 2 * u]),
+                             fmaf(phi, g0, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, 32 * c + e8 * 8)),
+                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                       : "memory");
+        }
     }
-    if (tid < kHalfRows) sStat[(b ^ 1) * kHalfRows + tid] = stat_next;
+    if (wg == 0 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
     incl = incl_next;
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (wg == 0) g1 = sG[128 + row];
+    suffix_in += g0 + g1;
     if (tid == 0) {
       tc_fence_after();
       const uint32_t id_kd = instr_desc(128, 64, 0, 1);   // A K-major (M = keys), B MN-major
-      const uint32_t id_qd = instr_desc(64, 64, 1, 1);    // A MN-major (M = 64 queries)
-      const uint32_t id_g = instr_desc(64, 16, 1, 0);
-      const uint32_t sQ = sQ0 + kHalfBytes * b, sD = sD0 + kHalfBytes * b;
+      const uint32_t id_qd = instr_desc(128, 64, 1, 1);   // A MN-major (M = queries)
+      const uint32_t id_g = instr_desc(128, 16, 1, 0);
+      const uint32_t sQ = sQ0 + kTileBytes * b, sD = sD0 + kTileBytes * b;
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {                    // contraction over the 128 keys
         const uint64_t a = smem_desc(sPd + 2048 * kk, kTileBytes, 1024);
@@ -768,80 +810,73 @@ __global__ void __launch_bounds__(128, 2) backward_main_kernel(
       }
       mma_commit(dqdone);
 #pragma unroll
-      for (int kq = 0; kq < 4; ++kq) {                    // contraction over the 64 queries
-        mma_ss(tDV, smem_desc(sSh + 32 * kq, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
+      for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
+        const uint32_t aoff = (kq >> 2) * kTileBytes + (kq & 3) * 32;
+        mma_ss(tDV, smem_desc(sSh + aoff, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
                (t > 0 || kq > 0));
-        mma_ss(tDK, smem_desc(sPd + 32 * kq, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
+        mma_ss(tDK, smem_desc(sPd + aoff, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
                (t > 0 || kq > 0));
       }
-    }
-    __syncwarp();
-    // dQ and ghat of this step.  Runs under the dV / dK MMAs.
-    mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    {
-      float dq[32], gh[32];
-      tmem_ld32(tG + lane_base, gh);
-      const int i = i0 + 16 * warp + lane;             // valid for lane < 16
-      const bool mine = lane < 16 && i < g.tq;
-      float* dst = dq_main + (row_base + i) * kHeadDim;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tDQ + lane_base + 32 * c, dq);
-        tmem_ld_wait(dq);
-        if (mine) {
-#pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4)
-            red_add_v4(dst + 32 * c + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale,
-                       dq[4 * c4 + 2] * g.scale, dq[4 * c4 + 3] * g.scale);
-        }
-      }
-      tmem_ld_wait(gh);
-      if (mine) atomicAdd(ghat + row_base + i, gh[0]);
-    }
-    tc_fence_before();
-    __syncthreads();                                     // S^T / dOV^T columns are free again
-    if (tid == 0) {
-      tc_fence_after();
       if (t + 1 < nsteps) {
         mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
         tc_fence_after();
-        mma_scores(tS, sK, sQ0 + kHalfBytes * (b ^ 1), 64);
-        mma_scores(tDOV, sV, sD0 + kHalfBytes * (b ^ 1), 64);
+        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
+        mma_scores(tDOV, sV, sD0 + kTileBytes * (b ^ 1), 128);
       }
       mma_commit(sdone);
     }
     __syncwarp();
+    // dQ and ghat of this tile: lane = query, each warpgroup takes 32 of the 64 columns.
+    // Runs under the remaining MMAs.
+    mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    {
+      float dq[32], gh[32];
+      tmem_ld32(tDQ + lane_base + 32 * wg, dq);
+      if (wg == 0) tmem_ld32(tG + lane_base, gh);
+      tmem_ld_wait(dq);
+      const int i = i0 + row;
+      if (i < g.tq) {
+        float* dst = dq_main + (row_base + i) * kHeadDim + 32 * wg;
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4)
+          red_add_v4(dst + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale,
+                     dq[4 * c4 + 2] * g.scale, dq[4 * c4 + 3] * g.scale);
+      }
+      if (wg == 0) {
+        tmem_ld_wait(gh);
+        if (i < g.tq) atomicAdd(ghat + row_base + i, gh[0]);
+      }
+    }
+    tc_fence_before();
   }
   mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
   {
+    // lane = key: each warpgroup stores 32 of the 64 columns of dk_main and dv
     float a[32];
-    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tDK + lane_base + 32 * c, a);
-      tmem_ld_wait(a);
-      if (!dead) {
+    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
+    tmem_ld32(tDK + lane_base + 32 * wg, a);
+    tmem_ld_wait(a);
+    if (!dead) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          *reinterpret_cast<float4*>(dk_main + o + 32 * c + e) =
-              make_float4(a[e] * g.scale, a[e + 1] * g.scale, a[e + 2] * g.scale, a[e + 3] * g.scale);
-      }
-      tmem_ld32(tDV + lane_base + 32 * c, a);
-      tmem_ld_wait(a);
-      if (!dead) {
+      for (int e = 0; e < 32; e += 4)
+        *reinterpret_cast<float4*>(dk_main + o + e) =
+            make_float4(a[e] * g.scale, a[e + 1] * g.scale, a[e + 2] * g.scale, a[e + 3] * g.scale);
+    }
+    tmem_ld32(tDV + lane_base + 32 * wg, a);
+    tmem_ld_wait(a);
+    if (!dead) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 8)
-          *reinterpret_cast<uint4*>(dv + o + 32 * c + e) =
-              make_uint4(pack_bf16(a[e], a[e + 1]), pack_bf16(a[e + 2], a[e + 3]),
-                         pack_bf16(a[e + 4], a[e + 5]), pack_bf16(a[e + 6], a[e + 7]));
-      }
+      for (int e = 0; e < 32; e += 8)
+        *reinterpret_cast<uint4*>(dv + o + e) =
+            make_uint4(pack_bf16(a[e], a[e + 1]), pack_bf16(a[e + 2], a[e + 3]),
+                       pack_bf16(a[e + 4], a[e + 5]), pack_bf16(a[e + 6], a[e + 7]));
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
+  if (warp == 0) tmem_free(tmem, 512);
 }
 
 // Softmax-Jacobian corrections (the reference's BC + dq epilogue, kernels.py:777-826):
@@ -1128,9 +1163,8 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
-  CUtensorMap mq64, md64;
-  if (int rc = make_map(&mq64, q, g.n, g.tq, err, errlen, kHalfRows)) return rc;
-  if (int rc = make_map(&md64, dop, g.n, g.tq, err, errlen, kHalfRows)) return rc;
+  CUtensorMap md;
+  if (int rc = make_map(&md, dop, g.n, g.tq, err, errlen)) return rc;
   const int64_t rows = g.n * g.tq;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
   mark("tc_backward_prep", st, 0);
@@ -1138,12 +1172,12 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
                                                                   (__nv_bfloat16*)dop, ghat, dq_main);
   mark("tc_backward_prep", st, 1);
   if (int rc = launch_status("tc backward_prep", err, errlen)) return rc;
-  constexpr int smem_bwd = kBwdSmem > kTwoPerSm ? kBwdSmem : kTwoPerSm;
-  static_assert(2 * (smem_bwd + 1024) <= 233472, "two CTAs of the backward main pass must fit one SM");
+  constexpr int smem_bwd = kBwdSmem;
+  static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
   if (int rc = set_smem_attr((const void*)backward_main_kernel, smem_bwd, err, errlen)) return rc;
   mark("tc_backward_main", st, 0);
-  backward_main_kernel<<<(unsigned)(g.n * nkb), 128, smem_bwd, st>>>(
-      mq64, mk, mv, md64, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
+  backward_main_kernel<<<(unsigned)(g.n * nkb), 256, smem_bwd, st>>>(
+      mq, mk, mv, md, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
