@@ -563,9 +563,6 @@ __global__ void backward_prep_kernel(const float* __restrict__ dout, const float
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-#ifdef DIL_EXP_NO_RED
-  return;
-#endif
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }

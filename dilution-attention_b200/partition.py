@@ -63,37 +63,47 @@ def exclusive_demand_prefix(local_total: torch.Tensor, seq: int, group=None):
     rows, tk = local_total.shape
     padded = local_total.new_zeros(rows, seq)
     padded[:, :tk] = local_total
-    gathered = [torch.empty_like(padded) for _ in range(world)]
-    dist.all_gather(gathered, padded, group=group)
-    base = padded.new_zeros(rows, seq)
-    for s in range(rank):
-        base += gathered[s]
-    demand = base.clone()
-    for s in range(rank, world):
-        demand += gathered[s]
+    gathered = padded.new_empty(world, rows, seq)
+    dist.all_gather(list(gathered.unbind(0)), padded, group=group)
+    demand = gathered.sum(dim=0)
+    base = gathered[:rank].sum(dim=0) if rank > 0 else padded.new_zeros(rows, seq)
     return base[:, :tk].contiguous(), demand
 
 
 def gather_keys(k_local: torch.Tensor, v_local: torch.Tensor, bounds: list[int], group=None):
-    """All-gather the K/V chunks of every rank into local memory and return the
+    """Bring the K/V chunks of every EARLIER rank into local memory and return the
     prefix [0, a_{rank+1}) this rank's queries can see.  k_local/v_local:
-    (rows, a_{r+1}-a_r, d)."""
+    (rows, a_{r+1}-a_r, d).
+
+    Causality makes the exchange triangular: rank r needs the chunks of ranks
+    s < r only, so it is done with point-to-point transfers of exactly those
+    chunks (no padding to the longest chunk, nothing sent to ranks that cannot use
+    it) instead of a symmetric all-gather.
+    """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     rows, _, d = k_local.shape
-    longest = max(bounds[r + 1] - bounds[r] for r in range(world))
-    pad = k_local.new_zeros(2, rows, longest, d)
-    pad[0, :, : k_local.shape[1]] = k_local
-    pad[1, :, : v_local.shape[1]] = v_local
-    parts = [torch.empty_like(pad) for _ in range(world)]
-    dist.all_gather(parts, pad, group=group)
     end = bounds[rank + 1]
     k = k_local.new_empty(rows, end, d)
     v = v_local.new_empty(rows, end, d)
-    for s in range(rank + 1):
+    k[:, bounds[rank]:end] = k_local
+    v[:, bounds[rank]:end] = v_local
+    if world == 1:
+        return k, v
+    mine = torch.stack((k_local, v_local)).contiguous()            # (2, rows, len_r, d)
+    ops, inbox = [], {}
+    for s in range(rank):                                           # receive from earlier ranks
+        buf = mine.new_empty(2, rows, bounds[s + 1] - bounds[s], d)
+        inbox[s] = buf
+        ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(group, s) if group else s, group))
+    for r in range(rank + 1, world):                                # send to later ranks
+        ops.append(dist.P2POp(dist.isend, mine, dist.get_global_rank(group, r) if group else r, group))
+    for req in dist.batch_isend_irecv(ops):
+        req.wait()
+    for s, buf in inbox.items():
         a, b = bounds[s], bounds[s + 1]
-        k[:, a:b] = parts[s][0, :, : b - a]
-        v[:, a:b] = parts[s][1, :, : b - a]
+        k[:, a:b] = buf[0]
+        v[:, a:b] = buf[1]
     return k, v
 
 
