@@ -587,7 +587,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).  dQ has its
 // own columns, so the next step's score MMAs are issued right behind this step's and
 // the dQ read-out runs under them.
-constexpr int kBwdSmem = 6 * kTileBytes + 4 * kTileBytes + 2048 + 2048 + 1024 + 1024 + 256;
+constexpr int kBwdSmem = 11 * kTileBytes + 2048 + 1024 + 1024 + 256;
 
 __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -600,11 +600,13 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
   const uint32_t sK = smem_u32(smem), sV = sK + kTileBytes;
   const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 4 * kTileBytes;     // [2] each
   const uint32_t sSh = sK + 6 * kTileBytes, sPd = sK + 8 * kTileBytes;      // 32 KB each
+  // a [128 keys][64] bf16 tile of ones: the second 64-column group of the dQ MMA's B operand
+  // (N = 80 = 64 columns of K + 16 of ones), so ghat comes out of the same instruction
   const uint32_t sOnes = sK + 10 * kTileBytes;
   uint8_t* ones_ptr = smem + 10 * kTileBytes;
-  float2* sStat = reinterpret_cast<float2*>(smem + 10 * kTileBytes + 2048);   // [2][128] (lse, dbar')
-  float* sG = reinterpret_cast<float*>(smem + 10 * kTileBytes + 4096);        // [2][128] half sums of dk_share
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * kTileBytes + 5120);
+  float2* sStat = reinterpret_cast<float2*>(smem + 11 * kTileBytes);          // [2][128] (lse, dbar')
+  float* sG = reinterpret_cast<float*>(smem + 11 * kTileBytes + 2048);        // [2][128] half sums of dk_share
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 11 * kTileBytes + 3072);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);         // qfull[2]
   const uint32_t sdone = smem_u32(bars + 3), dqdone = smem_u32(bars + 4);
@@ -642,7 +644,11 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
   if (wg == 0) sStat[row] = load_stats(nqb - 1);
-  else reinterpret_cast<uint4*>(ones_ptr)[row] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -796,14 +802,12 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     if (tid == 0) {
       tc_fence_after();
       const uint32_t id_kd = instr_desc(128, 64, 0, 1);   // A K-major (M = keys), B MN-major
-      const uint32_t id_qd = instr_desc(128, 64, 1, 1);   // A MN-major (M = queries)
-      const uint32_t id_g = instr_desc(128, 16, 1, 0);
+      const uint32_t id_qd = instr_desc(128, 80, 1, 1);   // A MN-major (M = queries); B = [K | ones]
       const uint32_t sQ = sQ0 + kTileBytes * b, sD = sD0 + kTileBytes * b;
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {                    // contraction over the 128 keys
         const uint64_t a = smem_desc(sPd + 2048 * kk, kTileBytes, 1024);
-        mma_ss(tDQ, a, smem_desc(sK + 2048 * kk, kTileBytes, 1024), id_qd, kk > 0);
-        mma_ss(tG, a, smem_desc(sOnes + 32 * (kk & 3), 16, 1024), id_g, kk > 0);
+        mma_ss(tDQ, a, smem_desc(sK + 2048 * kk, sOnes - sK, 1024), id_qd, kk > 0);
       }
       mma_commit(dqdone);
 #pragma unroll
