@@ -106,6 +106,23 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* m
       : "memory");
 }
 
+// Element-wise add of a shared-memory tile into global memory (performed at L2), one
+// instruction for the whole box; coordinates (col, row, n).  Rows/columns outside the
+// tensor are dropped.  The issuing thread commits the group and, before the tile is
+// overwritten, waits until the copy engine has read it.
+__device__ __forceinline__ void tma_reduce_add_tile(const CUtensorMap* map, uint32_t src, int col, int row,
+                                                    int n) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(col), "r"(row), "r"(n)
+      : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // ---- TMEM -----------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem),
