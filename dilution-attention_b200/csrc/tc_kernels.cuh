@@ -789,7 +789,7 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
         else chunk(std::false_type{}, keep_tag, vs, vd, qbase + 32 * c, c);
       }
     };
-    if (wg == 0) run(std::false_type{}); else run(std::true_type{});
+    run(std::true_type{});                           // one instruction stream for both warpgroups
     const float gsum = suffix - suffix_in;           // this half's sum of dk_share
     if (wg == 0) sG[row] = gsum;
     __syncthreads();                                 // warpgroup 0's half sums are visible
@@ -797,6 +797,9 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     if (wg == 1) {
       g0 = sG[row];
       sG[128 + row] = gsum;
+    }
+    {
+      const float fix = wg == 1 ? g0 : 0.f;          // warpgroup 0 started from the exact suffix
 #pragma unroll
       for (int c = 1; c >= 0; --c)
 #pragma unroll
@@ -806,10 +809,10 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
           for (int u = 0; u < 4; ++u) {
             const uint32_t pr = pk2[c * 16 + e8 * 4 + u];
             const float plo = __uint_as_float(pr << 16), phi = __uint_as_float(pr & 0xffff0000u);
-            o[u] = pack_bf16(fmaf(plo, g0, pdk[c * 32 + e8 * 8 + 2 * u]),
-                             fmaf(phi, g0, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
+            o[u] = pack_bf16(fmaf(plo, fix, pdk[c * 32 + e8 * 8 + 2 * u]),
+                             fmaf(phi, fix, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, 32 * c + e8 * 8)),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qbase + 32 * c + e8 * 8)),
                        "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                        : "memory");
         }
