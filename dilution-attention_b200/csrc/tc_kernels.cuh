@@ -986,6 +986,10 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
+    // this warpgroup's half of the W buffer doubled as its dQ staging area: the previous
+    // step's reduction must have read it before it is written again
+    if (row == 0) tma_wait_read_all();
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
     const int i0 = ib * kTileRows + 64 * wg;
     const bool masked_tile = dead || t == 0;
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
@@ -1074,14 +1078,11 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       fence_async_smem();
       tc_fence_before();
       asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
-      if (row == 0) {
-        tma_reduce_add_tile(&map_dq, sW + kTileBytes * wg, 32 * wg, ib * kTileRows, n);
-        tma_wait_read_all();
-      }
-      __syncthreads();                                   // the W buffer may be written again
+      if (row == 0) tma_reduce_add_tile(&map_dq, sW + kTileBytes * wg, 32 * wg, ib * kTileRows, n);
     }
     tc_fence_before();
   }
+  if (row == 0) tma_wait_read_all();
   mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
   {
