@@ -28,7 +28,7 @@ constexpr int kHeadDim = 64;
 constexpr uint32_t kTileBytes = kTileRows * kHeadDim * 2;   // 16 KB
 constexpr long long kWaitCycles = 4000000000LL;             // ~2 s: a live wait is microseconds
 
-enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103, kErrSelfTest = 199 };
+enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103, kErrAlign = 104, kErrSelfTest = 199 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

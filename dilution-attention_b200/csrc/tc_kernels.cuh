@@ -376,20 +376,26 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
 //   rs  [query x 16] += share * ones   (row sums of the SAME bf16 shares)
 // so the final divide out = O / (rs + eps) normalises exactly what was summed.
 // TMEM: S^T 128 columns, O 64, rs 16 (256 allocated; two CTAs per SM).
-constexpr int kMainSmem = 4 * kTileBytes + 2 * kTileBytes + 2048 + 512 + 1024 + 256;
+constexpr int kMainSmem = 7 * kTileBytes + 512 + 128;   // exact: the base must already be 1024-aligned
 
 __global__ void __launch_bounds__(256, 2) forward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, Geom g, const float* __restrict__ rmax,
     const float* __restrict__ rden, const float* __restrict__ carry,
     const float* __restrict__ carry_base, float* __restrict__ out, float* __restrict__ ssum) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {                      // no slack is requested: refuse instead of overrunning
+    if (threadIdx.x == 0) atomicCAS(&g_status, 0, kErrAlign);
+    return;
+  }
   const uint32_t sQ = smem_u32(smem), sK0 = sQ + kTileBytes, sV = sQ + 3 * kTileBytes;
-  const uint32_t sSh = sQ + 4 * kTileBytes, sOnes = sQ + 6 * kTileBytes;
-  uint8_t* ones_ptr = smem + 6 * kTileBytes;
-  float* sL = reinterpret_cast<float*>(smem + 6 * kTileBytes + 2048);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes + 2048 + 512);
+  // a [128 keys][64] bf16 tile of ones right behind V: the second 64-column group of the B
+  // operand of share @ [V | ones] (N = 80), so the row sums come out of the same MMA
+  const uint32_t sOnes = sQ + 4 * kTileBytes, sSh = sQ + 5 * kTileBytes;
+  uint8_t* ones_ptr = smem + 4 * kTileBytes;
+  float* sL = reinterpret_cast<float*>(smem + 7 * kTileBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * kTileBytes + 512);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t kfull = smem_u32(bars), vfull = smem_u32(bars + 2), sdone = smem_u32(bars + 3);
 
@@ -409,13 +415,17 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
   if (wg == 0) sL[row] = load_lse(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
-  else reinterpret_cast<uint4*>(ones_ptr)[row] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tO = tmem + 128, tR = tmem + 192;
+  const uint32_t tS = tmem, tO = tmem + 128, tR = tmem + 192;   // O (64) and row sums (16): one N = 80 tile
 
   if (tid == 0) {
     mbar_expect_tx(kfull, 2 * kTileBytes);
@@ -519,13 +529,11 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
       tc_fence_after();
       mbar_wait(vfull, jb & 1, ctl, &g_status, kErrWaitTma);
       tc_fence_after();
-      const uint32_t id_o = instr_desc(128, 64, 1, 1), id_r = instr_desc(128, 16, 1, 0);
+      const uint32_t id_o = instr_desc(128, 80, 1, 1);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint64_t a = smem_desc(sSh + 2048 * kk, kTileBytes, 1024);
-        mma_ss(tO, a, smem_desc(sV + 2048 * kk, kTileBytes, 1024), id_o, (jb > 0 || kk > 0));
-        mma_ss(tR, a, smem_desc(sOnes + 32 * (kk & 3), 16, 1024), id_r, (jb > 0 || kk > 0));
-      }
+      for (int kk = 0; kk < 8; ++kk)
+        mma_ss(tO, smem_desc(sSh + 2048 * kk, kTileBytes, 1024), smem_desc(sV + 2048 * kk, sOnes - sV, 1024), id_o,
+               (jb > 0 || kk > 0));
       if (jb + 1 < njb) {
         mbar_wait(kfull + 8 * (b ^ 1), ((jb + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
         tc_fence_after();
@@ -1182,8 +1190,8 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
-  constexpr int smem = kMainSmem > kTwoPerSm ? kMainSmem : kTwoPerSm;
-  static_assert(2 * (smem + 1024) <= 233472, "two CTAs of the main pass must fit one SM");
+  constexpr int smem = kMainSmem;
+  static_assert(2 * (smem + 1024) <= 233472 && 3 * (smem + 1024) > 233472, "exactly two CTAs of the main pass fit one SM");
   if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
