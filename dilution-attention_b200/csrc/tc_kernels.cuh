@@ -599,7 +599,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 
 // Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
 // key blocks with the most query blocks first; 256 threads, one CTA per SM (464 TMEM
-// columns: S^T 128 | dOV^T 128 | dV 64 | dK 64 | dQ 64 | ghat 16).
+// columns: S^T 128 | dOV^T 128 | dV 64 | dK 64 | dQ 64 + ghat 16 as one 80-column tile).
 // The CTA keeps the K and V tiles of 128 keys and walks the 128-row query blocks from
 // last to first.  S^T = K Q^T and (dO' V^T)^T = V dO'^T are [128 keys x 128 queries],
 // lane = key.  Two threads share a key: warpgroup 0 walks queries 127..64 of the tile,
@@ -610,13 +610,16 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 //            halves are independent;
 //   suffix : running sum of dk_share over later queries (kernels.py:763-764).  Warpgroup
 //            1 does not yet know the sum G0 of warpgroup 0's half; dp is linear in the
-//            suffix, so it keeps pdp (fp32) and p (bf16) in registers, and after one
-//            block-wide barrier adds p * G0 before it stores its half of the pdp tile.
+//            suffix, so pdp (fp32) and p (bf16) stay in registers, and after one
+//            block-wide barrier p * G0 is added before the pdp tile is stored.  Both
+//            warpgroups run this same instruction stream (warpgroup 0 adds zero): two
+//            unrolled variants did not fit the instruction cache with 8 warps.
 // Per step the CTA writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
 // K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q); pdp read
-// as MN-major is the A operand with M = queries (dQ = pdp K, ghat = pdp 1).  dQ has its
-// own columns, so the next step's score MMAs are issued right behind this step's and
-// the dQ read-out runs under them.
+// as MN-major is the A operand with M = queries: one MMA with N = 80 against
+// B = [K | ones] yields dQ = pdp K in 64 columns and ghat = pdp 1 in the next 16.  dQ has
+// its own columns, so the next step's score MMAs are issued right behind this step's
+// and the dQ read-out runs under them.
 constexpr int kBwdSmem = 11 * kTileBytes + 2048 + 1024 + 1024 + 256;
 
 __global__ void __launch_bounds__(256, 1) backward_main_kernel(
