@@ -738,6 +738,7 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     auto chunk = [&](auto mask_tag, auto keep_tag, const float* vs, const float* vd, int qc, int slot) {
       constexpr bool MASK = decltype(mask_tag)::value;
       constexpr bool KEEP = decltype(keep_tag)::value;
+      uint32_t shp[16];                              // this chunk's 32 shares as bf16 pairs
 #pragma unroll
       for (int e8 = 3; e8 >= 0; --e8) {
         float sh[8], pd[8], pp[8];
@@ -771,10 +772,8 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
           }
         }
         const uint32_t off8 = share_chunk_offset(row, qc + e8 * 8);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sSh + off8),
-                     "r"(pack_bf16(sh[0], sh[1])), "r"(pack_bf16(sh[2], sh[3])),
-                     "r"(pack_bf16(sh[4], sh[5])), "r"(pack_bf16(sh[6], sh[7]))
-                     : "memory");
+#pragma unroll
+        for (int u = 0; u < 4; ++u) shp[e8 * 4 + u] = pack_bf16(sh[2 * u], sh[2 * u + 1]);
         if (KEEP) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) pdk[slot * 32 + e8 * 8 + u] = pd[u];
@@ -787,6 +786,10 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
                        : "memory");
         }
       }
+      // the shares stay in TMEM, over score columns this warpgroup has already consumed (the
+      // upper half of its own 64-column range): lane = key is the M index of
+      // dV += share^T dO', two queries per 32-bit column
+      tmem_st16(tS + lane_base + qbase + 32 + 16 * slot, shp);
     };
     auto run = [&](auto keep_tag) {
 #pragma unroll
@@ -830,6 +833,7 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     }
     if (wg == 0 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
     incl = incl_next;
+    tmem_st_wait();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -849,8 +853,9 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
 #pragma unroll
       for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
         const uint32_t aoff = (kq >> 2) * kTileBytes + (kq & 3) * 32;
-        mma_ss(tDV, smem_desc(sSh + aoff, 16, 1024), smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd,
-               (t > 0 || kq > 0));
+        // queries [16kq, 16kq+16): 8 columns in the upper half of the owning warpgroup's score range
+        const uint32_t a_sh = tS + 64 * (kq >> 2) + 32 + 16 * ((kq & 3) >> 1) + 8 * (kq & 1);
+        mma_ts(tDV, a_sh, smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
         mma_ss(tDK, smem_desc(sPd + aoff, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
                (t > 0 || kq > 0));
       }
