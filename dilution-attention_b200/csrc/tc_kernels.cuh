@@ -815,21 +815,25 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     {
       const float fix = wg == 1 ? g0 : 0.f;          // warpgroup 0 started from the exact suffix
 #pragma unroll
-      for (int c = 1; c >= 0; --c)
+      for (int c = 1; c >= 0; --c) {
+        uint32_t pdt[16];                              // this chunk's 32 pdp values as bf16 pairs
 #pragma unroll
         for (int e8 = 3; e8 >= 0; --e8) {
-          uint32_t o[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const uint32_t pr = pk2[c * 16 + e8 * 4 + u];
             const float plo = __uint_as_float(pr << 16), phi = __uint_as_float(pr & 0xffff0000u);
-            o[u] = pack_bf16(fmaf(plo, fix, pdk[c * 32 + e8 * 8 + 2 * u]),
-                             fmaf(phi, fix, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
+            pdt[e8 * 4 + u] = pack_bf16(fmaf(plo, fix, pdk[c * 32 + e8 * 8 + 2 * u]),
+                                        fmaf(phi, fix, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
           }
+          // shared memory: the MN-major A operand of dQ | ghat (M = queries)
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qbase + 32 * c + e8 * 8)),
-                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                       "r"(pdt[e8 * 4]), "r"(pdt[e8 * 4 + 1]), "r"(pdt[e8 * 4 + 2]), "r"(pdt[e8 * 4 + 3])
                        : "memory");
         }
+        // TMEM, over consumed dOV^T columns: the A operand of dK (M = keys)
+        tmem_st16(tDOV + lane_base + qbase + 32 + 16 * c, pdt);
+      }
     }
     if (wg == 0 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
     incl = incl_next;
@@ -852,12 +856,10 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
       mma_commit(dqdone);
 #pragma unroll
       for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
-        const uint32_t aoff = (kq >> 2) * kTileBytes + (kq & 3) * 32;
         // queries [16kq, 16kq+16): 8 columns in the upper half of the owning warpgroup's score range
         const uint32_t a_sh = tS + 64 * (kq >> 2) + 32 + 16 * ((kq & 3) >> 1) + 8 * (kq & 1);
         mma_ts(tDV, a_sh, smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
-        mma_ss(tDK, smem_desc(sPd + aoff, 16, 1024), smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd,
-               (t > 0 || kq > 0));
+        mma_ts(tDK, a_sh - tS + tDOV, smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
       }
       if (t + 1 < nsteps) {
         mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
