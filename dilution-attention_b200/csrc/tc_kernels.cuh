@@ -923,6 +923,12 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
   if (warp == 0) tmem_free(tmem, 512);
 }
 
+// Barrier of the 128 threads of one warpgroup (named barriers 1 and 2).
+__device__ __forceinline__ void wg_barrier(int wg) {
+  if (wg == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
 // Softmax-Jacobian corrections (the reference's BC + dq epilogue, kernels.py:777-826):
 //   dk = dk_main - scale * P^T (ghat * Q)        (accumulated here per key block)
 //   dq = dq_main - scale * ghat * (P K)          (added to dq_main with vector reductions;
@@ -1007,7 +1013,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     // this warpgroup's half of the W buffer doubled as its dQ staging area: the previous
     // step's reduction must have read it before it is written again
     if (row == 0) tma_wait_read_all();
-    asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+    wg_barrier(wg);
     const int i0 = ib * kTileRows + 64 * wg;
     const bool masked_tile = dead || t == 0;
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
@@ -1016,6 +1022,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
       float vs[32];
+      uint32_t wt[16];                                 // this chunk's 32 W values as bf16 pairs
       tmem_ld32(tS + lane_base + 64 * wg + 32 * c, vs);
       tmem_ld_wait(vs);
       float4 snext[4];
@@ -1043,15 +1050,20 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
             w8[u] = p * gh[w];
           }
         }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) wt[e8 * 4 + u] = pack_bf16(w8[2 * u], w8[2 * u + 1]);
+        // shared memory: the MN-major A operand of dQc (M = queries)
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sW + share_chunk_offset(row, wg * 64 + c * 32 + e8 * 8)),
-                     "r"(pack_bf16(w8[0], w8[1])), "r"(pack_bf16(w8[2], w8[3])),
-                     "r"(pack_bf16(w8[4], w8[5])), "r"(pack_bf16(w8[6], w8[7]))
+                     "r"(wt[e8 * 4]), "r"(wt[e8 * 4 + 1]), "r"(wt[e8 * 4 + 2]), "r"(wt[e8 * 4 + 3])
                      : "memory");
       }
+      // TMEM, over the score columns just consumed: the A operand of dKc (M = keys)
+      tmem_st16(tS + lane_base + 64 * wg + 32 * c, wt);
     }
     };
     if (masked_tile) tile(std::true_type{}); else tile(std::false_type{});
     if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
+    tmem_st_wait();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -1061,7 +1073,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       const uint32_t sQ = sQ0 + kTileBytes * b;
 #pragma unroll
       for (int kq = 0; kq < 8; ++kq)
-        mma_ss(tDK, smem_desc(sW + (kq >> 2) * kTileBytes + (kq & 3) * 32, 16, 1024),
+        mma_ts(tDK, tS + 64 * (kq >> 2) + 32 * ((kq & 3) >> 1) + 8 * (kq & 1),
                smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
@@ -1095,7 +1107,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
                      : "memory");
       fence_async_smem();
       tc_fence_before();
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+      wg_barrier(wg);
       if (row == 0) tma_reduce_add_tile(&map_dq, sW + kTileBytes * wg, 32 * wg, ib * kTileRows, n);
     }
     tc_fence_before();
