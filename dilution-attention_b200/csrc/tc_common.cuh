@@ -28,7 +28,7 @@ constexpr int kHeadDim = 64;
 constexpr uint32_t kTileBytes = kTileRows * kHeadDim * 2;   // 16 KB
 constexpr long long kWaitCycles = 4000000000LL;             // ~2 s: a live wait is microseconds
 
-enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103, kErrAlign = 104, kErrSelfTest = 199 };
+enum : int { kErrWaitTma = 101, kErrWaitMma = 102, kErrWaitDrain = 103, kErrAlign = 104, kErrWaitTile = 105, kErrSelfTest = 199 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -232,6 +232,44 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
+}
+
+// The same instructions with each descriptor as two 32-bit halves.  The start address sits
+// in the low half, so stepping through a tile is one 32-bit add of a constant to a value
+// built once outside the loop: the issuing thread's own arithmetic, not the tensor pipe,
+// limits the issue rate of small MMAs (about 45 cycles per instruction back to back,
+// about 100 when each descriptor is rebuilt from an address).
+struct Desc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ Desc make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = smem_desc(saddr, lbo_bytes, sbo_bytes);
+  return Desc{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+// byte offsets are added in descriptor units of 16 bytes
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, Desc a, uint32_t a_off16, Desc b, uint32_t b_off16,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc),
+        "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, Desc b, uint32_t b_off16,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // S[128 x 128] = A[128 x 64] * B[128 x 64]^T, both K-major tiles: 4 instructions.

@@ -598,60 +598,74 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 
 // Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
-// key blocks with the most query blocks first; 256 threads, one CTA per SM (464 TMEM
-// columns: S^T 128 | dOV^T 128 | dV 64 | dK 64 | dQ 64 + ghat 16 as one 80-column tile).
-// The CTA keeps the K and V tiles of 128 keys and walks the 128-row query blocks from
-// last to first.  S^T = K Q^T and (dO' V^T)^T = V dO'^T are [128 keys x 128 queries],
-// lane = key.  Two threads share a key: warpgroup 0 walks queries 127..64 of the tile,
-// warpgroup 1 queries 63..0, both backwards, each with two registers:
-//   incl   : demand of the key including the current query.  It starts from the stored
-//            checkpoint of the next 64-row block and is walked backwards by subtracting
-//            p, so committed + p + eps = incl + eps needs no forward sweep and the two
-//            halves are independent;
-//   suffix : running sum of dk_share over later queries (kernels.py:763-764).  Warpgroup
-//            1 does not yet know the sum G0 of warpgroup 0's half; dp is linear in the
-//            suffix, so pdp (fp32) and p (bf16) stay in registers, and after one
-//            block-wide barrier p * G0 is added before the pdp tile is stored.  Both
-//            warpgroups run this same instruction stream (warpgroup 0 adds zero): two
-//            unrolled variants did not fit the instruction cache with 8 warps.
-// Per step the CTA writes two bf16 tiles [key][query]: share and pdp = p * dp.  Read as
-// K-major they are A operands with M = keys (dV += share^T dO', dK += pdp^T Q); pdp read
-// as MN-major is the A operand with M = queries: one MMA with N = 80 against
-// B = [K | ones] yields dQ = pdp K in 64 columns and ghat = pdp 1 in the next 16.  dQ has
-// its own columns, so the next step's score MMAs are issued right behind this step's
-// and the dQ read-out runs under them.
-constexpr int kBwdSmem = 11 * kTileBytes + 2048 + 1024 + 1024 + 256;
+// key blocks with the most query blocks first; one CTA per SM: eight compute warps and
+// one warp that issues every TMA copy and every MMA.
+// TMEM (496 of 512 columns): two stages of S^T (64 columns each) | two stages of dOV^T
+// (64 each) | dV 64 | dK 64 | dQ 64 + ghat 16 as one 80-column tile | the V tile as a
+// bf16 A operand (32).
+// The CTA keeps K (shared memory) and V (TMEM) of 128 keys and walks the queries from
+// last to first in half-steps of 64: S^T = K Q^T and (dO' V^T)^T = V dO'^T are
+// [128 keys x 64 queries], lane = key.  Two threads share a key and split the 64 queries
+// of a half-step at the only places where the key's demand is stored, the 64-row
+// checkpoints:
+//   warpgroup 0 walks queries 63..32 backwards from the checkpoint behind the half-step,
+//     subtracting p, with the exact suffix sum of dk_share (kernels.py:763-764);
+//   warpgroup 1 walks queries 0..31 forwards from the checkpoint in front of it, adding p,
+//     with the prefix sum of dk_share of its own queries.  dp is linear in the suffix, so
+//     it keeps p and pdp = p * dp in registers, and after one barrier of the compute
+//     warps adds p * (suffix behind the half-step - both warpgroups' sums).
+// Per half-step each thread writes 32 shares and 32 pdp values as bf16 pairs over TMEM
+// columns it has already read: lane = key is the M index, so they are the A operands of
+// dV += share^T dO' and dK += pdp^T Q without passing through shared memory.  pdp also goes
+// to shared memory as the MN-major A operand (M = queries) of one N = 80 MMA per 128
+// queries against B = [K | ones], which yields dQ = pdp K in 64 columns and ghat = pdp 1
+// in the next 16.
+// The issuing warp runs two half-steps ahead of the arithmetic: when the tiles of
+// half-step h are complete it issues dV, dK (and dQ | ghat after the second half) of h and
+// the score MMAs of h + 2 into the stage h has just left, so the tensor pipe works under
+// the arithmetic of h + 1.  Q and dO' tiles are triple-buffered.
+constexpr int kBwdThreads = 288;
+constexpr int kBwdSmem = 12 * kTileBytes + 2048 + 2048 + 256 + 1024;
 
-__global__ void __launch_bounds__(256, 1) backward_main_kernel(
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  *v = __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, Geom g,
+    const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq, Geom g,
+    const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
     const float* __restrict__ carry, const float* __restrict__ total, float* __restrict__ dq_main,
     float* __restrict__ dk_main, __nv_bfloat16* __restrict__ dv, float* __restrict__ ghat) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  const uint32_t sK = smem_u32(smem), sV = sK + kTileBytes;
-  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 4 * kTileBytes;     // [2] each
-  const uint32_t sSh = sK + 6 * kTileBytes, sPd = sK + 8 * kTileBytes;      // 32 KB each
+  const uint32_t sK = smem_u32(smem);
   // a [128 keys][64] bf16 tile of ones: the second 64-column group of the dQ MMA's B operand
   // (N = 80 = 64 columns of K + 16 of ones), so ghat comes out of the same instruction
-  const uint32_t sOnes = sK + 10 * kTileBytes;
-  uint8_t* ones_ptr = smem + 10 * kTileBytes;
-  float2* sStat = reinterpret_cast<float2*>(smem + 11 * kTileBytes);          // [2][128] (lse, dbar')
-  float* sG = reinterpret_cast<float*>(smem + 11 * kTileBytes + 2048);        // [2][128] half sums of dk_share
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 11 * kTileBytes + 3072);
-  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kvfull = smem_u32(bars), qfull = smem_u32(bars + 1);         // qfull[2]
-  const uint32_t sdone = smem_u32(bars + 3), dqdone = smem_u32(bars + 4);
+  const uint32_t sOnes = sK + kTileBytes;
+  uint8_t* ones_ptr = smem + kTileBytes;
+  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 5 * kTileBytes;        // [3] each
+  const uint32_t sPd = sK + 8 * kTileBytes;                                    // 32 KB
+  const uint32_t sDq = sK + 10 * kTileBytes;                                   // 32 KB: fp32 dQ staging
+  float2* sStat = reinterpret_cast<float2*>(smem + 12 * kTileBytes);           // [2][128] (lse, dbar')
+  float* sG = reinterpret_cast<float*>(smem + 12 * kTileBytes + 2048);         // [2][2][128] sums of dk_share
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 12 * kTileBytes + 4096);
+  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 12);
+  const uint32_t kfull = smem_u32(bars), qfull = smem_u32(bars + 1);           // qfull[3]
+  const uint32_t sdone = smem_u32(bars + 4), tiles = smem_u32(bars + 6);       // [2] each
+  const uint32_t dqdone = smem_u32(bars + 8);
 
-  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
-  const int half = 1 - wg;                          // warpgroup 0 owns the later 64 queries
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int n = (int)(blockIdx.x % g.n);
   const int jb = (int)(blockIdx.x / g.n);
   const int k0 = jb * kTileRows;
   const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
+  const int nhalf = 2 * nsteps;
   const int64_t row_base = (int64_t)n * g.tq;
   const int ja = k0 + row;
   const bool dead = ja >= g.tk;
@@ -662,22 +676,19 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
     if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
     return st;
   };
-  // demand of this thread's key through the last query of its half of block ib
-  auto load_incl = [&](int ib) {
-    const int rb = 2 * ib + half + 1;
-    if (dead) return 0.f;
-    return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
-  };
 
   if (tid == 0) {
     ctl->abort = 0;
-    for (int i = 0; i < 5; ++i) mbar_init(kvfull + 8 * i, 1);
+    for (int i = 0; i < 6; ++i) mbar_init(kfull + 8 * i, 1);      // kfull, qfull[3], sdone[2]
+    mbar_init(tiles, 8);
+    mbar_init(tiles + 8, 8);
+    mbar_init(dqdone, 1);
     fence_barrier_init();
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
   if (wg == 0) sStat[row] = load_stats(nqb - 1);
-  else {
+  else if (wg == 1) {
 #pragma unroll
     for (int c = 0; c < 8; ++c)
       reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
@@ -687,216 +698,305 @@ __global__ void __launch_bounds__(256, 1) backward_main_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tDOV = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
-                 tG = tmem + 448;
-
-  if (tid == 0) {
-    mbar_expect_tx(kvfull, 2 * kTileBytes);
-    tma_load_tile(sK, &map_k, k0, n, kvfull);
-    tma_load_tile(sV, &map_v, k0, n, kvfull);
-    mbar_expect_tx(qfull, 2 * kTileBytes);
-    tma_load_tile(sQ0, &map_q, (nqb - 1) * kTileRows, n, qfull);
-    tma_load_tile(sD0, &map_do, (nqb - 1) * kTileRows, n, qfull);
-    mbar_wait(kvfull, 0, ctl, &g_status, kErrWaitTma);
-    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    mma_scores(tS, sK, sQ0, 128);
-    mma_scores(tDOV, sV, sD0, 128);
-    mma_commit(sdone);
-  }
-  __syncwarp();
-
-  float suffix_in = 0.f;                            // suffix entering the tile (same in both warpgroups)
-  float incl = load_incl(nqb - 1);
+  const uint32_t tS0 = tmem, tDOV0 = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
+                 tG = tmem + 448, tV = tmem + 464;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const int qbase = 64 * half;                      // first query column of this warpgroup
-  for (int t = 0; t < nsteps; ++t) {
-    const int ib = nqb - 1 - t, b = t & 1;
-    // fetch what the next tile needs before waiting for this one
-    float2 stat_next = make_float2(INFINITY, 0.f);
-    float incl_next = 0.f;
-    if (t + 1 < nsteps) {
-      if (wg == 0) stat_next = load_stats(ib - 1);
-      incl_next = load_incl(ib - 1);
+
+  if (wg == 0) {
+    // this key's V row as an A operand: two head-dim elements per 32-bit column
+    uint32_t w[32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (!dead) x = reinterpret_cast<const uint4*>(v + ((int64_t)n * g.tk + ja) * kHeadDim)[c];
+      w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
     }
-    mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    if (tid == 0 && t + 1 < nsteps) {               // buffers of step t-1 are free
-      mbar_expect_tx(qfull + 8 * (b ^ 1), 2 * kTileBytes);
-      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
-      tma_load_tile(sD0 + kTileBytes * (b ^ 1), &map_do, (ib - 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+    tmem_st16(tV + lane_base, w);
+    tmem_st16(tV + lane_base + 16, w + 16);
+  }
+  if (wg < 2) {
+    // dV and dK start from zero, so that every MMA into them accumulates
+    uint32_t z[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) z[c] = 0u;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      tmem_st16(tDV + lane_base + 32 * wg + 16 * c, z);
+      tmem_st16(tDK + lane_base + 32 * wg + 16 * c, z);
+    }
+    tmem_st_wait();
+  }
+  if (tid == 256) {
+    mbar_expect_tx(kfull, kTileBytes);
+    tma_load_tile(sK, &map_k, k0, n, kfull);
+    for (int s = 0; s < 3 && s < nsteps; ++s) {
+      mbar_expect_tx(qfull + 8 * s, 2 * kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes * s, &map_q, (nqb - 1 - s) * kTileRows, n, qfull + 8 * s);
+      tma_load_tile(sD0 + kTileBytes * s, &map_do, (nqb - 1 - s) * kTileRows, n, qfull + 8 * s);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ the issuing warp
+    if (lane == 0) {
+      constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);     // scores: both operands K-major
+      constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);    // dV, dK: A from TMEM (M = keys), B MN-major
+      constexpr uint32_t id_qd = instr_desc(128, 80, 1, 1);    // dQ | ghat: A MN-major (M = queries)
+      // every descriptor is built once; inside the loop tile, stage and k-step are constant
+      // offsets (in 16-byte units: a tile is 1024, an MN-major k-step 128, a K-major one 2)
+      const Desc dKk = make_desc(sK, 16, 1024);                 // K, K-major: A of the scores
+      const Desc dKm = make_desc(sK, sOnes - sK, 1024);         // [K | ones], MN-major: B of dQ | ghat
+      const Desc dPm = make_desc(sPd, kTileBytes, 1024);        // pdp, MN-major: A of dQ | ghat
+      const Desc dQk = make_desc(sQ0, 16, 1024), dQm = make_desc(sQ0, kTileBytes, 1024);
+      const Desc dDk = make_desc(sD0, 16, 1024), dDm = make_desc(sD0, kTileBytes, 1024);
+      // scores of a half-step in stage ST of Q and dO'; even half-steps take queries 64..127
+      auto issue_scores = [&](auto odd_c, auto st_c) {
+        constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
+        constexpr uint32_t off = ST * 1024 + (ODD ? 0 : 512);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ss(tS0 + 64 * ODD, dKk, 2 * kk, dQk, off + 2 * kk, id_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ts(tDOV0 + 64 * ODD, tV + 8 * kk, dDk, off + 2 * kk, id_s, kk > 0);
+      };
+      mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
+      mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
+      tc_fence_after();
+      issue_scores(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
+      mma_commit(sdone);
+      issue_scores(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
+      mma_commit(sdone + 8);
+      // half-step h = 2s + ODD of step s, whose Q and dO' tiles sit in stage ST = s % 3
+      auto half = [&](auto odd_c, auto st_c, int s) {
+        constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
+        constexpr int ST1 = (ST + 1) % 3, ST2 = (ST + 2) % 3;
+        mbar_wait(tiles + 8 * ODD, s & 1, ctl, &g_status, kErrWaitTile);
+        tc_fence_after();
+#pragma unroll
+        for (int kq = 0; kq < 4; ++kq) {                    // contraction over the 64 queries
+          // queries [16kq, 16kq+16) of the half-step: 8 columns at the start of the owning
+          // warpgroup's 32-column range (warpgroup 1 owns queries 0..31)
+          constexpr uint32_t base = ST * 1024 + (ODD ? 0 : 4) * 128;
+          const uint32_t col = 64 * ODD + 32 * (kq >> 1) + 8 * (kq & 1);
+          mma_ts(tDV, tS0 + col, dDm, base + 128 * kq, id_kd, 1);
+          mma_ts(tDK, tDOV0 + col, dQm, base + 128 * kq, id_kd, 1);
+        }
+        if (ODD) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)                    // contraction over the 128 keys
+            mma_ss(tDQ, dPm, 128 * kk, dKm, 128 * kk, id_qd, kk > 0);
+          mma_commit(dqdone);
+        }
+        if (s + 1 < nsteps) {                               // half-step h + 2 belongs to step s + 1
+          if (!ODD) {
+            mbar_wait(qfull + 8 * ST1, ((s + 1) / 3) & 1, ctl, &g_status, kErrWaitTma);
+            tc_fence_after();
+          }
+          issue_scores(odd_c, std::integral_constant<int, ST1>{});
+        }
+        mma_commit(sdone + 8 * ODD);
+        if (!ODD && s >= 1 && s + 2 < nsteps) {
+          // every MMA of step s-1 has completed once the commit of its second half-step has:
+          // its Q and dO' stage takes step s+2
+          mbar_wait(sdone + 8, s & 1, ctl, &g_status, kErrWaitMma);
+          mbar_expect_tx(qfull + 8 * ST2, 2 * kTileBytes);
+          tma_load_tile(sQ0 + kTileBytes * ST2, &map_q, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
+          tma_load_tile(sD0 + kTileBytes * ST2, &map_do, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
+        }
+      };
+      using C0 = std::integral_constant<int, 0>;
+      using C1 = std::integral_constant<int, 1>;
+      using C2 = std::integral_constant<int, 2>;
+      for (int s = 0; s < nsteps; s += 3) {
+        half(C0{}, C0{}, s);
+        half(C1{}, C0{}, s);
+        if (s + 1 < nsteps) {
+          half(C0{}, C1{}, s + 1);
+          half(C1{}, C1{}, s + 1);
+        }
+        if (s + 2 < nsteps) {
+          half(C0{}, C2{}, s + 2);
+          half(C1{}, C2{}, s + 2);
+        }
+      }
     }
     __syncwarp();
-    const int i0 = ib * kTileRows;                   // first query of the tile (q_off == 0 here)
-    const bool masked_tile = dead || (i0 < k0 + kTileRows - 1);
-    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
-    float suffix = suffix_in;
-    float pdk[64];                                   // warpgroup 1: pdp without warpgroup 0's half sum
-    uint32_t pk2[32];                                // warpgroup 1: p as bf16 pairs
+  } else {
+    // ------------------------------------------------------------ the compute warps
+    const int cw = 32 * (1 - wg);                    // this warpgroup's columns of a stage
+    // demand of this thread's key where its walk starts: warpgroup 0 behind the half-step
+    // (inclusive of its last query), warpgroup 1 in front of it (exclusive of its first)
+    auto load_edge = [&](int h) {
+      if (dead) return 0.f;
+      const int rb = 2 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 1) + (wg == 0 ? 1 : 0);
+      return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
+    };
+    // dQ and ghat of the step's 128 queries: lane = query, each warpgroup takes 32 of the 64
+    // columns.  The fp32 tile is staged in shared memory in the copy engine's swizzled layout
+    // and added to dq_main by ONE tensor reduction per warpgroup (the caller has made sure
+    // that the previous reduction has read the staging buffer).
+    auto read_dq = [&](int sp) {
+      if (lane == 0) mbar_wait(dqdone, sp & 1, ctl, &g_status, kErrWaitMma);
+      __syncwarp();
+      tc_fence_after();
+      float dq[32], gh = 0.f;
+      tmem_ld32(tDQ + lane_base + 32 * wg, dq);
+      if (wg == 0) tmem_ld1(tG + lane_base, &gh);
+      tmem_ld_wait(dq);
+      const uint32_t stage = sDq + kTileBytes * wg + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + ((c ^ (row & 7)) << 4)),
+                     "f"(dq[4 * c] * g.scale), "f"(dq[4 * c + 1] * g.scale), "f"(dq[4 * c + 2] * g.scale),
+                     "f"(dq[4 * c + 3] * g.scale)
+                     : "memory");
+      fence_async_smem();
+      if (wg == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+      else asm volatile("bar.sync 3, 128;" ::: "memory");
+      const int ibq = nqb - 1 - sp;
+      if (row == 0) tma_reduce_add_tile(&map_dq, sDq + kTileBytes * wg, 32 * wg, ibq * kTileRows, n);
+      const int i = ibq * kTileRows + row;
+      if (wg == 0 && i < g.tq) atomicAdd(ghat + row_base + i, gh);
+    };
 
-    // one chunk = 32 queries [qc, qc+32) of the tile, visited from the last to the first
-    auto chunk = [&](auto mask_tag, auto keep_tag, const float* vs, const float* vd, int qc, int slot) {
-      constexpr bool MASK = decltype(mask_tag)::value;
-      constexpr bool KEEP = decltype(keep_tag)::value;
-      uint32_t shp[16];                              // this chunk's 32 shares as bf16 pairs
+    float sigma = 0.f;                               // suffix of dk_share behind the half-step
+    float incl = load_edge(0);
+    for (int h = 0; h < nhalf; ++h) {
+      const int s = h >> 1, odd = h & 1, ib = nqb - 1 - s, b = s & 1;
+      // fetch what the next half-step needs before waiting for this one
+      float incl_next = 0.f;
+      float st_max = INFINITY, st_den = 1.f, st_dbar = 0.f;
+      if (h + 1 < nhalf) incl_next = load_edge(h + 1);
+      const bool fetch_stats = !odd && wg == 0 && s + 1 < nsteps;
+      if (fetch_stats) {
+        const int i = (ib - 1) * kTileRows + row;     // ib >= 1 here, so i < tq
+        st_max = rmax[row_base + i];
+        st_den = rden[row_base + i];
+        st_dbar = dbarp[row_base + i];
+      }
+      if (lane == 0) mbar_wait(sdone + 8 * odd, s & 1, ctl, &g_status, kErrWaitMma);
+      __syncwarp();
+      tc_fence_after();
+      float vs[32], vd[32];
+      const uint32_t tcol = lane_base + 64 * odd + cw;
+      tmem_ld32(tS0 + tcol, vs);
+      tmem_ld32(tDOV0 + tcol, vd);
+      tmem_ld_wait(vs);
+      tmem_ld_wait(vd);
+      const int qc = (odd ? 0 : 64) + cw;             // first query column of this thread in the step's tile
+      const int iq0 = ib * kTileRows + qc;            // its position (q_off == 0 here)
+      const bool masked_tile = dead || (ib * kTileRows + (odd ? 0 : 64) < k0 + kTileRows - 1);
+      const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+      uint32_t shp[16];                                // 32 shares as bf16 pairs
+      float R = wg == 0 ? sigma : 0.f;                 // warpgroup 0: suffix; warpgroup 1: its own prefix
+      float incle = incl + g.eps;                      // demand + eps at the walk's position
+
+      // afterwards vs holds p and vd holds p * dp (warpgroup 1: without the suffix behind it)
+      auto chunk = [&](auto fwd_tag, auto mask_tag) {
+        constexpr bool FWD = decltype(fwd_tag)::value;
+        constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
-      for (int e8 = 3; e8 >= 0; --e8) {
-        float sh[8], pd[8], pp[8];
+        for (int k8 = 0; k8 < 4; ++k8) {
+          const int e8 = FWD ? k8 : 3 - k8;
+          float4 stt[4];                               // (lse, dbar') of eight queries
 #pragma unroll
-        for (int u2 = 3; u2 >= 0; --u2) {
-          const float4 st = St4[(qc + e8 * 8) / 2 + u2];       // two queries: (lse, dbar') x2
-          const float lse[2] = {st.x, st.z}, dbr[2] = {st.y, st.w};
+          for (int u2 = 0; u2 < 4; ++u2) stt[u2] = St4[(qc + e8 * 8) / 2 + u2];
+          float sh[8];
 #pragma unroll
-          for (int w = 1; w >= 0; --w) {
-            const int u = u2 * 2 + w, e = e8 * 8 + u;
-            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[w]));
-            bool off = false;
+          for (int k = 0; k < 8; ++k) {
+            const int u = FWD ? k : 7 - k, e = e8 * 8 + u;
+            const float lse = (u & 1) ? stt[u >> 1].z : stt[u >> 1].x;
+            const float dbr = (u & 1) ? stt[u >> 1].w : stt[u >> 1].y;
+            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse));
             if (MASK) {
-              off = dead || ja > i0 + qc + e;
-              if (off) p = 0.f;
+              if (dead || ja > iq0 + e) p = 0.f;
             }
             // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
-            //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share
-            const float den = MASK ? fmaxf(incl + g.eps, g.eps) : incl + g.eps;
-            const float inv = fast_rcp(den);
-            const float wv = (vd[e] - dbr[w]) * inv;
-            const float share = p * inv;
-            const float gneg = wv * share;                     // -dk_share
-            pd[u] = p * ((wv - gneg) + suffix);                // p * dp
-            sh[u] = share;
-            pp[u] = p;
-            if (!MASK || !off) {
-              suffix -= gneg;
-              incl -= p;
+            //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
+            //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
+            float den;
+            if (FWD) {
+              incle += p;
+              den = incle;
+            } else {
+              den = MASK ? fmaxf(incle, g.eps) : incle;
             }
+            const float inv = fast_rcp(den);
+            if (!FWD) incle -= p;
+            const float wv = (vd[e] - dbr) * inv;
+            const float share = p * inv;
+            float dp;
+            if (FWD) {
+              dp = wv + R;                             // minus the prefix: R holds -(sum of dk_share so far)
+              R = fmaf(wv, share, R);
+            } else {
+              R = fmaf(-wv, share, R);
+              dp = wv + R;
+            }
+            vd[e] = p * dp;
+            vs[e] = p;
+            sh[u] = share;
           }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) shp[e8 * 4 + u] = pack_bf16(sh[2 * u], sh[2 * u + 1]);
         }
-        const uint32_t off8 = share_chunk_offset(row, qc + e8 * 8);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) shp[e8 * 4 + u] = pack_bf16(sh[2 * u], sh[2 * u + 1]);
-        if (KEEP) {
-#pragma unroll
-          for (int u = 0; u < 8; ++u) pdk[slot * 32 + e8 * 8 + u] = pd[u];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) pk2[slot * 16 + e8 * 4 + u] = pack_bf16(pp[2 * u], pp[2 * u + 1]);
-        } else {
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + off8),
-                       "r"(pack_bf16(pd[0], pd[1])), "r"(pack_bf16(pd[2], pd[3])),
-                       "r"(pack_bf16(pd[4], pd[5])), "r"(pack_bf16(pd[6], pd[7]))
-                       : "memory");
-        }
+      };
+      if (wg == 0) {
+        if (masked_tile) chunk(std::false_type{}, std::true_type{});
+        else chunk(std::false_type{}, std::false_type{});
+      } else {
+        if (masked_tile) chunk(std::true_type{}, std::true_type{});
+        else chunk(std::true_type{}, std::false_type{});
       }
-      // the shares stay in TMEM, over score columns this warpgroup has already consumed (the
-      // upper half of its own 64-column range): lane = key is the M index of
-      // dV += share^T dO', two queries per 32-bit column
-      tmem_st16(tS + lane_base + qbase + 32 + 16 * slot, shp);
-    };
-    auto run = [&](auto keep_tag) {
+      // sum of -dk_share over this thread's 32 queries
+      const float gsum = wg == 0 ? sigma - R : R;
+      sG[(odd * 2 + wg) * 128 + row] = gsum;
+      // the shares stay in TMEM, over score columns this thread has consumed
+      tmem_st16(tS0 + tcol, shp);
+      // the thread that issued the previous dQ reduction: the staging buffer has been read
+      if (!odd && row == 0) tma_wait_read_all();
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // the compute warps
+      const float gother = sG[(odd * 2 + (1 - wg)) * 128 + row];
+      // FWD walked with dp = w - prefix; the true value is w + sigma - G0 - (G1 - prefix)
+      const float fix = wg == 1 ? sigma - gother - gsum : 0.f;
+      sigma -= gsum + gother;
+      // the dQ tile of the previous 128 queries read the pdp buffer that is written next
+      if (!odd && s >= 1) read_dq(s - 1);
+      {
+        uint32_t pdt[16];                              // 32 pdp values as bf16 pairs
 #pragma unroll
-      for (int c = 1; c >= 0; --c) {
-        float vs[32], vd[32];
-        tmem_ld32(tS + lane_base + qbase + 32 * c, vs);
-        tmem_ld32(tDOV + lane_base + qbase + 32 * c, vd);
-        tmem_ld_wait(vs);
-        tmem_ld_wait(vd);
-        if (masked_tile) chunk(std::true_type{}, keep_tag, vs, vd, qbase + 32 * c, c);
-        else chunk(std::false_type{}, keep_tag, vs, vd, qbase + 32 * c, c);
-      }
-    };
-    run(std::true_type{});                           // one instruction stream for both warpgroups
-    const float gsum = suffix - suffix_in;           // this half's sum of dk_share
-    if (wg == 0) sG[row] = gsum;
-    __syncthreads();                                 // warpgroup 0's half sums are visible
-    float g0 = gsum, g1 = gsum;
-    if (wg == 1) {
-      g0 = sG[row];
-      sG[128 + row] = gsum;
-    }
-    {
-      const float fix = wg == 1 ? g0 : 0.f;          // warpgroup 0 started from the exact suffix
-#pragma unroll
-      for (int c = 1; c >= 0; --c) {
-        uint32_t pdt[16];                              // this chunk's 32 pdp values as bf16 pairs
-#pragma unroll
-        for (int e8 = 3; e8 >= 0; --e8) {
+        for (int e8 = 0; e8 < 4; ++e8) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const uint32_t pr = pk2[c * 16 + e8 * 4 + u];
-            const float plo = __uint_as_float(pr << 16), phi = __uint_as_float(pr & 0xffff0000u);
-            pdt[e8 * 4 + u] = pack_bf16(fmaf(plo, fix, pdk[c * 32 + e8 * 8 + 2 * u]),
-                                        fmaf(phi, fix, pdk[c * 32 + e8 * 8 + 2 * u + 1]));
+            const int e = e8 * 8 + 2 * u;
+            pdt[e8 * 4 + u] = pack_bf16(fmaf(vs[e], fix, vd[e]), fmaf(vs[e + 1], fix, vd[e + 1]));
           }
           // shared memory: the MN-major A operand of dQ | ghat (M = queries)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qbase + 32 * c + e8 * 8)),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qc + e8 * 8)),
                        "r"(pdt[e8 * 4]), "r"(pdt[e8 * 4 + 1]), "r"(pdt[e8 * 4 + 2]), "r"(pdt[e8 * 4 + 3])
                        : "memory");
         }
         // TMEM, over consumed dOV^T columns: the A operand of dK (M = keys)
-        tmem_st16(tDOV + lane_base + qbase + 32 + 16 * c, pdt);
+        tmem_st16(tDOV0 + tcol, pdt);
       }
+      if (fetch_stats) sStat[(b ^ 1) * 128 + row] = make_float2(st_max + log2f(st_den), st_dbar);
+      incl = incl_next;
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tiles + 8 * odd);
     }
-    if (wg == 0 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
-    incl = incl_next;
-    tmem_st_wait();
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (wg == 0) g1 = sG[128 + row];
-    suffix_in += g0 + g1;
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t id_kd = instr_desc(128, 64, 0, 1);   // A K-major (M = keys), B MN-major
-      const uint32_t id_qd = instr_desc(128, 80, 1, 1);   // A MN-major (M = queries); B = [K | ones]
-      const uint32_t sQ = sQ0 + kTileBytes * b, sD = sD0 + kTileBytes * b;
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {                    // contraction over the 128 keys
-        const uint64_t a = smem_desc(sPd + 2048 * kk, kTileBytes, 1024);
-        mma_ss(tDQ, a, smem_desc(sK + 2048 * kk, sOnes - sK, 1024), id_qd, kk > 0);
-      }
-      mma_commit(dqdone);
-#pragma unroll
-      for (int kq = 0; kq < 8; ++kq) {                    // contraction over the 128 queries
-        // queries [16kq, 16kq+16): 8 columns in the upper half of the owning warpgroup's score range
-        const uint32_t a_sh = tS + 64 * (kq >> 2) + 32 + 16 * ((kq & 3) >> 1) + 8 * (kq & 1);
-        mma_ts(tDV, a_sh, smem_desc(sD + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
-        mma_ts(tDK, a_sh - tS + tDOV, smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
-      }
-      if (t + 1 < nsteps) {
-        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
-        tc_fence_after();
-        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
-        mma_scores(tDOV, sV, sD0 + kTileBytes * (b ^ 1), 128);
-      }
-      mma_commit(sdone);
-    }
-    __syncwarp();
-    // dQ and ghat of this tile: lane = query, each warpgroup takes 32 of the 64 columns.
-    // Runs under the remaining MMAs.
-    mbar_wait(dqdone, t & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    {
-      float dq[32], gh[32];
-      tmem_ld32(tDQ + lane_base + 32 * wg, dq);
-      if (wg == 0) tmem_ld32(tG + lane_base, gh);
-      tmem_ld_wait(dq);
-      const int i = i0 + row;
-      if (i < g.tq) {
-        float* dst = dq_main + (row_base + i) * kHeadDim + 32 * wg;
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4)
-          red_add_v4(dst + 4 * c4, dq[4 * c4] * g.scale, dq[4 * c4 + 1] * g.scale,
-                     dq[4 * c4 + 2] * g.scale, dq[4 * c4 + 3] * g.scale);
-      }
-      if (wg == 0) {
-        tmem_ld_wait(gh);
-        if (i < g.tq) atomicAdd(ghat + row_base + i, gh[0]);
-      }
-    }
-    tc_fence_before();
+    if (row == 0) tma_wait_read_all();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    read_dq(nsteps - 1);
+    if (row == 0) tma_wait_read_all();
   }
-  mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
+  mbar_wait(sdone + 8, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
-  {
+  if (warp < 8) {
     // lane = key: each warpgroup stores 32 of the 64 columns of dk_main and dv
     float a[32];
     const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
@@ -1227,10 +1327,9 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
                     const float* total, const float* ssum, float* dq_main, float* dk_main, float* ghat,
                     float* dbarp, void* dop, void* dq, void* dk, void* dv, cudaStream_t st, char* err,
                     size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk;
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
-  if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
   CUtensorMap md;
   if (int rc = make_map(&md, dop, g.n, g.tq, err, errlen)) return rc;
   const int64_t rows = g.n * g.tq;
@@ -1244,15 +1343,16 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
   if (int rc = set_smem_attr((const void*)backward_main_kernel, smem_bwd, err, errlen)) return rc;
   mark("tc_backward_main", st, 0);
-  backward_main_kernel<<<(unsigned)(g.n * nkb), 256, smem_bwd, st>>>(
-      mq, mk, mv, md, g, rmax, rden, dbarp, carry, total, dq_main, dk_main, (__nv_bfloat16*)dv, ghat);
+  CUtensorMap mdq;
+  if (int rc = make_map_f32(&mdq, dq_main, g.n, g.tq, err, errlen)) return rc;
+  backward_main_kernel<<<(unsigned)(g.n * nkb), kBwdThreads, smem_bwd, st>>>(
+      mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
+      (__nv_bfloat16*)dv, ghat);
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
   if (int rc = set_smem_attr((const void*)backward_correction_kernel, smem, err, errlen)) return rc;
   mark("tc_backward_correction", st, 0);
-  CUtensorMap mdq;
-  if (int rc = make_map_f32(&mdq, dq_main, g.n, g.tq, err, errlen)) return rc;
   backward_correction_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, mdq, g, rmax, rden, ghat,
                                                                      dk_main, (__nv_bfloat16*)dk);
   mark("tc_backward_correction", st, 1);
