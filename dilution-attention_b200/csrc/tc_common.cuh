@@ -272,12 +272,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, Desc b,
       : "memory");
 }
 
-// S[128 x 128] = A[128 x 64] * B[128 x 64]^T, both K-major tiles: 4 instructions.
+// S[128 x n_cols] = A[128 x 64] * B[n_cols x 64]^T, both K-major tiles: 4 instructions.
 __device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, int n_cols) {
   const uint32_t idesc = instr_desc(128, n_cols, 0, 0);
-  const uint64_t a = smem_desc(a_smem, 16, 1024), b = smem_desc(b_smem, 16, 1024);
+  const Desc a = make_desc(a_smem, 16, 1024), b = make_desc(b_smem, 16, 1024);
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) mma_ss(d_tmem, a + 2 * kk, b + 2 * kk, idesc, kk > 0);
+  for (int kk = 0; kk < 4; ++kk) mma_ss(d_tmem, a, 2 * kk, b, 2 * kk, idesc, kk > 0);
 }
 
 // Dynamic shared memory base rounded up to 1024 bytes.

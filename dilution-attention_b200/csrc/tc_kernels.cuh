@@ -529,11 +529,11 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
       tc_fence_after();
       mbar_wait(vfull, jb & 1, ctl, &g_status, kErrWaitTma);
       tc_fence_after();
-      const uint32_t id_o = instr_desc(128, 80, 1, 1);
+      constexpr uint32_t id_o = instr_desc(128, 80, 1, 1);
+      // descriptors are built once per tile; a k-step is a constant 2048 B (128 units) further
+      const Desc dSh = make_desc(sSh, kTileBytes, 1024), dVm = make_desc(sV, sOnes - sV, 1024);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_ss(tO, smem_desc(sSh + 2048 * kk, kTileBytes, 1024), smem_desc(sV + 2048 * kk, sOnes - sV, 1024), id_o,
-               (jb > 0 || kk > 0));
+      for (int kk = 0; kk < 8; ++kk) mma_ss(tO, dSh, 128 * kk, dVm, 128 * kk, id_o, (jb > 0 || kk > 0));
       if (jb + 1 < njb) {
         mbar_wait(kfull + 8 * (b ^ 1), ((jb + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
         tc_fence_after();
@@ -1169,16 +1169,16 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t id_kd = instr_desc(128, 64, 0, 1), id_qd = instr_desc(128, 64, 1, 1);
-      const uint32_t sQ = sQ0 + kTileBytes * b;
+      constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1), id_qd = instr_desc(128, 64, 1, 1);
+      // descriptors are built once per tile; a k-step is a constant 2048 B (128 units) further
+      const Desc dQm = make_desc(sQ0 + kTileBytes * b, kTileBytes, 1024);
+      const Desc dWm = make_desc(sW, kTileBytes, 1024), dKm = make_desc(sK, kTileBytes, 1024);
 #pragma unroll
       for (int kq = 0; kq < 8; ++kq)
-        mma_ts(tDK, tS + 64 * (kq >> 2) + 32 * ((kq & 3) >> 1) + 8 * (kq & 1),
-               smem_desc(sQ + 2048 * kq, kTileBytes, 1024), id_kd, (t > 0 || kq > 0));
+        mma_ts(tDK, tS + 64 * (kq >> 2) + 32 * ((kq & 3) >> 1) + 8 * (kq & 1), dQm, 128 * kq, id_kd,
+               (t > 0 || kq > 0));
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_ss(tDQ, smem_desc(sW + 2048 * kk, kTileBytes, 1024), smem_desc(sK + 2048 * kk, kTileBytes, 1024),
-               id_qd, kk > 0);
+      for (int kk = 0; kk < 8; ++kk) mma_ss(tDQ, dWm, 128 * kk, dKm, 128 * kk, id_qd, kk > 0);
       mma_commit(dqdone);                                // both products have read the W tile
       if (t + 1 < nsteps) {
         mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
