@@ -624,7 +624,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // half-step h are complete it issues dV, dK (and dQ | ghat after the second half) of h and
 // the score MMAs of h + 2 into the stage h has just left, so the tensor pipe works under
 // the arithmetic of h + 1.  Q and dO' tiles are triple-buffered.
-constexpr int kBwdThreads = 288;
+constexpr int kBwdThreads = 384;
 constexpr int kBwdSmem = 12 * kTileBytes + 2048 + 2048 + 256 + 1024;
 
 __device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
@@ -739,28 +739,32 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   __syncthreads();
   tc_fence_after();
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ the issuing warp
-    if (lane == 0) {
-      constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);     // scores: both operands K-major
-      constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);    // dV, dK: A from TMEM (M = keys), B MN-major
-      constexpr uint32_t id_qd = instr_desc(128, 80, 1, 1);    // dQ | ghat: A MN-major (M = queries)
-      // every descriptor is built once; inside the loop tile, stage and k-step are constant
-      // offsets (in 16-byte units: a tile is 1024, an MN-major k-step 128, a K-major one 2)
-      const Desc dKk = make_desc(sK, 16, 1024);                 // K, K-major: A of the scores
-      const Desc dKm = make_desc(sK, sOnes - sK, 1024);         // [K | ones], MN-major: B of dQ | ghat
-      const Desc dPm = make_desc(sPd, kTileBytes, 1024);        // pdp, MN-major: A of dQ | ghat
-      const Desc dQk = make_desc(sQ0, 16, 1024), dQm = make_desc(sQ0, kTileBytes, 1024);
-      const Desc dDk = make_desc(sD0, 16, 1024), dDm = make_desc(sD0, kTileBytes, 1024);
-      // scores of a half-step in stage ST of Q and dO'; even half-steps take queries 64..127
-      auto issue_scores = [&](auto odd_c, auto st_c) {
-        constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
-        constexpr uint32_t off = ST * 1024 + (ODD ? 0 : 512);
+  if (wg == 2) {
+    // ------------------------------------------------------------ warpgroup 2: issue and dQ read-out
+    // Thread 256 issues every MMA and TMA copy.  After the second half-step of a step all
+    // four warps (lane = query) move the finished dQ | ghat tile out, so that the compute
+    // warps never touch it.  The warpgroup hands most of its registers to the other two.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 128;");
+    constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);     // scores: both operands K-major
+    constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);    // dV, dK: A from TMEM (M = keys), B MN-major
+    constexpr uint32_t id_qd = instr_desc(128, 80, 1, 1);    // dQ | ghat: A MN-major (M = queries)
+    // every descriptor is built once; inside the loop tile, stage and k-step are constant
+    // offsets (in 16-byte units: a tile is 1024, an MN-major k-step 128, a K-major one 2)
+    const Desc dKk = make_desc(sK, 16, 1024);                 // K, K-major: A of the scores
+    const Desc dKm = make_desc(sK, sOnes - sK, 1024);         // [K | ones], MN-major: B of dQ | ghat
+    const Desc dPm = make_desc(sPd, kTileBytes, 1024);        // pdp, MN-major: A of dQ | ghat
+    const Desc dQk = make_desc(sQ0, 16, 1024), dQm = make_desc(sQ0, kTileBytes, 1024);
+    const Desc dDk = make_desc(sD0, 16, 1024), dDm = make_desc(sD0, kTileBytes, 1024);
+    // scores of a half-step in stage ST of Q and dO'; even half-steps take queries 64..127
+    auto issue_scores = [&](auto odd_c, auto st_c) {
+      constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
+      constexpr uint32_t off = ST * 1024 + (ODD ? 0 : 512);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) mma_ss(tS0 + 64 * ODD, dKk, 2 * kk, dQk, off + 2 * kk, id_s, kk > 0);
+      for (int kk = 0; kk < 4; ++kk) mma_ss(tS0 + 64 * ODD, dKk, 2 * kk, dQk, off + 2 * kk, id_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) mma_ts(tDOV0 + 64 * ODD, tV + 8 * kk, dDk, off + 2 * kk, id_s, kk > 0);
-      };
+      for (int kk = 0; kk < 4; ++kk) mma_ts(tDOV0 + 64 * ODD, tV + 8 * kk, dDk, off + 2 * kk, id_s, kk > 0);
+    };
+    if (tid == 256) {
       mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
       mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
       tc_fence_after();
@@ -768,10 +772,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       mma_commit(sdone);
       issue_scores(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
       mma_commit(sdone + 8);
-      // half-step h = 2s + ODD of step s, whose Q and dO' tiles sit in stage ST = s % 3
-      auto half = [&](auto odd_c, auto st_c, int s) {
-        constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
-        constexpr int ST1 = (ST + 1) % 3, ST2 = (ST + 2) % 3;
+    }
+    __syncwarp();
+    // half-step h = 2s + ODD of step s, whose Q and dO' tiles sit in stage ST = s % 3
+    auto half = [&](auto odd_c, auto st_c, int s) {
+      constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
+      constexpr int ST1 = (ST + 1) % 3, ST2 = (ST + 2) % 3;
+      if (tid == 256) {
         mbar_wait(tiles + 8 * ODD, s & 1, ctl, &g_status, kErrWaitTile);
         tc_fence_after();
 #pragma unroll
@@ -805,25 +812,64 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
           tma_load_tile(sQ0 + kTileBytes * ST2, &map_q, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
           tma_load_tile(sD0 + kTileBytes * ST2, &map_do, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
         }
-      };
-      using C0 = std::integral_constant<int, 0>;
-      using C1 = std::integral_constant<int, 1>;
-      using C2 = std::integral_constant<int, 2>;
-      for (int s = 0; s < nsteps; s += 3) {
-        half(C0{}, C0{}, s);
-        half(C1{}, C0{}, s);
-        if (s + 1 < nsteps) {
-          half(C0{}, C1{}, s + 1);
-          half(C1{}, C1{}, s + 1);
+      }
+      __syncwarp();
+      if (ODD) {
+        // dQ and ghat of the step's 128 queries: lane = query.  The fp32 tile is staged in
+        // shared memory in the copy engine's swizzled layout and added to dq_main by two
+        // tensor reductions of 32 columns.
+        if (lane == 0) mbar_wait(dqdone, s & 1, ctl, &g_status, kErrWaitMma);
+        __syncwarp();
+        tc_fence_after();
+        if (tid == 256) tma_wait_read_all();            // the previous reductions have read the staging buffer
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const uint32_t stage = sDq + row * 128;
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {                   // 16 columns at a time
+          float dq[16];
+          tmem_ld16(tDQ + lane_base + 16 * j, dq);
+          tmem_ld_wait16(dq);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + kTileBytes * (j >> 1) + (((4 * (j & 1) + c) ^ (row & 7)) << 4)),
+                         "f"(dq[4 * c] * g.scale), "f"(dq[4 * c + 1] * g.scale), "f"(dq[4 * c + 2] * g.scale),
+                         "f"(dq[4 * c + 3] * g.scale)
+                         : "memory");
         }
-        if (s + 2 < nsteps) {
-          half(C0{}, C2{}, s + 2);
-          half(C1{}, C2{}, s + 2);
+        float gh;
+        tmem_ld1(tG + lane_base, &gh);
+        tmem_ld_wait();
+        fence_async_smem();
+        tc_fence_before();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const int ibq = nqb - 1 - s;
+        if (tid == 256) {
+          tc_fence_after();
+          tma_reduce_add_tile(&map_dq, sDq, 0, ibq * kTileRows, n);
+          tma_reduce_add_tile(&map_dq, sDq + kTileBytes, 32, ibq * kTileRows, n);
         }
+        const int i = ibq * kTileRows + row;
+        if (i < g.tq) atomicAdd(ghat + row_base + i, gh);
+      }
+    };
+    using C0 = std::integral_constant<int, 0>;
+    using C1 = std::integral_constant<int, 1>;
+    using C2 = std::integral_constant<int, 2>;
+    for (int s = 0; s < nsteps; s += 3) {
+      half(C0{}, C0{}, s);
+      half(C1{}, C0{}, s);
+      if (s + 1 < nsteps) {
+        half(C0{}, C1{}, s + 1);
+        half(C1{}, C1{}, s + 1);
+      }
+      if (s + 2 < nsteps) {
+        half(C0{}, C2{}, s + 2);
+        half(C1{}, C2{}, s + 2);
       }
     }
-    __syncwarp();
+    if (tid == 256) tma_wait_read_all();
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     // ------------------------------------------------------------ the compute warps
     const int cw = 32 * (1 - wg);                    // this warpgroup's columns of a stage
     // demand of this thread's key where its walk starts: warpgroup 0 behind the half-step
@@ -833,34 +879,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       const int rb = 2 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 1) + (wg == 0 ? 1 : 0);
       return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
     };
-    // dQ and ghat of the step's 128 queries: lane = query, each warpgroup takes 32 of the 64
-    // columns.  The fp32 tile is staged in shared memory in the copy engine's swizzled layout
-    // and added to dq_main by ONE tensor reduction per warpgroup (the caller has made sure
-    // that the previous reduction has read the staging buffer).
-    auto read_dq = [&](int sp) {
-      if (lane == 0) mbar_wait(dqdone, sp & 1, ctl, &g_status, kErrWaitMma);
-      __syncwarp();
-      tc_fence_after();
-      float dq[32], gh = 0.f;
-      tmem_ld32(tDQ + lane_base + 32 * wg, dq);
-      if (wg == 0) tmem_ld1(tG + lane_base, &gh);
-      tmem_ld_wait(dq);
-      const uint32_t stage = sDq + kTileBytes * wg + row * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + ((c ^ (row & 7)) << 4)),
-                     "f"(dq[4 * c] * g.scale), "f"(dq[4 * c + 1] * g.scale), "f"(dq[4 * c + 2] * g.scale),
-                     "f"(dq[4 * c + 3] * g.scale)
-                     : "memory");
-      fence_async_smem();
-      if (wg == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
-      else asm volatile("bar.sync 3, 128;" ::: "memory");
-      const int ibq = nqb - 1 - sp;
-      if (row == 0) tma_reduce_add_tile(&map_dq, sDq + kTileBytes * wg, 32 * wg, ibq * kTileRows, n);
-      const int i = ibq * kTileRows + row;
-      if (wg == 0 && i < g.tq) atomicAdd(ghat + row_base + i, gh);
-    };
-
     float sigma = 0.f;                               // suffix of dk_share behind the half-step
     float incl = load_edge(0);
     for (int h = 0; h < nhalf; ++h) {
@@ -955,15 +973,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       sG[(odd * 2 + wg) * 128 + row] = gsum;
       // the shares stay in TMEM, over score columns this thread has consumed
       tmem_st16(tS0 + tcol, shp);
-      // the thread that issued the previous dQ reduction: the staging buffer has been read
-      if (!odd && row == 0) tma_wait_read_all();
       asm volatile("bar.sync 1, 256;" ::: "memory");   // the compute warps
       const float gother = sG[(odd * 2 + (1 - wg)) * 128 + row];
       // FWD walked with dp = w - prefix; the true value is w + sigma - G0 - (G1 - prefix)
       const float fix = wg == 1 ? sigma - gother - gsum : 0.f;
       sigma -= gsum + gother;
-      // the dQ tile of the previous 128 queries read the pdp buffer that is written next
-      if (!odd && s >= 1) read_dq(s - 1);
+      // the dQ MMAs of the previous 128 queries read the pdp buffer that is written next
+      if (!odd && s >= 1) {
+        if (lane == 0) mbar_wait(dqdone, (s - 1) & 1, ctl, &g_status, kErrWaitMma);
+        __syncwarp();
+      }
       {
         uint32_t pdt[16];                              // 32 pdp values as bf16 pairs
 #pragma unroll
@@ -989,10 +1008,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       __syncwarp();
       if (lane == 0) mbar_arrive(tiles + 8 * odd);
     }
-    if (row == 0) tma_wait_read_all();
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    read_dq(nsteps - 1);
-    if (row == 0) tma_wait_read_all();
   }
   mbar_wait(sdone + 8, nsteps & 1, ctl, &g_status, kErrWaitMma);
   tc_fence_after();
