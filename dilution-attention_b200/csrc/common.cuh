@@ -31,6 +31,31 @@ __device__ __forceinline__ float fast_rcp(float x) {
   return y;
 }
 
+// 2^x for x <= 0 on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5];
+// a minimax polynomial gives 2^f (relative error 2.7e-6 with degree 4, 7.5e-5 with
+// degree 3) and n is added to the exponent field.  The special-function unit does 16
+// exponentials per clock and SM; kernels bound by it hand a fixed share of their
+// exponentials to this routine, whose ten instructions go to otherwise idle issue slots.
+template <int DEG>
+__device__ __forceinline__ float poly_exp2(float x) {
+  static_assert(DEG == 3 || DEG == 4, "degree 3 or 4");
+  x = fmaxf(x, -125.f);
+  const float r = x + 12582912.f;                 // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = x - (r - 12582912.f);
+  float p;
+  if (DEG == 4) {
+    p = fmaf(f, 0.009570085443556309f, 0.05591784790158272f);
+    p = fmaf(p, f, 0.240247443318367f);
+    p = fmaf(p, f, 0.6931217908859253f);
+    p = fmaf(p, f, 0.9999992847442627f);
+  } else {
+    p = fmaf(f, 0.05517148599028587f, 0.24261091649532318f);
+    p = fmaf(p, f, 0.6932609677314758f);
+    p = fmaf(p, f, 0.9999280571937561f);
+  }
+  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -209,7 +209,12 @@ __global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant_
         if (nm > -INFINITY) {
           float ps = 0.f;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ps += fast_exp2(fmaf(v[e], g.zscale, -nm));
+          for (int e = 0; e < 32; ++e) {
+            // the pass is bound by the special-function unit: every fourth exponential
+            // is a polynomial on the FMA pipe instead
+            const float z = fmaf(v[e], g.zscale, -nm);
+            ps += (e & 3) == 3 ? poly_exp2<4>(z) : fast_exp2(z);
+          }
           s = s * fast_exp2(m - nm) + ps;
           m = nm;
         }
