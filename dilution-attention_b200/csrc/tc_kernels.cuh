@@ -597,14 +597,10 @@ __global__ void backward_prep_kernel(const float* __restrict__ dout, const float
   }
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 // Main reverse pass (the reference's BA, kernels.py:677-775).  grid = n * ceil(t/128),
-// key blocks with the most query blocks first; one CTA per SM: eight compute warps and
-// one warp that issues every TMA copy and every MMA.
+// key blocks with the most query blocks first; one CTA per SM, three warpgroups: two of
+// compute warps and one whose first thread issues every TMA copy and every MMA and whose
+// four warps move the finished dQ tiles out.
 // TMEM (496 of 512 columns): two stages of S^T (64 columns each) | two stages of dOV^T
 // (64 each) | dV 64 | dK 64 | dQ 64 + ghat 16 as one 80-column tile | the V tile as a
 // bf16 A operand (32).
@@ -625,10 +621,11 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // to shared memory as the MN-major A operand (M = queries) of one N = 80 MMA per 128
 // queries against B = [K | ones], which yields dQ = pdp K in 64 columns and ghat = pdp 1
 // in the next 16.
-// The issuing warp runs two half-steps ahead of the arithmetic: when the tiles of
+// The issuing thread runs two half-steps ahead of the arithmetic: when the tiles of
 // half-step h are complete it issues dV, dK (and dQ | ghat after the second half) of h and
 // the score MMAs of h + 2 into the stage h has just left, so the tensor pipe works under
-// the arithmetic of h + 1.  Q and dO' tiles are triple-buffered.
+// the arithmetic of h + 1.  Q and dO' tiles are triple-buffered.  After setup the third
+// warpgroup gives registers up (setmaxnreg) and the compute warpgroups take them.
 constexpr int kBwdThreads = 384;
 constexpr int kBwdSmem = 12 * kTileBytes + 2048 + 2048 + 256 + 1024;
 

@@ -126,3 +126,37 @@ def test_host_buffer_entry_point_matches_device_op(kernels):
     fwd_only = kernels.dilution_attention_host(qb, kb, vb, dot_precision="bf16", slabs=3)
     torch.cuda.synchronize()
     assert torch.equal(fwd_only, out)
+
+
+def test_backward_size_independent_properties_at_16k(kernels):
+    """T=16384, one (b,h) row, bf16, tensor-core kernels: identities of the true gradient that
+    need no T^2 oracle.
+    (a) the scores depend on q and k only through q.k, so <q, dq> == <k, dk>;
+    (b) out is linear in v (out = A v, dv = A^T dout), so <v, dv> == <out, dout>;
+    (c) the gradients are linear in dout."""
+    t, d = 16384, 64
+    q, k, v, dout = make_inputs(1, 1, t, d, 21, scales=(0.5, 0.5, 1.0, 1e-2))
+    _, _, _, dout2 = make_inputs(1, 1, t, d, 22, scales=(0.5, 0.5, 1.0, 1e-2))
+
+    def run(g):
+        qs, ks, vs = (x.bfloat16().to(DEV).requires_grad_(True) for x in (q, k, v))
+        out = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+        out.backward(g.to(DEV))
+        return out.detach(), qs, ks, vs
+
+    out, qs, ks, vs = run(dout)
+    dq, dk, dv = (x.grad.double() for x in (qs, ks, vs))
+    assert all(torch.isfinite(x).all() for x in (dq, dk, dv))
+    qdq = (qs.detach().double() * dq).sum().item()
+    kdk = (ks.detach().double() * dk).sum().item()
+    scale_qk = (qs.detach().double() * dq).abs().sum().item()
+    assert abs(qdq - kdk) < 2e-3 * scale_qk, (qdq, kdk, scale_qk)
+    vdv = (vs.detach().double() * dv).sum().item()
+    odo = (out.double() * dout.to(DEV).double()).sum().item()
+    scale_v = (out.double() * dout.to(DEV).double()).abs().sum().item()
+    assert abs(vdv - odo) < 2e-3 * scale_v, (vdv, odo, scale_v)
+    _, q2, k2, v2 = run(dout2)
+    _, q3, k3, v3 = run(dout + dout2)
+    for name, a, b, c in (("dq", qs, q2, q3), ("dk", ks, k2, k3), ("dv", vs, v2, v3)):
+        s = a.grad.float() + b.grad.float()
+        assert rel_err(c.grad.float().cpu(), s.cpu()) < 2e-2, name
