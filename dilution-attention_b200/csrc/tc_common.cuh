@@ -226,41 +226,17 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, int a_mn, int b_
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; one instruction covers 16 contraction elements.
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0),
-        "r"(0)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]: A is an M x 16 bf16 operand held in TMEM, row m on
-// lane m, two consecutive contraction elements per 32-bit column (8 columns).
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
-      : "memory");
-}
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
 
-// The same instructions with each descriptor as two 32-bit halves.  The start address sits
-// in the low half, so stepping through a tile is one 32-bit add of a constant to a value
-// built once outside the loop: the issuing thread's own arithmetic, not the tensor pipe,
-// limits the issue rate of small MMAs (about 45 cycles per instruction back to back,
-// about 100 when each descriptor is rebuilt from an address).
+// A descriptor is kept as two 32-bit halves.  The start address sits in the low half, so
+// stepping through a tile is one 32-bit add of a constant to a value built once outside
+// the loop: the issuing thread's own arithmetic, not the tensor pipe, limits the issue
+// rate of small MMAs (about 45 cycles per instruction back to back, about 100 when each
+// descriptor is rebuilt from an address).
 struct Desc {
   uint32_t lo, hi;
 };
@@ -268,7 +244,8 @@ __device__ __forceinline__ Desc make_desc(uint32_t saddr, uint32_t lbo_bytes, ui
   const uint64_t d = smem_desc(saddr, lbo_bytes, sbo_bytes);
   return Desc{(uint32_t)d, (uint32_t)(d >> 32)};
 }
-// byte offsets are added in descriptor units of 16 bytes
+// D[tmem] (+)= A[smem] * B[smem]; one instruction covers 16 contraction elements.
+// Offsets are added in descriptor units of 16 bytes.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, Desc a, uint32_t a_off16, Desc b, uint32_t b_off16,
                                        uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -282,6 +259,8 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, Desc a, uint32_t a_off16
         "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: A is an M x 16 bf16 operand held in TMEM, row m on
+// lane m, two consecutive contraction elements per 32-bit column (8 columns).
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, Desc b, uint32_t b_off16,
                                        uint32_t idesc, uint32_t accumulate) {
   asm volatile(
