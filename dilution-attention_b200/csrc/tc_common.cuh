@@ -66,12 +66,12 @@ struct Ctl {
   uint32_t tmem;        // written by tcgen05.alloc
 };
 
-// Bounded wait.  Returns false (at once, if the CTA is already aborting) when
+// Bounded wait.  Returns false (after one probe, if the CTA is already aborting) when
 // the phase did not complete in time.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, int* status,
                                           int code, long long limit = kWaitCycles) {
+  if (mbar_try(bar, parity)) return true;      // the common case costs one instruction
   if (ctl->abort) return false;
-  if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (clock64() - t0 > limit) {
