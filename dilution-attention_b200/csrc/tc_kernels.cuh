@@ -896,8 +896,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
         st_den = rden[row_base + i];
         st_dbar = dbarp[row_base + i];
       }
-      if (lane == 0) mbar_wait(sdone + 8 * odd, s & 1, ctl, &g_status, kErrWaitMma);
-      __syncwarp();
+      mbar_wait(sdone + 8 * odd, s & 1, ctl, &g_status, kErrWaitMma);
       tc_fence_after();
       float vs[32], vd[32];
       const uint32_t tcol = lane_base + 64 * odd + cw;
@@ -982,8 +981,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       sigma -= gsum + gother;
       // the dQ MMAs of the previous 128 queries read the pdp buffer that is written next
       if (!odd && s >= 1) {
-        if (lane == 0) mbar_wait(dqdone, (s - 1) & 1, ctl, &g_status, kErrWaitMma);
-        __syncwarp();
+        mbar_wait(dqdone, (s - 1) & 1, ctl, &g_status, kErrWaitMma);
       }
       {
         uint32_t pdt[16];                              // 32 pdp values as bf16 pairs
