@@ -882,13 +882,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
     };
     float sigma = 0.f;                               // suffix of dk_share behind the half-step
+    // the checkpoints are read once from a buffer far larger than L2: each load is issued two
+    // half-steps before its value is used
     float incl = load_edge(0);
+    float incl_next = nhalf > 1 ? load_edge(1) : 0.f;
     for (int h = 0; h < nhalf; ++h) {
       const int s = h >> 1, odd = h & 1, ib = nqb - 1 - s, b = s & 1;
-      // fetch what the next half-step needs before waiting for this one
-      float incl_next = 0.f;
+      // fetch what the coming half-steps need before waiting for this one
+      float incl_next2 = 0.f;
       float st_max = INFINITY, st_den = 1.f, st_dbar = 0.f;
-      if (h + 1 < nhalf) incl_next = load_edge(h + 1);
+      if (h + 2 < nhalf) incl_next2 = load_edge(h + 2);
       const bool fetch_stats = !odd && wg == 0 && s + 1 < nsteps;
       if (fetch_stats) {
         const int i = (ib - 1) * kTileRows + row;     // ib >= 1 here, so i < tq
@@ -1002,6 +1005,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       }
       if (fetch_stats) sStat[(b ^ 1) * 128 + row] = make_float2(st_max + log2f(st_den), st_dbar);
       incl = incl_next;
+      incl_next = incl_next2;
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before();
