@@ -1120,8 +1120,15 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   for (int t = 0; t < nsteps; ++t) {
     const int ib = jb + t, b = t & 1;
-    float2 stat_next = make_float2(INFINITY, 0.f);
-    if (wg == 1 && t + 1 < nsteps) stat_next = load_stats(ib + 1);
+    // next step's statistics as raw values: they are combined at the store below, when the
+    // loads have long returned, so that no instruction waits for them here
+    float nx_max = INFINITY, nx_den = 1.f, nx_gh = 0.f;
+    if (wg == 1 && t + 1 < nsteps && (ib + 1) * kTileRows + row < g.tq) {
+      const int64_t i = row_base + (ib + 1) * kTileRows + row;
+      nx_max = rmax[i];
+      nx_den = rden[i];
+      nx_gh = ghat[i];
+    }
     mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && t >= 1 && t + 1 < nsteps) {      // the Q stage of step t-1 is free
@@ -1181,7 +1188,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     }
     };
     if (masked_tile) tile(std::true_type{}); else tile(std::false_type{});
-    if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = stat_next;
+    if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = make_float2(nx_max + log2f(nx_den), nx_gh);
     tmem_st_wait();
     fence_async_smem();
     tc_fence_before();
