@@ -1136,6 +1136,10 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
     }
     __syncwarp();
+    // this warpgroup's half of the W buffer doubled as its dQ staging area: the previous
+    // step's reduction must have read it before it is written again
+    if (row == 0) tma_wait_read_all();
+    wg_barrier(wg);
     const int i0 = ib * kTileRows + 64 * wg;
     const bool masked_tile = dead || t == 0;
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
@@ -1174,12 +1178,6 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) wt[e8 * 4 + u] = pack_bf16(w8[2 * u], w8[2 * u + 1]);
-        if (e8 == 0 && c == 0) {
-          // this warpgroup's half of the W buffer doubled as its dQ staging area: the previous
-          // step's reduction must have read it before the first store of this step
-          if (row == 0) tma_wait_read_all();
-          wg_barrier(wg);
-        }
         // shared memory: the MN-major A operand of dQc (M = queries)
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sW + share_chunk_offset(row, wg * 64 + c * 32 + e8 * 8)),
                      "r"(wt[e8 * 4]), "r"(wt[e8 * 4 + 1]), "r"(wt[e8 * 4 + 2]), "r"(wt[e8 * 4 + 3])
