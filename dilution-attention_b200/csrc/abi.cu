@@ -182,11 +182,13 @@ struct BwdScratch {
 };
 BwdScratch carve_bwd(void* scratch, int64_t n, int64_t t, int d) {
   BwdScratch s;
+  // dop is a TMA source (16-byte aligned start): it comes before the two (n, t) vectors,
+  // whose length n * t may be odd
   s.dq_main = (float*)scratch;
   s.dk_main = s.dq_main + n * t * d;
-  s.ghat = s.dk_main + n * t * d;
+  s.dop = s.dk_main + n * t * d;
+  s.ghat = (float*)((char*)s.dop + 2 * (size_t)(n * t * d));
   s.dbar = s.ghat + n * t;
-  s.dop = s.dbar + n * t;
   return s;
 }
 

@@ -47,10 +47,22 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver entry point and wants a current context.  A thread that
+// has only selected the device (an autograd engine thread calling the backward first) may
+// not have one yet: a runtime call that touches the device binds the primary context.
+inline void ensure_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 // (n, t, 64) bf16 row-major -> 3-D map {64, t, n}, box {64, 128, 1}, 128-byte swizzle.
 // Rows past t read as zero, and a box never crosses into the next (batch, head) row.
 inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen,
                     int box_rows = kTileRows) {
+  ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
@@ -77,6 +89,7 @@ inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, ch
 // (n, t, 64) fp32 row-major -> 3-D map {64, t, n}, box {32, 128, 1} (128 bytes wide),
 // 128-byte swizzle: the target of the dQ tile reductions.
 inline int make_map_f32(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen) {
+  ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");

@@ -160,3 +160,19 @@ def test_backward_size_independent_properties_at_16k(kernels):
     for name, a, b, c in (("dq", qs, q2, q3), ("dk", ks, k2, k3), ("dv", vs, v2, v3)):
         s = a.grad.float() + b.grad.float()
         assert rel_err(c.grad.float().cpu(), s.cpu()) < 2e-2, name
+
+
+@pytest.mark.parametrize("seq", [1, 2, 63, 64, 65, 127, 128, 129, 192, 193, 320])
+def test_bf16_tensor_path_backward_ragged_lengths(kernels, seq):
+    """Lengths around the 64-row checkpoint and 128-row tile boundaries (half-steps that are
+    partly or wholly past the end, a single tile, one row) on the tensor-core kernels."""
+    q, k, v, dout = make_inputs(1, 3, seq, 64, 300 + seq, scales=(0.5, 0.5, 1.0, 1e-1))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref = O.dilution_backward(qb.float(), kb.float(), vb.float(), dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+    out.backward(dout.to(DEV))
+    assert (out.detach().cpu() - ref[0]).abs().max().item() < 2e-2
+    for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
+        assert torch.isfinite(t.grad).all(), name
+        assert (t.grad.float().cpu() - gr).abs().max().item() < 2e-2, name
