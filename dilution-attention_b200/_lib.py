@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libdilution_b200.so")
 
 F32, BF16 = 0, 1
 PREC = {"ieee": 0, "tf32": 1, "bf16": 2}
-CARRY_ROWS = 64
+CARRY_ROWS = 32
 
 _P, _I, _L, _F, _Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 

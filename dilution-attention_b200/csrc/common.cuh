@@ -8,7 +8,7 @@
 namespace dil {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kCarryRows = 64;  // query rows per demand checkpoint (DILUTION_CARRY_ROWS)
+constexpr int kCarryRows = 32;  // query rows per demand checkpoint (DILUTION_CARRY_ROWS)
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }

@@ -17,6 +17,7 @@ namespace dil {
 namespace simt {
 
 constexpr int TS = 64;    // tile side
+static_assert(TS == 2 * kCarryRows, "two demand checkpoints per tile");
 constexpr int NT = 256;   // threads per CTA
 constexpr int SL = 65;    // leading dimension of score tiles
 
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   float* sRinv = sM + TS;
   float* sPart = sRinv + TS;  // [4][64]
   const int nqb = (g.tq + TS - 1) / TS;
+  const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
   load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
@@ -221,8 +223,13 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
     sPart[seg * TS + col] = part;
     __syncthreads();
     if (seg == 0) {
-      if (ja < g.tk) carry[(n * nqb + ib) * (int64_t)g.tk + ja] = base + local;
-      local += (sPart[col] + sPart[TS + col]) + (sPart[2 * TS + col] + sPart[3 * TS + col]);
+      // two checkpoints per tile: in front of its first and of its 33rd query row
+      const float half0 = sPart[col] + sPart[TS + col];
+      if (ja < g.tk) {
+        carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] = base + local;
+        if (2 * ib + 1 < ncb) carry[(n * ncb + 2 * ib + 1) * (int64_t)g.tk + ja] = base + local + half0;
+      }
+      local += half0 + (sPart[2 * TS + col] + sPart[3 * TS + col]);
     }
   }
   if (seg == 0 && ja < g.tk) total[n * g.tk + ja] = local;
@@ -263,7 +270,8 @@ __global__ void __launch_bounds__(NT) main_kernel(
 
   const int last_key = min(g.tk - 1, g.q_off + ib * TS + TS - 1);
   const int njb = last_key / TS + 1;
-  const float* carry_row = carry + (n * nqb + ib) * (int64_t)g.tk;
+  const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
+  const float* carry_row = carry + (n * ncb + 2 * ib) * (int64_t)g.tk;
   for (int jb = 0; jb < njb; ++jb) {
     __syncthreads();
     load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
@@ -360,6 +368,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   float* sDbar = sRinv + TS;
   float* sSinv = sDbar + TS;
   const int nqb = (g.tq + TS - 1) / TS;
+  const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
   load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
@@ -399,7 +408,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
     __syncthreads();
     if (threadIdx.x < TS) {
       const int col = threadIdx.x, ja = jb * TS + col;
-      float c = (ja < g.tk) ? carry[(n * nqb + ib) * (int64_t)g.tk + ja] : 0.f;
+      float c = (ja < g.tk) ? carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] : 0.f;
       for (int i = 0; i < TS; ++i) {          // forward: exclusive demand
         sC[i * SL + col] = c;
         c += sP[i * SL + col];

@@ -255,10 +255,10 @@ __global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant_
 // ---------------------------------------------------------------- pass 2: column sums + scan
 // grid = n * ceil(tk/128), key blocks with the most query blocks first.
 // S^T = K Q^T, lane = key.  The CTA keeps its K tile and walks the query blocks
-// in causal order.  Each warpgroup sums p over its 64 queries of the tile; the
-// thread of warpgroup 0 owns the key's running sum — the exclusive scan — and
-// stores one checkpoint per 64 query rows, one tile behind the sums.
-constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 1024 + 1024 + 256;
+// in causal order.  Each warpgroup sums p over its 64 queries of the tile, 32 at a
+// time; the thread of warpgroup 0 owns the key's running sum — the exclusive scan —
+// and stores one checkpoint per 32 query rows, one tile behind the sums.
+constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 2048 + 1024 + 256;
 
 __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
@@ -268,8 +268,8 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes;
   float* sL = reinterpret_cast<float*>(smem + 3 * kTileBytes);                 // [2][128]
-  float* sCs = reinterpret_cast<float*>(smem + 3 * kTileBytes + 1024);         // [2][128] sums of warpgroup 1
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 2048);
+  float2* sCs = reinterpret_cast<float2*>(smem + 3 * kTileBytes + 1024);       // [2][128] the two sums of warpgroup 1
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 3072);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2);
 
@@ -308,7 +308,20 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
   const int ja = k0 + row;
   const bool live = ja < g.tk;
   const float base = (carry_base != nullptr && live) ? carry_base[(int64_t)n * g.tk + ja] : 0.f;
-  float local = 0.f, prev = 0.f;      // warpgroup 0: scan state and its own sum of the previous tile
+  float local = 0.f, prev0 = 0.f, prev1 = 0.f;   // warpgroup 0: scan state, its two sums of the previous tile
+  // the four checkpoints of 128-row tile `tile`, and the scan moved past it
+  auto store_checkpoints = [&](int tile, float2 w1) {
+    const int rb = tile * 4;
+    const float c0 = base + local, c1 = c0 + prev0, c2 = c1 + prev1, c3 = c2 + w1.x;
+    if (live) {
+      const int64_t o = ((int64_t)n * ncb + rb) * g.tk + ja;
+      if (rb < ncb) carry[o] = c0;
+      if (rb + 1 < ncb) carry[o + g.tk] = c1;
+      if (rb + 2 < ncb) carry[o + 2 * (int64_t)g.tk] = c2;
+      if (rb + 3 < ncb) carry[o + 3 * (int64_t)g.tk] = c3;
+    }
+    local += (prev0 + prev1) + (w1.x + w1.y);
+  };
   const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
   for (int it = 0; it < nib; ++it) {
     const int ib = ib0 + it, b = it & 1;
@@ -322,14 +335,7 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
     // while the MMA runs: next tile's statistics, and the checkpoints of the previous tile
     float lse_next = 0.f;
     if (wg == 1 && it + 1 < nib) lse_next = load_lse(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq);
-    if (wg == 0 && it > 0) {
-      const int rb = (ib - 1) * 2;
-      if (live) {
-        if (rb < ncb) carry[((int64_t)n * ncb + rb) * g.tk + ja] = base + local;
-        if (rb + 1 < ncb) carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] = base + local + prev;
-      }
-      local += prev + sCs[((it - 1) & 1) * 128 + row];
-    }
+    if (wg == 0 && it > 0) store_checkpoints(ib - 1, sCs[((it - 1) & 1) * 128 + row]);
     mbar_wait(sdone, it & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
     if (tid == 0 && it + 2 < nib) {
@@ -340,7 +346,7 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
     const int i0 = g.q_off + ib * kTileRows + 64 * wg;   // absolute position of this half's first query
     const bool edge = i0 < k0 + kTileRows - 1;            // part of the diagonal tile
     const float4* L4 = reinterpret_cast<const float4*>(sL + 128 * b + 64 * wg);
-    float colsum = 0.f;
+    float colsum0 = 0.f, colsum1 = 0.f;      // queries 0-31 and 32-63 of this warpgroup's half
     auto tile = [&](auto edge_tag) {
       constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll 1
@@ -360,22 +366,23 @@ __global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
             part[u] += p;
           }
         }
-        colsum += (part[0] + part[1]) + (part[2] + part[3]);
+        const float cs = (part[0] + part[1]) + (part[2] + part[3]);
+        if (c == 0) colsum0 = cs; else colsum1 = cs;
       }
     };
     if (edge) tile(std::true_type{}); else tile(std::false_type{});
-    if (wg == 0) prev = colsum; else sCs[b * 128 + row] = colsum;
+    if (wg == 0) {
+      prev0 = colsum0;
+      prev1 = colsum1;
+    } else {
+      sCs[b * 128 + row] = make_float2(colsum0, colsum1);
+    }
     if (wg == 1 && it + 1 < nib) sL[128 * (b ^ 1) + row] = lse_next;
     tc_fence_before();
     __syncthreads();
   }
   if (wg == 0 && live) {
-    if (nib > 0) {
-      const int rb = (nqb - 1) * 2;
-      if (rb < ncb) carry[((int64_t)n * ncb + rb) * g.tk + ja] = base + local;
-      if (rb + 1 < ncb) carry[((int64_t)n * ncb + rb + 1) * g.tk + ja] = base + local + prev;
-      local += prev + sCs[((nib - 1) & 1) * 128 + row];
-    }
+    if (nib > 0) store_checkpoints(nqb - 1, sCs[((nib - 1) & 1) * 128 + row]);
     total[(int64_t)n * g.tk + ja] = local;
   }
   tc_fence_before();
@@ -462,8 +469,8 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   }
   __syncwarp();
 
-  // the checkpoint row this warpgroup starts from: rows 2*ib (queries 0-63) and 2*ib+1 (64-127)
-  const int rb = 2 * ib + wg;
+  // the checkpoint row this warpgroup starts from: rows 4*ib (queries 0-63) and 4*ib+2 (64-127)
+  const int rb = 4 * ib + 2 * wg;
   const bool have_rows = rb < ncb;                 // false only for a ragged last half block
   const int64_t carry_row = ((int64_t)n * ncb + (have_rows ? rb : 0)) * g.tk;
   const float4* L4 = reinterpret_cast<const float4*>(sL + 64 * wg);
@@ -619,15 +626,18 @@ __global__ void backward_prep_kernel(const float* __restrict__ dout, const float
 // bf16 A operand (32).
 // The CTA keeps K (shared memory) and V (TMEM) of 128 keys and walks the queries from
 // last to first in half-steps of 64: S^T = K Q^T and (dO' V^T)^T = V dO'^T are
-// [128 keys x 64 queries], lane = key.  Two threads share a key and split the 64 queries
-// of a half-step at the only places where the key's demand is stored, the 64-row
-// checkpoints:
-//   warpgroup 0 walks queries 63..32 backwards from the checkpoint behind the half-step,
-//     subtracting p, with the exact suffix sum of dk_share (kernels.py:763-764);
-//   warpgroup 1 walks queries 0..31 forwards from the checkpoint in front of it, adding p,
-//     with the prefix sum of dk_share of its own queries.  dp is linear in the suffix, so
-//     it keeps p and pdp = p * dp in registers, and after one barrier of the compute
-//     warps adds p * (suffix behind the half-step - both warpgroups' sums).
+// [128 keys x 64 queries], lane = key.  Two threads share a key and take 32 queries of a
+// half-step each; the key's demand is stored every 32 query rows, so each starts from a
+// stored checkpoint.  Each thread sweeps its 32 queries twice:
+//   forwards for p and 1/(committed + p + eps), the demand accumulated from the checkpoint
+//     exactly as the forward pass did (walking it backwards by subtraction cancels
+//     catastrophically once attention is peaked);
+//   backwards for the suffix sum of dk_share (kernels.py:763-764), in the reference's order:
+//     its terms grow towards a key's first bidders, so a forward prefix would lose the small
+//     ones.  Warpgroup 0 (queries 63..32) starts from the suffix behind the half-step;
+//     warpgroup 1 (31..0) starts from zero, keeps p and pdp = p * dp in registers, and after
+//     one barrier of the compute warps adds p * (the suffix warpgroup 0 ended with): dp is
+//     linear in the suffix.
 // Per half-step each thread writes 32 shares and 32 pdp values as bf16 pairs over TMEM
 // columns it has already read: lane = key is the M index, so they are the A operands of
 // dV += share^T dO' and dK += pdp^T Q without passing through shared memory.  pdp also goes
@@ -665,7 +675,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 5 * kTileBytes;        // [3] each
   const uint32_t sPd = sK + 8 * kTileBytes;                                    // 32 KB
   const uint32_t sDq = sK + 10 * kTileBytes;                                   // 32 KB: fp32 dQ staging
-  float2* sStat = reinterpret_cast<float2*>(smem + 12 * kTileBytes);           // [2][128] (lse, dbar')
+  float* sLse = reinterpret_cast<float*>(smem + 12 * kTileBytes);              // [2][128] log-sum-exp of a step's queries
+  float* sDbar = sLse + 256;                                                   // [2][128] their dbar'
   float* sG = reinterpret_cast<float*>(smem + 12 * kTileBytes + 2048);         // [2][2][128] sums of dk_share
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 12 * kTileBytes + 4096);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 12);
@@ -702,7 +713,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
-  if (wg == 0) sStat[row] = load_stats(nqb - 1);
+  if (wg == 0) {
+    const float2 st = load_stats(nqb - 1);
+    sLse[row] = st.x;
+    sDbar[row] = st.y;
+  }
   else if (wg == 1) {
 #pragma unroll
     for (int c = 0; c < 8; ++c)
@@ -887,11 +902,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
     asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     // ------------------------------------------------------------ the compute warps
     const int cw = 32 * (1 - wg);                    // this warpgroup's columns of a stage
-    // demand of this thread's key where its walk starts: warpgroup 0 behind the half-step
-    // (inclusive of its last query), warpgroup 1 in front of it (exclusive of its first)
+    // demand of this thread's key in front of its 32 queries of half-step h (exclusive of the
+    // first): the stored checkpoint of that 32-row block (past the end: any value, p is 0 there)
     auto load_edge = [&](int h) {
       if (dead) return 0.f;
-      const int rb = 2 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 1) + (wg == 0 ? 1 : 0);
+      const int rb = 4 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 2) + (wg == 0 ? 1 : 0);
       return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
     };
     float sigma = 0.f;                               // suffix of dk_share behind the half-step
@@ -923,78 +938,68 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       const int qc = (odd ? 0 : 64) + cw;             // first query column of this thread in the step's tile
       const int iq0 = ib * kTileRows + qc;            // its position (q_off == 0 here)
       const bool masked_tile = dead || (ib * kTileRows + (odd ? 0 : 64) < k0 + kTileRows - 1);
-      const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128);
+      const float4* Lse4 = reinterpret_cast<const float4*>(sLse + b * 128 + qc);
+      const float4* Dbar4 = reinterpret_cast<const float4*>(sDbar + b * 128 + qc);
       uint32_t shp[16];                                // 32 shares as bf16 pairs
-      float R = wg == 0 ? sigma : 0.f;                 // warpgroup 0: suffix; warpgroup 1: its own prefix
+      // warpgroup 0 (queries 32..63) knows the suffix of dk_share behind its queries; warpgroup 1
+      // starts from zero and adds p * (the suffix warpgroup 0 ends with) afterwards: dp is linear in it
+      float R = wg == 0 ? sigma : 0.f;
       float incle = incl + g.eps;                      // demand + eps at the walk's position
 
-      // afterwards vs holds p and vd holds p * dp (warpgroup 1: without the suffix behind it)
-      auto chunk = [&](auto fwd_tag, auto mask_tag) {
-        constexpr bool FWD = decltype(fwd_tag)::value;
+      // Two sweeps over the thread's 32 queries.  Forwards: p and 1/(committed+p+eps), the demand
+      // accumulated from the checkpoint in front exactly as the forward pass did.  Backwards: the
+      // suffix of dk_share (kernels.py:763-764), accumulated from the last query to the first as
+      // the reference does — its terms grow towards a key's first bidders, so the other order
+      // loses the small ones.  Afterwards vs holds p and vd holds p * dp.
+      auto chunk = [&](auto mask_tag) {
         constexpr bool MASK = decltype(mask_tag)::value;
+        float inv[32];
 #pragma unroll
-        for (int k8 = 0; k8 < 4; ++k8) {
-          const int e8 = FWD ? k8 : 3 - k8;
-          float4 stt[4];                               // (lse, dbar') of eight queries
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = Lse4[e4];
+          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-          for (int u2 = 0; u2 < 4; ++u2) stt[u2] = St4[(qc + e8 * 8) / 2 + u2];
-          float sh[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int u = FWD ? k : 7 - k, e = e8 * 8 + u;
-            const float lse = (u & 1) ? stt[u >> 1].z : stt[u >> 1].x;
-            const float dbr = (u & 1) ? stt[u >> 1].w : stt[u >> 1].y;
-            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse));
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 * 4 + u;
+            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[u]));
             if (MASK) {
               if (dead || ja > iq0 + e) p = 0.f;
             }
+            incle += p;
+            inv[e] = fast_rcp(incle);
+            vs[e] = p;
+          }
+        }
+#pragma unroll
+        for (int e4 = 7; e4 >= 0; --e4) {
+          const float4 d4 = Dbar4[e4];
+          const float dbr[4] = {d4.x, d4.y, d4.z, d4.w};
+          float sh[4];
+#pragma unroll
+          for (int u = 3; u >= 0; --u) {
+            const int e = e4 * 4 + u;
             // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
             //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
             //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
-            float den;
-            if (FWD) {
-              incle += p;
-              den = incle;
-            } else {
-              den = MASK ? fmaxf(incle, g.eps) : incle;
-            }
-            const float inv = fast_rcp(den);
-            if (!FWD) incle -= p;
-            const float wv = (vd[e] - dbr) * inv;
-            const float share = p * inv;
-            float dp;
-            if (FWD) {
-              dp = wv + R;                             // minus the prefix: R holds -(sum of dk_share so far)
-              R = fmaf(wv, share, R);
-            } else {
-              R = fmaf(-wv, share, R);
-              dp = wv + R;
-            }
-            vd[e] = p * dp;
-            vs[e] = p;
+            const float wv = (vd[e] - dbr[u]) * inv[e];
+            const float share = vs[e] * inv[e];
+            R = fmaf(-wv, share, R);
+            vd[e] = vs[e] * (wv + R);
             sh[u] = share;
           }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) shp[e8 * 4 + u] = pack_bf16(sh[2 * u], sh[2 * u + 1]);
+          shp[e4 * 2] = pack_bf16(sh[0], sh[1]);
+          shp[e4 * 2 + 1] = pack_bf16(sh[2], sh[3]);
         }
       };
-      if (wg == 0) {
-        if (masked_tile) chunk(std::false_type{}, std::true_type{});
-        else chunk(std::false_type{}, std::false_type{});
-      } else {
-        if (masked_tile) chunk(std::true_type{}, std::true_type{});
-        else chunk(std::true_type{}, std::false_type{});
-      }
-      // sum of -dk_share over this thread's 32 queries
-      const float gsum = wg == 0 ? sigma - R : R;
-      sG[(odd * 2 + wg) * 128 + row] = gsum;
+      if (masked_tile) chunk(std::true_type{}); else chunk(std::false_type{});
+      // warpgroup 0: the suffix behind query 32; warpgroup 1: minus its own sum of -dk_share
+      sG[(odd * 2 + wg) * 128 + row] = R;
       // the shares stay in TMEM, over score columns this thread has consumed
       tmem_st16(tS0 + tcol, shp);
       asm volatile("bar.sync 1, 256;" ::: "memory");   // the compute warps
-      const float gother = sG[(odd * 2 + (1 - wg)) * 128 + row];
-      // FWD walked with dp = w - prefix; the true value is w + sigma - G0 - (G1 - prefix)
-      const float fix = wg == 1 ? sigma - gother - gsum : 0.f;
-      sigma -= gsum + gother;
+      const float rother = sG[(odd * 2 + (1 - wg)) * 128 + row];
+      const float fix = wg == 1 ? rother : 0.f;
+      sigma = R + rother;                              // the suffix behind the next half-step
       // the dQ MMAs of the previous 128 queries read the pdp buffer that is written next
       if (!odd && s >= 1) {
         mbar_wait(dqdone, (s - 1) & 1, ctl, &g_status, kErrWaitMma);
@@ -1016,7 +1021,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
         // TMEM, over consumed dOV^T columns: the A operand of dK (M = keys)
         tmem_st16(tDOV0 + tcol, pdt);
       }
-      if (fetch_stats) sStat[(b ^ 1) * 128 + row] = make_float2(st_max + log2f(st_den), st_dbar);
+      if (fetch_stats) {
+        sLse[(b ^ 1) * 128 + row] = st_max + log2f(st_den);
+        sDbar[(b ^ 1) * 128 + row] = st_dbar;
+      }
       incl = incl_next;
       incl_next = incl_next2;
       tmem_st_wait();

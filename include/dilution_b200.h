@@ -40,7 +40,7 @@ extern "C" {
 #endif
 
 #define DILUTION_ABI_VERSION 1
-#define DILUTION_CARRY_ROWS 64      /* query rows per carry checkpoint (aux["bwd_block_m"]) */
+#define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint (aux["bwd_block_m"]) */
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
 enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */

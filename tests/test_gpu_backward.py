@@ -176,3 +176,20 @@ def test_bf16_tensor_path_backward_ragged_lengths(kernels, seq):
     for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
         assert torch.isfinite(t.grad).all(), name
         assert (t.grad.float().cpu() - gr).abs().max().item() < 2e-2, name
+
+
+@pytest.mark.parametrize("scale", [2.0, 4.0, 8.0])
+def test_bf16_backward_peaked_attention(kernels, scale):
+    """Scores with a standard deviation of 4, 16 and 64: softmax rows close to one-hot, keys whose
+    first bids are tiny.  The demand must be accumulated forwards from its checkpoints and the
+    suffix of dk_share backwards; either sum taken in the other direction loses these cases."""
+    q, k, v, dout = make_inputs(1, 2, 1024, 64, 5, scales=(scale, scale, 1.0, 1e-1))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref = O.dilution_backward(qb.float(), kb.float(), vb.float(), dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+    out.backward(dout.to(DEV))
+    assert rel_err(out.detach().cpu(), ref[0]) < 1e-2
+    for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):
+        assert torch.isfinite(t.grad).all(), name
+        assert rel_err(t.grad.float().cpu(), gr) < 3e-2, name
