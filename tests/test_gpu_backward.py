@@ -120,9 +120,11 @@ def test_host_buffer_entry_point_matches_device_op(kernels):
     ref = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
     ref.backward(dout.to(DEV))
     assert torch.equal(out, ref.detach().cpu())
-    assert torch.equal(dv, vs.grad.cpu()) and torch.equal(dk, ks.grad.cpu())
-    # dq is accumulated with floating-point reductions whose order varies between runs
+    assert torch.equal(dv, vs.grad.cpu())
+    # dq and ghat (hence dk) are accumulated across key blocks with floating-point reductions
+    # whose order varies between runs
     assert rel_err(dq.float(), qs.grad.float().cpu()) < 2e-2
+    assert rel_err(dk.float(), ks.grad.float().cpu()) < 2e-3
     fwd_only = kernels.dilution_attention_host(qb, kb, vb, dot_precision="bf16", slabs=3)
     torch.cuda.synchronize()
     assert torch.equal(fwd_only, out)

@@ -37,9 +37,11 @@ def test_side_stream_matches_default_stream(kernels):
         got = _run(kernels, q, k, v, dout)
     side.synchronize()
     assert torch.equal(got[0], ref[0])
-    assert torch.equal(got[2], ref[2]) and torch.equal(got[3], ref[3])
-    # dq is accumulated with floating-point reductions whose order varies between runs
+    assert torch.equal(got[3], ref[3])
+    # dq and ghat (hence dk) are accumulated across key blocks with floating-point reductions
+    # whose order varies between runs: equal up to the last bits, not bitwise
     assert rel_err(got[1].float().cpu(), ref[1].float().cpu()) < 2e-2
+    assert rel_err(got[2].float().cpu(), ref[2].float().cpu()) < 2e-3
 
 
 def test_partial_gradients_and_strided_upstream_gradient(kernels):
