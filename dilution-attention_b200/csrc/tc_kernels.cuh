@@ -958,10 +958,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
         for (int e4 = 0; e4 < 8; ++e4) {
           const float4 l4 = Lse4[e4];
           const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float2 zs = make_float2(g.zscale, g.zscale);
+          const float2 z01 = fma2(make_float2(vs[e4 * 4], vs[e4 * 4 + 1]), zs, make_float2(-lse[0], -lse[1]));
+          const float2 z23 = fma2(make_float2(vs[e4 * 4 + 2], vs[e4 * 4 + 3]), zs, make_float2(-lse[2], -lse[3]));
+          const float z[4] = {z01.x, z01.y, z23.x, z23.y};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e4 * 4 + u;
-            float p = fast_exp2(fmaf(vs[e], g.zscale, -lse[u]));
+            float p = fast_exp2(z[u]);
             if (MASK) {
               if (dead || ja > iq0 + e) p = 0.f;
             }
@@ -974,21 +978,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
         for (int e4 = 7; e4 >= 0; --e4) {
           const float4 d4 = Dbar4[e4];
           const float dbr[4] = {d4.x, d4.y, d4.z, d4.w};
-          float sh[4];
+          // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
+          //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
+          //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
+          // (element-wise parts two queries per instruction; the suffix itself is serial)
 #pragma unroll
-          for (int u = 3; u >= 0; --u) {
-            const int e = e4 * 4 + u;
-            // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
-            //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
-            //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
-            const float wv = (vd[e] - dbr[u]) * inv[e];
-            const float share = vs[e] * inv[e];
-            R = fmaf(-wv, share, R);
-            vd[e] = vs[e] * (wv + R);
-            sh[u] = share;
+          for (int h = 1; h >= 0; --h) {
+            const int e = e4 * 4 + 2 * h;
+            const float2 p2 = make_float2(vs[e], vs[e + 1]), i2 = make_float2(inv[e], inv[e + 1]);
+            const float2 w2 = mul2(sub2(make_float2(vd[e], vd[e + 1]), make_float2(dbr[2 * h], dbr[2 * h + 1])), i2);
+            const float2 s2 = mul2(p2, i2);
+            const float r1 = fmaf(-w2.y, s2.y, R);
+            R = fmaf(-w2.x, s2.x, r1);
+            const float2 pd2 = mul2(p2, add2(w2, make_float2(R, r1)));
+            vd[e] = pd2.x;
+            vd[e + 1] = pd2.y;
+            shp[e4 * 2 + h] = pack_bf16(s2.x, s2.y);
           }
-          shp[e4 * 2] = pack_bf16(sh[0], sh[1]);
-          shp[e4 * 2 + 1] = pack_bf16(sh[2], sh[3]);
         }
       };
       if (masked_tile) chunk(std::true_type{}); else chunk(std::false_type{});
@@ -1011,7 +1017,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e8 * 8 + 2 * u;
-            pdt[e8 * 4 + u] = pack_bf16(fmaf(vs[e], fix, vd[e]), fmaf(vs[e + 1], fix, vd[e + 1]));
+            const float2 f2 = fma2(make_float2(vs[e], vs[e + 1]), make_float2(fix, fix), make_float2(vd[e], vd[e + 1]));
+            pdt[e8 * 4 + u] = pack_bf16(f2.x, f2.y);
           }
           // shared memory: the MN-major A operand of dQ | ghat (M = queries)
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qc + e8 * 8)),
