@@ -252,10 +252,25 @@ def run_ours(args, rank, world):
     if dom is not None:
         mm = next((m for key, m in share.items() if key in dom), 0)
         achieved = causal_flops(n_rows, T, D, mm) / (kernels_ms[dom] * 1e-3) / 1e12
+        # DRAM bytes per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel at
+        # T=4096 (64 rows, 528 causal 128x128 tiles per row: 1354.26 MB), scaled by the number of
+        # causal tiles this launch processes -- the dQ tile reductions dominate it and grow with
+        # the tile count.  Only the backward main pass has a captured figure.
+        tiles = n_rows * (T // 128) * (T // 128 + 1) // 2
+        traffic = 1354.26e6 / (64 * 528) * tiles if "backward_main" in dom else None
         roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
-                    "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
+                    "traffic_source": "ncu capture at T=4096 (profiles/train_kernels_T4096_ncu_full.md), "
+                                      "scaled by causal 128x128 tiles per launch; bytes",
                     "peak_source": f"{peaks['source']} sustained bf16", "matmuls_in_kernel": mm,
-                    "step_frac_of_peak": value / world / peaks["tensor"]}
+                    "step_frac_of_peak": value / world / peaks["tensor"],
+                    # matmul-equivalents the tensor cores actually run per step: QK^T in the row,
+                    # column-sum, main, reverse and correction passes (5), share@V, dO V^T, dV, dQ,
+                    # dK (5), and the two correction products W Q and W^T K (2); the ones columns
+                    # that give row sums and ghat (N = 80 instead of 64) are not counted
+                    "executed": {"matmuls_per_step": 12,
+                                 "value": value / world * 12 / 7, "unit": "TFLOP/s",
+                                 "frac": value / world * 12 / 7 / peaks["tensor"]}}
 
     e2e = None
     if not args.no_e2e:
@@ -370,7 +385,12 @@ def run_decode(K, L, dev, rank, world, peaks, barrier, distributed):
             "config": "batch 64 x 16 heads, d=64, bf16 KV, fp32 demand; heads sharded across GPUs; "
                       "demand initialised analytically (ln(L/j)), KV N(0,1) generated on device",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm"], "traffic": None,
+                         "frac": achieved / peaks["hbm"],
+                         # ncu capture at 64 rows x 128K keys: scores + sweep kernels read and wrote
+                         # 2.2319 GB of DRAM for 64 * 131074 keys = 266 B per key; bytes per step
+                         "traffic": 266.0 * rows * mean_len,
+                         "traffic_source": "ncu capture at 64 rows (profiles/decode_rows64_len131072_ncu_full.md), "
+                                           "scaled by keys per step; bytes",
                          "algorithmic_bytes_per_key": 2 * d * 2 + 8,
                          "peak_source": f"{peaks['source']} copy bandwidth"},
             "kernels_ms": {n: tot / cnt for n, (cnt, tot) in prof.items()}}
