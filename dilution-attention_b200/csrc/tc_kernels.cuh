@@ -1227,13 +1227,16 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
       // descriptors are built once per tile; a k-step is a constant 2048 B (128 units) further
       const Desc dQm = make_desc(sQ0 + kTileBytes * b, kTileBytes, 1024);
       const Desc dWm = make_desc(sW, kTileBytes, 1024), dKm = make_desc(sK, kTileBytes, 1024);
+      // dQc first: its tile is what the threads read out next, and only it reads the shared-
+      // memory W tile (the staging area of that read-out); dKc takes W from TMEM and runs,
+      // with the next scores, under the read-out
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) mma_ss(tDQ, dWm, 128 * kk, dKm, 128 * kk, id_qd, kk > 0);
+      mma_commit(dqdone);
 #pragma unroll
       for (int kq = 0; kq < 8; ++kq)
         mma_ts(tDK, tS + 64 * (kq >> 2) + 32 * ((kq & 3) >> 1) + 8 * (kq & 1), dQm, 128 * kq, id_kd,
                (t > 0 || kq > 0));
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) mma_ss(tDQ, dWm, 128 * kk, dKm, 128 * kk, id_qd, kk > 0);
-      mma_commit(dqdone);                                // both products have read the W tile
       if (t + 1 < nsteps) {
         mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
         tc_fence_after();
