@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant_
 // and stores one checkpoint per 32 query rows, one tile behind the sums.
 constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 2048 + 1024 + 256;
 
-__global__ void __launch_bounds__(256, 3) colsum_scan_kernel(
+__global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden,
     const float* __restrict__ carry_base, float* __restrict__ carry, float* __restrict__ total) {
