@@ -508,7 +508,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
     const bool dead = ja >= g.tk;
     auto tile = [&](auto mask_tag) {
     constexpr bool MASK = decltype(mask_tag)::value;
-#pragma unroll 1
+#pragma unroll
     for (int c = 0; c < 2; ++c) {
       float v[32];
       tmem_ld32(taddr + 32 * c, v);
@@ -1173,7 +1173,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
     const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
     auto tile = [&](auto mask_tag) {
     constexpr bool MASK = decltype(mask_tag)::value;
-#pragma unroll 1
+#pragma unroll
     for (int c = 0; c < 2; ++c) {
       float vs[32];
       uint32_t wt[16];                                 // this chunk's 32 W values as bf16 pairs
