@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant_
     // the mask arithmetic exists only in the instantiation used for edge tiles
     auto tile = [&](auto edge_tag) {
       constexpr bool EDGE = decltype(edge_tag)::value;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(taddr + 32 * c, v);
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     float colsum0 = 0.f, colsum1 = 0.f;      // queries 0-31 and 32-63 of this warpgroup's half
     auto tile = [&](auto edge_tag) {
       constexpr bool EDGE = decltype(edge_tag)::value;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(taddr + 32 * c, v);
