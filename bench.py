@@ -140,6 +140,9 @@ def run_reference(args, rank):
     """The reference's CPU path (oracle port of kernels.py:40-68) on the host cores."""
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to every rank; the other ranks exit without work, so
+    # rank 0 takes all the host's cores, as it does when launched without torchrun
+    torch.set_num_threads(os.cpu_count() or 1)
     t = 8192
     for _ in range(args.warmup):
         cpu_sample(t, 1)
