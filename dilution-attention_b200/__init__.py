@@ -21,13 +21,16 @@ from .kernels import (  # noqa: F401
     dilution_attention_forward,
     dilution_attention_host,
     dilution_attention_reference,
+    dilution_decode_append_step,
     dilution_decode_step,
     install,
+    uninstall,
 )
 
 _sys.modules.setdefault("dilution_attention_b200", _sys.modules[__name__])
 
 __all__ = [
     "kernels", "partition", "dilution_attention", "dilution_attention_forward",
-    "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step", "install",
+    "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step",
+    "dilution_decode_append_step", "install", "uninstall",
 ]

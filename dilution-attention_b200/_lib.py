@@ -32,9 +32,10 @@ SIGNATURES = {
                                    _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_backward_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F,
-                               _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+                               _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_decode_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_decode": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
+    "dilution_decode_append": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
     "dilution_decode_static": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P]),
 }
 

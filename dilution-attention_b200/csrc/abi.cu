@@ -272,7 +272,8 @@ dil::decode::Scratch carve_decode(void* scratch, int64_t n, int64_t len, int d) 
 template <typename T, int D>
 int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
-                  cudaStream_t st, bool timing = true) {
+                  cudaStream_t st, bool timing = true, const void* knew = nullptr,
+                  const void* vnew = nullptr) {
   using namespace dil::decode;
   const int chunk = decode_chunk(n, len);
   const int nch = (int)((len + chunk - 1) / chunk);
@@ -282,13 +283,15 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
   {
     Prof prof("decode_scores", st, timing);
     scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
-                                             scale * dil::kLog2e, stride, s.aff, s.part);
+                                             scale * dil::kLog2e, stride, s.aff, s.part,
+                                             (const T*)knew, (T*)const_cast<void*>(kc));
   }
   if (int rc = check_launch("decode scores")) return rc;
   {
     Prof prof("decode_sweep", st, timing);
     sweep_kernel<T, D><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
-                                            committed, s.pout, s.psum);
+                                            committed, s.pout, s.psum, (const T*)vnew,
+                                            (T*)const_cast<void*>(vc));
   }
   if (int rc = check_launch("decode sweep")) return rc;
   {
@@ -306,6 +309,7 @@ constexpr int64_t kStaticMaxKeys = DILUTION_DECODE_STATIC_MAX_KEYS;
 constexpr size_t kStaticBytes =
     sizeof(float) * (size_t)kStaticMaxKeys +
     sizeof(float) * (size_t)kStaticMaxRows * dil::decode::MAX_CHUNKS * (2 + 128 + 1);
+static_assert(kStaticBytes == DILUTION_DECODE_STATIC_BYTES, "header and library disagree on the array size");
 static __device__ __align__(256) unsigned char g_decode_static[kStaticBytes];
 
 constexpr int kMaxDevices = 64;
@@ -466,26 +470,30 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d) {
 }
 
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
-                      int64_t n, int64_t t, int d, float scale, float eps, const float* dout,
-                      const float* out, const float* rmax, const float* rden, const float* carry,
+                      int64_t n, int64_t t, int d, float scale, float eps, const void* dout,
+                      int dout_dtype, const float* out, const float* rmax, const float* rden, const float* carry,
                       const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
                       void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_backward", dtype, precision, n, t, t, 0, d)) return rc;
   if (!q || !k || !v || !dout || !out || !rmax || !rden || !carry || !total || !ssum || !scratch ||
       !dq || !dk || !dv)
     return fail(DILUTION_ERR_ARG, "dilution_backward: null pointer");
+  if (dout_dtype != DILUTION_F32 && dout_dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_backward: dout_dtype must be DILUTION_F32 or DILUTION_BF16");
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
 #if DILUTION_TC_HAS_BACKWARD
   if (dil::tc::supported(dtype, precision, d, 0))
-    return dil::tc::backward(q, k, v, g, dout, out, rmax, rden, carry, total, ssum, s.dq_main, s.dk_main,
+    return dil::tc::backward(q, k, v, g, dout, dout_dtype, out, rmax, rden, carry, total, ssum, s.dq_main, s.dk_main,
                              s.ghat, s.dbar, s.dop, dq, dk, dv, st, g_err, sizeof(g_err), mark_scope);
 #endif
   if (!pk) return fail(DILUTION_ERR_ARG, "dilution_backward: the fp32 path needs pk from dilution_forward_main");
 #endif
-  DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, dout, out, rmax, rden, carry, ssum,
+  if (dout_dtype != DILUTION_F32)
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_backward: the fp32 path takes an fp32 dout");
+  DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, (const float*)dout, out, rmax, rden, carry, ssum,
                                                        pk, s, dq, dk, dv, st)))
   return DILUTION_OK;
 }
@@ -513,6 +521,28 @@ int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, in
   cudaStream_t st = (cudaStream_t)stream;
   DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
                                                      committed, out, scratch, st)))
+  return DILUTION_OK;
+}
+
+int dilution_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                           int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
+                           float eps, float* committed, void* out, void* scratch, void* stream) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_append: dtype must be DILUTION_F32 or DILUTION_BF16");
+  if (!valid_d(d))
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_decode_append: head_dim %d not in {16, 32, 64, 128}", d);
+  if (n < 1 || n > 65535)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_append: n must be in [1, 65535] rows per call");
+  if (capacity < 1 || length < 1 || length > capacity || capacity > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "dilution_decode_append: decode step past the cache capacity "
+                "(length %lld, capacity %lld)", (long long)length, (long long)capacity);
+  if (!q1 || !k1 || !v1 || !k_cache || !v_cache || !committed || !out || !scratch)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_append: null pointer");
+  if (((uintptr_t)q1 | (uintptr_t)k1 | (uintptr_t)v1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+    return fail(DILUTION_ERR_ARG, "dilution_decode_append: q1 / k1 / v1 / caches must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
+                                                     committed, out, scratch, st, true, k1, v1)))
   return DILUTION_OK;
 }
 

@@ -7,6 +7,9 @@
 //   sweep_kernel   : combine the chunk statistics, p_j, share_j = p/(c+p+eps),
 //                    c_j += p_j in place, stream V once, partial share@V;
 //   finalize_kernel: out = sum(partials) / (sum(share) + eps).
+// Optionally the step also appends the new token (the model's _append_kv,
+// model.py:85-93): given its k and v rows, the CTA that owns position len-1 takes
+// them from there and writes them into the caches on the way.
 // A warp reads cache rows 16 bytes per lane, so one load instruction covers
 // 32/TPK whole rows (TPK = lanes per row) and every 128-byte line is consumed
 // by the instruction that fetched it.
@@ -66,7 +69,8 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
                                                     const T* __restrict__ kc, int64_t cap,
                                                     int len, int chunk, float zscale,
                                                     int64_t stride, float* __restrict__ aff,
-                                                    float2* __restrict__ part) {
+                                                    float2* __restrict__ part,
+                                                    const T* __restrict__ knew, T* __restrict__ kc_out) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   const int64_t n = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -80,6 +84,7 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   }
   const int k0 = blockIdx.x * chunk, k1 = min(len, k0 + chunk);
   const T* krow = kc + n * cap * D + t * E;
+  const int fresh = knew != nullptr ? len - 1 : -1;   // position whose row comes from knew
   float m = -INFINITY, s = 0.f;
   for (int base = k0 + warp * 32; base < k1; base += ROUND) {
     float mine = -INFINITY;
@@ -87,7 +92,11 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
       const int key = base + grp * TPK + u;
-      raw[u] = key < k1 ? ld_stream(krow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
+      raw[u] = (key < k1 && key != fresh) ? ld_stream(krow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
+      if (key == fresh) {
+        raw[u] = *reinterpret_cast<const uint4*>(knew + n * D + t * E);
+        *reinterpret_cast<uint4*>(kc_out + n * cap * D + (int64_t)key * D + t * E) = raw[u];
+      }
     }
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
@@ -131,7 +140,8 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
                                                    const float2* __restrict__ part,
                                                    float* __restrict__ committed,
                                                    float* __restrict__ pout,
-                                                   float* __restrict__ psum) {
+                                                   float* __restrict__ psum,
+                                                   const T* __restrict__ vnew, T* __restrict__ vc_out) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   const int64_t n = blockIdx.y;
   const int nch = gridDim.x;
@@ -167,6 +177,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
 
   const int k0 = blockIdx.x * chunk, k1 = min(len, k0 + chunk);
   const T* vrow = vc + n * cap * D + t * E;
+  const int fresh = vnew != nullptr ? len - 1 : -1;
   float acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
@@ -176,13 +187,17 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
       const int key = base + grp * TPK + u;
-      raw[u] = key < k1 ? ld_stream(vrow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
+      raw[u] = (key < k1 && key != fresh) ? ld_stream(vrow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
+      if (key == fresh) {
+        raw[u] = *reinterpret_cast<const uint4*>(vnew + n * D + t * E);
+        *reinterpret_cast<uint4*>(vc_out + n * cap * D + (int64_t)key * D + t * E) = raw[u];
+      }
     }
     const int key = base + lane;
     float share = 0.f;
     if (key < k1) {
       const float a = aff[n * stride + key];
-      const float c = committed[n * cap + key];
+      const float c = key == fresh ? 0.f : committed[n * cap + key];   // a fresh key has no demand yet
       const float p = exp2f(a - gmax) * rinv;
       share = p / (c + p + eps);
       committed[n * cap + key] = c + p;

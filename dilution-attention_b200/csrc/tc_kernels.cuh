@@ -11,11 +11,13 @@
 //                                          per-query statistics it needs are
 //                                          warp-uniform and come from shared
 //                                          memory as broadcasts.
-// All kernels: 128 threads (warp w owns TMEM lanes 32w..32w+31), thread 0 issues
-// TMA and MMA, two CTAs per SM overlap one CTA's MMA/TMA latency with the
-// other's arithmetic.
+// Warp w of a CTA reads TMEM lanes 32*(w%4)..32*(w%4)+31.  The forward passes and the
+// correction pass run 256 threads (two warpgroups that split a tile's columns), thread 0
+// issuing TMA and MMA, two to four CTAs per SM hiding each other's MMA/TMA latency; the
+// main reverse pass runs 384 threads, one CTA per SM, with a dedicated issuing warpgroup.
 #pragma once
 
+#include <mutex>
 #include <type_traits>
 
 #include "tc_common.cuh"
@@ -58,10 +60,47 @@ inline void ensure_context() {
   }
 }
 
+// Encoded maps are kept: a map depends only on (base, n, t, element type, box), and the same
+// tensors come back on every step of a training loop or every pass of a forward.
+struct MapKey {
+  const void* base;
+  int64_t n, t;
+  int kind;      // 0: bf16 box {64, rows, 1}; 1: fp32 box {32, 128, 1}
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && n == o.n && t == o.t && kind == o.kind && box_rows == o.box_rows;
+  }
+};
+struct MapCache {
+  static constexpr int kSlots = 64;
+  std::mutex mu;
+  MapKey keys[kSlots];
+  CUtensorMap maps[kSlots];
+  int used = 0, next = 0;
+  bool find(const MapKey& k, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) { *out = maps[i]; return true; }
+    return false;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    std::lock_guard<std::mutex> lk(mu);
+    const int i = used < kSlots ? used++ : (next = (next + 1) % kSlots);
+    keys[i] = k;
+    maps[i] = m;
+  }
+};
+inline MapCache& map_cache() {
+  static MapCache c;
+  return c;
+}
+
 // (n, t, 64) bf16 row-major -> 3-D map {64, t, n}, box {64, 128, 1}, 128-byte swizzle.
 // Rows past t read as zero, and a box never crosses into the next (batch, head) row.
 inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen,
                     int box_rows = kTileRows) {
+  const MapKey key{base, n, t, 0, box_rows};
+  if (map_cache().find(key, map)) return 0;
   ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
@@ -83,12 +122,15 @@ inline int make_map(CUtensorMap* map, const void* base, int64_t n, int64_t t, ch
     snprintf(err, errlen, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     return 3;
   }
+  map_cache().put(key, *map);
   return 0;
 }
 
 // (n, t, 64) fp32 row-major -> 3-D map {64, t, n}, box {32, 128, 1} (128 bytes wide),
 // 128-byte swizzle: the target of the dQ tile reductions.
 inline int make_map_f32(CUtensorMap* map, const void* base, int64_t n, int64_t t, char* err, size_t errlen) {
+  const MapKey key{base, n, t, 1, kTileRows};
+  if (map_cache().find(key, map)) return 0;
   ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
@@ -106,6 +148,7 @@ inline int make_map_f32(CUtensorMap* map, const void* base, int64_t n, int64_t t
     snprintf(err, errlen, "cuTensorMapEncodeTiled (fp32) failed (%d)", (int)r);
     return 3;
   }
+  map_cache().put(key, *map);
   return 0;
 }
 
@@ -141,7 +184,7 @@ __device__ __forceinline__ float load_lse(const float* __restrict__ rmax, const 
 // halves of a row are merged once at the end.  TMEM: 128 columns; 4 CTAs per SM.
 constexpr int kRowstatsSmem = 3 * kTileBytes + 1024 + 1024 + 256;
 
-__global__ void __launch_bounds__(256, 3) rowstats_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant__ CUtensorMap map_q,
                                                           const __grid_constant__ CUtensorMap map_k,
                                                           Geom g, float* __restrict__ rmax,
                                                           float* __restrict__ rden) {
@@ -598,14 +641,21 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
 // do' = bf16(sinv * dout); zeroes the dq / ghat accumulators.  Folding sinv into dO
 // turns  ds = (do.v - dbar) * sinv  into  do'.v - dbar'  and  dv = attn^T do  into
 // share^T do', so the main pass never multiplies by sinv per element.
-__global__ void backward_prep_kernel(const float* __restrict__ dout, const float* __restrict__ out,
+template <typename TD>
+__global__ void backward_prep_kernel(const TD* __restrict__ dout, const float* __restrict__ out,
                                      const float* __restrict__ ssum, float eps, int64_t rows,
                                      float* __restrict__ dbarp, __nv_bfloat16* __restrict__ dop,
                                      float* __restrict__ ghat, float* __restrict__ dq_main) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
-  const float2 a = reinterpret_cast<const float2*>(dout + row * kHeadDim)[lane];
+  float2 a;
+  if (std::is_same<TD, float>::value) {
+    a = reinterpret_cast<const float2*>(dout + row * kHeadDim)[lane];
+  } else {
+    const uint32_t raw = reinterpret_cast<const uint32_t*>(dout + row * kHeadDim)[lane];
+    a = make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
+  }
   const float2 b = reinterpret_cast<const float2*>(out + row * kHeadDim)[lane];
   const float sinv = 1.f / (ssum[row] + eps);
   const float dot = warp_sum(a.x * b.x + a.y * b.y);
@@ -1312,11 +1362,32 @@ __global__ void cast_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __r
 #define DILUTION_TC_HAS_MAIN 1
 #define DILUTION_TC_HAS_BACKWARD 1
 
+// The opt-in to more than 48 KB of dynamic shared memory is per kernel and per device: it is
+// made on the first launch of that kernel on that device and remembered.
 inline int set_smem_attr(const void* fn, int bytes, char* err, size_t errlen) {
+  constexpr int kKernels = 16, kDevices = 64;
+  static std::mutex mu;
+  static const void* fns[kKernels];
+  static bool done[kKernels][kDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kDevices) dev = -1;
+  int slot = -1;
+  if (dev >= 0) {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < kKernels && slot < 0; ++i) {
+      if (fns[i] == fn) slot = i;
+      else if (fns[i] == nullptr) { fns[i] = fn; slot = i; }
+    }
+    if (slot >= 0 && done[slot][dev]) return 0;
+  }
   const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   if (e != cudaSuccess) {
     snprintf(err, errlen, "cudaFuncSetAttribute(%d): %s", bytes, cudaGetErrorString(e));
     return 3;
+  }
+  if (slot >= 0) {
+    std::lock_guard<std::mutex> lk(mu);
+    done[slot][dev] = true;
   }
   return 0;
 }
@@ -1379,8 +1450,8 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
 }
 
 // dop: (n, t, 64) bf16 scratch for the pre-scaled dout.
-inline int backward(const void* q, const void* k, const void* v, const Geom& g, const float* dout,
-                    const float* out, const float* rmax, const float* rden, const float* carry,
+inline int backward(const void* q, const void* k, const void* v, const Geom& g, const void* dout,
+                    int dout_dtype, const float* out, const float* rmax, const float* rden, const float* carry,
                     const float* total, const float* ssum, float* dq_main, float* dk_main, float* ghat,
                     float* dbarp, void* dop, void* dq, void* dk, void* dv, cudaStream_t st, char* err,
                     size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
@@ -1392,8 +1463,12 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   const int64_t rows = g.n * g.tq;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
   mark("tc_backward_prep", st, 0);
-  backward_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dout, out, ssum, g.eps, rows, dbarp,
-                                                                  (__nv_bfloat16*)dop, ghat, dq_main);
+  if (dout_dtype == 0)
+    backward_prep_kernel<float><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+        (const float*)dout, out, ssum, g.eps, rows, dbarp, (__nv_bfloat16*)dop, ghat, dq_main);
+  else
+    backward_prep_kernel<__nv_bfloat16><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+        (const __nv_bfloat16*)dout, out, ssum, g.eps, rows, dbarp, (__nv_bfloat16*)dop, ghat, dq_main);
   mark("tc_backward_prep", st, 1);
   if (int rc = launch_status("tc backward_prep", err, errlen)) return rc;
   constexpr int smem_bwd = kBwdSmem;
@@ -1446,6 +1521,8 @@ inline int selftest_wait(int* gave_up_dev, cudaStream_t st, char* err, size_t er
 // Reads (and clears) the device status word; synchronises the device.
 inline int read_status(int* out) {
   int v = 0;
+  // kernels on non-blocking streams are not ordered before a copy on the default stream
+  if (cudaDeviceSynchronize() != cudaSuccess) return 3;
   if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return 3;
   if (v != 0) {
     const int zero = 0;

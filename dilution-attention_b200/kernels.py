@@ -9,6 +9,7 @@ libdilution_b200.so instead of Triton:
                                return_aux=..., _save_pk=...)
     dilution_attention(q, k, v, dot_precision=...)             kernels.py:906-930
     dilution_decode_step(q1, k_cache, v_cache, committed, t)   kernels.py:994-1038
+    dilution_decode_append_step(q1, k1, v1, cache)             model.py:85-93 + :236-239
 
 The operator (docs/operator.md of the reference):
 
@@ -186,7 +187,14 @@ class _DilutionAttentionFn(torch.autograd.Function):
         batch, heads, seq, head_dim = q.shape
         (qf, kf, vf), code, prec, n = _prepare(q, k, v, ctx.dot_precision)
         dev = q.device
-        dof = dout.reshape(n, seq, head_dim).float().contiguous()
+        # the tensor-core path reads a bf16 upstream gradient as it is (its first kernel makes a
+        # scaled bf16 copy anyway); everything else is widened to fp32 as the reference does
+        on_tc = _lib.tensor_core_path(code, prec, head_dim)
+        dof = dout.reshape(n, seq, head_dim)
+        if not (on_tc and dof.dtype == torch.bfloat16):
+            dof = dof.float()
+        dof = dof.contiguous()
+        do_code = _lib.BF16 if dof.dtype == torch.bfloat16 else _lib.F32
         of = out.reshape(n, seq, head_dim)
         gdt = qf.dtype
         dq = torch.empty(n, seq, head_dim, device=dev, dtype=gdt)
@@ -196,7 +204,7 @@ class _DilutionAttentionFn(torch.autograd.Function):
         scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
         _lib.check(lib.dilution_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim,
-            1.0 / math.sqrt(head_dim), EPS, dof.data_ptr(), of.data_ptr(),
+            1.0 / math.sqrt(head_dim), EPS, dof.data_ptr(), do_code, of.data_ptr(),
             rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), total.data_ptr(), ssum.data_ptr(),
             _ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _stream(dev)),
             "dilution_backward")
@@ -245,25 +253,8 @@ def decode_scratch(n: int, capacity: int, head_dim: int, device) -> torch.Tensor
     return torch.empty(nbytes, device=device, dtype=torch.uint8)
 
 
-def dilution_decode_step(
-    q1: torch.Tensor,
-    k_cache: torch.Tensor,
-    v_cache: torch.Tensor,
-    committed: torch.Tensor,
-    length: int,
-    block_n: int = 512,
-    num_warps: int = 8,
-    scratch: torch.Tensor | None = None,
-) -> torch.Tensor:
-    """Fused decode step (kernels.py:994-1038).  Returns (B, H, 1, D) in q1.dtype.
-
-    q1: (B, H, 1, D).  k_cache / v_cache: contiguous (B, H, capacity, D) buffers
-    whose first `length` positions are valid, the new token already written at
-    length-1.  committed: contiguous (B, H, capacity) fp32 accumulator, advanced
-    IN PLACE to include this row; positions >= length are never touched.
-    `scratch` (optional, from decode_scratch) avoids a per-call allocation.
-    """
-    lib = _lib.load()
+def _decode_args(q1, k_cache, v_cache, committed, length):
+    """Validation shared by the decode entry points (kernels.py:1012-1021)."""
     batch, heads, one, head_dim = q1.shape
     if one != 1:
         raise ValueError("decode step takes exactly one query row per (batch, head)")
@@ -278,14 +269,43 @@ def dilution_decode_step(
         raise ValueError("decode supports float32 and bfloat16 caches")
     if k_cache.dtype != q1.dtype or v_cache.dtype != q1.dtype or committed.dtype != torch.float32:
         raise ValueError("caches must have q1's dtype and committed must be float32")
+    return batch, heads, head_dim, capacity
+
+
+def _rows(x, n, head_dim):
+    x = x.reshape(n, head_dim)
+    return x if x.is_contiguous() else x.contiguous()
+
+
+def dilution_decode_step(
+    q1: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    committed: torch.Tensor,
+    length: int,
+    block_n: int = 512,
+    num_warps: int = 8,
+    scratch: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Fused decode step (kernels.py:994-1038).  Returns (B, H, 1, D) in q1.dtype.
+
+    q1: (B, H, 1, D).  k_cache / v_cache: contiguous (B, H, capacity, D) buffers
+    whose first `length` positions are valid, the new token already written at
+    length-1.  committed: contiguous (B, H, capacity) fp32 accumulator, advanced
+    IN PLACE to include this row; positions >= length are never touched.
+    `scratch` (from decode_scratch) and `out` ((B*H, D) in q1.dtype) are optional
+    caller buffers that keep allocation out of the token loop.
+    """
+    lib = _lib.load()
+    batch, heads, head_dim, capacity = _decode_args(q1, k_cache, v_cache, committed, length)
     n = batch * heads
-    qf = q1.reshape(n, head_dim)
-    if not qf.is_contiguous():
-        qf = qf.contiguous()
+    qf = _rows(q1, n, head_dim)
     kf = k_cache.view(n, capacity, head_dim)      # .view: the caches must be contiguous
     vf = v_cache.view(n, capacity, head_dim)
     cf = committed.view(n, capacity)
-    out = torch.empty(n, head_dim, device=q1.device, dtype=q1.dtype)
+    if out is None:
+        out = torch.empty(n, head_dim, device=q1.device, dtype=q1.dtype)
     need = lib.dilution_decode_scratch_bytes(n, length, head_dim)
     if scratch is None or scratch.numel() * scratch.element_size() < need:
         scratch = torch.empty(need, device=q1.device, dtype=torch.uint8)
@@ -297,8 +317,54 @@ def dilution_decode_step(
     return out.view(batch, heads, 1, head_dim)
 
 
+def dilution_decode_append_step(
+    q1: torch.Tensor,
+    k1: torch.Tensor,
+    v1: torch.Tensor,
+    cache: dict,
+    scratch: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """One cached token with the append fused in: what the model does as
+    `_append_kv(cache, k1, v1)` (model.py:85-93) followed by
+    `dilution_decode_step(q1, cache["k"], cache["v"], cache["committed"], t)`
+    (model.py:236-239), as three kernel launches and no separate copy.
+
+    q1, k1, v1: (B, H, 1, D) of the new token.  cache: the model's dict
+    {"k", "v", "len", "committed"} (model.py:76-83, 224-228); its k / v rows at
+    position len are written by the kernels, committed is advanced in place and
+    cache["len"] grows by one.  Raises ValueError past the capacity, as
+    _append_kv does.  Returns (B, H, 1, D) in q1.dtype.
+    """
+    lib = _lib.load()
+    t = cache["len"]
+    if t >= cache["k"].shape[2]:
+        raise ValueError("decode step past the cache capacity (context_length)")
+    k_cache, v_cache, committed = cache["k"], cache["v"], cache["committed"]
+    batch, heads, head_dim, capacity = _decode_args(q1, k_cache, v_cache, committed, t + 1)
+    if k1.dtype != q1.dtype or v1.dtype != q1.dtype:
+        raise ValueError("k1 and v1 must have q1's dtype")
+    n = batch * heads
+    qf, kn, vn = (_rows(x, n, head_dim) for x in (q1, k1, v1))
+    kf = k_cache.view(n, capacity, head_dim)
+    vf = v_cache.view(n, capacity, head_dim)
+    cf = committed.view(n, capacity)
+    if out is None:
+        out = torch.empty(n, head_dim, device=q1.device, dtype=q1.dtype)
+    need = lib.dilution_decode_scratch_bytes(n, t + 1, head_dim)
+    if scratch is None or scratch.numel() * scratch.element_size() < need:
+        scratch = torch.empty(need, device=q1.device, dtype=torch.uint8)
+    code = _lib.BF16 if q1.dtype == torch.bfloat16 else _lib.F32
+    _lib.check(lib.dilution_decode_append(qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), kf.data_ptr(),
+                                          vf.data_ptr(), code, n, capacity, t + 1, head_dim,
+                                          1.0 / math.sqrt(head_dim), EPS, cf.data_ptr(), out.data_ptr(),
+                                          scratch.data_ptr(), _stream(q1.device)), "dilution_decode_append")
+    cache["len"] = t + 1
+    return out.view(batch, heads, 1, head_dim)
+
+
 def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", device=None, slabs: int = 8,
-                            out=None, grads=None):
+                            out=None, grads=None, wait: bool = True):
     """The operator for tensors that live in HOST memory (ideally pinned).
 
     q, k, v: (B, H, T, D) CPU tensors; dout: optional (B, H, T, D) upstream gradient.
@@ -310,7 +376,13 @@ def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", dev
     slabs that flow through three CUDA streams: host->device copy of slab i+1,
     forward+backward of slab i and device->host copy of slab i-1 run at the same
     time.  End-to-end time approaches max(compute, one copy direction) instead of
-    their sum.  The maths and kernels are those of `dilution_attention`.
+    their sum.  The maths and kernels are those of `dilution_attention`.  dout
+    may be bf16 (a bf16 model's upstream gradient): it is then copied and used as
+    it is, which halves that part of the host->device traffic.
+
+    With wait=True (default) the call returns once the results are in the host
+    buffers.  wait=False returns as soon as everything is queued; the caller must
+    then synchronise the device (or the current stream) before reading them.
     """
     lib_device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     batch, heads, seq, head_dim = q.shape
@@ -370,18 +442,70 @@ def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", dev
                 x.record_stream(s_out)
         staged[i] = None
     main.wait_stream(s_out)
+    if wait:
+        s_out.synchronize()       # the device->host copies are asynchronous: the host waits for them here
     return out if dout is None else (out, *grads)
 
 
-def install(target=None):
+def _fused_step_cache(self, x1, cache):
+    """DilutionAttention.step_cache (model.py:231-240) with the append fused into
+    the decode launch; falls back to the model's own method whenever that one
+    would not take the kernel path."""
+    if not self._kernel_ok(x1) or not self._standard():
+        return self._unfused_step_cache(x1, cache)
+    batch = x1.shape[0]
+    q1, k1, v1 = self._split_heads(x1, offset=cache["len"])
+    y = dilution_decode_append_step(q1, k1, v1, cache).to(q1.dtype)
+    return self._merge_heads(y, batch, 1)
+
+
+def install(target=None, fused_decode: bool = False):
     """Plug this backend into the reference package: assign the fused entry
     points onto `dilution.kernels` (or `target`), the same way the reference's
     scripts/train_kernel_variant.py:39 swaps implementations.  The model looks
     the functions up at call time (model.py:145-150), so DilutionLM then runs on
-    these kernels after enable_dilution_kernel()."""
+    these kernels after enable_dilution_kernel().
+
+    fused_decode=True also replaces `DilutionAttention.step_cache` of the
+    imported `dilution.model` with a version that hands the new token's k and v
+    to the decode kernels instead of writing them into the caches first
+    (model.py:85-93): one torch copy pair less per layer and token.  The original
+    method stays reachable and is used whenever the kernel path does not apply.
+    `uninstall()` undoes both.
+    """
     if target is None:
         import dilution.kernels as target  # the reference package, if importable
+    saved = getattr(target, "_b200_saved", None)
+    if saved is None:
+        saved = {name: getattr(target, name, None)
+                 for name in ("dilution_attention_forward", "dilution_attention", "dilution_decode_step",
+                              "HAS_TRITON")}
+        target._b200_saved = saved
     for name in ("dilution_attention_forward", "dilution_attention", "dilution_decode_step"):
         setattr(target, name, globals()[name])
     target.HAS_TRITON = True   # the reference gates its kernel path on this flag
+    if fused_decode:
+        import dilution.model as model
+        cls = model.DilutionAttention
+        if not hasattr(cls, "_unfused_step_cache"):
+            cls._unfused_step_cache = cls.step_cache
+            cls.step_cache = _fused_step_cache
+    return target
+
+
+def uninstall(target=None):
+    """Put back what install() replaced."""
+    if target is None:
+        import dilution.kernels as target
+    saved = getattr(target, "_b200_saved", None)
+    if saved is not None:
+        for name, value in saved.items():
+            if value is not None:
+                setattr(target, name, value)
+        del target._b200_saved
+    import sys
+    model = sys.modules.get("dilution.model")
+    if model is not None and hasattr(model.DilutionAttention, "_unfused_step_cache"):
+        model.DilutionAttention.step_cache = model.DilutionAttention._unfused_step_cache
+        del model.DilutionAttention._unfused_step_cache
     return target

@@ -93,13 +93,17 @@ def gather_keys(k_local: torch.Tensor, v_local: torch.Tensor, bounds: list[int],
     mine = torch.stack((k_local, v_local)).contiguous()            # (2, rows, len_r, d)
     ops, inbox = [], {}
     for s in range(rank):                                           # receive from earlier ranks
+        if bounds[s + 1] == bounds[s]:
+            continue                                                # an empty chunk is never sent
         buf = mine.new_empty(2, rows, bounds[s + 1] - bounds[s], d)
         inbox[s] = buf
         ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(group, s) if group else s, group))
     for r in range(rank + 1, world):                                # send to later ranks
-        ops.append(dist.P2POp(dist.isend, mine, dist.get_global_rank(group, r) if group else r, group))
-    for req in dist.batch_isend_irecv(ops):
-        req.wait()
+        if end > bounds[rank]:
+            ops.append(dist.P2POp(dist.isend, mine, dist.get_global_rank(group, r) if group else r, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
     for s, buf in inbox.items():
         a, b = bounds[s], bounds[s + 1]
         k[:, a:b] = buf[0]
@@ -108,19 +112,30 @@ def gather_keys(k_local: torch.Tensor, v_local: torch.Tensor, bounds: list[int],
 
 
 def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "bf16",
-                  demand_prefix=None, exchange=None):
+                  demand_prefix=None, exchange=None, mark=None):
     """Forward of one contiguous query chunk against the keys it can see.
 
     q_local (rows, tq, d) at absolute positions q_offset..; k_seen/v_seen
     (rows, q_offset+tq, d).  `exchange(local_total)` -> base is called between
     pass 2 and pass 3 and returns the demand committed by earlier chunks (the
     cross-rank exscan, or a cached prefix); `demand_prefix` supplies it directly.
-    Returns out (rows, tq, d) fp32 and local_total (rows, tk) fp32.
+    Returns out (rows, tq, d) fp32 and local_total (rows, tk) fp32.  An empty
+    chunk (tq == 0) launches nothing but still takes part in the exchange, with a
+    zero total.  `mark(name)` (optional) is called at the phase boundaries.
     """
     lib = _lib.load()
     rows, tq, d = q_local.shape
     tk = k_seen.shape[1]
     dev = q_local.device
+    mark = mark or (lambda name: None)
+    if tq == 0:
+        total = torch.zeros(rows, tk, device=dev, dtype=torch.float32)
+        mark("passes_1_2")
+        if exchange is not None:
+            exchange(total)
+        mark("exchange")
+        mark("pass_3")
+        return torch.empty(rows, 0, d, device=dev, dtype=torch.float32), total
     lowp, _ = K._resolve_precision(dot_precision)
     want = torch.bfloat16 if (lowp or q_local.dtype == torch.bfloat16) else torch.float32
     qf, kf, vf = (x.to(want).contiguous() for x in (q_local, k_seen, v_seen))
@@ -139,34 +154,41 @@ def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "
     _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, rows, tq, tk, q_offset,
                                         d, scale, rmax.data_ptr(), rden.data_ptr(), None,
                                         carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
+    mark("passes_1_2")
     base = demand_prefix
     if exchange is not None:
         base = exchange(total)
     if base is not None:
         base = base.to(torch.float32).contiguous()
+    mark("exchange")
     _lib.check(lib.dilution_forward_main(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec,
                                          rows, tq, tk, q_offset, d, scale, K.EPS,
                                          rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
                                          None if base is None else base.data_ptr(),
                                          out.data_ptr(), ssum.data_ptr(), None, st),
                "dilution_forward_main")
+    mark("pass_3")
     return out, total
 
 
 def sequence_parallel_prefill(q_local, k_local, v_local, seq: int, bounds: list[int] | None = None,
-                              dot_precision: str = "bf16", group=None):
+                              dot_precision: str = "bf16", group=None, mark=None):
     """Sequence-parallel prefill of a (rows, seq, d) problem.
 
     Every rank passes ITS chunk of q, k, v (rows, a_{r+1}-a_r, d) for the
     boundaries `bounds` (default: equal_area_bounds).  Returns
       out    (rows, a_{r+1}-a_r, d) fp32 for the local query rows,
       demand (rows, seq) fp32: the decode accumulator, identical on all ranks.
+    `mark(name)` (optional) is called after each phase — "gather_keys",
+    "passes_1_2", "exchange", "pass_3" — so that a caller can record CUDA events.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if bounds is None:
         bounds = equal_area_bounds(seq, world)
     k_seen, v_seen = gather_keys(k_local, v_local, bounds, group)
+    if mark is not None:
+        mark("gather_keys")
     result = {}
 
     def exchange(local_total):
@@ -174,5 +196,5 @@ def sequence_parallel_prefill(q_local, k_local, v_local, seq: int, bounds: list[
         result["demand"] = demand
         return base
 
-    out, _ = prefill_chunk(q_local, k_seen, v_seen, bounds[rank], dot_precision, exchange=exchange)
+    out, _ = prefill_chunk(q_local, k_seen, v_seen, bounds[rank], dot_precision, exchange=exchange, mark=mark)
     return out, result["demand"]

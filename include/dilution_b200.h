@@ -4,8 +4,8 @@
  * Drop-in boundary for ONE path of Royer-Research-Labs/Dilution-Attention: the
  * entry points of its `dilution.kernels` module (src/dilution/kernels.py).  The
  * reference launches Triton kernels from Python; a host that wants this library
- * instead binds the functions below (ctypes from Python) and
- * keeps the Python-level signatures unchanged.
+ * instead binds the functions below (ctypes from Python) and keeps the
+ * Python-level signatures unchanged.
  *
  * Conventions
  *  - every pointer is a DEVICE pointer owned by the caller; nothing here
@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define DILUTION_ABI_VERSION 1
+#define DILUTION_ABI_VERSION 2
 #define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint (aux["bwd_block_m"]) */
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
@@ -61,7 +61,8 @@ const char* dilution_last_error(void);
 
 /* Every wait inside a kernel (on a TMA copy or a tensor-core batch) is bounded; a
  * wait that runs out records a code in a device status word and the kernel
- * drains and returns instead of hanging.  This call SYNCHRONISES the device,
+ * drains and returns instead of hanging.  This call SYNCHRONISES the device
+ * (cudaDeviceSynchronize, so kernels on non-blocking streams are included),
  * returns DILUTION_ERR_DEVICE if a code was recorded since the last call (and
  * clears it), else DILUTION_OK.  No reference counterpart. */
 int dilution_device_status(void);
@@ -127,7 +128,9 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
 /* Pass 4 — backward of the whole operator.
  * Replaces torch dbar (kernels.py:866), _dilution_ba (:677-775), _dilution_bc
  * (:777-809) and _dilution_dq_epilogue (:814-826).
- * dout, out: (n, t, d) fp32.  rmax, rden, ssum: (n, t).  carry and total as written
+ * out: (n, t, d) fp32.  dout: (n, t, d) in `dout_dtype` — fp32 as autograd hands it
+ * over (kernels.py:860-866), or bf16 when the upstream gradient already is (tensor-core
+ * path only; halves what a host-resident caller has to copy in).  rmax, rden, ssum: (n, t).  carry and total as written
  * by dilution_colsum_scan with tq == tk == t, q_offset == 0, carry_base == NULL.
  * pk as written by dilution_forward_main; it may be NULL for bf16 inputs with
  * BF16 precision and d == 64 (the tensor-core backward applies the dq correction
@@ -135,7 +138,7 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
  * dq, dk, dv: (n, t, d) in `dtype` (the input dtype, as kernels.py:873-875). */
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
                       int64_t n, int64_t t, int d, float scale, float eps,
-                      const float* dout, const float* out,
+                      const void* dout, int dout_dtype, const float* out,
                       const float* rmax, const float* rden, const float* carry, const float* total,
                       const float* ssum, const float* pk,
                       void* scratch, void* dq, void* dk, void* dv, void* stream);
@@ -152,6 +155,17 @@ size_t dilution_decode_scratch_bytes(int64_t n, int64_t length, int d);
 int dilution_decode(const void* q1, const void* k_cache, const void* v_cache, int dtype,
                     int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
                     float* committed, void* out, void* scratch, void* stream);
+
+/* The same step with the token append fused in: replaces the model's _append_kv
+ * (model.py:85-93) followed by dilution_decode_step (kernels.py:994-1038), so a token
+ * costs three launches and no separate copy.  k1, v1: (n, d) rows of the new token in
+ * `dtype`; the kernels write them to position length-1 of k_cache / v_cache (which they
+ * therefore take as writable) and use them from registers; the demand at length-1 is
+ * taken as zero whatever the buffer holds (a new key has none) and set to this step's p.
+ * `length` counts the new token, as in dilution_decode.  Everything else as there. */
+int dilution_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                           int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
+                           float eps, float* committed, void* out, void* scratch, void* stream);
 
 /* The same decode step for callers that cannot hand over scratch memory.
  * No counterpart in the reference (its decode allocates out and scratch with

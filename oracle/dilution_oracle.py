@@ -157,6 +157,83 @@ def dilution_backward_analytic(q, k, v, dout):
     return dq, dk, dv, dict(ghat=ghat.squeeze(-1), pk=pk, dbar=dbar.squeeze(-1), out=out)
 
 
+def dilution_backward_chunked(q, k, v, dout, chunk: int = 1024):
+    """out, dq, dk, dv with O(chunk * T) memory: the closed-form gradient of
+    `dilution_backward_analytic` (kernels.py:460-465, 677-826) evaluated in
+    query-row chunks.  A forward sweep (first chunk to last) records the demand
+    in front of every chunk and the outputs; a reverse sweep (last chunk to
+    first) carries the per-key suffix of dk_share (kernels.py:763-764).  Every
+    row sees all of its keys inside one chunk, so ghat is complete per chunk.
+    For lengths where autograd through the dense T x T version does not fit.
+    """
+    q, k, v, dout = (t.float() for t in (q, k, v, dout))
+    seq, head_dim = q.shape[-2], q.shape[-1]
+    lead = q.shape[:-2]
+    scale = 1.0 / math.sqrt(head_dim)
+    starts = list(range(0, seq, chunk))
+    demand = torch.zeros(*lead, seq)
+    before = []                                   # demand in front of each chunk, keys [0, b)
+    out = torch.empty(*lead, seq, v.shape[-1])
+    for a in starts:
+        b = min(a + chunk, seq)
+        p = bids(q[..., a:b, :], k[..., :b, :], q_offset=a)
+        before.append(demand[..., :b].clone())
+        c = before[-1][..., None, :] + p.cumsum(dim=-2) - p
+        share = p / (c + p + EPS)
+        attn = share / (share.sum(dim=-1, keepdim=True) + EPS)
+        out[..., a:b, :] = attn @ v[..., :b, :]
+        demand[..., :b] += p.sum(dim=-2)
+    dq = torch.zeros_like(q)
+    dk = torch.zeros_like(k)
+    dv = torch.zeros_like(v)
+    suffix_carry = torch.zeros(*lead, seq)        # sum of dk_share over the chunks already visited
+    for idx in range(len(starts) - 1, -1, -1):
+        a = starts[idx]
+        b = min(a + chunk, seq)
+        p = bids(q[..., a:b, :], k[..., :b, :], q_offset=a)
+        c = before[idx][..., None, :] + p.cumsum(dim=-2) - p
+        inv = 1.0 / (c + p + EPS)
+        share = p * inv
+        sinv = 1.0 / (share.sum(dim=-1, keepdim=True) + EPS)
+        attn = share * sinv
+        do = dout[..., a:b, :]
+        dbar = (do * out[..., a:b, :]).sum(dim=-1, keepdim=True)
+        ds = (do @ v[..., :b, :].transpose(-2, -1) - dbar) * sinv * (p > 0)
+        g = -ds * p * inv * inv
+        suffix = g.flip(-2).cumsum(dim=-2).flip(-2) - g + suffix_carry[..., None, :b]
+        pdp = p * (ds * (c + EPS) * inv * inv + suffix)
+        dz = pdp - p * pdp.sum(dim=-1, keepdim=True)
+        dq[..., a:b, :] = scale * (dz @ k[..., :b, :])
+        dk[..., :b, :] += scale * (dz.transpose(-2, -1) @ q[..., a:b, :])
+        dv[..., :b, :] += attn.transpose(-2, -1) @ do
+        suffix_carry[..., :b] += g.sum(dim=-2)
+    return out, dq, dk, dv
+
+
+def demand_before(q, k, upto: int, chunk: int = 2048) -> torch.Tensor:
+    """Per-key demand committed by query rows [0, upto): column sums of p over
+    those rows (kernels.py:65 evaluated at row `upto`), (..., upto) fp32, in
+    query-row chunks."""
+    demand = torch.zeros(*q.shape[:-2], upto)
+    for a in range(0, upto, chunk):
+        b = min(a + chunk, upto)
+        demand[..., :b] += bids(q[..., a:b, :], k[..., :b, :], q_offset=a).sum(dim=-2)
+    return demand
+
+
+def dilution_rows(q, k, v, row_a: int, row_b: int, chunk: int = 2048) -> torch.Tensor:
+    """Output rows [row_a, row_b) of the operator without the rows behind them:
+    the demand in front of row_a by `demand_before`, then kernels.py:64-68 on
+    the block.  (..., row_b - row_a, D) fp32."""
+    front = demand_before(q, k, row_a, chunk)
+    p = bids(q[..., row_a:row_b, :], k[..., :row_b, :], q_offset=row_a)
+    committed = p.cumsum(dim=-2) - p
+    committed[..., :row_a] += front[..., None, :]
+    share = p / (committed + p + EPS)
+    attn = share / (share.sum(dim=-1, keepdim=True) + EPS)
+    return attn @ v[..., :row_b, :].float()
+
+
 def decode_step(q1, k_cache, v_cache, committed, length: int) -> torch.Tensor:
     """One cached decode step, the eager maths of model.py:242-257 with the
     softmax bid (kernels_bid.py bids_from_affinity, 'softmax' branch).

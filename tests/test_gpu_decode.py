@@ -87,3 +87,40 @@ def test_decode_sequence_of_steps_bf16_d64(kernels):
         out = kernels.dilution_decode_step(qb[:, :, t:t + 1].to(DEV), kc, vc, committed, t + 1)
         assert (out[:, :, 0].float().cpu() - rows[:, :, t]).abs().max().item() < 2e-2
     assert rel_err(committed.cpu(), O.demand_totals(qb.float(), kb.float())) < 2e-2
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 64), (torch.float32, 32)])
+def test_fused_append_equals_append_then_step(kernels, dtype, d):
+    """dilution_decode_append_step == the model's _append_kv (model.py:85-93) followed by
+    dilution_decode_step, over a run of tokens that crosses a key-chunk boundary; caches,
+    demand and outputs must agree, and the dict's len must advance."""
+    b, h, prefix, steps = 2, 3, 250, 12
+    cap = prefix + steps + 2
+    g = torch.Generator().manual_seed(17)
+    k = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    v = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    k[:, :, prefix:], v[:, :, prefix:] = 0, 0
+    com = torch.zeros(b, h, cap)
+    com[:, :, :prefix] = torch.rand(b, h, prefix, generator=g)
+    a = {"k": k.to(DEV), "v": v.to(DEV), "len": prefix, "committed": com.to(DEV)}
+    f = {"k": k.to(DEV), "v": v.to(DEV), "len": prefix, "committed": com.to(DEV)}
+    # the fused path must not depend on what the demand buffer holds at the new position
+    f["committed"][:, :, prefix:] = 7.0
+    ck, cv, cc = k.clone(), v.clone(), com.clone()
+    for s in range(steps):
+        q1, k1, v1 = (torch.randn(b, h, 1, d, generator=g).to(dtype) for _ in range(3))
+        t = a["len"]
+        a["k"][:, :, t], a["v"][:, :, t] = k1[:, :, 0].to(DEV), v1[:, :, 0].to(DEV)
+        a["len"] = t + 1
+        ya = kernels.dilution_decode_step(q1.to(DEV), a["k"], a["v"], a["committed"], t + 1)
+        yf = kernels.dilution_decode_append_step(q1.to(DEV), k1.to(DEV), v1.to(DEV), f)
+        assert f["len"] == t + 1
+        assert torch.equal(ya, yf), s
+        ck[:, :, t], cv[:, :, t] = k1[:, :, 0], v1[:, :, 0]
+        ref = O.decode_step(q1, ck, cv, cc, t + 1)
+        assert (yf.float().cpu() - ref).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-2)
+    n = prefix + steps
+    assert torch.equal(a["k"], f["k"]) and torch.equal(a["v"], f["v"])
+    assert torch.equal(a["committed"][:, :, :n], f["committed"][:, :, :n])
+    assert (f["committed"][:, :, n:] == 7.0).all()          # rows past the length stay untouched
+    assert rel_err(f["committed"][:, :, :n].cpu(), cc[:, :, :n]) < 1e-5

@@ -53,6 +53,19 @@ def test_install_swaps_entry_points_on_a_module():
     assert fake.dilution_attention is pkg.kernels.dilution_attention
     assert fake.dilution_decode_step is pkg.kernels.dilution_decode_step
     assert fake.HAS_TRITON is True
+    pkg.uninstall(fake)
+    assert fake.HAS_TRITON is False
+
+
+def test_fused_append_refuses_a_full_cache_like_append_kv():
+    """model.py:88-89: a step past the capacity is a ValueError before anything runs."""
+    K = load_package().kernels
+    cache = {"k": torch.zeros(1, 1, 4, 32), "v": torch.zeros(1, 1, 4, 32), "len": 4,
+             "committed": torch.zeros(1, 1, 4)}
+    x = torch.randn(1, 1, 1, 32)
+    with pytest.raises(ValueError, match="past the cache capacity"):
+        K.dilution_decode_append_step(x, x, x, cache)
+    assert cache["len"] == 4
 
 
 def test_row_shard_covers_rows_exactly():

@@ -117,3 +117,36 @@ def test_equal_area_bounds():
     assert b[0] == 0 and b[-1] == 131072 and all(x % 128 == 0 for x in b)
     areas = [b[i + 1] ** 2 - b[i] ** 2 for i in range(8)]
     assert max(areas) / min(areas) < 1.05
+
+
+@pytest.mark.parametrize("chunk", [7, 64, 1024])
+def test_chunked_backward_matches_reference_goldens(chunk):
+    """The row-chunked closed-form backward against the reference's autograd gradients."""
+    g = golden("c1_b1h4t512d64.npz")
+    q, k, v, dout = make_inputs(1, 4, 512, 64, int(g["seed"]))
+    out, dq, dk, dv = O.dilution_backward_chunked(q, k, v, dout, chunk=chunk)
+    assert rel_err(out, torch.from_numpy(g["out"])) < 1e-5
+    for name, got in dict(dq=dq, dk=dk, dv=dv).items():
+        assert rel_err(got, torch.from_numpy(g[name])) < 1e-4, name
+    for t, _ in SMALL:
+        c = _small(t)
+        res = O.dilution_backward_chunked(c["q"], c["k"], c["v"], c["dout"], chunk=chunk)
+        for name, got in zip(("out", "dq", "dk", "dv"), res):
+            assert rel_err(got, c[name]) < 2e-4, (t, name)
+
+
+def test_chunked_backward_matches_dense_autograd_at_4096():
+    """One (b,h) row at T=4096 with the benchmark's value scales: chunked == dense autograd."""
+    q, k, v, dout = make_inputs(1, 1, 4096, 64, 1339, scales=(0.5, 0.5, 1.0, 1e-2))
+    ref = O.dilution_backward(q, k, v, dout)
+    got = O.dilution_backward_chunked(q, k, v, dout, chunk=512)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, ref):
+        assert rel_err(a, b) < 1e-4, name
+
+
+def test_row_block_helpers_match_dense():
+    c = _small(257)
+    assert rel_err(O.demand_before(c["q"], c["k"], 100, chunk=32),
+                   O.bids(c["q"], c["k"])[..., :100, :100].sum(-2)) < 1e-6
+    assert rel_err(O.dilution_rows(c["q"], c["k"], c["v"], 100, 180, chunk=32), c["out"][..., 100:180, :]) < 2e-5
+    assert rel_err(O.dilution_rows(c["q"], c["k"], c["v"], 0, 64), c["out"][..., :64, :]) < 2e-5

@@ -57,12 +57,14 @@ def _worker(rank, world, port, seq, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_sequence_parallel_exchange_matches_whole_sequence(world):
+@pytest.mark.parametrize("world,seq", [(2, 96), (4, 96), (4, 16)])
+def test_sequence_parallel_exchange_matches_whole_sequence(world, seq):
+    """seq=16 on four ranks leaves two ranks with an empty query chunk: they must still take
+    part in both exchanges instead of leaving the others waiting."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 96, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, seq, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]

@@ -7,7 +7,9 @@ dilution_decode_static, which takes no scratch pointer.  This test drives it
 through the C ABI exactly as such a host would (raw pointers, no torch
 allocation between the calls), twice in a row on the same caches, and requires
 the same outputs and the same advanced demand as dilution_decode with
-caller-provided scratch.  It is collected last so that a failure here cannot
+caller-provided scratch, and as the CPU oracle's decode step.  One case sits at
+the limits of the built-in array (128 rows, head_dim 128, rows x keys = 2^21).
+It is collected last so that a failure here cannot
 hide any other test.
 """
 
@@ -19,6 +21,7 @@ import pytest
 import torch
 
 from conftest import load_package
+from oracle import dilution_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -35,17 +38,21 @@ def _call(lib, name, q1, kc, vc, com, out, length, scratch=None):
     return getattr(lib, name)(*args)
 
 
-@pytest.mark.parametrize("dtype,d,n,length", [(torch.bfloat16, 64, 8, 3000), (torch.float32, 32, 5, 77)])
+@pytest.mark.parametrize("dtype,d,n,length", [(torch.bfloat16, 64, 8, 3000), (torch.float32, 32, 5, 77),
+                                              (torch.bfloat16, 128, 128, 16383)])
 def test_static_scratch_decode_equals_decode_with_scratch_twice(dtype, d, n, length):
     pkg = load_package()
     lib = pkg._lib.load()
     cap = length + 4
     g = torch.Generator().manual_seed(length)
-    kc = torch.randn(n, cap, d, generator=g).to(dtype).to(DEV)
-    vc = torch.randn(n, cap, d, generator=g).to(dtype).to(DEV)
-    qs = [torch.randn(n, d, generator=g).to(dtype).to(DEV) for _ in range(2)]
+    kc_h = torch.randn(n, cap, d, generator=g).to(dtype)
+    vc_h = torch.randn(n, cap, d, generator=g).to(dtype)
+    kc, vc = kc_h.to(DEV), vc_h.to(DEV)
+    qs_h = [torch.randn(n, d, generator=g).to(dtype) for _ in range(2)]
+    qs = [x.to(DEV) for x in qs_h]
     com0 = torch.rand(n, cap, generator=g)
     com0[:, length - 1:] = 0
+    com_ref = com0.clone()
     com_a, com_b = com0.to(DEV), com0.to(DEV)
     out_a = torch.empty(n, d, device=DEV, dtype=dtype)
     out_b = torch.empty_like(out_a)
@@ -61,6 +68,10 @@ def test_static_scratch_decode_equals_decode_with_scratch_twice(dtype, d, n, len
         assert (out_a.float() - out_b.float()).abs().max().item() <= tol
         assert (com_a - com_b).abs().max().item() <= 1e-6
         assert com_b[:, ln:].abs().max().item() == 0
+        ref = O.decode_step(qs_h[step].view(1, n, 1, d), kc_h.view(1, n, cap, d), vc_h.view(1, n, cap, d),
+                            com_ref.view(1, n, cap), ln)
+        assert (out_b.float().cpu() - ref.view(n, d)).abs().max().item() <= max(tol, 1e-4)
+        assert (com_b.cpu() - com_ref).abs().max().item() <= 1e-5 * max(1.0, com_ref.abs().max().item())
 
 
 def test_static_scratch_decode_refuses_sizes_beyond_its_array():
