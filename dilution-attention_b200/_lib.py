@@ -27,6 +27,8 @@ SIGNATURES = {
     "dilution_profile_enable": (_I, [_I]),
     "dilution_profile_collect": (_I, [ctypes.c_char_p, _Z]),
     "dilution_rowstats": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P]),
+    "dilution_rowstats_pk": (_I, [_P, _P, _I, _I, _L, _L, _I, _F, _P, _P, _P, _P]),
+    "dilution_softmax_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _P]),
     "dilution_colsum_scan": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _P, _P, _P]),
     "dilution_forward_main": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _F,
                                    _P, _P, _P, _P, _P, _P, _P, _P]),

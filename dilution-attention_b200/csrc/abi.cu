@@ -14,6 +14,7 @@
 #include "simt_kernels.cuh"
 #if __has_include("tc_kernels.cuh")
 #include "tc_kernels.cuh"
+#include "tc_rowpass_kernels.cuh"
 #define DILUTION_TENSOR_PATH 1
 #endif
 
@@ -421,6 +422,41 @@ int dilution_rowstats(const void* q, const void* k, int dtype, int precision, in
   return DILUTION_OK;
 }
 
+int dilution_rowstats_pk(const void* q, const void* k, int dtype, int precision, int64_t n, int64_t t,
+                         int d, float scale, float* rmax, float* rden, float* pk, void* stream) {
+  if (int rc = check_common("dilution_rowstats_pk", dtype, precision, n, t, t, 0, d)) return rc;
+  if (!q || !k || !rmax || !rden || !pk) return fail(DILUTION_ERR_ARG, "dilution_rowstats_pk: null pointer");
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, 0)) {
+    const dil::Geom g = make_geom(n, t, t, 0, scale, 0.f);
+    cudaStream_t st = (cudaStream_t)stream;
+    Prof prof("tc_rowstats_pk", st);
+    return dil::tc::rowstats_pk(q, k, g, rmax, rden, pk, st, g_err, sizeof(g_err));
+  }
+#endif
+  return fail(DILUTION_ERR_UNSUPPORTED, "dilution_rowstats_pk: bf16 inputs, BF16 precision and head_dim 64 only "
+              "(other cases get pk from dilution_forward_main)");
+}
+
+int dilution_softmax_forward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                             int64_t tq, int64_t tk, int64_t q_offset, int d, float scale, float* rmax,
+                             float* rden, void* out, void* stream) {
+  if (int rc = check_common("dilution_softmax_forward", dtype, precision, n, tq, tk, q_offset, d)) return rc;
+  if (!q || !k || !v || !out) return fail(DILUTION_ERR_ARG, "dilution_softmax_forward: null pointer");
+  if ((rmax == nullptr) != (rden == nullptr))
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_forward: rmax and rden go together");
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+    const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
+    cudaStream_t st = (cudaStream_t)stream;
+    Prof prof("tc_softmax_forward", st);
+    return dil::tc::softmax_forward(q, k, v, g, rmax, rden, out, st, g_err, sizeof(g_err));
+  }
+#endif
+  return fail(DILUTION_ERR_UNSUPPORTED, "dilution_softmax_forward: bf16 inputs, BF16 precision, head_dim 64 and "
+              "q_offset a multiple of 128 only");
+}
+
 int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision, int64_t n,
                          int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
                          const float* rmax, const float* rden, const float* carry_base,
@@ -486,7 +522,7 @@ int dilution_backward(const void* q, const void* k, const void* v, int dtype, in
 #ifdef DILUTION_TENSOR_PATH
 #if DILUTION_TC_HAS_BACKWARD
   if (dil::tc::supported(dtype, precision, d, 0))
-    return dil::tc::backward(q, k, v, g, dout, dout_dtype, out, rmax, rden, carry, total, ssum, s.dq_main, s.dk_main,
+    return dil::tc::backward(q, k, v, g, dout, dout_dtype, out, rmax, rden, carry, total, ssum, pk, s.dq_main, s.dk_main,
                              s.ghat, s.dbar, s.dop, dq, dk, dv, st, g_err, sizeof(g_err), mark_scope);
 #endif
   if (!pk) return fail(DILUTION_ERR_ARG, "dilution_backward: the fp32 path needs pk from dilution_forward_main");

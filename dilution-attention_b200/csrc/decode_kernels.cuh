@@ -82,9 +82,12 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
 #pragma unroll
     for (int e = 0; e < E; ++e) qf[e] *= zscale;
   }
-  const int k0 = blockIdx.x * chunk, k1 = min(len, k0 + chunk);
+  const int k0 = blockIdx.x * chunk;
+  // with an append, position len-1 (the last key of the last chunk) is not read from the cache:
+  // the streaming loop stops in front of it and warp 0 takes its row from knew afterwards
+  const bool appends = knew != nullptr && k0 + chunk >= len;
+  const int k1 = min(len, k0 + chunk) - (appends ? 1 : 0);
   const T* krow = kc + n * cap * D + t * E;
-  const int fresh = knew != nullptr ? len - 1 : -1;   // position whose row comes from knew
   float m = -INFINITY, s = 0.f;
   for (int base = k0 + warp * 32; base < k1; base += ROUND) {
     float mine = -INFINITY;
@@ -92,11 +95,7 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
       const int key = base + grp * TPK + u;
-      raw[u] = (key < k1 && key != fresh) ? ld_stream(krow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
-      if (key == fresh) {
-        raw[u] = *reinterpret_cast<const uint4*>(knew + n * D + t * E);
-        *reinterpret_cast<uint4*>(kc_out + n * cap * D + (int64_t)key * D + t * E) = raw[u];
-      }
+      raw[u] = key < k1 ? ld_stream(krow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
@@ -114,6 +113,26 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
       aff[n * stride + key] = mine;
       const float nm = fmaxf(m, mine);
       s = s * exp2f(m - nm) + exp2f(mine - nm);
+      m = nm;
+    }
+  }
+  if (appends && warp == 0) {
+    // the new token's key: into the cache, and its score from registers
+    float dot = 0.f;
+    if (lane < TPK) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(knew + n * D + lane * E);
+      *reinterpret_cast<uint4*>(kc_out + n * cap * D + (int64_t)(len - 1) * D + lane * E) = raw;
+      float kf[E];
+      Unpack<T>::run(raw, kf);
+#pragma unroll
+      for (int e = 0; e < E; ++e) dot = fmaf(qf[e], kf[e], dot);
+    }
+#pragma unroll
+    for (int o = TPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) {
+      aff[n * stride + len - 1] = dot;
+      const float nm = fmaxf(m, dot);
+      s = s * exp2f(m - nm) + exp2f(dot - nm);
       m = nm;
     }
   }
@@ -175,9 +194,10 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
   }
   const float gmax = sstat[0], rinv = sstat[1];
 
-  const int k0 = blockIdx.x * chunk, k1 = min(len, k0 + chunk);
+  const int k0 = blockIdx.x * chunk;
+  const bool appends = vnew != nullptr && k0 + chunk >= len;     // as in scores_kernel
+  const int k1 = min(len, k0 + chunk) - (appends ? 1 : 0);
   const T* vrow = vc + n * cap * D + t * E;
-  const int fresh = vnew != nullptr ? len - 1 : -1;
   float acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
@@ -187,17 +207,13 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
 #pragma unroll
     for (int u = 0; u < TPK; ++u) {
       const int key = base + grp * TPK + u;
-      raw[u] = (key < k1 && key != fresh) ? ld_stream(vrow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
-      if (key == fresh) {
-        raw[u] = *reinterpret_cast<const uint4*>(vnew + n * D + t * E);
-        *reinterpret_cast<uint4*>(vc_out + n * cap * D + (int64_t)key * D + t * E) = raw[u];
-      }
+      raw[u] = key < k1 ? ld_stream(vrow + (int64_t)key * D) : make_uint4(0, 0, 0, 0);
     }
     const int key = base + lane;
     float share = 0.f;
     if (key < k1) {
       const float a = aff[n * stride + key];
-      const float c = key == fresh ? 0.f : committed[n * cap + key];   // a fresh key has no demand yet
+      const float c = committed[n * cap + key];
       const float p = exp2f(a - gmax) * rinv;
       share = p / (c + p + eps);
       committed[n * cap + key] = c + p;
@@ -210,6 +226,25 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
       Unpack<T>::run(raw[u], vf);
 #pragma unroll
       for (int e = 0; e < E; ++e) acc[e] = fmaf(sh, vf[e], acc[e]);
+    }
+  }
+  if (appends && warp == 0) {
+    // the new token: no demand on it yet (whatever the buffer holds), its value row from vnew
+    float share = 0.f;
+    if (lane == 0) {
+      const float p = exp2f(aff[n * stride + len - 1] - gmax) * rinv;
+      share = p / (p + eps);
+      committed[n * cap + len - 1] = p;
+      ssh += share;
+    }
+    share = __shfl_sync(0xffffffffu, share, 0);
+    if (lane < TPK) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(vnew + n * D + lane * E);
+      *reinterpret_cast<uint4*>(vc_out + n * cap * D + (int64_t)(len - 1) * D + lane * E) = raw;
+      float vf[E];
+      Unpack<T>::run(raw, vf);
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = fmaf(share, vf[e], acc[e]);
     }
   }
   // lanes with the same slice t hold partial sums of the same output elements

@@ -1449,10 +1449,17 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   return launch_status("tc forward_main", err, errlen);
 }
 
-// dop: (n, t, 64) bf16 scratch for the pre-scaled dout.
+int backward_tail_with_pk(const CUtensorMap& mq, const CUtensorMap& mk, const Geom& g, const float* rmax,
+                          const float* rden, const float* ghat, const float* dk_main, const float* dq_main,
+                          const float* pk, void* dq, void* dk, cudaStream_t st, char* err, size_t errlen,
+                          void (*mark)(const char*, cudaStream_t, int));
+
+// dop: (n, t, 64) bf16 scratch for the pre-scaled dout.  pk: the query correction saved by the
+// forward (rowstats_pk), or null: the correction pass then recomputes it.
 inline int backward(const void* q, const void* k, const void* v, const Geom& g, const void* dout,
                     int dout_dtype, const float* out, const float* rmax, const float* rden, const float* carry,
-                    const float* total, const float* ssum, float* dq_main, float* dk_main, float* ghat,
+                    const float* total, const float* ssum, const float* pk, float* dq_main, float* dk_main,
+                    float* ghat,
                     float* dbarp, void* dop, void* dq, void* dk, void* dv, cudaStream_t st, char* err,
                     size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
   CUtensorMap mq, mk;
@@ -1482,6 +1489,8 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
       (__nv_bfloat16*)dv, ghat);
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
+  if (pk != nullptr)
+    return backward_tail_with_pk(mq, mk, g, rmax, rden, ghat, dk_main, dq_main, pk, dq, dk, st, err, errlen, mark);
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;
   if (int rc = set_smem_attr((const void*)backward_correction_kernel, smem, err, errlen)) return rc;
   mark("tc_backward_correction", st, 0);

@@ -10,6 +10,7 @@ libdilution_b200.so instead of Triton:
     dilution_attention(q, k, v, dot_precision=...)             kernels.py:906-930
     dilution_decode_step(q1, k_cache, v_cache, committed, t)   kernels.py:994-1038
     dilution_decode_append_step(q1, k1, v1, cache)             model.py:85-93 + :236-239
+    softmax_attention_forward(q, k, v)                         model.py:96-117 (forward)
 
 The operator (docs/operator.md of the reference):
 
@@ -31,6 +32,7 @@ bwd_*, b3_*, b4_*) are accepted and ignored.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -41,6 +43,11 @@ CARRY_ROWS = _lib.CARRY_ROWS    # query rows per demand checkpoint
 KEY_FORWARD_MIN_SEQ = 256       # read by the reference's scripts; no meaning here
 HAS_TRITON = False              # this backend never uses Triton
 HAS_CUDA_LIB = _lib.available()
+# Training forward on the tensor-core path: pass 1 also saves pk = scale * softmax(q k^T) k (as the
+# reference's K1 does, kernels.py:161-188), and the backward's correction pass then has only its
+# key half left.  False (or DILUTION_SAVE_PK=0 in the environment): nothing is saved and the
+# correction pass recomputes the query half.
+TC_SAVE_PK = os.environ.get("DILUTION_SAVE_PK", "1") != "0"
 
 
 def _resolve_precision(dot_precision: str) -> tuple[int, str]:
@@ -85,12 +92,19 @@ def _prepare(q, k, v, dot_precision):
 
 def _forward_rows(lib, qf, kf, vf, code, prec, scale, out, ssum, rmax, rden, carry, total, pk,
                   q_offset=0, carry_base=None):
-    """Passes 1-3 on a slab of (batch*head) rows."""
+    """Passes 1-3 on a slab of (batch*head) rows.  On the tensor-core path a requested pk comes
+    out of pass 1; otherwise out of pass 3 (the fp32 kernel)."""
     n, tq, d = qf.shape
     tk = kf.shape[1]
     st = _stream(qf.device)
-    _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
-                                     d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
+    if pk is not None and _lib.tensor_core_path(code, prec, d) and q_offset == 0 and tq == tk:
+        _lib.check(lib.dilution_rowstats_pk(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, d, scale,
+                                            rmax.data_ptr(), rden.data_ptr(), pk.data_ptr(), st),
+                   "dilution_rowstats_pk")
+        pk = None
+    else:
+        _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
+                                         d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
     _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
                                         d, scale, rmax.data_ptr(), rden.data_ptr(), None,
                                         carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
@@ -168,13 +182,13 @@ class _DilutionAttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, dot_precision):
-        # the tensor-core backward applies the dq correction itself and needs no saved pk
+        # the tensor-core backward can apply the dq correction itself, without a saved pk
         lowp, _ = _resolve_precision(dot_precision)
         on_tc = _lib.tensor_core_path(_lib.BF16 if (lowp or q.dtype == torch.bfloat16) else _lib.F32,
                                       _lib.PREC[dot_precision], q.shape[-1])
         out, aux = dilution_attention_forward(
             q, k, v, dot_precision=dot_precision, return_aux=True,
-            _save_pk=any(ctx.needs_input_grad[:3]) and not on_tc)
+            _save_pk=any(ctx.needs_input_grad[:3]) and (TC_SAVE_PK or not on_tc))
         ctx.save_for_backward(q, k, v, out, aux["rmax"], aux["rden"], aux["carry"], aux["ssum"], aux["pk"],
                               aux["committed_total"])
         ctx.dot_precision = dot_precision
@@ -244,6 +258,39 @@ def dilution_attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     the reference's dense PyTorch version nothing (T x T)-shaped is materialised.
     """
     return _DilutionAttentionFn.apply(q.float(), k.float(), v.float(), "ieee")
+
+
+def softmax_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, return_lse: bool = False):
+    """Causal softmax attention on the same tcgen05 pipeline: what the reference's
+    CausalSelfAttention layers compute with F.scaled_dot_product_attention(q, k, v,
+    is_causal=True) (model.py:96-117).  Forward only (inference / prefill).
+
+    q, k, v: (B, H, T, 64) bfloat16 on a CUDA device.  Returns (B, H, T, 64) bfloat16 and, with
+    return_lse, the natural-log row log-sum-exp of the scaled scores (B, H, T) fp32.
+    Pass 1 of dilution attention plus a plain P V product is exactly this operator
+    (tests/test_kernels.py:349-357 of the reference shows it for share_cumsum=False).
+    """
+    lib = _lib.load()
+    if not q.is_cuda:
+        raise RuntimeError("softmax attention needs CUDA tensors (no CPU fallback in this backend)")
+    batch, heads, seq, head_dim = q.shape
+    if q.dtype != torch.bfloat16 or head_dim != 64:
+        raise ValueError("softmax_attention_forward takes bfloat16 tensors with head_dim 64")
+    (qf, kf, vf), code, prec, n = _prepare(q, k, v, "bf16")
+    out = torch.empty(n, seq, head_dim, device=q.device, dtype=torch.bfloat16)
+    rmax = rden = None
+    if return_lse:
+        rmax = torch.empty(n, seq, device=q.device, dtype=torch.float32)
+        rden = torch.empty_like(rmax)
+    _lib.check(lib.dilution_softmax_forward(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq,
+                                            kf.shape[1], 0, head_dim, 1.0 / math.sqrt(head_dim), _ptr(rmax),
+                                            _ptr(rden), out.data_ptr(), _stream(q.device)),
+               "dilution_softmax_forward")
+    result = out.reshape(batch, heads, seq, head_dim)
+    if return_lse:
+        lse = (rmax + torch.log2(rden)) * math.log(2.0)
+        return result, lse.reshape(batch, heads, seq)
+    return result
 
 
 def decode_scratch(n: int, capacity: int, head_dim: int, device) -> torch.Tensor:

@@ -93,6 +93,25 @@ int dilution_rowstats(const void* q, const void* k, int dtype, int precision,
                       int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
                       float* rmax, float* rden, void* stream);
 
+/* Pass 1 with the saved query correction: rmax, rden as dilution_rowstats writes them, and
+ * pk = scale * softmax(q k^T) k, (n, t, d) fp32, from the same sweep — what the reference's K1
+ * computes with PK set (kernels.py:161-188).  Whole sequences only (tq == tk == t, offset 0);
+ * bf16 inputs, BF16 precision, d == 64 (DILUTION_ERR_UNSUPPORTED otherwise: the fp32 kernels
+ * produce pk in dilution_forward_main).  dilution_backward given this pk skips the query
+ * half of its correction pass. */
+int dilution_rowstats_pk(const void* q, const void* k, int dtype, int precision,
+                         int64_t n, int64_t t, int d, float scale,
+                         float* rmax, float* rden, float* pk, void* stream);
+
+/* Causal softmax attention forward, out = softmax(q k^T * scale) v: the reference's
+ * CausalSelfAttention layers (model.py:96-117, F.scaled_dot_product_attention with
+ * is_causal=True) on the same pipeline — pass 1 plus a plain P V product.
+ * bf16 inputs, BF16 precision, d == 64, q_offset a multiple of 128.
+ * out: (n, tq, d) bf16.  rmax, rden: optional (n, tq) fp32 row statistics (both or neither). */
+int dilution_softmax_forward(const void* q, const void* k, const void* v, int dtype, int precision,
+                             int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
+                             float* rmax, float* rden, void* out, void* stream);
+
 /* Pass 2 — per-(query-block, key-block) column sums of p and their exclusive
  * scan over query blocks, in one key-stationary sweep.
  * Replaces _dilution_k1's sweep 2 (kernels.py:190-198) + _dilution_scan (:250-264).
@@ -132,8 +151,8 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
  * over (kernels.py:860-866), or bf16 when the upstream gradient already is (tensor-core
  * path only; halves what a host-resident caller has to copy in).  rmax, rden, ssum: (n, t).  carry and total as written
  * by dilution_colsum_scan with tq == tk == t, q_offset == 0, carry_base == NULL.
- * pk as written by dilution_forward_main; it may be NULL for bf16 inputs with
- * BF16 precision and d == 64 (the tensor-core backward applies the dq correction
+ * pk as written by dilution_forward_main or dilution_rowstats_pk; it may be NULL for bf16
+ * inputs with BF16 precision and d == 64 (the tensor-core backward then recomputes the dq correction
  * itself).  scratch: dilution_backward_scratch_bytes.
  * dq, dk, dv: (n, t, d) in `dtype` (the input dtype, as kernels.py:873-875). */
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,

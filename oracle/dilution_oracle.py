@@ -265,3 +265,10 @@ def equal_area_bounds(seq: int, ranks: int, tile: int = 128) -> list[int]:
         bounds.append(min(max(a, bounds[-1]), seq))
     bounds.append(seq)
     return bounds
+
+
+def softmax_attention(q, k, v, q_offset: int = 0) -> torch.Tensor:
+    """Causal softmax attention in fp32: what the reference's softmax layers compute with
+    F.scaled_dot_product_attention(q, k, v, is_causal=True) (model.py:96-117).  The same bids as
+    kernels.py:60-64 followed by a plain product with v."""
+    return bids(q, k, q_offset) @ v.float()
