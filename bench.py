@@ -735,13 +735,16 @@ def run_lm(c, args):
     alternating softmax attention with RoPE and dilution attention without position encoding
     (layer_attention = [softmax, dilution] * 6 with positional = rope_alt, which rotates layers
     0, 2, 4, ...), weight-only LayerNorm (the reference has no RMSNorm), random initial weights,
-    uniform random token ids, bf16 autocast."""
+    uniform random token ids, bf16 autocast.  The headline figures run with everything this
+    library offers installed (dilution kernels, fused decode append, fused head split + RoPE,
+    softmax layers' inference on the row pass and the streaming decode kernels);
+    `dilution_kernels_only` repeats them with only `dilution.kernels` replaced, i.e. with the
+    softmax layers and the head split as the reference's model runs them (SDPA, torch RoPE)."""
     try:
         if reference_package() is None:
             return {"unavailable": "no installed copy of the reference package under baseline/_ref"}
         from dilution.config import ModelConfig
         from dilution.model import DilutionLM
-        c.pkg.install(fused_decode=True)
         dev = c.dev
         launches0 = c.L.launch_count()
 
@@ -753,69 +756,86 @@ def run_lm(c, args):
         res = {"config": {"model": "DilutionLM 12L d1024 16H ffn4096 vocab50304, softmax+RoPE / dilution "
                                    "alternating, weight-only LayerNorm, tied embeddings, random init",
                           "dtype": "bf16 autocast, fp32 master weights"}}
-        # ---- training step: forward, loss, backward, gradient clipping, fused AdamW
         B, T = LM["train_B"], args.lm_seq or LM["train_T"]
-        torch.manual_seed(1344)
-        model = DilutionLM(config(T)).to(dev).train()
-        model.enable_dilution_kernel()
-        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+        nb, prompt, new = LM["gen_batch"], args.lm_prompt or LM["gen_prompt"], LM["gen_new"]
         g = torch.Generator().manual_seed(1344)
         idx_h = torch.randint(0, LM["vocab"], (B, T + 1), generator=g).pin_memory()
+        idx_gen = torch.randint(0, LM["vocab"], (nb, prompt), generator=g).to(dev)
 
-        def train_step(i):
-            tok = idx_h.to(dev, non_blocking=True)           # token ids come from the host every step
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                _, loss = model(tok[:, :-1], tok[:, 1:])
-            loss.backward()
-            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
-            opt.step()
-            opt.zero_grad(set_to_none=True)
-            return loss.item()                               # the loss is read back every step
+        def train(steps):
+            """forward, loss, backward, gradient clipping, fused AdamW; token ids come from the host
+            and the loss is read back every step"""
+            torch.manual_seed(1344)
+            model = DilutionLM(config(T)).to(dev).train()
+            model.enable_dilution_kernel()
+            opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
 
-        for i in range(2):
-            train_step(i)
-        steps = max(1, min(args.steps, 3))
-        ms = c.timed(train_step, steps)
-        res["train"] = {"tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms, "steps": steps, "batch": B,
-                        "seq_len": T, "params": sum(p.numel() for p in model.parameters()),
-                        "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
-        del model, opt
-        torch.cuda.empty_cache()
-        # ---- prefill + greedy cached decode (DilutionLM.prefill / decode_step, model.py:451-470)
-        nb, prompt, new = LM["gen_batch"], args.lm_prompt or LM["gen_prompt"], LM["gen_new"]
-        torch.manual_seed(1345)
-        model = DilutionLM(config(prompt + new)).to(dev).eval()
-        model.enable_dilution_kernel()
-        idx = torch.randint(0, LM["vocab"], (nb, prompt), generator=g).to(dev)
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-            logits, caches = model.prefill(idx[:, :256], capacity=300)      # warm-up of both paths
-            model.decode_step(logits[:, -1].argmax(-1, keepdim=True), 256, caches)
-            del caches
-            torch.cuda.synchronize()
-            ev[0].record()
-            logits, caches = model.prefill(idx, capacity=prompt + new)
-            ev[1].record()
-            tok = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
-            for s in range(new - 1):
-                logits = model.decode_step(tok, prompt + s, caches)
+            def step(i):
+                tok = idx_h.to(dev, non_blocking=True)
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    _, loss = model(tok[:, :-1], tok[:, 1:])
+                loss.backward()
+                torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                opt.step()
+                opt.zero_grad(set_to_none=True)
+                return loss.item()
+
+            for i in range(2):
+                step(i)
+            torch.cuda.reset_peak_memory_stats(dev)
+            ms = c.timed(step, steps)
+            out = {"tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms, "steps": steps, "batch": B,
+                   "seq_len": T, "params": sum(p.numel() for p in model.parameters()),
+                   "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+            del model, opt
+            torch.cuda.empty_cache()
+            return out
+
+        def generate(new_tokens):
+            """DilutionLM.prefill + greedy decode_step loop (model.py:451-470, 498-509)"""
+            torch.manual_seed(1345)
+            model = DilutionLM(config(prompt + new)).to(dev).eval()
+            model.enable_dilution_kernel()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                logits, caches = model.prefill(idx_gen[:, :256], capacity=300)      # warm-up of both paths
+                model.decode_step(logits[:, -1].argmax(-1, keepdim=True), 256, caches)
+                del caches
+                torch.cuda.synchronize()
+                ev[0].record()
+                logits, caches = model.prefill(idx_gen, capacity=prompt + new)
+                ev[1].record()
                 tok = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
-            ev[2].record()
-            torch.cuda.synchronize()
-        pre_ms, dec_ms = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
-        res["generate"] = {"decode_tok_s": nb * (new - 1) / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / (new - 1),
-                           "prefill_ms": pre_ms, "prefill_tok_s": nb * prompt / (pre_ms * 1e-3), "batch": nb,
-                           "prompt": prompt, "new_tokens": new,
-                           "decode_path": "step_cache with the token append fused into the decode launch"}
+                for s in range(new_tokens - 1):
+                    logits = model.decode_step(tok, prompt + s, caches)
+                    tok = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+                ev[2].record()
+                torch.cuda.synchronize()
+            pre_ms, dec_ms = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+            del model, caches
+            torch.cuda.empty_cache()
+            return {"decode_tok_s": nb * (new_tokens - 1) / (dec_ms * 1e-3),
+                    "decode_ms_per_token": dec_ms / (new_tokens - 1), "prefill_ms": pre_ms,
+                    "prefill_tok_s": nb * prompt / (pre_ms * 1e-3), "batch": nb, "prompt": prompt,
+                    "new_tokens": new_tokens}
+
+        steps = max(1, min(args.steps, 3))
+        c.pkg.install(fused_decode=True)
+        c.pkg.install_layers()
+        res["train"] = train(steps)
+        res["generate"] = generate(new)
+        c.pkg.uninstall_layers()
+        c.pkg.uninstall()
+        c.pkg.install()
+        res["dilution_kernels_only"] = {"train": train(steps), "generate": generate(min(new, 33))}
         res["gpu_launches"] = c.L.launch_count() - launches0
-        del model, caches
-        torch.cuda.empty_cache()
         return res
     except Exception as e:  # noqa: BLE001
         torch.cuda.empty_cache()
         return {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     finally:
         try:
+            c.pkg.uninstall_layers()
             c.pkg.uninstall()
         except Exception:  # noqa: BLE001
             pass

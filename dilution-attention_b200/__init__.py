@@ -15,7 +15,7 @@ After the first import it is also registered as `dilution_attention_b200`.
 
 import sys as _sys
 
-from . import _lib, kernels, partition  # noqa: F401
+from . import _lib, kernels, layers, partition  # noqa: F401
 from .kernels import (  # noqa: F401
     dilution_attention,
     dilution_attention_forward,
@@ -24,13 +24,16 @@ from .kernels import (  # noqa: F401
     dilution_decode_append_step,
     dilution_decode_step,
     install,
+    softmax_attention_forward,
     uninstall,
 )
+from .layers import install_layers, softmax_decode_append_step, split_heads_rope, uninstall_layers  # noqa: F401
 
 _sys.modules.setdefault("dilution_attention_b200", _sys.modules[__name__])
 
 __all__ = [
     "kernels", "partition", "dilution_attention", "dilution_attention_forward",
     "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step",
-    "dilution_decode_append_step", "install", "uninstall",
+    "dilution_decode_append_step", "softmax_attention_forward", "softmax_decode_append_step",
+    "split_heads_rope", "install", "uninstall", "install_layers", "uninstall_layers", "layers",
 ]

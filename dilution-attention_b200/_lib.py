@@ -38,6 +38,8 @@ SIGNATURES = {
     "dilution_decode_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_decode": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
     "dilution_decode_append": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
+    "dilution_softmax_decode_append": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _P, _P, _P]),
+    "dilution_split_heads_rope": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _I, _P]),
     "dilution_decode_static": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P]),
 }
 

@@ -11,6 +11,7 @@
 
 #include "../../include/dilution_b200.h"
 #include "decode_kernels.cuh"
+#include "layer_kernels.cuh"
 #include "simt_kernels.cuh"
 #if __has_include("tc_kernels.cuh")
 #include "tc_kernels.cuh"
@@ -270,7 +271,7 @@ dil::decode::Scratch carve_decode(void* scratch, int64_t n, int64_t len, int d) 
   return s;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool DILUTE = true>
 int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
                   cudaStream_t st, bool timing = true, const void* knew = nullptr,
@@ -290,7 +291,7 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
   if (int rc = check_launch("decode scores")) return rc;
   {
     Prof prof("decode_sweep", st, timing);
-    sweep_kernel<T, D><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
+    sweep_kernel<T, D, DILUTE><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
                                             committed, s.pout, s.psum, (const T*)vnew,
                                             (T*)const_cast<void*>(vc));
   }
@@ -579,6 +580,58 @@ int dilution_decode_append(const void* q1, const void* k1, const void* v1, void*
   cudaStream_t st = (cudaStream_t)stream;
   DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, length, scale, eps,
                                                      committed, out, scratch, st, true, k1, v1)))
+  return DILUTION_OK;
+}
+
+int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                              const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
+                              int inverse, void* stream) {
+  if (!qkv || !q || !k || !v) return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: null pointer");
+  if ((cos_table == nullptr) != (sin_table == nullptr))
+    return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: cos and sin tables go together");
+  if (d != 64 && d != 128 && d != 32)
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_split_heads_rope: head_dim %d not in {32, 64, 128}", d);
+  if (batch < 1 || seq < 1 || heads < 1 || batch * seq * heads * (d / 8) >= ((int64_t)1 << 39))
+    return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: sizes out of range");
+  if (((uintptr_t)qkv | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15 ||
+      ((uintptr_t)cos_table | (uintptr_t)sin_table) & 7)
+    return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: tensors must be 16-byte aligned (tables 8)");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = batch * seq * heads * (d / 8);
+  const unsigned grid = (unsigned)((total + 255) / 256);
+  using bf = __nv_bfloat16;
+  Prof prof(inverse ? "merge_heads_rope_grad" : "split_heads_rope", st);
+#define DIL_ROPE(DD)                                                                                           \
+  if (inverse)                                                                                                 \
+    dil::layer::split_heads_rope_kernel<false, DD><<<grid, 256, 0, st>>>(                                      \
+        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads);      \
+  else                                                                                                         \
+    dil::layer::split_heads_rope_kernel<true, DD><<<grid, 256, 0, st>>>(                                       \
+        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads);
+  if (d == 32) { DIL_ROPE(32) } else if (d == 64) { DIL_ROPE(64) } else { DIL_ROPE(128) }
+#undef DIL_ROPE
+  return check_launch("split_heads_rope");
+}
+
+int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache,
+                                   void* v_cache, int dtype, int64_t n, int64_t capacity, int64_t length,
+                                   int d, float scale, void* out, void* scratch, void* stream) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: dtype must be DILUTION_F32 or DILUTION_BF16");
+  if (!valid_d(d))
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_softmax_decode_append: head_dim %d not in {16, 32, 64, 128}", d);
+  if (n < 1 || n > 65535)
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: n must be in [1, 65535] rows per call");
+  if (capacity < 1 || length < 1 || length > capacity || capacity > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: decode step past the cache capacity "
+                "(length %lld, capacity %lld)", (long long)length, (long long)capacity);
+  if (!q1 || !k_cache || !v_cache || !out || !scratch || ((k1 == nullptr) != (v1 == nullptr)))
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: null pointer");
+  if (((uintptr_t)q1 | (uintptr_t)k1 | (uintptr_t)v1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+    return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: q1 / k1 / v1 / caches must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D, false>(q1, k_cache, v_cache, n, capacity, length, scale,
+                                                            0.f, nullptr, out, scratch, st, true, k1, v1)))
   return DILUTION_OK;
 }
 

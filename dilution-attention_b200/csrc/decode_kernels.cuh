@@ -151,8 +151,10 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   }
 }
 
-// grid = (chunks, n)
-template <typename T, int D>
+// grid = (chunks, n).  DILUTE = false turns the step into plain softmax attention of the new
+// token over the cache (share = p, no demand read or written): the cached step of the
+// reference's softmax layers (model.py:112-117).
+template <typename T, int D, bool DILUTE = true>
 __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int64_t cap, int len,
                                                    int chunk, float eps, int64_t stride,
                                                    const float* __restrict__ aff,
@@ -213,10 +215,14 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (key < k1) {
       const float a = aff[n * stride + key];
-      const float c = committed[n * cap + key];
       const float p = exp2f(a - gmax) * rinv;
-      share = p / (c + p + eps);
-      committed[n * cap + key] = c + p;
+      if (DILUTE) {
+        const float c = committed[n * cap + key];
+        share = p / (c + p + eps);
+        committed[n * cap + key] = c + p;
+      } else {
+        share = p;
+      }
       ssh += share;
     }
 #pragma unroll
@@ -233,8 +239,8 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (lane == 0) {
       const float p = exp2f(aff[n * stride + len - 1] - gmax) * rinv;
-      share = p / (p + eps);
-      committed[n * cap + len - 1] = p;
+      share = DILUTE ? p / (p + eps) : p;
+      if (DILUTE) committed[n * cap + len - 1] = p;
       ssh += share;
     }
     share = __shfl_sync(0xffffffffu, share, 0);

@@ -410,6 +410,18 @@ def dilution_decode_append_step(
     return out.view(batch, heads, 1, head_dim)
 
 
+_COPY_STREAMS: dict = {}
+
+
+def _copy_streams(device):
+    """The copy-in and copy-out streams of a device, created once: the caching allocator keeps
+    a pool per stream, so fresh streams on every call would never find a cached block."""
+    key = (device.type, device.index)
+    if key not in _COPY_STREAMS:
+        _COPY_STREAMS[key] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    return _COPY_STREAMS[key]
+
+
 def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", device=None, slabs: int = 8,
                             out=None, grads=None, wait: bool = True):
     """The operator for tensors that live in HOST memory (ideally pinned).
@@ -446,7 +458,7 @@ def dilution_attention_host(q, k, v, dout=None, dot_precision: str = "bf16", dev
     gh = None if dout is None else tuple(x.reshape(n, 1, seq, head_dim) for x in grads)
 
     main = torch.cuda.current_stream(lib_device)
-    s_in, s_out = torch.cuda.Stream(lib_device), torch.cuda.Stream(lib_device)
+    s_in, s_out = _copy_streams(lib_device)
     s_in.wait_stream(main)
     staged, done = [], []
 

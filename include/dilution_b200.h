@@ -186,6 +186,27 @@ int dilution_decode_append(const void* q1, const void* k1, const void* v1, void*
                            int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
                            float eps, float* committed, void* out, void* scratch, void* stream);
 
+/* The cached step of a softmax layer on the same streaming kernels: attention of one new
+ * token per row over `length` cached keys, the token's k1, v1 rows written to position
+ * length-1 on the way.  Replaces CausalSelfAttention.step_cache's _append_kv +
+ * F.scaled_dot_product_attention over the cache (model.py:112-117).  k1 and v1 may both be
+ * NULL when the token is already in the caches.  scratch: dilution_decode_scratch_bytes.
+ * out: (n, d) in `dtype`. */
+int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache,
+                                   void* v_cache, int dtype, int64_t n, int64_t capacity, int64_t length,
+                                   int d, float scale, void* out, void* scratch, void* stream);
+
+/* Head split of the fused q/k/v projection with rotary position embedding applied on the way
+ * (model.py:59-67 + rope.py:26-44), and its transpose for the backward.
+ * qkv: (batch, seq, 3, heads, d) bf16.  q, k, v: contiguous (batch, heads, seq, d) bf16.
+ * cos_table, sin_table: (seq, d/2) bf16 for the positions of the rows, built as the reference
+ * builds them (fp32 angles cast to bf16), or both NULL for no rotation; q and k are rotated,
+ * v is moved.  inverse == 0: qkv -> q, k, v.  inverse != 0: (dq, dk, dv) -> dqkv with the
+ * inverse rotation.  d in {32, 64, 128}. */
+int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                              const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
+                              int inverse, void* stream);
+
 /* The same decode step for callers that cannot hand over scratch memory.
  * No counterpart in the reference (its decode allocates out and scratch with
  * torch on every call, kernels.py:1029-1030).

@@ -272,3 +272,28 @@ def softmax_attention(q, k, v, q_offset: int = 0) -> torch.Tensor:
     F.scaled_dot_product_attention(q, k, v, is_causal=True) (model.py:96-117).  The same bids as
     kernels.py:60-64 followed by a plain product with v."""
     return bids(q, k, q_offset) @ v.float()
+
+
+def rope(x: torch.Tensor, offset: int = 0, theta: float = 10000.0) -> torch.Tensor:
+    """Rotary position embedding of (..., T, D) as rope.py:26-44: adjacent pairs (2i, 2i+1),
+    fp32 angles pos * theta^(-2i/D) cast to x's dtype, out = x*cos + rotate(x)*sin in x's dtype."""
+    seq, dim = x.shape[-2], x.shape[-1]
+    positions = torch.arange(offset, offset + seq, dtype=torch.float32)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))      # :34-36
+    freqs = torch.outer(positions, inv_freq)
+    cos = freqs.cos().to(x.dtype).repeat_interleave(2, dim=-1)                            # :38-41
+    sin = freqs.sin().to(x.dtype).repeat_interleave(2, dim=-1)
+    pairs = x.reshape(*x.shape[:-1], dim // 2, 2)
+    rotated = torch.stack((-pairs[..., 1], pairs[..., 0]), dim=-1).flatten(-2)            # :43
+    return x * cos + rotated * sin
+
+
+def split_heads(qkv: torch.Tensor, heads: int, offset: int = 0, theta: float | None = 10000.0):
+    """q, k, v (B, H, T, D) from the fused projection (B, T, 3*H*D) as model.py:59-67; q and k
+    rotated unless theta is None."""
+    batch, seq, width = qkv.shape
+    d = width // (3 * heads)
+    q, k, v = (t.view(batch, seq, heads, d).transpose(1, 2) for t in qkv.split(heads * d, dim=2))
+    if theta is not None:
+        q, k = rope(q, offset, theta), rope(k, offset, theta)
+    return q, k, v

@@ -15,6 +15,9 @@ Fixture layout (all fp32 unless noted):
   small_cases.npz      T in {1, 8, 65, 257}: q, k, v, dout, out, dq, dk, dv,
                        demand (= p.sum(-2)) and pk (= p@k/sqrt(D))
   decode_b2h4d32.npz   prefix 37 + 6 steps: q, k, v and the reference rows
+  layers_b2t24h2d32.npz  the model's softmax layer pieces: RopeModule outputs at two offsets
+                       (bf16 and fp32 inputs) and softmax-attention rows
+                       (F.scaled_dot_product_attention, is_causal) for the same q, k, v
 """
 
 from __future__ import annotations
@@ -93,6 +96,17 @@ def main():
              q=q.numpy(), k=k.numpy(), v=v.numpy(), rows=rows.numpy(),
              demand_prefix=p[:, :, :prefix].sum(-2)[..., :prefix].numpy(),
              demand_final=p.sum(-2).numpy(), prefix=np.array(prefix))
+    # the softmax layers' pieces (src/dilution/rope.py, model.py:96-117)
+    from dilution.rope import RopeModule
+    b, h, t, d = 2, 2, 24, 32
+    q, k, v, _ = make_inputs(b, h, t, d, 5151)
+    rope = RopeModule(d, theta=10000.0)
+    qb = q.bfloat16()
+    sdpa = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    np.savez(os.path.join(HERE, "layers_b2t24h2d32.npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(),
+             rope_f32_off0=rope(q, 0).numpy(), rope_f32_off9=rope(q, 9).numpy(),
+             rope_bf16_off0=rope(qb, 0).float().numpy(), rope_bf16_off9=rope(qb, 9).float().numpy(),
+             sdpa=sdpa.numpy(), theta=np.array(10000.0))
     print("wrote fixtures to", HERE)
 
 

@@ -132,7 +132,9 @@ def test_host_buffer_entry_point_matches_device_op(kernels):
     assert rel_err(dk.float(), ks.grad.float().cpu()) < 2e-3
     fwd_only = kernels.dilution_attention_host(qb, kb, vb, dot_precision="bf16", slabs=3)
     torch.cuda.synchronize()
-    assert torch.equal(fwd_only, out)
+    # the forward-only call takes its row statistics from the plain row pass, the training call
+    # from the row pass that also saves pk: same values up to the last bits
+    assert (fwd_only - out).abs().max().item() < 1e-3
 
 
 def test_backward_size_independent_properties_at_16k(kernels):

@@ -115,12 +115,13 @@ def test_fused_append_equals_append_then_step(kernels, dtype, d):
         ya = kernels.dilution_decode_step(q1.to(DEV), a["k"], a["v"], a["committed"], t + 1)
         yf = kernels.dilution_decode_append_step(q1.to(DEV), k1.to(DEV), v1.to(DEV), f)
         assert f["len"] == t + 1
-        assert torch.equal(ya, yf), s
+        # the appended key joins the chunk's sums last instead of in key order
+        assert (ya.float() - yf.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2), s
         ck[:, :, t], cv[:, :, t] = k1[:, :, 0], v1[:, :, 0]
         ref = O.decode_step(q1, ck, cv, cc, t + 1)
         assert (yf.float().cpu() - ref).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-2)
     n = prefix + steps
     assert torch.equal(a["k"], f["k"]) and torch.equal(a["v"], f["v"])
-    assert torch.equal(a["committed"][:, :, :n], f["committed"][:, :, :n])
+    assert rel_err(a["committed"][:, :, :n], f["committed"][:, :, :n]) < 1e-5
     assert (f["committed"][:, :, n:] == 7.0).all()          # rows past the length stay untouched
     assert rel_err(f["committed"][:, :, :n].cpu(), cc[:, :, :n]) < 1e-5

@@ -150,3 +150,21 @@ def test_row_block_helpers_match_dense():
                    O.bids(c["q"], c["k"])[..., :100, :100].sum(-2)) < 1e-6
     assert rel_err(O.dilution_rows(c["q"], c["k"], c["v"], 100, 180, chunk=32), c["out"][..., 100:180, :]) < 2e-5
     assert rel_err(O.dilution_rows(c["q"], c["k"], c["v"], 0, 64), c["out"][..., :64, :]) < 2e-5
+
+
+def test_rope_and_softmax_attention_match_reference_modules():
+    """The oracle's RoPE (rope.py:26-44) and softmax attention (model.py:96-117) against
+    outputs of the reference's RopeModule and of F.scaled_dot_product_attention."""
+    g = golden("layers_b2t24h2d32.npz")
+    q, k, v = (torch.from_numpy(g[n]) for n in "qkv")
+    theta = float(g["theta"])
+    for off in (0, 9):
+        assert torch.equal(O.rope(q, off, theta), torch.from_numpy(g[f"rope_f32_off{off}"]))
+        assert torch.equal(O.rope(q.bfloat16(), off, theta).float(), torch.from_numpy(g[f"rope_bf16_off{off}"]))
+    assert rel_err(O.softmax_attention(q, k, v), torch.from_numpy(g["sdpa"])) < 1e-6
+    # the head split of a fused projection: the three parts, per head, q and k rotated
+    b, h, t, d = q.shape
+    qkv = torch.cat([x.transpose(1, 2).reshape(b, t, h * d) for x in (q, k, v)], dim=2)
+    sq, sk, sv = O.split_heads(qkv, h, 9, theta)
+    assert torch.equal(sq, torch.from_numpy(g["rope_f32_off9"])) and torch.equal(sv, v)
+    assert torch.equal(sk, O.rope(k, 9, theta))
