@@ -22,6 +22,9 @@ Also on the line:
   decode         cached decode tok/s at 131072 and 16384 cached keys (batch 64 x 16
                  heads, 256 steps, heads sharded over ranks) against the measured HBM
                  copy bandwidth;
+  other_shapes   (1 GPU) forward + backward at the smaller shapes the reference publishes;
+  config1_fp32   (1 GPU) BASELINE config 1 on the exact-fp32 kernels, with the reference's
+                 CPU operator at the same shape;
   lm             (1 GPU, when a copy of the reference package is installed under
                  baseline/_ref) the reference's unmodified DilutionLM on these kernels:
                  train-step tokens/s at B=4 T=16384 and prefill 32K + 512 greedy
@@ -293,9 +296,10 @@ def run_triton(args):
         b.record()
         torch.cuda.synchronize()
         dms = a.elapsed_time(b) / steps
+        other = time_other_shapes(rk.dilution_attention, dev)
         import triton
         print(json.dumps({
-            "impl": "triton", "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
+            "impl": "triton", "other_shapes": other, "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
             "unit": "TFLOP/s", "ms_per_step": ms, "steps": len(times), "n_gpus": 1, "dtype": "bf16",
             "config": {"workload": f"train_fwd_bwd_B{B}_H{H}_T{T}_d{D}",
                        "path": "dilution.kernels.dilution_attention of the reference, Triton "
@@ -305,6 +309,42 @@ def run_triton(args):
                        "hbm_gbs": rows * (L0 + 3 + (steps + 1) / 2) * 264 / (dms * 1e-3) / 1e9}}), flush=True)
     except Exception as e:  # noqa: BLE001
         unavailable(f"{type(e).__name__}: {e}")
+
+
+# Smaller shapes the reference publishes times for (docs/kernels.md:206-209 of the reference,
+# measured there on another card), bf16, d=64: (batch, heads, seq).
+OTHER_SHAPES = ((32, 12, 1024), (8, 8, 4096), (2, 12, 16384))
+
+
+def time_other_shapes(op, dev, iters=10):
+    """Median CUDA-event ms of forward + backward of `op` at OTHER_SHAPES (warm-up 3)."""
+    out = {}
+    for b, h, t in OTHER_SHAPES:
+        g = torch.Generator(device=dev).manual_seed(b * t)
+        q, k, v = (torch.empty(b, h, t, 64, device=dev, dtype=torch.bfloat16).normal_(generator=g)
+                   .mul_(0.5 if i < 2 else 1.0).requires_grad_(True) for i in range(3))
+        dout = torch.empty(b, h, t, 64, device=dev).normal_(generator=g).mul_(1e-2)
+
+        def step():
+            q.grad = k.grad = v.grad = None
+            op(q, k, v, dot_precision="bf16").backward(dout)
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(iters):
+            a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(e))
+        ms = statistics.median(times)
+        out[f"B{b}_H{h}_T{t}"] = {"ms": ms, "tflops": causal_flops(b * h, t, 64, 7) / (ms * 1e-3) / 1e12}
+        del q, k, v, dout
+    torch.cuda.empty_cache()
+    return out
 
 
 # ------------------------------------------------------------------------------ our arm
@@ -447,6 +487,10 @@ def run_ours(args):
     kernels_ms = {name: tot / cnt for name, (cnt, tot) in prof.items()}
     roofline = train_roofline(kernels_ms, n_rows, T, D, value / c.world, c.peaks)
 
+    other = fp32_c1 = None
+    if c.world == 1 and not args.no_other:
+        other = time_other_shapes(K.dilution_attention, c.dev)
+        fp32_c1 = run_config1(c)
     sharded = None if args.no_sharded else run_train_sharded(c, args, devt)
     e2e = None if args.no_e2e else run_e2e(c, args, host, total_flops)
     del devt, q, k, v, dout, host
@@ -467,12 +511,52 @@ def run_ours(args):
                            "l2": "inputs exceed L2 (q,k,v 134 MB each, dout/out 268 MB at T=16384)",
                            "flop_count": "7*N*T*(T+1)*D"},
                 "roofline": roofline, "kernels_ms": kernels_ms, "e2e": e2e, "gpu_launches": launches,
-                "clocks": clocks.summary(), "train_sharded": sharded, "prefill": prefill,
+                "clocks": clocks.summary(), "other_shapes": other, "config1_fp32": fp32_c1,
+                "train_sharded": sharded, "prefill": prefill,
                 "decode": decode, "lm": lm}
         if c.world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_block()
         print(json.dumps(line), flush=True)
     c.close()
+
+
+def run_config1(c, iters=10):
+    """BASELINE config 1 (B1 H4 T512 d64 fp32, forward + autograd backward of
+    dilution_attention_reference): this library's exact-fp32 kernels on the GPU, and the reference's
+    CPU operator at the same shape on the host cores."""
+    g = torch.Generator().manual_seed(1338)
+    hq, hk, hv, hd = (torch.randn(1, 4, 512, 64, generator=g) for _ in range(4))
+    q, k, v = (x.to(c.dev).requires_grad_(True) for x in (hq, hk, hv))
+    dout = hd.to(c.dev)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        c.K.dilution_attention_reference(q, k, v).backward(dout)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(e))
+    res = {"workload": "B1_H4_T512_d64 fp32 forward + backward", "gpu_ms": statistics.median(times),
+           "gpu_path": "exact-fp32 FFMA kernels (dot_precision ieee)"}
+    if reference_package() is not None:
+        from dilution.kernels import dilution_attention_reference as ref
+        cpu = []
+        for _ in range(4):
+            qs, ks, vs = (x.clone().requires_grad_(True) for x in (hq, hk, hv))
+            t0 = time.perf_counter()
+            ref(qs, ks, vs).backward(hd)
+            cpu.append((time.perf_counter() - t0) * 1e3)
+        res["cpu_reference_ms"] = statistics.median(cpu[1:])
+        res["cpu_threads"] = torch.get_num_threads()
+    return res
 
 
 def run_train_sharded(c, args, devt):
@@ -855,6 +939,7 @@ def main():
     ap.add_argument("--no-lm", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other", action="store_true", help="skip the smaller shapes and config 1")
     ap.add_argument("--no-triton", action="store_true", help="--impl reference: skip the Triton child run")
     ap.add_argument("--decode-rows", type=int, default=DECODE["batch"] * DECODE["H"],
                     help="(batch*head) rows of the decode workload (profiling captures use fewer)")

@@ -167,7 +167,11 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
       // special-function unit)
       const float z0 = fmaf(v[e], g.zscale, -mr), z1 = fmaf(v[e + 1], g.zscale, -mr);
       const float p0 = fast_exp2(z0);
+#ifdef DILUTION_ROWPASS_NOPOLY
+      const float p1 = fast_exp2(z1);
+#else
       const float p1 = (e & 2) ? poly_exp2<4>(z1) : fast_exp2(z1);
+#endif
       ps0 += p0;
       ps1 += p1;
       pw[e >> 1] = pack_bf16(p0, p1);
@@ -422,6 +426,171 @@ __global__ void __launch_bounds__(256, 2) backward_key_correction_kernel(
   if (warp == 0) tmem_free(tmem, 256);
 }
 
+// The same pass in half-steps of 64 queries: S^T [128 keys x 64 queries] needs 64 TMEM columns, so
+// a CTA allocates 128 and four CTAs share an SM (32 warps to hide each other's MMA round trips,
+// as in the column-sum pass).  The two warpgroups split a half-step's 64 query columns.
+constexpr int kCorrKey64Smem = 3 * kTileBytes + 2048 + 1024 + 256;
+static_assert(5 * (kCorrKey64Smem + 1024) > 233472, "at most four CTAs of the half-step correction pass share an SM");
+
+__global__ void __launch_bounds__(256, 4) backward_key_correction64_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
+    const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ ghat,
+    const float* __restrict__ dk_main, __nv_bfloat16* __restrict__ dk) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes;
+  float2* sStat = reinterpret_cast<float2*>(smem + 3 * kTileBytes);           // [2][128] (lse, ghat)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 2048);
+  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
+  const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
+  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
+  const int n = (int)(blockIdx.x % g.n);
+  const int jb = (int)(blockIdx.x / g.n);
+  const int k0 = jb * kTileRows;
+  const int nsteps = nqb - jb, nhalf = 2 * nsteps;
+  const int64_t row_base = (int64_t)n * g.tq;
+
+  if (tid == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < 3; ++i) mbar_init(qfull + 8 * i, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 128);
+  if (wg == 1) {
+    const int i = jb * kTileRows + row;
+    float2 st = make_float2(INFINITY, 0.f);
+    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), ghat[row_base + i]);
+    sStat[row] = st;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem;
+  const uint32_t tS = tmem, tDK = tmem + 64;
+  constexpr uint32_t id_s = instr_desc(128, 64, 0, 0), id_kd = instr_desc(128, 64, 0, 1);
+  // scores of half-step (stage, odd): queries 64*odd.. of the Q tile in that stage (K-major: a
+  // row is 128 B = 8 units)
+  auto issue_scores = [&](int stage, int odd) {
+    const Desc dKk = make_desc(sK, 16, 1024), dQk = make_desc(sQ0 + kTileBytes * stage, 16, 1024);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) mma_ss(tS, dKk, 2 * kk, dQk, 512 * odd + 2 * kk, id_s, kk > 0);
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(qfull, 2 * kTileBytes);
+    tma_load_tile(sK, &map_k, k0, n, qfull);
+    tma_load_tile(sQ0, &map_q, jb * kTileRows, n, qfull);
+    if (nsteps > 1) {
+      mbar_expect_tx(qfull + 8, kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes, &map_q, (jb + 1) * kTileRows, n, qfull + 8);
+    }
+    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
+    tc_fence_after();
+    issue_scores(0, 0);
+    mma_commit(sdone);
+  }
+  __syncwarp();
+
+  const int ja = k0 + row;
+  const bool dead = ja >= g.tk;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const uint32_t tcol = tS + lane_base + 32 * wg;
+  for (int h = 0; h < nhalf; ++h) {
+    const int t = h >> 1, odd = h & 1, ib = jb + t, b = t & 1;
+    float nx_max = INFINITY, nx_den = 1.f, nx_gh = 0.f;
+    const bool fetch = odd == 0 && wg == 1 && t + 1 < nsteps;
+    if (fetch && (ib + 1) * kTileRows + row < g.tq) {
+      const int64_t i = row_base + (ib + 1) * kTileRows + row;
+      nx_max = rmax[i];
+      nx_den = rden[i];
+      nx_gh = ghat[i];
+    }
+    // scores of this half-step are ready; every earlier dKc product has completed
+    mbar_wait(sdone, h & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    if (tid == 0 && odd == 0 && t >= 1 && t + 1 < nsteps) {      // the Q stage of step t-1 is free
+      mbar_expect_tx(qfull + 8 * (b ^ 1), kTileBytes);
+      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
+    }
+    __syncwarp();
+    const int i0 = ib * kTileRows + 64 * odd + 32 * wg;           // first query of this thread's 32
+    const bool masked = dead || t == 0;
+    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * odd + 32 * wg);
+    float vs[32];
+    uint32_t wt[16];
+    tmem_ld32(tcol, vs);
+    tmem_ld_wait(vs);
+    auto tile = [&](auto mask_tag) {
+      constexpr bool MASK = decltype(mask_tag)::value;
+#pragma unroll
+      for (int e2 = 0; e2 < 16; ++e2) {
+        const float4 st = St4[e2];                                // (lse, ghat) of two queries
+        float p0 = fast_exp2(fmaf(vs[2 * e2], g.zscale, -st.x));
+        float p1 = fast_exp2(fmaf(vs[2 * e2 + 1], g.zscale, -st.z));
+        if (MASK) {
+          if (dead || ja > i0 + 2 * e2) p0 = 0.f;
+          if (dead || ja > i0 + 2 * e2 + 1) p1 = 0.f;
+        }
+        wt[e2] = pack_bf16(p0 * st.y, p1 * st.w);
+      }
+    };
+    if (masked) tile(std::true_type{}); else tile(std::false_type{});
+    tmem_st16(tcol, wt);            // W over the first 16 of the 32 consumed columns
+    if (fetch) sStat[(b ^ 1) * 128 + row] = make_float2(nx_max + log2f(nx_den), nx_gh);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const Desc dQm = make_desc(sQ0 + kTileBytes * b, kTileBytes, 1024);
+#pragma unroll
+      for (int kq = 0; kq < 4; ++kq)        // 16 queries per instruction: 16 rows of 128 B = 128 units
+        mma_ts(tDK, tS + 32 * (kq >> 1) + 8 * (kq & 1), dQm, 128 * (4 * odd + kq), id_kd, (h > 0 || kq > 0));
+      if (h + 1 < nhalf) {
+        if (odd) {                          // the next half-step opens step t+1
+          mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+          tc_fence_after();
+          issue_scores(b ^ 1, 0);
+        } else {
+          issue_scores(b, 1);
+        }
+      }
+      mma_commit(sdone);
+    }
+    __syncwarp();
+  }
+  mbar_wait(sdone, nhalf & 1, ctl, &g_status, kErrWaitMma);
+  tc_fence_after();
+  {
+    float a[32];
+    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
+    tmem_ld32(tDK + lane_base + 32 * wg, a);
+    tmem_ld_wait(a);
+    if (!dead) {
+      float m[32];
+#pragma unroll
+      for (int e = 0; e < 32; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(dk_main + o + e);
+        m[e] = x.x - g.scale * a[e];
+        m[e + 1] = x.y - g.scale * a[e + 1];
+        m[e + 2] = x.z - g.scale * a[e + 2];
+        m[e + 3] = x.w - g.scale * a[e + 3];
+      }
+#pragma unroll
+      for (int e = 0; e < 32; e += 8)
+        *reinterpret_cast<uint4*>(dk + o + e) =
+            make_uint4(pack_bf16(m[e], m[e + 1]), pack_bf16(m[e + 2], m[e + 3]),
+                       pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 128);
+}
+
 // dq = bf16(dq_main - ghat * pk): the query half of the correction from the saved pk
 // (the reference's dq epilogue, kernels.py:814-826; pk already carries the scale).
 __global__ void dq_from_pk_kernel(const float* __restrict__ dq_main, const float* __restrict__ pk,
@@ -473,11 +642,19 @@ inline int backward_tail_with_pk(const CUtensorMap& mq, const CUtensorMap& mk, c
                                  const float* dq_main, const float* pk, void* dq, void* dk, cudaStream_t st,
                                  char* err, size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
+#ifdef DILUTION_CORR_KEY128
   constexpr int smem = kCorrKeySmem > kTwoPerSm ? kCorrKeySmem : kTwoPerSm;
   if (int rc = set_smem_attr((const void*)backward_key_correction_kernel, smem, err, errlen)) return rc;
   mark("tc_backward_key_correction", st, 0);
   backward_key_correction_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, ghat, dk_main,
                                                                          (__nv_bfloat16*)dk);
+#else
+  constexpr int smem = kCorrKey64Smem;
+  if (int rc = set_smem_attr((const void*)backward_key_correction64_kernel, smem, err, errlen)) return rc;
+  mark("tc_backward_key_correction", st, 0);
+  backward_key_correction64_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, ghat,
+                                                                           dk_main, (__nv_bfloat16*)dk);
+#endif
   mark("tc_backward_key_correction", st, 1);
   if (int rc = launch_status("tc backward_key_correction", err, errlen)) return rc;
   const int64_t n4 = g.n * g.tq * kHeadDim / 4;
