@@ -15,10 +15,13 @@
 // accumulator O_wg [128 queries x 64] in TMEM, fed by P~ = 2^(z - reference) written as bf16
 // pairs over the score columns the thread has just consumed (the A operand of O_wg += P~ B, with
 // B the MN-major view of the K or V tile).  The two halves are merged once, at the end.
-// The reference maximum follows the running maximum lazily: it moves only when the running
-// maximum has outgrown it by more than 2^kRefSlack, and only then is the accumulator rescaled
-// (one TMEM round trip per warp), so that the common tile costs no rescaling at all and P~
-// stays within bf16 range.
+// The reference exponent follows the scores lazily: it is set from the first tile's maximum and
+// moves again only when a tile's P~ sum to more than 2^40, and only then is the accumulator
+// rescaled (one TMEM round trip per warp).  The common tile therefore takes no maximum and no
+// rescaling; bf16 has fp32's exponent range, so P~ of any magnitude below that limit keeps its
+// 8 bits, and sums run in fp32.  rmax therefore holds the reference, not the exact row maximum:
+// the pair (rmax, rden) is exact only as the log-sum-exp rmax + log2(rden), which is all the
+// other passes use.
 // TMEM: S 128 columns + 2 x 64 accumulator columns = 256; two CTAs per SM.
 #pragma once
 
@@ -27,7 +30,7 @@
 namespace dil {
 namespace tc {
 
-constexpr float kRefSlack = 8.f;                     // log2: P~ <= 2^8
+constexpr float kRefLimit = 1099511627776.f;         // 2^40: a tile whose P~ sum to more moves the reference
 template <int MODE> struct RowpassSmem {
   // Q | K[stages] | (V[stages]) | stats [2][128] float4 | barriers + control.  Three stages when
   // K is the only streamed operand; two of K and two of V otherwise, so that two CTAs fit an SM.
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
   }
   __syncwarp();
 
-  float m_true = -INFINITY, m_ref = -INFINITY, s = 0.f;
+  float m_ref = -INFINITY, s = 0.f;
   const int ia = q0 + row;
   const uint32_t taddr = tS + lane_base + 64 * wg;
   for (int jb = 0; jb < njb; ++jb) {
@@ -124,59 +127,79 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
     tmem_ld32(taddr + 32, v + 32);
     tmem_ld_wait(v);
     tmem_ld_wait(v + 32);
-    const bool edge = (jb * kTileRows + kTileRows - 1 > q0) || ((jb + 1) * kTileRows > g.tk);
-    float cmax = -INFINITY;
-    if (edge) {
-#pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        const int ja = jb * kTileRows + wg * 64 + e;
-        if (ja > ia || ja >= g.tk) v[e] = -INFINITY;
-        cmax = fmaxf(cmax, v[e]);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 64; ++e) cmax = fmaxf(cmax, v[e]);
-    }
-    m_true = fmaxf(m_true, cmax * g.zscale);
-    // move the reference (and rescale what was accumulated under the old one) only when needed
-    const bool need = m_true > m_ref + kRefSlack;          // also true for the first finite maximum
-    if (__any_sync(0xffffffffu, need)) {
-      const bool fresh = __all_sync(0xffffffffu, m_ref == -INFINITY);   // nothing accumulated yet
-      const float f = m_true == -INFINITY ? 1.f : fast_exp2(m_ref - m_true);
-      if (!fresh) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float o[16];
-          tmem_ld16(tO + lane_base + 16 * c, o);
-          tmem_ld_wait16(o);
-          uint32_t w[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) w[e] = __float_as_uint(o[e] * f);
-          tmem_st16(tO + lane_base + 16 * c, w);
-        }
-      }
-      s *= f;
-      m_ref = m_true;
-    }
-    const float mr = m_ref == -INFINITY ? 0.f : m_ref;
     uint32_t pw[32];
-    float ps0 = 0.f, ps1 = 0.f;
+    float ps = 0.f;
+    // P~ = 2^(z - reference) for the thread's 64 scores, two per instruction; their sum in ps
+    auto exponentials = [&]() {
+      const float mr = m_ref == -INFINITY ? 0.f : m_ref;
+      const float2 zs = make_float2(g.zscale, g.zscale), off = make_float2(-mr, -mr);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int e = 0; e < 64; e += 2) {
-      // every fourth exponential is a polynomial on the FMA pipe (the pass is bound by the
-      // special-function unit)
-      const float z0 = fmaf(v[e], g.zscale, -mr), z1 = fmaf(v[e + 1], g.zscale, -mr);
-      const float p0 = fast_exp2(z0);
-#ifdef DILUTION_ROWPASS_NOPOLY
-      const float p1 = fast_exp2(z1);
-#else
-      const float p1 = (e & 2) ? poly_exp2<4>(z1) : fast_exp2(z1);
-#endif
-      ps0 += p0;
-      ps1 += p1;
-      pw[e >> 1] = pack_bf16(p0, p1);
+      for (int e = 0; e < 64; e += 4) {
+        const float2 z0 = fma2(make_float2(v[e], v[e + 1]), zs, off);
+        const float2 z1 = fma2(make_float2(v[e + 2], v[e + 3]), zs, off);
+        const float2 p0 = make_float2(fast_exp2(z0.x), fast_exp2(z0.y));
+        const float2 p1 = make_float2(fast_exp2(z1.x), fast_exp2(z1.y));
+        acc0 = add2(acc0, p0);
+        acc1 = add2(acc1, p1);
+        pw[e >> 1] = pack_bf16(p0.x, p0.y);
+        pw[(e >> 1) + 1] = pack_bf16(p1.x, p1.y);
+      }
+      const float2 acc = add2(acc0, acc1);
+      ps = acc.x + acc.y;
+    };
+    // The common tile takes no maximum at all: the reference stays where it is as long as the
+    // tile's sum of P~ stays below 2^40 (then every P~ does, and nothing overflowed).
+    // Edge tiles (masking), rows that have not seen a score yet and tiles that outgrow the
+    // reference take the slow path: mask, take the tile's maximum, move the reference there,
+    // rescale what was accumulated under the old one, and form P~ again.
+    const bool edge = (jb * kTileRows + kTileRows - 1 > q0) || ((jb + 1) * kTileRows > g.tk);
+    bool slow = edge || __any_sync(0xffffffffu, m_ref == -INFINITY);
+    if (!slow) {
+      exponentials();
+      slow = __any_sync(0xffffffffu, !(ps < kRefLimit));
+      if (slow) {                      // rare: the scores are still in TMEM, fetch them again
+        tmem_ld32(taddr, v);
+        tmem_ld32(taddr + 32, v + 32);
+        tmem_ld_wait(v);
+        tmem_ld_wait(v + 32);
+      }
     }
-    s += ps0 + ps1;
+    if (slow) {
+      float cmax = -INFINITY;
+      if (edge) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+          const int ja = jb * kTileRows + wg * 64 + e;
+          if (ja > ia || ja >= g.tk) v[e] = -INFINITY;
+          cmax = fmaxf(cmax, v[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) cmax = fmaxf(cmax, v[e]);
+      }
+      const float m_new = fmaxf(m_ref, cmax * g.zscale);
+      if (__any_sync(0xffffffffu, m_new != m_ref)) {
+        const bool fresh = __all_sync(0xffffffffu, m_ref == -INFINITY);   // nothing accumulated yet
+        const float f = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        if (!fresh) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float o[16];
+            tmem_ld16(tO + lane_base + 16 * c, o);
+            tmem_ld_wait16(o);
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) w[e] = __float_as_uint(o[e] * f);
+            tmem_st16(tO + lane_base + 16 * c, w);
+          }
+        }
+        s *= f;
+        m_ref = m_new;
+      }
+      exponentials();
+    }
+    s += ps;
     // P~ goes over the first 32 of this thread's 64 consumed score columns: keys 2c, 2c+1 of the
     // warpgroup's half in column c
     tmem_st16(taddr, pw);
@@ -214,7 +237,7 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
     tmem_ld32(tO + lane_base + 32, o + 32);
     tmem_ld_wait(o);
     tmem_ld_wait(o + 32);
-    sStat[WG * 128 + row] = make_float4(m_ref, s, m_true, 0.f);
+    sStat[WG * 128 + row] = make_float4(m_ref, s, 0.f, 0.f);
     float* give = sX + ((1 - WG) * 128 + row) * 32;         // read by the other warpgroup
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -255,9 +278,10 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
                          pack_bf16(r[8 * c + 4], r[8 * c + 5]), pack_bf16(r[8 * c + 6], r[8 * c + 7]));
       }
       if (WG == 0 && rmax != nullptr) {
-        const float mt = fmaxf(m_true, other.z);
-        rmax[(int64_t)n * g.tq + i] = mt;
-        rden[(int64_t)n * g.tq + i] = den * fast_exp2(m - mt);
+        // the merged reference, not necessarily the row maximum (it lags behind it by design);
+        // every consumer uses the pair only as the log-sum-exp rmax + log2(rden)
+        rmax[(int64_t)n * g.tq + i] = m;
+        rden[(int64_t)n * g.tq + i] = den;
       }
     }
   };
@@ -528,13 +552,24 @@ __global__ void __launch_bounds__(256, 4) backward_key_correction64_kernel(
 #pragma unroll
       for (int e2 = 0; e2 < 16; ++e2) {
         const float4 st = St4[e2];                                // (lse, ghat) of two queries
+#ifdef DILUTION_CORR_PACKED
+        const float2 z = fma2(make_float2(vs[2 * e2], vs[2 * e2 + 1]), make_float2(g.zscale, g.zscale),
+                              make_float2(-st.x, -st.z));
+        float p0 = fast_exp2(z.x), p1 = fast_exp2(z.y);
+#else
         float p0 = fast_exp2(fmaf(vs[2 * e2], g.zscale, -st.x));
         float p1 = fast_exp2(fmaf(vs[2 * e2 + 1], g.zscale, -st.z));
+#endif
         if (MASK) {
           if (dead || ja > i0 + 2 * e2) p0 = 0.f;
           if (dead || ja > i0 + 2 * e2 + 1) p1 = 0.f;
         }
+#ifdef DILUTION_CORR_PACKED
+        const float2 w = mul2(make_float2(p0, p1), make_float2(st.y, st.w));
+        wt[e2] = pack_bf16(w.x, w.y);
+#else
         wt[e2] = pack_bf16(p0 * st.y, p1 * st.w);
+#endif
       }
     };
     if (masked) tile(std::true_type{}); else tile(std::false_type{});
