@@ -291,413 +291,15 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
   if (warp == 0) tmem_free(tmem, 256);
 }
 
-// The pk flavour of the same pass with the score tile cut into two halves of 64 keys, each
-// with its own TMEM buffer: while the threads work on one half, the scores of the half after the
-// next are already being produced, so the MMA round trip no longer sits between two tiles of
-// arithmetic.  S 2 x 64 columns + 2 x 64 accumulator columns = 256; two CTAs per SM.
-// Per half-tile each warpgroup owns 32 keys; P~ goes over the first 16 of a thread's 32 consumed
-// columns; K tiles stream through a four-slot ring (a slot is free once both halves' products
-// of its tile have completed, which the threads learn three half-tiles later).
-constexpr int kPkStages = 4;
-constexpr int kPkSmem = (1 + kPkStages) * (int)kTileBytes + 4096 + 256 + 1024;
-
-__global__ void __launch_bounds__(256, 2) rowpass_pk_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
-    float* __restrict__ rmax, float* __restrict__ rden, float* __restrict__ out) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
-  const uint32_t sQ = smem_u32(smem), sK0 = sQ + kTileBytes;
-  constexpr int kTiles = 1 + kPkStages;
-  float4* sStat = reinterpret_cast<float4*>(smem + kTiles * kTileBytes);            // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTiles * kTileBytes + 4096);
-  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kfull = smem_u32(bars), sdone = smem_u32(bars + 4);               // kfull[4], sdone[2]
-  float* sX = reinterpret_cast<float*>(smem + kTileBytes);    // merge area over the K stages: [2][128][32]
-
-  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
-  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  const int n = (int)(blockIdx.x % g.n);
-  const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
-  const int q0 = g.q_off + ib * kTileRows;
-  const int njb = min(g.tk - 1, q0 + kTileRows - 1) / kTileRows + 1;
-  const int nhalf = 2 * njb;
-
-  if (tid == 0) {
-    ctl->abort = 0;
-    for (int i = 0; i < kPkStages; ++i) mbar_init(kfull + 8 * i, 1);
-    mbar_init(sdone, 1);
-    mbar_init(sdone + 8, 1);
-    fence_barrier_init();
-  }
-  __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const uint32_t tS = tmem, tO = tmem + 128 + 64 * wg;      // two score buffers; this warpgroup's accumulator
-  {
-    uint32_t z[16];
-#pragma unroll
-    for (int c = 0; c < 16; ++c) z[c] = 0u;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) tmem_st16(tO + lane_base + 16 * c, z);
-    tmem_st_wait();
-  }
-  auto load_stage = [&](int jb) {          // thread 0: K tile jb into its ring slot
-    const int st = jb % kPkStages;
-    mbar_expect_tx(kfull + 8 * st, kTileBytes);
-    tma_load_tile(sK0 + kTileBytes * st, &map_k, jb * kTileRows, n, kfull + 8 * st);
-  };
-  constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);
-  // scores of half-tile h into buffer h & 1: keys 64*(h&1).. of K tile h>>1 (K-major: 8 units a row)
-  auto issue_scores = [&](int h) {
-    const Desc dQk = make_desc(sQ, 16, 1024), dKk = make_desc(sK0 + kTileBytes * ((h >> 1) % kPkStages), 16, 1024);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-      mma_ss(tS + 64 * (h & 1), dQk, 2 * kk, dKk, 512 * (h & 1) + 2 * kk, id_s, kk > 0);
-  };
-  if (tid == 0) {
-    mbar_expect_tx(kfull, 2 * kTileBytes);
-    tma_load_tile(sQ, &map_q, ib * kTileRows, n, kfull);
-    tma_load_tile(sK0, &map_k, 0, n, kfull);
-    for (int jb = 1; jb < kPkStages && jb < njb; ++jb) load_stage(jb);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (tid == 0) {
-    mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    issue_scores(0);
-    mma_commit(sdone);
-    issue_scores(1);
-    mma_commit(sdone + 8);
-  }
-  __syncwarp();
-
-  float m_ref = -INFINITY, s = 0.f;
-  const int ia = q0 + row;
-  for (int h = 0; h < nhalf; ++h) {
-    const int jb = h >> 1, b = h & 1;
-    const uint32_t taddr = tS + lane_base + 64 * b + 32 * wg;
-    // scores of half-tile h are ready; the products of half-tile h-2 (same buffer) have completed
-    mbar_wait(sdone + 8 * b, (h >> 1) & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    // every product of K tile (h-3)/2 has completed (its second half was committed with the
-    // scores this iteration waited for two iterations ago): its slot takes tile (h-3)/2 + 4
-    if (tid == 0 && b == 1 && h >= 3 && (h - 3) / 2 + kPkStages < njb) load_stage((h - 3) / 2 + kPkStages);
-    __syncwarp();
-    float v[32];
-    tmem_ld32(taddr, v);
-    tmem_ld_wait(v);
-    uint32_t pw[16];
-    float ps = 0.f;
-    auto exponentials = [&]() {
-      const float mr = m_ref == -INFINITY ? 0.f : m_ref;
-      const float2 zs = make_float2(g.zscale, g.zscale), off = make_float2(-mr, -mr);
-      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        const float2 z0 = fma2(make_float2(v[e], v[e + 1]), zs, off);
-        const float2 z1 = fma2(make_float2(v[e + 2], v[e + 3]), zs, off);
-        const float2 p0 = make_float2(fast_exp2(z0.x), fast_exp2(z0.y));
-        const float2 p1 = make_float2(fast_exp2(z1.x), fast_exp2(z1.y));
-        acc0 = add2(acc0, p0);
-        acc1 = add2(acc1, p1);
-        pw[e >> 1] = pack_bf16(p0.x, p0.y);
-        pw[(e >> 1) + 1] = pack_bf16(p1.x, p1.y);
-      }
-      const float2 acc = add2(acc0, acc1);
-      ps = acc.x + acc.y;
-    };
-    const int key0 = jb * kTileRows + 64 * b;                           // first key of this half-tile
-    const bool edge = (key0 + 63 > q0) || (key0 + 64 > g.tk);
-    bool slow = edge || __any_sync(0xffffffffu, m_ref == -INFINITY);
-    if (!slow) {
-      exponentials();
-      slow = __any_sync(0xffffffffu, !(ps < kRefLimit));
-      if (slow) {                      // rare: the scores are still in TMEM, fetch them again
-        tmem_ld32(taddr, v);
-        tmem_ld_wait(v);
-      }
-    }
-    if (slow) {
-      float cmax = -INFINITY;
-      if (edge) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int ja = key0 + wg * 32 + e;
-          if (ja > ia || ja >= g.tk) v[e] = -INFINITY;
-          cmax = fmaxf(cmax, v[e]);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) cmax = fmaxf(cmax, v[e]);
-      }
-      const float m_new = fmaxf(m_ref, cmax * g.zscale);
-      if (__any_sync(0xffffffffu, m_new != m_ref)) {
-        // the accumulator is touched only by products that have completed: those of half-tile
-        // h-1 were committed together with the scores of half-tile h+1, so wait for that commit
-        if (h >= 1) mbar_wait(sdone + 8 * (b ^ 1), ((h + 1) >> 1) & 1, ctl, &g_status, kErrWaitMma);
-        tc_fence_after();
-        const bool fresh = __all_sync(0xffffffffu, m_ref == -INFINITY);   // nothing accumulated yet
-        const float f = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
-        if (!fresh) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float o[16];
-            tmem_ld16(tO + lane_base + 16 * c, o);
-            tmem_ld_wait16(o);
-            uint32_t w[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) w[e] = __float_as_uint(o[e] * f);
-            tmem_st16(tO + lane_base + 16 * c, w);
-          }
-        }
-        s *= f;
-        m_ref = m_new;
-      }
-      exponentials();
-    }
-    s += ps;
-    tmem_st16(taddr, pw);               // P~ over the first 16 of this thread's 32 consumed columns
-    tmem_st_wait();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      constexpr uint32_t id_pv = instr_desc(128, 64, 0, 1);   // A from TMEM (M = queries), B MN-major
-      const Desc dB = make_desc(sK0 + kTileBytes * (jb % kPkStages), kTileBytes, 1024);
-#pragma unroll
-      for (int w = 0; w < 2; ++w)
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk)      // 16 keys per instruction: 16 rows of 128 B = 128 units
-          mma_ts(tmem + 128 + 64 * w, tS + 64 * b + 32 * w + 8 * kk, dB, 128 * (4 * b + 2 * w + kk), id_pv, 1);
-      if (h + 2 < nhalf) {
-        if (b == 0) {                       // half-tile h+2 opens K tile jb+1
-          const int sn = (jb + 1) % kPkStages;
-          mbar_wait(kfull + 8 * sn, ((jb + 1) / kPkStages) & 1, ctl, &g_status, kErrWaitTma);
-          tc_fence_after();
-        }
-        issue_scores(h + 2);
-      }
-      mma_commit(sdone + 8 * b);
-    }
-    __syncwarp();
-  }
-  // the last two commits cover the last products
-  mbar_wait(sdone, njb & 1, ctl, &g_status, kErrWaitMma);
-  mbar_wait(sdone + 8, njb & 1, ctl, &g_status, kErrWaitMma);
-  tc_fence_after();
-  auto merge = [&](auto wg_c) {
-    constexpr int WG = decltype(wg_c)::value;
-    float o[64];
-    tmem_ld32(tO + lane_base, o);
-    tmem_ld32(tO + lane_base + 32, o + 32);
-    tmem_ld_wait(o);
-    tmem_ld_wait(o + 32);
-    sStat[WG * 128 + row] = make_float4(m_ref, s, 0.f, 0.f);
-    float* give = sX + ((1 - WG) * 128 + row) * 32;         // read by the other warpgroup
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      constexpr int base = 32 * (1 - WG);
-      reinterpret_cast<float4*>(give)[c ^ (row & 7)] =
-          make_float4(o[base + 4 * c], o[base + 4 * c + 1], o[base + 4 * c + 2], o[base + 4 * c + 3]);
-    }
-    __syncthreads();
-    const float4 other = sStat[(1 - WG) * 128 + row];
-    const float m = fmaxf(m_ref, other.x);                  // finite: warpgroup 0 always sees key 0
-    const float f_own = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m);
-    const float f_oth = other.x == -INFINITY ? 0.f : fast_exp2(other.x - m);
-    const float den = s * f_own + other.y * f_oth;
-    const float inv = g.scale / den;
-    const float a_own = f_own * inv, a_oth = f_oth * inv;
-    const float* take = sX + (WG * 128 + row) * 32;
-    const int i = ib * kTileRows + row;
-    if (i < g.tq) {
-      float4* dst = reinterpret_cast<float4*>(out + ((int64_t)n * g.tq + i) * kHeadDim + 32 * WG);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const float4 x = reinterpret_cast<const float4*>(take)[c ^ (row & 7)];
-        dst[c] = make_float4(o[32 * WG + 4 * c] * a_own + x.x * a_oth, o[32 * WG + 4 * c + 1] * a_own + x.y * a_oth,
-                             o[32 * WG + 4 * c + 2] * a_own + x.z * a_oth, o[32 * WG + 4 * c + 3] * a_own + x.w * a_oth);
-      }
-      if (WG == 0) {
-        rmax[(int64_t)n * g.tq + i] = m;        // the merged reference exponent (see above)
-        rden[(int64_t)n * g.tq + i] = den;
-      }
-    }
-  };
-  if (wg == 0) merge(std::integral_constant<int, 0>{}); else merge(std::integral_constant<int, 1>{});
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
-}
-
 // Key half of the softmax-Jacobian correction alone (the reference's BC, kernels.py:777-809),
 // for a backward that has pk saved:  dk = dk_main - scale * P^T (ghat * Q).
 // grid = n * ceil(t/128) key blocks; S^T = K Q^T, lane = key; W = p * ghat goes back into TMEM
 // over the consumed score columns as the A operand (M = keys) of dKc += W Q.  Nothing passes
 // through shared memory and nothing is reduced across CTAs.
-// TMEM: S^T 128 + dKc 64 (256 allocated; two CTAs per SM).
-constexpr int kCorrKeySmem = 3 * kTileBytes + 2048 + 1024 + 256;
-
-__global__ void __launch_bounds__(256, 2) backward_key_correction_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
-    const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ ghat,
-    const float* __restrict__ dk_main, __nv_bfloat16* __restrict__ dk) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
-  const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes;
-  float2* sStat = reinterpret_cast<float2*>(smem + 3 * kTileBytes);           // [2][128] (lse, ghat)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 2048);
-  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2);
-
-  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
-  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  const int n = (int)(blockIdx.x % g.n);
-  const int jb = (int)(blockIdx.x / g.n);
-  const int k0 = jb * kTileRows;
-  const int nsteps = nqb - jb;
-  const int64_t row_base = (int64_t)n * g.tq;
-
-  if (tid == 0) {
-    ctl->abort = 0;
-    for (int i = 0; i < 3; ++i) mbar_init(qfull + 8 * i, 1);
-    fence_barrier_init();
-  }
-  __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  if (wg == 1) {
-    const int i = jb * kTileRows + row;
-    float2 st = make_float2(INFINITY, 0.f);
-    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), ghat[row_base + i]);
-    sStat[row] = st;
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tDK = tmem + 128;
-
-  if (tid == 0) {
-    mbar_expect_tx(qfull, 2 * kTileBytes);
-    tma_load_tile(sK, &map_k, k0, n, qfull);
-    tma_load_tile(sQ0, &map_q, jb * kTileRows, n, qfull);
-    if (nsteps > 1) {
-      mbar_expect_tx(qfull + 8, kTileBytes);
-      tma_load_tile(sQ0 + kTileBytes, &map_q, (jb + 1) * kTileRows, n, qfull + 8);
-    }
-    mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    mma_scores(tS, sK, sQ0, 128);
-    mma_commit(sdone);
-  }
-  __syncwarp();
-
-  const int ja = k0 + row;
-  const bool dead = ja >= g.tk;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  for (int t = 0; t < nsteps; ++t) {
-    const int ib = jb + t, b = t & 1;
-    float nx_max = INFINITY, nx_den = 1.f, nx_gh = 0.f;
-    if (wg == 1 && t + 1 < nsteps && (ib + 1) * kTileRows + row < g.tq) {
-      const int64_t i = row_base + (ib + 1) * kTileRows + row;
-      nx_max = rmax[i];
-      nx_den = rden[i];
-      nx_gh = ghat[i];
-    }
-    // scores of step t are ready; the dKc product of step t-1 (which read the Q stage b^1 and
-    // the W columns) has completed
-    mbar_wait(sdone, t & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    if (tid == 0 && t >= 1 && t + 1 < nsteps) {
-      mbar_expect_tx(qfull + 8 * (b ^ 1), kTileBytes);
-      tma_load_tile(sQ0 + kTileBytes * (b ^ 1), &map_q, (ib + 1) * kTileRows, n, qfull + 8 * (b ^ 1));
-    }
-    __syncwarp();
-    const int i0 = ib * kTileRows + 64 * wg;
-    const bool masked_tile = dead || t == 0;
-    const float4* St4 = reinterpret_cast<const float4*>(sStat + b * 128 + 64 * wg);
-    auto tile = [&](auto mask_tag) {
-      constexpr bool MASK = decltype(mask_tag)::value;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float vs[32];
-        uint32_t wt[16];
-        tmem_ld32(tS + lane_base + 64 * wg + 32 * c, vs);
-        tmem_ld_wait(vs);
-#pragma unroll
-        for (int e2 = 0; e2 < 16; ++e2) {
-          const float4 st = St4[c * 16 + e2];             // (lse, ghat) of two queries
-          float p0 = fast_exp2(fmaf(vs[2 * e2], g.zscale, -st.x));
-          float p1 = fast_exp2(fmaf(vs[2 * e2 + 1], g.zscale, -st.z));
-          if (MASK) {
-            if (dead || ja > i0 + c * 32 + 2 * e2) p0 = 0.f;
-            if (dead || ja > i0 + c * 32 + 2 * e2 + 1) p1 = 0.f;
-          }
-          wt[e2] = pack_bf16(p0 * st.y, p1 * st.w);
-        }
-        tmem_st16(tS + lane_base + 64 * wg + 32 * c, wt);
-      }
-    };
-    if (masked_tile) tile(std::true_type{}); else tile(std::false_type{});
-    if (wg == 1 && t + 1 < nsteps) sStat[(b ^ 1) * 128 + row] = make_float2(nx_max + log2f(nx_den), nx_gh);
-    tmem_st_wait();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);
-      const Desc dQm = make_desc(sQ0 + kTileBytes * b, kTileBytes, 1024);
-#pragma unroll
-      for (int kq = 0; kq < 8; ++kq)
-        mma_ts(tDK, tS + 64 * (kq >> 2) + 32 * ((kq & 3) >> 1) + 8 * (kq & 1), dQm, 128 * kq, id_kd,
-               (t > 0 || kq > 0));
-      if (t + 1 < nsteps) {
-        mbar_wait(qfull + 8 * (b ^ 1), ((t + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
-        tc_fence_after();
-        mma_scores(tS, sK, sQ0 + kTileBytes * (b ^ 1), 128);
-      }
-      mma_commit(sdone);
-    }
-    __syncwarp();
-  }
-  mbar_wait(sdone, nsteps & 1, ctl, &g_status, kErrWaitMma);
-  tc_fence_after();
-  {
-    float a[32];
-    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
-    tmem_ld32(tDK + lane_base + 32 * wg, a);
-    tmem_ld_wait(a);
-    if (!dead) {
-      float m[32];
-#pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        const float4 x = *reinterpret_cast<const float4*>(dk_main + o + e);
-        m[e] = x.x - g.scale * a[e];
-        m[e + 1] = x.y - g.scale * a[e + 1];
-        m[e + 2] = x.z - g.scale * a[e + 2];
-        m[e + 3] = x.w - g.scale * a[e + 3];
-      }
-#pragma unroll
-      for (int e = 0; e < 32; e += 8)
-        *reinterpret_cast<uint4*>(dk + o + e) =
-            make_uint4(pack_bf16(m[e], m[e + 1]), pack_bf16(m[e + 2], m[e + 3]),
-                       pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
-}
-
-// The same pass in half-steps of 64 queries: S^T [128 keys x 64 queries] needs 64 TMEM columns, so
-// a CTA allocates 128 and four CTAs share an SM (32 warps to hide each other's MMA round trips,
-// as in the column-sum pass).  The two warpgroups split a half-step's 64 query columns.
+// The pass runs in half-steps of 64 queries: S^T [128 keys x 64 queries] needs 64 TMEM columns, so
+// a CTA allocates 128 (S^T 64 + dKc 64) and four CTAs share an SM (32 warps to hide each other's
+// MMA round trips, as in the column-sum pass; a version with 128-query steps and two CTAs per SM
+// measured 5% slower).  The two warpgroups split a half-step's 64 query columns.
 constexpr int kCorrKey64Smem = 3 * kTileBytes + 2048 + 1024 + 256;
 static_assert(5 * (kCorrKey64Smem + 1024) > 233472, "at most four CTAs of the half-step correction pass share an SM");
 
@@ -881,17 +483,10 @@ inline int rowstats_pk(const void* q, const void* k, const Geom& g, float* rmax,
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-#ifdef DILUTION_ROWPASS_SINGLE
   auto kern = rowpass_product_kernel<1, float>;
   constexpr int smem = RowpassSmem<1>::kBytes > kTwoPerSm ? RowpassSmem<1>::kBytes : kTwoPerSm;
   if (int rc = set_smem_attr((const void*)kern, smem, err, errlen)) return rc;
   kern<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mk, g, rmax, rden, pk);
-#else
-  constexpr int smem = kPkSmem > kTwoPerSm ? kPkSmem : kTwoPerSm;
-  static_assert(2 * (smem + 1024) <= 233472, "two CTAs of the pk row pass fit one SM");
-  if (int rc = set_smem_attr((const void*)rowpass_pk_kernel, smem, err, errlen)) return rc;
-  rowpass_pk_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, g, rmax, rden, pk);
-#endif
   return launch_status("tc rowstats_pk", err, errlen);
 }
 
@@ -918,19 +513,11 @@ inline int backward_tail_with_pk(const CUtensorMap& mq, const CUtensorMap& mk, c
                                  const float* dq_main, const float* pk, void* dq, void* dk, cudaStream_t st,
                                  char* err, size_t errlen, void (*mark)(const char*, cudaStream_t, int)) {
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
-#ifdef DILUTION_CORR_KEY128
-  constexpr int smem = kCorrKeySmem > kTwoPerSm ? kCorrKeySmem : kTwoPerSm;
-  if (int rc = set_smem_attr((const void*)backward_key_correction_kernel, smem, err, errlen)) return rc;
-  mark("tc_backward_key_correction", st, 0);
-  backward_key_correction_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, ghat, dk_main,
-                                                                         (__nv_bfloat16*)dk);
-#else
   constexpr int smem = kCorrKey64Smem;
   if (int rc = set_smem_attr((const void*)backward_key_correction64_kernel, smem, err, errlen)) return rc;
   mark("tc_backward_key_correction", st, 0);
   backward_key_correction64_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, ghat,
                                                                            dk_main, (__nv_bfloat16*)dk);
-#endif
   mark("tc_backward_key_correction", st, 1);
   if (int rc = launch_status("tc backward_key_correction", err, errlen)) return rc;
   const int64_t n4 = g.n * g.tq * kHeadDim / 4;
