@@ -793,8 +793,12 @@ def run_prefill(c, args):
         events[name] = torch.cuda.Event(enable_timing=True)
         events[name].record()
 
+    c.L.profile(True)
+    c.L.profile_collect()
     out, demand = step(mark)
     c.barrier()
+    kernels_ms = {name: tot / cnt for name, (cnt, tot) in c.L.profile_collect().items()}
+    c.L.profile(False)
     phases, prev = {}, "start"
     for name in names:
         phases[name] = c.max_over_ranks(events[prev].elapsed_time(events[name]))
@@ -804,7 +808,7 @@ def run_prefill(c, args):
     flops = causal_flops(H, T, D, 2)
     return {"metric": "prefill TFLOP/s @T=128K (B1 H16 d64, forward + demand)",
             "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
-            "scaling": "strong", "device_status": status, "phases_ms": phases,
+            "scaling": "strong", "device_status": status, "phases_ms": phases, "kernels_ms": kernels_ms,
             "demand_sum_over_T": None if demand_sum is None else demand_sum / T,
             "config": {"workload": f"prefill_B1_H{H}_T{T}_d{D}", "query_chunk_bounds": bounds,
                        "parallelism": f"sequence-parallel x{c.world}: triangular point-to-point K/V exchange + "
