@@ -180,11 +180,8 @@ __device__ __forceinline__ float load_lse(const float* __restrict__ rmax, const 
 
 // ---------------------------------------------------------------- pass 1: row statistics
 // grid = n * ceil(tq/128), longest rows first.  S = Q K^T, lane = query: each
-// thread sums 2^(z - m) over its 64 key columns of the tile against a lazily moved
-// reference exponent m; the two halves of a row are merged once at the end.  rmax holds
-// the merged reference (not necessarily the exact row maximum): the pair (rmax, rden) is
-// exact as the log-sum-exp rmax + log2(rden), which is all the other passes use.
-// TMEM: 128 columns; 4 CTAs per SM.
+// thread reduces its 64 key columns of the tile with an online max / sum; the two
+// halves of a row are merged once at the end.  TMEM: 128 columns; 4 CTAs per SM.
 constexpr int kRowstatsSmem = 3 * kTileBytes + 1024 + 1024 + 256;
 
 __global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -247,55 +244,39 @@ __global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant_
     }
     __syncwarp();
     const bool edge = (jb * kTileRows + kTileRows - 1 > q0) || ((jb + 1) * kTileRows > g.tk);
-    // m is a reference exponent, not a running maximum: the common chunk takes no maximum at
-    // all and keeps m as long as its sum of 2^(z - m) stays below 2^40 (nothing overflowed, fp32
-    // sums absorb the range).  Edge tiles (masking), rows that have not seen a score yet and
-    // chunks that outgrow the reference take the slow path: mask, take the chunk's maximum, move
-    // the reference there, rescale the sum, form the exponentials again.
+    // the mask arithmetic exists only in the instantiation used for edge tiles
+    auto tile = [&](auto edge_tag) {
+      constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float v[32];
-      tmem_ld32(taddr + 32 * c, v);
-      tmem_ld_wait(v);
-      float ps = 0.f;
-      auto exponentials = [&]() {
-        const float mr = m == -INFINITY ? 0.f : m;
-        const float2 zs = make_float2(g.zscale, g.zscale), off = make_float2(-mr, -mr);
-        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float2 z0 = fma2(make_float2(v[e], v[e + 1]), zs, off);
-          const float2 z1 = fma2(make_float2(v[e + 2], v[e + 3]), zs, off);
-          acc0 = add2(acc0, make_float2(fast_exp2(z0.x), fast_exp2(z0.y)));
-          acc1 = add2(acc1, make_float2(fast_exp2(z1.x), fast_exp2(z1.y)));
-        }
-        const float2 acc = add2(acc0, acc1);
-        ps = acc.x + acc.y;
-      };
-      bool slow = edge || __any_sync(0xffffffffu, m == -INFINITY);
-      if (!slow) {
-        exponentials();
-        slow = __any_sync(0xffffffffu, !(ps < 1099511627776.f));
-      }
-      if (slow) {
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(taddr + 32 * c, v);
+        tmem_ld_wait(v);
         float cmax = -INFINITY;          // max of the raw scores (zscale > 0 keeps the order)
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          if (edge) {
+          if (EDGE) {
             const int ja = jb * kTileRows + wg * 64 + c * 32 + e;
             if (ja > ia || ja >= g.tk) v[e] = -INFINITY;
           }
           cmax = fmaxf(cmax, v[e]);
         }
         const float nm = fmaxf(m, cmax * g.zscale);
-        if (nm != m) {
-          s *= fast_exp2(m - nm);        // m == -inf: s is 0 and stays 0
+        if (nm > -INFINITY) {
+          float ps = 0.f;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            // the pass is bound by the special-function unit: every fourth exponential
+            // is a polynomial on the FMA pipe instead
+            const float z = fmaf(v[e], g.zscale, -nm);
+            ps += (e & 3) == 3 ? poly_exp2<4>(z) : fast_exp2(z);
+          }
+          s = s * fast_exp2(m - nm) + ps;
           m = nm;
         }
-        exponentials();
       }
-      s += ps;
-    }
+    };
+    if (edge) tile(std::true_type{}); else tile(std::false_type{});
     tc_fence_before();
     __syncthreads();
   }
