@@ -433,11 +433,11 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
     mm = next((m for key, m in share.items() if key in dom), 0)
     achieved = causal_flops(n_rows, T, D, mm) / (kernels_ms[dom] * 1e-3) / 1e12
     # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of this kernel in one
-    # ncu capture at T=4096 (64 rows, 528 causal 128x128 tiles per row: 1354.26 MB), scaled by the
+    # ncu capture at T=4096 (64 rows, 528 causal 128x128 tiles per row: 1341.02 MB), scaled by the
     # number of causal tiles this launch processes -- the dQ tile reductions dominate it and grow
     # with the tile count.  Only the backward main pass has a captured figure.
     tiles = n_rows * (T // 128) * (T // 128 + 1) // 2
-    traffic = 1354.26e6 / (64 * 528) * tiles if "backward_main" in dom else None
+    traffic = 1341.02e6 / (64 * 528) * tiles if "backward_main" in dom else None
     return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
             "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
             "traffic_source": "constant from one ncu capture of this kernel at T=4096, scaled by causal "
