@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libdilution_b200.so")
 
 F32, BF16 = 0, 1
 PREC = {"ieee": 0, "tf32": 1, "bf16": 2}
-CARRY_ROWS = 32
+CARRY_ROWS = 32   # the fp32 kernels' checkpoint spacing; see carry_rows()
 
 _P, _I, _L, _F, _Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 
@@ -29,12 +29,13 @@ SIGNATURES = {
     "dilution_rowstats": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P]),
     "dilution_rowstats_pk": (_I, [_P, _P, _I, _I, _L, _L, _I, _F, _P, _P, _P, _P]),
     "dilution_softmax_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _P]),
-    "dilution_colsum_scan": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _P, _P, _P]),
+    "dilution_carry_rows": (_I, [_I, _I, _I, _I]),
+    "dilution_colsum_scan": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _I, _P, _P, _P]),
     "dilution_forward_main": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _F,
-                                   _P, _P, _P, _P, _P, _P, _P, _P]),
+                                   _P, _P, _P, _I, _P, _P, _P, _P, _P]),
     "dilution_backward_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F,
-                               _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+                               _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_decode_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_decode": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
     "dilution_decode_append": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P, _P]),
@@ -90,6 +91,16 @@ def profile_collect() -> dict:
         name, count, ms = line.split()
         out[name] = (int(count), float(ms))
     return out
+
+
+def carry_rows(dtype_code: int, precision_code: int, head_dim: int, training: bool) -> int:
+    """Query rows per demand checkpoint for this case (dilution_carry_rows of the C ABI).
+    DILUTION_TRAIN_CARRY_ROWS=32 in the environment selects the tensor-core backward with two
+    compute warpgroups (32 queries per thread) instead of four (16 per thread)."""
+    rows = int(load().dilution_carry_rows(dtype_code, precision_code, head_dim, 1 if training else 0))
+    if training and rows == 16 and os.environ.get("DILUTION_TRAIN_CARRY_ROWS") == "32":
+        rows = 32
+    return rows
 
 
 def tensor_core_path(dtype_code: int, precision_code: int, head_dim: int) -> bool:

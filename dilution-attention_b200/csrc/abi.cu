@@ -101,8 +101,13 @@ int check_common(const char* fn, int dtype, int precision, int64_t n, int64_t tq
   return DILUTION_OK;
 }
 
-dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps) {
+// Checkpoint spacings: the tensor-core kernels take 16, 32 or 64 query rows; the fp32 kernels 32.
+int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_offset, int carry_rows);
+
+dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps,
+                    int carry_rows = dil::kCarryRows) {
   dil::Geom g;
+  g.carry_rows = carry_rows;
   g.n = n;
   g.tq = (int)tq;
   g.tk = (int)tk;
@@ -341,7 +346,28 @@ int static_scratch(void** out) {
 
 }  // namespace
 
+namespace {
+int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_offset, int carry_rows) {
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, q_offset)) {
+    if (carry_rows == 16 || carry_rows == 32 || carry_rows == 64) return DILUTION_OK;
+    return fail(DILUTION_ERR_ARG, "%s: carry_rows must be 16, 32 or 64 (got %d)", fn, carry_rows);
+  }
+#endif
+  if (carry_rows == dil::kCarryRows) return DILUTION_OK;
+  return fail(DILUTION_ERR_ARG, "%s: the fp32 kernels store a checkpoint every %d query rows (got %d)", fn,
+              dil::kCarryRows, carry_rows);
+}
+}  // namespace
+
 extern "C" {
+
+int dilution_carry_rows(int dtype, int precision, int d, int training) {
+#ifdef DILUTION_TENSOR_PATH
+  if (dil::tc::supported(dtype, precision, d, 0)) return training ? 16 : 64;
+#endif
+  return dil::kCarryRows;
+}
 
 int dilution_version(void) { return DILUTION_ABI_VERSION; }
 
@@ -461,11 +487,12 @@ int dilution_softmax_forward(const void* q, const void* k, const void* v, int dt
 int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision, int64_t n,
                          int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
                          const float* rmax, const float* rden, const float* carry_base,
-                         float* carry, float* total, void* stream) {
+                         int carry_rows, float* carry, float* total, void* stream) {
   if (int rc = check_common("dilution_colsum_scan", dtype, precision, n, tq, tk, q_offset, d)) return rc;
   if (!q || !k || !rmax || !rden || !carry || !total)
     return fail(DILUTION_ERR_ARG, "dilution_colsum_scan: null pointer");
-  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f);
+  if (int rc = check_carry_rows("dilution_colsum_scan", dtype, precision, d, q_offset, carry_rows)) return rc;
+  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, 0.f, carry_rows);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
   if (dil::tc::supported(dtype, precision, d, q_offset)) {
@@ -480,12 +507,13 @@ int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
 int dilution_forward_main(const void* q, const void* k, const void* v, int dtype, int precision,
                           int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
                           float eps, const float* rmax, const float* rden, const float* carry,
-                          const float* carry_base, float* out, float* ssum, float* pk,
+                          int carry_rows, const float* carry_base, float* out, float* ssum, float* pk,
                           void* stream) {
   if (int rc = check_common("dilution_forward_main", dtype, precision, n, tq, tk, q_offset, d)) return rc;
   if (!q || !k || !v || !rmax || !rden || !carry || !out || !ssum)
     return fail(DILUTION_ERR_ARG, "dilution_forward_main: null pointer");
-  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, eps);
+  if (int rc = check_carry_rows("dilution_forward_main", dtype, precision, d, q_offset, carry_rows)) return rc;
+  const dil::Geom g = make_geom(n, tq, tk, q_offset, scale, eps, carry_rows);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH
 #if DILUTION_TC_HAS_MAIN
@@ -509,15 +537,17 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d) {
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
                       int64_t n, int64_t t, int d, float scale, float eps, const void* dout,
                       int dout_dtype, const float* out, const float* rmax, const float* rden, const float* carry,
-                      const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
-                      void* dk, void* dv, void* stream) {
+                      int carry_rows, const float* total, const float* ssum, const float* pk, void* scratch,
+                      void* dq, void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_backward", dtype, precision, n, t, t, 0, d)) return rc;
   if (!q || !k || !v || !dout || !out || !rmax || !rden || !carry || !total || !ssum || !scratch ||
       !dq || !dk || !dv)
     return fail(DILUTION_ERR_ARG, "dilution_backward: null pointer");
   if (dout_dtype != DILUTION_F32 && dout_dtype != DILUTION_BF16)
     return fail(DILUTION_ERR_ARG, "dilution_backward: dout_dtype must be DILUTION_F32 or DILUTION_BF16");
-  const dil::Geom g = make_geom(n, t, t, 0, scale, eps);
+  if (int rc = check_carry_rows("dilution_backward", dtype, precision, d, 0, carry_rows)) return rc;
+  if (carry_rows == 64) return fail(DILUTION_ERR_ARG, "dilution_backward: checkpoints every 64 rows serve forward-only calls");
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, carry_rows);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef DILUTION_TENSOR_PATH

@@ -8,7 +8,7 @@
 namespace dil {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kCarryRows = 32;  // query rows per demand checkpoint (DILUTION_CARRY_ROWS)
+constexpr int kCarryRows = 32;  // query rows per demand checkpoint of the fp32 kernels
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -111,6 +111,7 @@ struct Geom {
   float zscale;   // scale * log2(e): scores are kept in the log2 domain
   float scale;
   float eps;
+  int carry_rows; // query rows per demand checkpoint (16, 32 or 64)
 };
 
 }  // namespace dil

@@ -39,7 +39,7 @@ import torch
 from . import _lib
 
 EPS = 1e-9                      # kernels.py:66-67 of the reference, twice
-CARRY_ROWS = _lib.CARRY_ROWS    # query rows per demand checkpoint
+CARRY_ROWS = _lib.CARRY_ROWS    # query rows per demand checkpoint of the fp32 kernels
 KEY_FORWARD_MIN_SEQ = 256       # read by the reference's scripts; no meaning here
 HAS_TRITON = False              # this backend never uses Triton
 HAS_CUDA_LIB = _lib.available()
@@ -91,7 +91,7 @@ def _prepare(q, k, v, dot_precision):
 
 
 def _forward_rows(lib, qf, kf, vf, code, prec, scale, out, ssum, rmax, rden, carry, total, pk,
-                  q_offset=0, carry_base=None):
+                  carry_rows, q_offset=0, carry_base=None):
     """Passes 1-3 on a slab of (batch*head) rows.  On the tensor-core path a requested pk comes
     out of pass 1; otherwise out of pass 3 (the fp32 kernel)."""
     n, tq, d = qf.shape
@@ -106,11 +106,11 @@ def _forward_rows(lib, qf, kf, vf, code, prec, scale, out, ssum, rmax, rden, car
         _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
                                          d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
     _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
-                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None,
+                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None, carry_rows,
                                         carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
     _lib.check(lib.dilution_forward_main(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec,
                                          n, tq, tk, q_offset, d, scale, EPS,
-                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
+                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), carry_rows,
                                          _ptr(carry_base), out.data_ptr(), ssum.data_ptr(), _ptr(pk), st),
                "dilution_forward_main")
 
@@ -127,6 +127,7 @@ def dilution_attention_forward(
     num_stages: int = 2,
     _save_pk: bool = False,
     scratch_budget_gib: float = 16.0,
+    _training: bool | None = None,
 ):
     """Fused forward; returns fp32 (B, H, T, D)  (kernels.py:328-455).
 
@@ -135,7 +136,10 @@ def dilution_attention_forward(
     dot_precision, num_warps and committed_total (B, H, T) fp32 — the inclusive
     column totals of p, i.e. the decode accumulator after this prefix.
     `carry` holds one per-key demand checkpoint every aux["bwd_block_m"] query
-    rows; entries for keys a row block cannot see are unwritten.
+    rows; entries for keys a row block cannot see are unwritten.  The spacing
+    follows the kernels that will read it: 16 rows when the autograd op will run
+    its backward on the tensor-core kernels, 64 for their forward-only calls, 32
+    on the fp32 kernels (the reference stores every 32 or 64, kernels.py:374-377).
 
     Without return_aux the (batch*head) rows are processed in slabs so that the
     quadratic carry scratch stays under scratch_budget_gib; rows are independent,
@@ -146,7 +150,9 @@ def dilution_attention_forward(
     batch, heads, seq, head_dim = q.shape
     dev = q.device
     scale = 1.0 / math.sqrt(head_dim)
-    ncb = (seq + CARRY_ROWS - 1) // CARRY_ROWS
+    training = _save_pk if _training is None else _training
+    carry_rows = _lib.carry_rows(code, prec, head_dim, training)
+    ncb = (seq + carry_rows - 1) // carry_rows
 
     f32 = dict(device=dev, dtype=torch.float32)
     out = torch.empty(n, seq, head_dim, **f32)
@@ -165,11 +171,11 @@ def dilution_attention_forward(
         b = min(a + rows, n)
         _forward_rows(lib, qf[a:b], kf[a:b], vf[a:b], code, prec, scale, out[a:b], ssum[a:b],
                       rmax[a:b], rden[a:b], carry[: b - a], total[a:b],
-                      None if pk is None else pk[a:b])
+                      None if pk is None else pk[a:b], carry_rows)
 
     result = out.reshape(batch, heads, seq, head_dim)
     if return_aux:
-        aux = dict(pk=pk, rmax=rmax, rden=rden, carry=carry, ssum=ssum, bwd_block_m=CARRY_ROWS,
+        aux = dict(pk=pk, rmax=rmax, rden=rden, carry=carry, ssum=ssum, bwd_block_m=carry_rows,
                    block_m=block_m, block_n=block_n, dot_precision=dot_precision,
                    num_warps=num_warps,
                    committed_total=total.reshape(batch, heads, seq))
@@ -188,7 +194,9 @@ class _DilutionAttentionFn(torch.autograd.Function):
                                       _lib.PREC[dot_precision], q.shape[-1])
         out, aux = dilution_attention_forward(
             q, k, v, dot_precision=dot_precision, return_aux=True,
-            _save_pk=any(ctx.needs_input_grad[:3]) and (TC_SAVE_PK or not on_tc))
+            _save_pk=any(ctx.needs_input_grad[:3]) and (TC_SAVE_PK or not on_tc),
+            _training=any(ctx.needs_input_grad[:3]))
+        ctx.carry_rows = aux["bwd_block_m"]
         ctx.save_for_backward(q, k, v, out, aux["rmax"], aux["rden"], aux["carry"], aux["ssum"], aux["pk"],
                               aux["committed_total"])
         ctx.dot_precision = dot_precision
@@ -219,7 +227,7 @@ class _DilutionAttentionFn(torch.autograd.Function):
         _lib.check(lib.dilution_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim,
             1.0 / math.sqrt(head_dim), EPS, dof.data_ptr(), do_code, of.data_ptr(),
-            rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), total.data_ptr(), ssum.data_ptr(),
+            rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), ctx.carry_rows, total.data_ptr(), ssum.data_ptr(),
             _ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _stream(dev)),
             "dilution_backward")
         shape4 = (batch, heads, seq, head_dim)

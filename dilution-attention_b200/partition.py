@@ -143,7 +143,10 @@ def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "
     prec = _lib.PREC[dot_precision]
     scale = 1.0 / math.sqrt(d)
     f32 = dict(device=dev, dtype=torch.float32)
-    ncb = (tq + K.CARRY_ROWS - 1) // K.CARRY_ROWS
+    # forward only: the coarsest spacing the kernels for this case take (an offset that is not a
+    # multiple of the tile size runs on the fp32 kernels)
+    carry_rows = _lib.carry_rows(code, prec, d, False) if q_offset % TILE == 0 else _lib.CARRY_ROWS
+    ncb = (tq + carry_rows - 1) // carry_rows
     rmax, rden, ssum = (torch.empty(rows, tq, **f32) for _ in range(3))
     carry = torch.empty(rows, ncb, tk, **f32)
     total = torch.empty(rows, tk, **f32)
@@ -152,7 +155,7 @@ def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "
     _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, rows, tq, tk, q_offset,
                                      d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
     _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, rows, tq, tk, q_offset,
-                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None,
+                                        d, scale, rmax.data_ptr(), rden.data_ptr(), None, carry_rows,
                                         carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")
     mark("passes_1_2")
     base = demand_prefix
@@ -163,7 +166,7 @@ def prefill_chunk(q_local, k_seen, v_seen, q_offset: int, dot_precision: str = "
     mark("exchange")
     _lib.check(lib.dilution_forward_main(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec,
                                          rows, tq, tk, q_offset, d, scale, K.EPS,
-                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
+                                         rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(), carry_rows,
                                          None if base is None else base.data_ptr(),
                                          out.data_ptr(), ssum.data_ptr(), None, st),
                "dilution_forward_main")

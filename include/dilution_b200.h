@@ -22,10 +22,13 @@
  *  - `q_offset`: absolute position of local query row 0 (0 for a whole sequence;
  *    a multiple of 128 for a sequence-parallel rank that owns a query chunk).
  *    Query i (local) sees keys j <= i + q_offset, j < tk;
- *  - carry rows are checkpoints of per-key cumulative demand every
- *    DILUTION_CARRY_ROWS query rows: carry[n][rb][j] = (carry_base[n][j]) +
- *    sum over local rows i < rb*DILUTION_CARRY_ROWS of p_ij.  Entries for keys
- *    a row block cannot see are left unwritten (as kernels.py:353-354);
+ *  - carry rows are checkpoints of per-key cumulative demand every `carry_rows`
+ *    query rows (aux["bwd_block_m"] of the reference, kernels.py:374-377):
+ *    carry[n][rb][j] = (carry_base[n][j]) + sum over local rows i < rb*carry_rows
+ *    of p_ij.  Entries for keys a row block cannot see are left unwritten (as
+ *    kernels.py:353-354).  The spacing is the caller's choice among what the kernels
+ *    for its case take — dilution_carry_rows() names the preferred one — and must be
+ *    the same in every call that shares a carry buffer;
  *  - return value 0 = ok; otherwise an error code, with a message available
  *    from dilution_last_error() (thread-local).
  */
@@ -39,8 +42,8 @@
 extern "C" {
 #endif
 
-#define DILUTION_ABI_VERSION 2
-#define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint (aux["bwd_block_m"]) */
+#define DILUTION_ABI_VERSION 3
+#define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint of the fp32 kernels */
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
 enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */
@@ -86,6 +89,13 @@ unsigned long long dilution_launch_count(void);
 int dilution_profile_enable(int on);
 int dilution_profile_collect(char* buf, size_t cap);
 
+/* Preferred checkpoint spacing for this case: 16 query rows when a backward will follow on the
+ * tensor-core kernels (bf16, BF16 precision, d == 64: its main pass gives every thread 16
+ * queries), 64 for their forward-only calls (a quarter of the scratch), 32 for the fp32
+ * kernels (the reference's bwd_block_m).  The tensor-core kernels accept 16, 32 and 64 (the
+ * backward 16 and 32), the fp32 kernels 32 only. */
+int dilution_carry_rows(int dtype, int precision, int d, int training);
+
 /* Pass 1 — causal-softmax row statistics for every query.
  * Replaces _dilution_k1's sweep 1 (kernels.py:158-185).
  * rmax, rden: (n, tq) fp32 out. */
@@ -117,13 +127,13 @@ int dilution_softmax_forward(const void* q, const void* k, const void* v, int dt
  * Replaces _dilution_k1's sweep 2 (kernels.py:190-198) + _dilution_scan (:250-264).
  * carry_base: optional (n, tk) fp32 demand already committed by earlier query
  *   chunks (sequence-parallel ranks), or NULL.
- * carry: (n, ceil(tq/DILUTION_CARRY_ROWS), tk) fp32 out.
+ * carry: (n, ceil(tq/carry_rows), tk) fp32 out.
  * total: (n, tk) fp32 out, column sums of p over the LOCAL rows (the decode
  *   accumulator `committed_total`, kernels.py:451-453, when tq covers the sequence). */
 int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
                          int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d, float scale,
                          const float* rmax, const float* rden, const float* carry_base,
-                         float* carry, float* total, void* stream);
+                         int carry_rows, float* carry, float* total, void* stream);
 
 /* Pass 3 — main forward pass: rebuild p, committed = carry + in-tile exclusive
  * column cumsum, share = p/(committed+p+eps), out = (share@v)/(rowsum(share)+eps).
@@ -136,7 +146,7 @@ int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
 int dilution_forward_main(const void* q, const void* k, const void* v, int dtype, int precision,
                           int64_t n, int64_t tq, int64_t tk, int64_t q_offset, int d,
                           float scale, float eps,
-                          const float* rmax, const float* rden, const float* carry,
+                          const float* rmax, const float* rden, const float* carry, int carry_rows,
                           const float* carry_base,
                           float* out, float* ssum, float* pk, void* stream);
 
@@ -158,8 +168,8 @@ size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
 int dilution_backward(const void* q, const void* k, const void* v, int dtype, int precision,
                       int64_t n, int64_t t, int d, float scale, float eps,
                       const void* dout, int dout_dtype, const float* out,
-                      const float* rmax, const float* rden, const float* carry, const float* total,
-                      const float* ssum, const float* pk,
+                      const float* rmax, const float* rden, const float* carry, int carry_rows,
+                      const float* total, const float* ssum, const float* pk,
                       void* scratch, void* dq, void* dk, void* dv, void* stream);
 
 /* Bytes of scratch dilution_decode needs for n rows at this `length`. */

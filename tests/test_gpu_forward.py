@@ -86,6 +86,26 @@ def test_checkpoints_totals_and_row_stats(kernels, seq):
     torch.testing.assert_close(lse, rmax + torch.log2(rden), atol=1e-4, rtol=1e-5)
 
 
+@pytest.mark.parametrize("training", [False, True])
+@pytest.mark.parametrize("seq", [64, 200, 1000])
+def test_tensor_core_checkpoints_at_both_spacings(kernels, seq, training):
+    """bf16, d=64: the column-sum pass stores a checkpoint every 16 rows when a backward will
+    follow and every 64 rows otherwise; both against the oracle's block carry."""
+    q, k, v, _ = make_inputs(1, 2, seq, 64, 60 + seq, scales=(0.7, 0.7, 1.0, 1.0))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    out, aux = kernels.dilution_attention_forward(*_cuda(qb, kb, vb), dot_precision="bf16", return_aux=True,
+                                                  _training=training)
+    bm = aux["bwd_block_m"]
+    assert bm == (16 if training else 64)
+    carry = aux["carry"].cpu()
+    assert carry.shape[1] == (seq + bm - 1) // bm
+    expected = O.block_carry(qb.float(), kb.float(), bm).reshape(2, -1, seq)
+    for rb in range(carry.shape[1]):
+        end = min((rb + 1) * bm, seq)      # only the causal key range is initialised
+        assert (carry[:, rb, :end] - expected[:, rb, :end]).abs().max().item() < 2e-2 * max(1.0, expected.abs().max().item())
+    assert (out.cpu() - O.dilution_dense(qb.float(), kb.float(), vb.float())).abs().max().item() < 2e-2
+
+
 def test_bf16_inputs_against_fp32_oracle(kernels):
     q, k, v, _ = make_inputs(2, 4, 128, 64, 0)
     ref = O.dilution_dense(q, k, v)
