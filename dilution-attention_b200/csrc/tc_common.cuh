@@ -168,6 +168,13 @@ __device__ __forceinline__ void tmem_ld_wait(float* v) {
                : "memory");
 }
 
+// One fp32 column of this thread's lane.
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  *v = __uint_as_float(r);
+}
+
 // 16 consecutive fp32 columns of this thread's lane.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);

@@ -17,6 +17,7 @@
 // main reverse pass runs 384 threads, one CTA per SM, with a dedicated issuing warpgroup.
 #pragma once
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -644,6 +645,203 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   if (warp == 0) tmem_free(tmem, 256);
 }
 
+// The same pass with four warpgroups: each takes 32 of the tile's 128 queries from a checkpoint of
+// its own (g.carry_rows 16 or 32), so a thread walks 32 queries per tile instead of 64 and twice
+// the warps cover the share@V / next-score MMA round trip between tiles.  512 threads at 64
+// registers; two CTAs per SM as before.
+
+
+__global__ void __launch_bounds__(512, 2) forward_main4_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, Geom g, const float* __restrict__ rmax,
+    const float* __restrict__ rden, const float* __restrict__ carry,
+    const float* __restrict__ carry_base, float* __restrict__ out, float* __restrict__ ssum) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {                      // no slack is requested: refuse instead of overrunning
+    if (threadIdx.x == 0) atomicCAS(&g_status, 0, kErrAlign);
+    return;
+  }
+  const uint32_t sQ = smem_u32(smem), sK0 = sQ + kTileBytes, sV = sQ + 3 * kTileBytes;
+  // a [128 keys][64] bf16 tile of ones right behind V: the second 64-column group of the B
+  // operand of share @ [V | ones] (N = 80), so the row sums come out of the same MMA
+  const uint32_t sOnes = sQ + 4 * kTileBytes, sSh = sQ + 5 * kTileBytes;
+  uint8_t* ones_ptr = smem + 4 * kTileBytes;
+  float* sL = reinterpret_cast<float*>(smem + 7 * kTileBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * kTileBytes + 512);
+  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
+  const uint32_t kfull = smem_u32(bars), vfull = smem_u32(bars + 2), sdone = smem_u32(bars + 3);
+
+  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
+  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
+  const int ncb = (g.tq + g.carry_rows - 1) / g.carry_rows;
+  const int n = (int)(blockIdx.x % g.n);
+  const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
+  const int q0 = g.q_off + ib * kTileRows;
+  const int njb = min(g.tk - 1, q0 + kTileRows - 1) / kTileRows + 1;
+
+  if (tid == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(kfull + 8 * i, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
+  if (wg == 0) sL[row] = load_lse(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
+  else if (wg == 1) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem;
+  const uint32_t tS = tmem, tO = tmem + 128, tR = tmem + 192;   // O (64) and row sums (16): one N = 80 tile
+
+  if (tid == 0) {
+    mbar_expect_tx(kfull, 2 * kTileBytes);
+    tma_load_tile(sQ, &map_q, ib * kTileRows, n, kfull);
+    tma_load_tile(sK0, &map_k, 0, n, kfull);
+    mbar_expect_tx(vfull, kTileBytes);
+    tma_load_tile(sV, &map_v, 0, n, vfull);
+    if (njb > 1) {
+      mbar_expect_tx(kfull + 8, kTileBytes);
+      tma_load_tile(sK0 + kTileBytes, &map_k, kTileRows, n, kfull + 8);
+    }
+    mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
+    tc_fence_after();
+    mma_scores(tS, sK0, sQ, 128);
+    mma_commit(sdone);
+  }
+  __syncwarp();
+
+  // the checkpoint row this warpgroup starts from: the one in front of query 32*wg of the block
+  const int rb = (ib * kTileRows + 32 * wg) / g.carry_rows;
+  const bool have_rows = rb < ncb;                 // false only for a ragged last half block
+  const int64_t carry_row = ((int64_t)n * ncb + (have_rows ? rb : 0)) * g.tk;
+  const float4* L4 = reinterpret_cast<const float4*>(sL + 32 * wg);
+  const uint32_t taddr = tS + ((uint32_t)((warp & 3) * 32) << 16) + 32 * wg;
+  const int qh = q0 + 32 * wg;                     // absolute position of this warpgroup's first query
+  auto load_den = [&](int jbx) {
+    const int jx = jbx * kTileRows + row;
+    float d = g.eps;
+    if (jx < g.tk && have_rows) {
+      d += carry[carry_row + jx];
+      if (carry_base != nullptr) d += carry_base[(int64_t)n * g.tk + jx];
+    }
+    return d;
+  };
+  float den_next = load_den(0);
+  for (int jb = 0; jb < njb; ++jb) {
+    const int b = jb & 1;
+    const int ja = jb * kTileRows + row;
+    float den = den_next;
+    mbar_wait(sdone, jb & 1, ctl, &g_status, kErrWaitMma);
+    tc_fence_after();
+    if (tid == 0) {
+      if (jb >= 1) {                      // the V buffer is free: the previous share*V finished
+        mbar_expect_tx(vfull, kTileBytes);
+        tma_load_tile(sV, &map_v, jb * kTileRows, n, vfull);
+      }
+      if (jb >= 1 && jb + 1 < njb) {      // K stage of tile jb-1 is free
+        mbar_expect_tx(kfull + 8 * (b ^ 1), kTileBytes);
+        tma_load_tile(sK0 + kTileBytes * (b ^ 1), &map_k, (jb + 1) * kTileRows, n, kfull + 8 * (b ^ 1));
+      }
+    }
+    __syncwarp();
+    if (jb + 1 < njb) den_next = load_den(jb + 1);   // lands while this tile is processed
+    const bool diag = jb * kTileRows + kTileRows - 1 > qh;
+    const bool dead = ja >= g.tk;
+    auto tile = [&](auto mask_tag) {
+    constexpr bool MASK = decltype(mask_tag)::value;
+    {
+      constexpr int c = 0;
+      float v[32];
+      tmem_ld32(taddr, v);
+      tmem_ld_wait(v);
+      // the statistics of group e8+1 are read before group e8 is stored: shared-memory
+      // loads cannot be hoisted above the stores by the compiler
+      float4 lnext[2] = {L4[c * 8], L4[c * 8 + 1]};
+#pragma unroll
+      for (int e8 = 0; e8 < 4; ++e8) {
+        uint32_t packed[4];
+        const float4 lcur[2] = {lnext[0], lnext[1]};
+        if (e8 < 3) {
+          lnext[0] = L4[c * 8 + e8 * 2 + 2];
+          lnext[1] = L4[c * 8 + e8 * 2 + 3];
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float ls[4] = {lcur[h].x, lcur[h].y, lcur[h].z, lcur[h].w};
+          float sh[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e8 * 8 + h * 4 + u;
+            float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
+            if (MASK && (dead || ja > qh + c * 32 + e)) p = 0.f;
+            den += p;
+            sh[u] = p * fast_rcp(den);
+          }
+          packed[h * 2 + 0] = pack_bf16(sh[0], sh[1]);
+          packed[h * 2 + 1] = pack_bf16(sh[2], sh[3]);
+        }
+        const uint32_t dst = sSh + share_chunk_offset(row, wg * 32 + e8 * 8);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]),
+                     "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+                     : "memory");
+      }
+    }
+    };
+    if (diag || dead) tile(std::true_type{}); else tile(std::false_type{});
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      mbar_wait(vfull, jb & 1, ctl, &g_status, kErrWaitTma);
+      tc_fence_after();
+      constexpr uint32_t id_o = instr_desc(128, 80, 1, 1);
+      // descriptors are built once per tile; a k-step is a constant 2048 B (128 units) further
+      const Desc dSh = make_desc(sSh, kTileBytes, 1024), dVm = make_desc(sV, sOnes - sV, 1024);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) mma_ss(tO, dSh, 128 * kk, dVm, 128 * kk, id_o, (jb > 0 || kk > 0));
+      if (jb + 1 < njb) {
+        mbar_wait(kfull + 8 * (b ^ 1), ((jb + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
+        tc_fence_after();
+        mma_scores(tS, sK0 + kTileBytes * (b ^ 1), sQ, 128);
+      }
+      mma_commit(sdone);
+    }
+    __syncwarp();
+  }
+  mbar_wait(sdone, njb & 1, ctl, &g_status, kErrWaitMma);
+  tc_fence_after();
+  {
+    // lane = query now: each warpgroup stores 16 of the 64 output columns of row `row`
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    float o[16], r;
+    tmem_ld16(tO + lane_base + 16 * wg, o);
+    tmem_ld1(tR + lane_base, &r);
+    tmem_ld_wait16(o);
+    tmem_ld_wait();
+    const int i = ib * kTileRows + row;
+    if (i < g.tq) {
+      const float inv = 1.f / (r + g.eps);
+      float4* dst = reinterpret_cast<float4*>(out + ((int64_t)n * g.tq + i) * kHeadDim + 16 * wg);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        dst[c] = make_float4(o[4 * c] * inv, o[4 * c + 1] * inv, o[4 * c + 2] * inv, o[4 * c + 3] * inv);
+      if (wg == 0) ssum[(int64_t)n * g.tq + i] = r;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, 256);
+}
+
+
 // ---------------------------------------------------------------- pass 4: backward
 // Pre-pass, one warp per query row: sinv = 1/(ssum+eps); dbar' = sinv * (dout . out);
 // do' = bf16(sinv * dout); zeroes the dq / ghat accumulators.  Folding sinv into dO
@@ -709,12 +907,6 @@ __global__ void backward_prep_kernel(const TD* __restrict__ dout, const float* _
 // warpgroup gives registers up (setmaxnreg) and the compute warpgroups take them.
 constexpr int kBwdThreads = 384;
 constexpr int kBwdSmem = 12 * kTileBytes + 2048 + 2048 + 256 + 1024;
-
-__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
-  uint32_t r;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-  *v = __uint_as_float(r);
-}
 
 __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -1134,8 +1326,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
 // warps per scheduler hide the dependent chains of the two sweeps; the suffix of dk_share still
 // costs one barrier per half-step (warpgroup 0, the last 16 queries, starts from the suffix
 // behind the half-step, the others from zero, and each adds p * (the suffix in front of its
-// segment) afterwards).  Register budget: 512 compute threads x 112 + 128 x 64 = the whole file.
+// segment) afterwards).  Register budget: setmaxnreg moves registers inside the CTA's launch
+// allocation only (640 threads x 96, the most 640 threads can get), so 512 compute threads x 104
+// + 128 x 64 = 61440 uses exactly that; asking for more would block the increase for ever.
 constexpr int kBwd4Threads = 640;
+constexpr int kBwd4LaunchRegs = 96, kBwd4ComputeRegs = 104, kBwd4IssueRegs = 64;
+static_assert(kBwd4LaunchRegs * kBwd4Threads <= 65536 && 512 * kBwd4ComputeRegs + 128 * kBwd4IssueRegs <= kBwd4LaunchRegs * kBwd4Threads,
+              "setmaxnreg can only redistribute the registers the CTA was launched with");
 constexpr int kBwd4Smem = 12 * kTileBytes + 2048 + 4096 + 256 + 1024;
 
 __global__ void __launch_bounds__(kBwd4Threads, 1) backward_main4_kernel(
@@ -1254,7 +1451,7 @@ __global__ void __launch_bounds__(kBwd4Threads, 1) backward_main4_kernel(
     // Thread 512 issues every MMA and TMA copy.  After the second half-step of a step all
     // four warps (lane = query) move the finished dQ | ghat tile out, so that the compute
     // warps never touch it.  The warpgroup hands most of its registers to the other two.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");   // kBwd4IssueRegs
     constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);     // scores: both operands K-major
     constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);    // dV, dK: A from TMEM (M = keys), B MN-major
     constexpr uint32_t id_qd = instr_desc(128, 80, 1, 1);    // dQ | ghat: A MN-major (M = queries)
@@ -1379,7 +1576,7 @@ __global__ void __launch_bounds__(kBwd4Threads, 1) backward_main4_kernel(
     }
     if (tid == 512) tma_wait_read_all();
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");  // kBwd4ComputeRegs
     // ------------------------------------------------------------ the compute warps
     const int cw = 16 * (3 - wg);                    // this warpgroup's columns of a stage: warpgroup 0 the last 16 queries
     // demand of this thread's key in front of its 16 queries of half-step h (exclusive of the
@@ -1877,10 +2074,17 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   if (int rc = make_map(&mv, v, g.n, g.tk, err, errlen)) return rc;
   constexpr int smem = kMainSmem;
   static_assert(2 * (smem + 1024) <= 233472 && 3 * (smem + 1024) > 233472, "exactly two CTAs of the main pass fit one SM");
-  if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
-                                                              out, ssum);
+  static const bool two_warpgroups = getenv("DILUTION_FWD_WG2") != nullptr;     // A/B switch
+  if (g.carry_rows <= 32 && !two_warpgroups) {
+    if (int rc = set_smem_attr((const void*)forward_main4_kernel, smem, err, errlen)) return rc;
+    forward_main4_kernel<<<(unsigned)(g.n * nqb), 512, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
+                                                                 out, ssum);
+  } else {
+    if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
+    forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
+                                                                out, ssum);
+  }
   return launch_status("tc forward_main", err, errlen);
 }
 
@@ -1919,6 +2123,17 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
     constexpr int smem_bwd = kBwd4Smem;
     static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
     if (int rc = set_smem_attr((const void*)backward_main4_kernel, smem_bwd, err, errlen)) return rc;
+    // the kernel redistributes registers between its warpgroups; that only works inside what the
+    // CTA was launched with, so make sure the compiled kernel has the allocation the split assumes
+    static const int launch_regs = [] {
+      cudaFuncAttributes a;
+      return cudaFuncGetAttributes(&a, backward_main4_kernel) == cudaSuccess ? a.numRegs : 0;
+    }();
+    if (launch_regs * kBwd4Threads < 512 * kBwd4ComputeRegs + 128 * kBwd4IssueRegs) {
+      snprintf(err, errlen, "backward_main4_kernel was compiled with %d registers per thread; its register "
+               "split needs %d", launch_regs, kBwd4LaunchRegs);
+      return 3;
+    }
     mark("tc_backward_main", st, 0);
     backward_main4_kernel<<<(unsigned)(g.n * nkb), kBwd4Threads, smem_bwd, st>>>(
         mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
