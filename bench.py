@@ -445,9 +445,9 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
             "peak_source": f"{peaks['source']} sustained bf16", "matmuls_in_kernel": mm,
             "step_frac_of_peak": value_per_gpu / peaks["tensor"],
             # matmul-equivalents the tensor cores actually run per step: QK^T in the row,
-            # column-sum, main, reverse and correction passes (5), share@V, dO V^T, dV, dQ,
-            # dK (5), and the two correction products W Q and W^T K (2); the ones columns
-            # that give row sums and ghat (N = 80 instead of 64) are not counted
+            # column-sum, main, reverse and key-correction passes (5), share@V, dO V^T, dV, dQ,
+            # dK (5), the pk product of the row pass and the key-correction product W Q (2);
+            # the ones columns that give row sums and ghat (N = 80 instead of 64) are not counted
             "executed": {"matmuls_per_step": 12, "value": value_per_gpu * 12 / 7, "unit": "TFLOP/s",
                          "frac": value_per_gpu * 12 / 7 / peaks["tensor"]}}
 

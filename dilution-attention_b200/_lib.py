@@ -94,13 +94,8 @@ def profile_collect() -> dict:
 
 
 def carry_rows(dtype_code: int, precision_code: int, head_dim: int, training: bool) -> int:
-    """Query rows per demand checkpoint for this case (dilution_carry_rows of the C ABI).
-    DILUTION_TRAIN_CARRY_ROWS=32 in the environment selects the tensor-core backward with two
-    compute warpgroups (32 queries per thread) instead of four (16 per thread)."""
-    rows = int(load().dilution_carry_rows(dtype_code, precision_code, head_dim, 1 if training else 0))
-    if training and rows == 16 and os.environ.get("DILUTION_TRAIN_CARRY_ROWS") == "32":
-        rows = 32
-    return rows
+    """Query rows per demand checkpoint for this case (dilution_carry_rows of the C ABI)."""
+    return int(load().dilution_carry_rows(dtype_code, precision_code, head_dim, 1 if training else 0))
 
 
 def tensor_core_path(dtype_code: int, precision_code: int, head_dim: int) -> bool:

@@ -101,7 +101,7 @@ int check_common(const char* fn, int dtype, int precision, int64_t n, int64_t tq
   return DILUTION_OK;
 }
 
-// Checkpoint spacings: the tensor-core kernels take 16, 32 or 64 query rows; the fp32 kernels 32.
+// Checkpoint spacings: the tensor-core kernels take 32 or 64 query rows; the fp32 kernels 32.
 int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_offset, int carry_rows);
 
 dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps,
@@ -350,8 +350,8 @@ namespace {
 int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_offset, int carry_rows) {
 #ifdef DILUTION_TENSOR_PATH
   if (dil::tc::supported(dtype, precision, d, q_offset)) {
-    if (carry_rows == 16 || carry_rows == 32 || carry_rows == 64) return DILUTION_OK;
-    return fail(DILUTION_ERR_ARG, "%s: carry_rows must be 16, 32 or 64 (got %d)", fn, carry_rows);
+    if (carry_rows == 32 || carry_rows == 64) return DILUTION_OK;
+    return fail(DILUTION_ERR_ARG, "%s: carry_rows must be 32 or 64 (got %d)", fn, carry_rows);
   }
 #endif
   if (carry_rows == dil::kCarryRows) return DILUTION_OK;
@@ -364,7 +364,7 @@ extern "C" {
 
 int dilution_carry_rows(int dtype, int precision, int d, int training) {
 #ifdef DILUTION_TENSOR_PATH
-  if (dil::tc::supported(dtype, precision, d, 0)) return training ? 16 : 64;
+  if (dil::tc::supported(dtype, precision, d, 0)) return training ? 32 : 64;
 #endif
   return dil::kCarryRows;
 }

@@ -17,7 +17,6 @@
 // main reverse pass runs 384 threads, one CTA per SM, with a dedicated issuing warpgroup.
 #pragma once
 
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -299,31 +298,33 @@ __global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant_
 // ---------------------------------------------------------------- pass 2: column sums + scan
 // grid = n * ceil(tk/128), key blocks with the most query blocks first.
 // S^T = K Q^T, lane = key.  The CTA keeps its K tile and walks the query blocks
-// in causal order.  Each warpgroup sums p over its 64 queries of the tile, 16 at a
+// in causal order.  Each warpgroup sums p over its 64 queries of the tile, 32 at a
 // time; the thread of warpgroup 0 owns the key's running sum — the exclusive scan —
-// and stores one checkpoint per g.carry_rows (16, 32 or 64) query rows, one tile
-// behind the sums.
-constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 4096 + 1024 + 256;
+// and stores one checkpoint per CR query rows, one tile behind the sums.  CR = 32 when
+// a backward will read the checkpoints (two threads per key there, 32 queries each),
+// 64 for forward-only calls (the main forward pass starts its two warpgroups at queries
+// 0 and 64 of a tile): half the scratch and half the checkpoint stores.
+constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 2048 + 1024 + 256;
 
+template <int CR>
 __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden,
     const float* __restrict__ carry_base, float* __restrict__ carry, float* __restrict__ total) {
+  static_assert(CR == 32 || CR == 64, "checkpoints every 32 or 64 query rows");
+  constexpr int kPerTile = kTileRows / CR;                                      // 4 or 2
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   const uint32_t sK = smem_u32(smem), sQ0 = sK + kTileBytes;
   float* sL = reinterpret_cast<float*>(smem + 3 * kTileBytes);                 // [2][128]
-  float4* sCs = reinterpret_cast<float4*>(smem + 3 * kTileBytes + 1024);       // [2][128] the four sums of warpgroup 1
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 5120);
+  float2* sCs = reinterpret_cast<float2*>(smem + 3 * kTileBytes + 1024);       // [2][128] the two sums of warpgroup 1
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes + 3072);
   Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
   const uint32_t qfull = smem_u32(bars), sdone = smem_u32(bars + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  const int cr = g.carry_rows;
-  const int ncb = (g.tq + cr - 1) / cr;
-  const int cr_shift = cr == 16 ? 4 : (cr == 32 ? 5 : 6);
-  const int per_tile = kTileRows >> cr_shift;                          // checkpoints per 128-row tile: 8, 4 or 2
+  const int ncb = (g.tq + CR - 1) / CR;
   const int n = (int)(blockIdx.x % g.n);
   const int jb = (int)(blockIdx.x / g.n);
   const int k0 = jb * kTileRows;
@@ -356,24 +357,25 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
   const int ja = k0 + row;
   const bool live = ja < g.tk;
   const float base = (carry_base != nullptr && live) ? carry_base[(int64_t)n * g.tk + ja] : 0.f;
-  float local = 0.f;                               // warpgroup 0: the scan in front of the previous tile
-  float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);   // its four 16-query sums of the previous tile
-  // the checkpoints of 128-row tile `tile` (in front of every carry_rows-th of its queries), and
-  // the scan moved past it; w1 = the four sums of warpgroup 1 (queries 64..127)
-  auto store_checkpoints = [&](int tile, float4 w1) {
-    const float s16[8] = {prev.x, prev.y, prev.z, prev.w, w1.x, w1.y, w1.z, w1.w};
+  float local = 0.f, prev0 = 0.f, prev1 = 0.f;   // warpgroup 0: scan state, its two sums of the previous tile
+  // the checkpoints of 128-row tile `tile` (in front of its queries 0, 32, 64, 96 — or 0 and 64),
+  // and the scan moved past it
+  auto store_checkpoints = [&](int tile, float2 w1) {
+    const int rb = tile * kPerTile;
+    const float c0 = base + local, c1 = c0 + prev0, c2 = c1 + prev1, c3 = c2 + w1.x;
     if (live) {
-      const int rb = tile * per_tile;
-      float* dst = carry + ((int64_t)n * ncb + rb) * g.tk + ja;
-      float run = base + local;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int k = (c * 16) >> cr_shift;                            // checkpoint index within the tile
-        if (((c * 16) & (cr - 1)) == 0 && rb + k < ncb) dst[(int64_t)k * g.tk] = run;
-        run += s16[c];
+      const int64_t o = ((int64_t)n * ncb + rb) * g.tk + ja;
+      if (CR == 32) {
+        if (rb < ncb) carry[o] = c0;
+        if (rb + 1 < ncb) carry[o + g.tk] = c1;
+        if (rb + 2 < ncb) carry[o + 2 * (int64_t)g.tk] = c2;
+        if (rb + 3 < ncb) carry[o + 3 * (int64_t)g.tk] = c3;
+      } else {
+        if (rb < ncb) carry[o] = c0;
+        if (rb + 1 < ncb) carry[o + g.tk] = c2;
       }
     }
-    local += ((prev.x + prev.y) + (prev.z + prev.w)) + ((w1.x + w1.y) + (w1.z + w1.w));
+    local += (prev0 + prev1) + (w1.x + w1.y);
   };
   const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
   for (int it = 0; it < nib; ++it) {
@@ -399,7 +401,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     const int i0 = g.q_off + ib * kTileRows + 64 * wg;   // absolute position of this half's first query
     const bool edge = i0 < k0 + kTileRows - 1;            // part of the diagonal tile
     const float4* L4 = reinterpret_cast<const float4*>(sL + 128 * b + 64 * wg);
-    float cs[4] = {0.f, 0.f, 0.f, 0.f};      // queries 0-15, 16-31, 32-47, 48-63 of this warpgroup's half
+    float colsum0 = 0.f, colsum1 = 0.f;      // queries 0-31 and 32-63 of this warpgroup's half
     auto tile = [&](auto edge_tag) {
       constexpr bool EDGE = decltype(edge_tag)::value;
 #pragma unroll
@@ -407,28 +409,29 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
         float v[32];
         tmem_ld32(taddr + 32 * c, v);
         tmem_ld_wait(v);
+        float part[4] = {0.f, 0.f, 0.f, 0.f};     // four independent sums
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {            // the chunk's two groups of 16 queries
-          float part[4] = {0.f, 0.f, 0.f, 0.f};     // four independent sums
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l = L4[c * 8 + e4];
+          const float ls[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
-          for (int e4 = 0; e4 < 4; ++e4) {
-            const float4 l = L4[c * 8 + hh * 4 + e4];
-            const float ls[4] = {l.x, l.y, l.z, l.w};
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int e = hh * 16 + e4 * 4 + u;
-              float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
-              if (EDGE && ja > i0 + c * 32 + e) p = 0.f;
-              part[u] += p;
-            }
+          for (int u = 0; u < 4; ++u) {
+            float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
+            if (EDGE && ja > i0 + c * 32 + e4 * 4 + u) p = 0.f;
+            part[u] += p;
           }
-          cs[c * 2 + hh] = (part[0] + part[1]) + (part[2] + part[3]);
         }
+        const float cs = (part[0] + part[1]) + (part[2] + part[3]);
+        if (c == 0) colsum0 = cs; else colsum1 = cs;
       }
     };
     if (edge) tile(std::true_type{}); else tile(std::false_type{});
-    if (wg == 0) prev = make_float4(cs[0], cs[1], cs[2], cs[3]);
-    else sCs[b * 128 + row] = make_float4(cs[0], cs[1], cs[2], cs[3]);
+    if (wg == 0) {
+      prev0 = colsum0;
+      prev1 = colsum1;
+    } else {
+      sCs[b * 128 + row] = make_float2(colsum0, colsum1);
+    }
     if (wg == 1 && it + 1 < nib) sL[128 * (b ^ 1) + row] = lse_next;
     tc_fence_before();
     __syncthreads();
@@ -644,203 +647,6 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 256);
 }
-
-// The same pass with four warpgroups: each takes 32 of the tile's 128 queries from a checkpoint of
-// its own (g.carry_rows 16 or 32), so a thread walks 32 queries per tile instead of 64 and twice
-// the warps cover the share@V / next-score MMA round trip between tiles.  512 threads at 64
-// registers; two CTAs per SM as before.
-
-
-__global__ void __launch_bounds__(512, 2) forward_main4_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, Geom g, const float* __restrict__ rmax,
-    const float* __restrict__ rden, const float* __restrict__ carry,
-    const float* __restrict__ carry_base, float* __restrict__ out, float* __restrict__ ssum) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw;
-  if (smem_u32(smem) & 1023u) {                      // no slack is requested: refuse instead of overrunning
-    if (threadIdx.x == 0) atomicCAS(&g_status, 0, kErrAlign);
-    return;
-  }
-  const uint32_t sQ = smem_u32(smem), sK0 = sQ + kTileBytes, sV = sQ + 3 * kTileBytes;
-  // a [128 keys][64] bf16 tile of ones right behind V: the second 64-column group of the B
-  // operand of share @ [V | ones] (N = 80), so the row sums come out of the same MMA
-  const uint32_t sOnes = sQ + 4 * kTileBytes, sSh = sQ + 5 * kTileBytes;
-  uint8_t* ones_ptr = smem + 4 * kTileBytes;
-  float* sL = reinterpret_cast<float*>(smem + 7 * kTileBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * kTileBytes + 512);
-  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 8);
-  const uint32_t kfull = smem_u32(bars), vfull = smem_u32(bars + 2), sdone = smem_u32(bars + 3);
-
-  const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, row = tid & 127;
-  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  const int ncb = (g.tq + g.carry_rows - 1) / g.carry_rows;
-  const int n = (int)(blockIdx.x % g.n);
-  const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
-  const int q0 = g.q_off + ib * kTileRows;
-  const int njb = min(g.tk - 1, q0 + kTileRows - 1) / kTileRows + 1;
-
-  if (tid == 0) {
-    ctl->abort = 0;
-    for (int i = 0; i < 4; ++i) mbar_init(kfull + 8 * i, 1);
-    fence_barrier_init();
-  }
-  __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  if (wg == 0) sL[row] = load_lse(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
-  else if (wg == 1) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem;
-  const uint32_t tS = tmem, tO = tmem + 128, tR = tmem + 192;   // O (64) and row sums (16): one N = 80 tile
-
-  if (tid == 0) {
-    mbar_expect_tx(kfull, 2 * kTileBytes);
-    tma_load_tile(sQ, &map_q, ib * kTileRows, n, kfull);
-    tma_load_tile(sK0, &map_k, 0, n, kfull);
-    mbar_expect_tx(vfull, kTileBytes);
-    tma_load_tile(sV, &map_v, 0, n, vfull);
-    if (njb > 1) {
-      mbar_expect_tx(kfull + 8, kTileBytes);
-      tma_load_tile(sK0 + kTileBytes, &map_k, kTileRows, n, kfull + 8);
-    }
-    mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
-    tc_fence_after();
-    mma_scores(tS, sK0, sQ, 128);
-    mma_commit(sdone);
-  }
-  __syncwarp();
-
-  // the checkpoint row this warpgroup starts from: the one in front of query 32*wg of the block
-  const int rb = (ib * kTileRows + 32 * wg) / g.carry_rows;
-  const bool have_rows = rb < ncb;                 // false only for a ragged last half block
-  const int64_t carry_row = ((int64_t)n * ncb + (have_rows ? rb : 0)) * g.tk;
-  const float4* L4 = reinterpret_cast<const float4*>(sL + 32 * wg);
-  const uint32_t taddr = tS + ((uint32_t)((warp & 3) * 32) << 16) + 32 * wg;
-  const int qh = q0 + 32 * wg;                     // absolute position of this warpgroup's first query
-  auto load_den = [&](int jbx) {
-    const int jx = jbx * kTileRows + row;
-    float d = g.eps;
-    if (jx < g.tk && have_rows) {
-      d += carry[carry_row + jx];
-      if (carry_base != nullptr) d += carry_base[(int64_t)n * g.tk + jx];
-    }
-    return d;
-  };
-  float den_next = load_den(0);
-  for (int jb = 0; jb < njb; ++jb) {
-    const int b = jb & 1;
-    const int ja = jb * kTileRows + row;
-    float den = den_next;
-    mbar_wait(sdone, jb & 1, ctl, &g_status, kErrWaitMma);
-    tc_fence_after();
-    if (tid == 0) {
-      if (jb >= 1) {                      // the V buffer is free: the previous share*V finished
-        mbar_expect_tx(vfull, kTileBytes);
-        tma_load_tile(sV, &map_v, jb * kTileRows, n, vfull);
-      }
-      if (jb >= 1 && jb + 1 < njb) {      // K stage of tile jb-1 is free
-        mbar_expect_tx(kfull + 8 * (b ^ 1), kTileBytes);
-        tma_load_tile(sK0 + kTileBytes * (b ^ 1), &map_k, (jb + 1) * kTileRows, n, kfull + 8 * (b ^ 1));
-      }
-    }
-    __syncwarp();
-    if (jb + 1 < njb) den_next = load_den(jb + 1);   // lands while this tile is processed
-    const bool diag = jb * kTileRows + kTileRows - 1 > qh;
-    const bool dead = ja >= g.tk;
-    auto tile = [&](auto mask_tag) {
-    constexpr bool MASK = decltype(mask_tag)::value;
-    {
-      constexpr int c = 0;
-      float v[32];
-      tmem_ld32(taddr, v);
-      tmem_ld_wait(v);
-      // the statistics of group e8+1 are read before group e8 is stored: shared-memory
-      // loads cannot be hoisted above the stores by the compiler
-      float4 lnext[2] = {L4[c * 8], L4[c * 8 + 1]};
-#pragma unroll
-      for (int e8 = 0; e8 < 4; ++e8) {
-        uint32_t packed[4];
-        const float4 lcur[2] = {lnext[0], lnext[1]};
-        if (e8 < 3) {
-          lnext[0] = L4[c * 8 + e8 * 2 + 2];
-          lnext[1] = L4[c * 8 + e8 * 2 + 3];
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const float ls[4] = {lcur[h].x, lcur[h].y, lcur[h].z, lcur[h].w};
-          float sh[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int e = e8 * 8 + h * 4 + u;
-            float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
-            if (MASK && (dead || ja > qh + c * 32 + e)) p = 0.f;
-            den += p;
-            sh[u] = p * fast_rcp(den);
-          }
-          packed[h * 2 + 0] = pack_bf16(sh[0], sh[1]);
-          packed[h * 2 + 1] = pack_bf16(sh[2], sh[3]);
-        }
-        const uint32_t dst = sSh + share_chunk_offset(row, wg * 32 + e8 * 8);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]),
-                     "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
-                     : "memory");
-      }
-    }
-    };
-    if (diag || dead) tile(std::true_type{}); else tile(std::false_type{});
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      mbar_wait(vfull, jb & 1, ctl, &g_status, kErrWaitTma);
-      tc_fence_after();
-      constexpr uint32_t id_o = instr_desc(128, 80, 1, 1);
-      // descriptors are built once per tile; a k-step is a constant 2048 B (128 units) further
-      const Desc dSh = make_desc(sSh, kTileBytes, 1024), dVm = make_desc(sV, sOnes - sV, 1024);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) mma_ss(tO, dSh, 128 * kk, dVm, 128 * kk, id_o, (jb > 0 || kk > 0));
-      if (jb + 1 < njb) {
-        mbar_wait(kfull + 8 * (b ^ 1), ((jb + 1) >> 1) & 1, ctl, &g_status, kErrWaitTma);
-        tc_fence_after();
-        mma_scores(tS, sK0 + kTileBytes * (b ^ 1), sQ, 128);
-      }
-      mma_commit(sdone);
-    }
-    __syncwarp();
-  }
-  mbar_wait(sdone, njb & 1, ctl, &g_status, kErrWaitMma);
-  tc_fence_after();
-  {
-    // lane = query now: each warpgroup stores 16 of the 64 output columns of row `row`
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    float o[16], r;
-    tmem_ld16(tO + lane_base + 16 * wg, o);
-    tmem_ld1(tR + lane_base, &r);
-    tmem_ld_wait16(o);
-    tmem_ld_wait();
-    const int i = ib * kTileRows + row;
-    if (i < g.tq) {
-      const float inv = 1.f / (r + g.eps);
-      float4* dst = reinterpret_cast<float4*>(out + ((int64_t)n * g.tq + i) * kHeadDim + 16 * wg);
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        dst[c] = make_float4(o[4 * c] * inv, o[4 * c + 1] * inv, o[4 * c + 2] * inv, o[4 * c + 3] * inv);
-      if (wg == 0) ssum[(int64_t)n * g.tq + i] = r;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, 256);
-}
-
 
 // ---------------------------------------------------------------- pass 4: backward
 // Pre-pass, one warp per query row: sinv = 1/(ssum+eps); dbar' = sinv * (dout . out);
@@ -1320,438 +1126,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   if (warp == 0) tmem_free(tmem, 512);
 }
 
-// The same pass with FOUR compute warpgroups (and the issuing / read-out warpgroup as the
-// fifth): each thread takes 16 of a half-step's 64 queries instead of 32, from a checkpoint of its
-// own, so the pass needs the demand stored every 16 query rows (g.carry_rows == 16).  Twice the
-// warps per scheduler hide the dependent chains of the two sweeps; the suffix of dk_share still
-// costs one barrier per half-step (warpgroup 0, the last 16 queries, starts from the suffix
-// behind the half-step, the others from zero, and each adds p * (the suffix in front of its
-// segment) afterwards).  Register budget: setmaxnreg moves registers inside the CTA's launch
-// allocation only (640 threads x 96, the most 640 threads can get), so 512 compute threads x 104
-// + 128 x 64 = 61440 uses exactly that; asking for more would block the increase for ever.
-constexpr int kBwd4Threads = 640;
-constexpr int kBwd4LaunchRegs = 96, kBwd4ComputeRegs = 104, kBwd4IssueRegs = 64;
-static_assert(kBwd4LaunchRegs * kBwd4Threads <= 65536 && 512 * kBwd4ComputeRegs + 128 * kBwd4IssueRegs <= kBwd4LaunchRegs * kBwd4Threads,
-              "setmaxnreg can only redistribute the registers the CTA was launched with");
-constexpr int kBwd4Smem = 12 * kTileBytes + 2048 + 4096 + 256 + 1024;
-
-__global__ void __launch_bounds__(kBwd4Threads, 1) backward_main4_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq, Geom g,
-    const __nv_bfloat16* __restrict__ v,
-    const float* __restrict__ rmax, const float* __restrict__ rden, const float* __restrict__ dbarp,
-    const float* __restrict__ carry, const float* __restrict__ total, float* __restrict__ dq_main,
-    float* __restrict__ dk_main, __nv_bfloat16* __restrict__ dv, float* __restrict__ ghat) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
-  const uint32_t sK = smem_u32(smem);
-  // a [128 keys][64] bf16 tile of ones: the second 64-column group of the dQ MMA's B operand
-  // (N = 80 = 64 columns of K + 16 of ones), so ghat comes out of the same instruction
-  const uint32_t sOnes = sK + kTileBytes;
-  uint8_t* ones_ptr = smem + kTileBytes;
-  const uint32_t sQ0 = sK + 2 * kTileBytes, sD0 = sK + 5 * kTileBytes;        // [3] each
-  const uint32_t sPd = sK + 8 * kTileBytes;                                    // 32 KB
-  const uint32_t sDq = sK + 10 * kTileBytes;                                   // 32 KB: fp32 dQ staging
-  float* sLse = reinterpret_cast<float*>(smem + 12 * kTileBytes);              // [2][128] log-sum-exp of a step's queries
-  float* sDbar = sLse + 256;                                                   // [2][128] their dbar'
-  float* sG = reinterpret_cast<float*>(smem + 12 * kTileBytes + 2048);         // [2][4][128] sums of dk_share
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 12 * kTileBytes + 6144);
-  Ctl* ctl = reinterpret_cast<Ctl*>(bars + 12);
-  const uint32_t kfull = smem_u32(bars), qfull = smem_u32(bars + 1);           // qfull[3]
-  const uint32_t sdone = smem_u32(bars + 4), tiles = smem_u32(bars + 6);       // [2] each
-  const uint32_t dqdone = smem_u32(bars + 8);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = tid >> 7, row = tid & 127;
-  const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  const int ncb = (g.tq + 15) / 16;                // this pass reads checkpoints every 16 query rows
-  const int n = (int)(blockIdx.x % g.n);
-  const int jb = (int)(blockIdx.x / g.n);
-  const int k0 = jb * kTileRows;
-  const int nsteps = nqb - jb;                     // query blocks jb .. nqb-1, visited in reverse
-  const int nhalf = 2 * nsteps;
-  const int64_t row_base = (int64_t)n * g.tq;
-  const int ja = k0 + row;
-  const bool dead = ja >= g.tk;
-
-  auto load_stats = [&](int ib) {
-    const int i = ib * kTileRows + row;
-    float2 st = make_float2(INFINITY, 0.f);
-    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
-    return st;
-  };
-
-  if (tid == 0) {
-    ctl->abort = 0;
-    for (int i = 0; i < 6; ++i) mbar_init(kfull + 8 * i, 1);      // kfull, qfull[3], sdone[2]
-    mbar_init(tiles, 16);
-    mbar_init(tiles + 8, 16);
-    mbar_init(dqdone, 1);
-    fence_barrier_init();
-  }
-  __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 512);
-  if (wg == 0) {
-    const float2 st = load_stats(nqb - 1);
-    sLse[row] = st.x;
-    sDbar[row] = st.y;
-  }
-  else if (wg == 1) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem;
-  const uint32_t tS0 = tmem, tDOV0 = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384,
-                 tG = tmem + 448, tV = tmem + 464;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-
-  if (wg == 0) {
-    // this key's V row as an A operand: two head-dim elements per 32-bit column
-    uint32_t w[32];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint4 x = make_uint4(0u, 0u, 0u, 0u);
-      if (!dead) x = reinterpret_cast<const uint4*>(v + ((int64_t)n * g.tk + ja) * kHeadDim)[c];
-      w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
-    }
-    tmem_st16(tV + lane_base, w);
-    tmem_st16(tV + lane_base + 16, w + 16);
-  }
-  if (wg < 2) {
-    // dV and dK start from zero, so that every MMA into them accumulates
-    uint32_t z[16];
-#pragma unroll
-    for (int c = 0; c < 16; ++c) z[c] = 0u;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_st16(tDV + lane_base + 32 * wg + 16 * c, z);
-      tmem_st16(tDK + lane_base + 32 * wg + 16 * c, z);
-    }
-    tmem_st_wait();
-  }
-  if (tid == 512) {
-    mbar_expect_tx(kfull, kTileBytes);
-    tma_load_tile(sK, &map_k, k0, n, kfull);
-    for (int s = 0; s < 3 && s < nsteps; ++s) {
-      mbar_expect_tx(qfull + 8 * s, 2 * kTileBytes);
-      tma_load_tile(sQ0 + kTileBytes * s, &map_q, (nqb - 1 - s) * kTileRows, n, qfull + 8 * s);
-      tma_load_tile(sD0 + kTileBytes * s, &map_do, (nqb - 1 - s) * kTileRows, n, qfull + 8 * s);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-
-  if (wg == 4) {
-    // ------------------------------------------------------------ warpgroup 4: issue and dQ read-out
-    // Thread 512 issues every MMA and TMA copy.  After the second half-step of a step all
-    // four warps (lane = query) move the finished dQ | ghat tile out, so that the compute
-    // warps never touch it.  The warpgroup hands most of its registers to the other two.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");   // kBwd4IssueRegs
-    constexpr uint32_t id_s = instr_desc(128, 64, 0, 0);     // scores: both operands K-major
-    constexpr uint32_t id_kd = instr_desc(128, 64, 0, 1);    // dV, dK: A from TMEM (M = keys), B MN-major
-    constexpr uint32_t id_qd = instr_desc(128, 80, 1, 1);    // dQ | ghat: A MN-major (M = queries)
-    // every descriptor is built once; inside the loop tile, stage and k-step are constant
-    // offsets (in 16-byte units: a tile is 1024, an MN-major k-step 128, a K-major one 2)
-    const Desc dKk = make_desc(sK, 16, 1024);                 // K, K-major: A of the scores
-    const Desc dKm = make_desc(sK, sOnes - sK, 1024);         // [K | ones], MN-major: B of dQ | ghat
-    const Desc dPm = make_desc(sPd, kTileBytes, 1024);        // pdp, MN-major: A of dQ | ghat
-    const Desc dQk = make_desc(sQ0, 16, 1024), dQm = make_desc(sQ0, kTileBytes, 1024);
-    const Desc dDk = make_desc(sD0, 16, 1024), dDm = make_desc(sD0, kTileBytes, 1024);
-    // scores of a half-step in stage ST of Q and dO'; even half-steps take queries 64..127
-    auto issue_scores = [&](auto odd_c, auto st_c) {
-      constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
-      constexpr uint32_t off = ST * 1024 + (ODD ? 0 : 512);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) mma_ss(tS0 + 64 * ODD, dKk, 2 * kk, dQk, off + 2 * kk, id_s, kk > 0);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) mma_ts(tDOV0 + 64 * ODD, tV + 8 * kk, dDk, off + 2 * kk, id_s, kk > 0);
-    };
-    if (tid == 512) {
-      mbar_wait(kfull, 0, ctl, &g_status, kErrWaitTma);
-      mbar_wait(qfull, 0, ctl, &g_status, kErrWaitTma);
-      tc_fence_after();
-      issue_scores(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
-      mma_commit(sdone);
-      issue_scores(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
-      mma_commit(sdone + 8);
-    }
-    __syncwarp();
-    // half-step h = 2s + ODD of step s, whose Q and dO' tiles sit in stage ST = s % 3
-    auto half = [&](auto odd_c, auto st_c, int s) {
-      constexpr int ODD = decltype(odd_c)::value, ST = decltype(st_c)::value;
-      constexpr int ST1 = (ST + 1) % 3, ST2 = (ST + 2) % 3;
-      if (tid == 512) {
-        mbar_wait(tiles + 8 * ODD, s & 1, ctl, &g_status, kErrWaitTile);
-        tc_fence_after();
-#pragma unroll
-        for (int kq = 0; kq < 4; ++kq) {                    // contraction over the 64 queries
-          // queries [16kq, 16kq+16) of the half-step: 8 columns at the start of the owning
-          // warpgroup's 16-column range (warpgroup 3 owns queries 0..15)
-          constexpr uint32_t base = ST * 1024 + (ODD ? 0 : 4) * 128;
-          const uint32_t col = 64 * ODD + 16 * kq;
-          mma_ts(tDV, tS0 + col, dDm, base + 128 * kq, id_kd, 1);
-          mma_ts(tDK, tDOV0 + col, dQm, base + 128 * kq, id_kd, 1);
-        }
-        if (ODD) {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)                    // contraction over the 128 keys
-            mma_ss(tDQ, dPm, 128 * kk, dKm, 128 * kk, id_qd, kk > 0);
-          mma_commit(dqdone);
-        }
-        if (s + 1 < nsteps) {                               // half-step h + 2 belongs to step s + 1
-          if (!ODD) {
-            mbar_wait(qfull + 8 * ST1, ((s + 1) / 3) & 1, ctl, &g_status, kErrWaitTma);
-            tc_fence_after();
-          }
-          issue_scores(odd_c, std::integral_constant<int, ST1>{});
-        }
-        mma_commit(sdone + 8 * ODD);
-        if (!ODD && s >= 1 && s + 2 < nsteps) {
-          // every MMA of step s-1 has completed once the commit of its second half-step has:
-          // its Q and dO' stage takes step s+2
-          mbar_wait(sdone + 8, s & 1, ctl, &g_status, kErrWaitMma);
-          mbar_expect_tx(qfull + 8 * ST2, 2 * kTileBytes);
-          tma_load_tile(sQ0 + kTileBytes * ST2, &map_q, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
-          tma_load_tile(sD0 + kTileBytes * ST2, &map_do, (nqb - 3 - s) * kTileRows, n, qfull + 8 * ST2);
-        }
-      }
-      __syncwarp();
-      if (ODD) {
-        // dQ and ghat of the step's 128 queries: lane = query.  The fp32 tile is staged in
-        // shared memory in the copy engine's swizzled layout and added to dq_main by two
-        // tensor reductions of 32 columns.
-        if (lane == 0) mbar_wait(dqdone, s & 1, ctl, &g_status, kErrWaitMma);
-        __syncwarp();
-        tc_fence_after();
-        if (tid == 512) tma_wait_read_all();            // the previous reductions have read the staging buffer
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        const uint32_t stage = sDq + row * 128;
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {                   // 16 columns at a time
-          float dq[16];
-          tmem_ld16(tDQ + lane_base + 16 * j, dq);
-          tmem_ld_wait16(dq);
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + kTileBytes * (j >> 1) + (((4 * (j & 1) + c) ^ (row & 7)) << 4)),
-                         "f"(dq[4 * c] * g.scale), "f"(dq[4 * c + 1] * g.scale), "f"(dq[4 * c + 2] * g.scale),
-                         "f"(dq[4 * c + 3] * g.scale)
-                         : "memory");
-        }
-        float gh;
-        tmem_ld1(tG + lane_base, &gh);
-        tmem_ld_wait();
-        fence_async_smem();
-        tc_fence_before();
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        const int ibq = nqb - 1 - s;
-        if (tid == 512) {
-          tc_fence_after();
-          tma_reduce_add_tile(&map_dq, sDq, 0, ibq * kTileRows, n);
-          tma_reduce_add_tile(&map_dq, sDq + kTileBytes, 32, ibq * kTileRows, n);
-        }
-        const int i = ibq * kTileRows + row;
-        if (i < g.tq) atomicAdd(ghat + row_base + i, gh);
-      }
-    };
-    using C0 = std::integral_constant<int, 0>;
-    using C1 = std::integral_constant<int, 1>;
-    using C2 = std::integral_constant<int, 2>;
-    for (int s = 0; s < nsteps; s += 3) {
-      half(C0{}, C0{}, s);
-      half(C1{}, C0{}, s);
-      if (s + 1 < nsteps) {
-        half(C0{}, C1{}, s + 1);
-        half(C1{}, C1{}, s + 1);
-      }
-      if (s + 2 < nsteps) {
-        half(C0{}, C2{}, s + 2);
-        half(C1{}, C2{}, s + 2);
-      }
-    }
-    if (tid == 512) tma_wait_read_all();
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");  // kBwd4ComputeRegs
-    // ------------------------------------------------------------ the compute warps
-    const int cw = 16 * (3 - wg);                    // this warpgroup's columns of a stage: warpgroup 0 the last 16 queries
-    // demand of this thread's key in front of its 16 queries of half-step h (exclusive of the
-    // first): the stored checkpoint of that 16-row block (past the end: any value, p is 0 there)
-    auto load_edge = [&](int h) {
-      if (dead) return 0.f;
-      const int rb = 8 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 4) + (3 - wg);
-      return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
-    };
-    float sigma = 0.f;                               // suffix of dk_share behind the half-step
-    // the checkpoints are read once from a buffer far larger than L2: each load is issued two
-    // half-steps before its value is used
-    float incl = load_edge(0);
-    float incl_next = nhalf > 1 ? load_edge(1) : 0.f;
-    for (int h = 0; h < nhalf; ++h) {
-      const int s = h >> 1, odd = h & 1, ib = nqb - 1 - s, b = s & 1;
-      // fetch what the coming half-steps need before waiting for this one
-      float incl_next2 = 0.f;
-      float st_max = INFINITY, st_den = 1.f, st_dbar = 0.f;
-      if (h + 2 < nhalf) incl_next2 = load_edge(h + 2);
-      const bool fetch_stats = !odd && wg == 0 && s + 1 < nsteps;
-      if (fetch_stats) {
-        const int i = (ib - 1) * kTileRows + row;     // ib >= 1 here, so i < tq
-        st_max = rmax[row_base + i];
-        st_den = rden[row_base + i];
-        st_dbar = dbarp[row_base + i];
-      }
-      mbar_wait(sdone + 8 * odd, s & 1, ctl, &g_status, kErrWaitMma);
-      tc_fence_after();
-      float vs[16], vd[16];
-      const uint32_t tcol = lane_base + 64 * odd + cw;
-      tmem_ld16(tS0 + tcol, vs);
-      tmem_ld16(tDOV0 + tcol, vd);
-      tmem_ld_wait16(vs);
-      tmem_ld_wait16(vd);
-      const int qc = (odd ? 0 : 64) + cw;             // first query column of this thread in the step's tile
-      const int iq0 = ib * kTileRows + qc;            // its position (q_off == 0 here)
-      const bool masked_tile = dead || (ib * kTileRows + (odd ? 0 : 64) < k0 + kTileRows - 1);
-      const float4* Lse4 = reinterpret_cast<const float4*>(sLse + b * 128 + qc);
-      const float4* Dbar4 = reinterpret_cast<const float4*>(sDbar + b * 128 + qc);
-      uint32_t shp[8];                                 // 16 shares as bf16 pairs
-      // warpgroup 0 (the last 16 queries) knows the suffix of dk_share behind its queries; the
-      // others start from zero and add p * (the suffix in front of their segment) afterwards:
-      // dp is linear in it
-      float R = wg == 0 ? sigma : 0.f;
-      float incle = incl + g.eps;                      // demand + eps at the walk's position
-
-      // Two sweeps over the thread's 16 queries.  Forwards: p and 1/(committed+p+eps), the demand
-      // accumulated from the checkpoint in front exactly as the forward pass did.  Backwards: the
-      // suffix of dk_share (kernels.py:763-764), accumulated from the last query to the first as
-      // the reference does — its terms grow towards a key's first bidders, so the other order
-      // loses the small ones.  Afterwards vs holds p and vd holds p * dp.
-      auto chunk = [&](auto mask_tag) {
-        constexpr bool MASK = decltype(mask_tag)::value;
-        float inv[16];
-#pragma unroll
-        for (int e4 = 0; e4 < 4; ++e4) {
-          const float4 l4 = Lse4[e4];
-          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float2 zs = make_float2(g.zscale, g.zscale);
-          const float2 z01 = fma2(make_float2(vs[e4 * 4], vs[e4 * 4 + 1]), zs, make_float2(-lse[0], -lse[1]));
-          const float2 z23 = fma2(make_float2(vs[e4 * 4 + 2], vs[e4 * 4 + 3]), zs, make_float2(-lse[2], -lse[3]));
-          const float z[4] = {z01.x, z01.y, z23.x, z23.y};
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int e = e4 * 4 + u;
-            float p = fast_exp2(z[u]);
-            if (MASK) {
-              if (dead || ja > iq0 + e) p = 0.f;
-            }
-            incle += p;
-            inv[e] = fast_rcp(incle);
-            vs[e] = p;
-          }
-        }
-#pragma unroll
-        for (int e4 = 3; e4 >= 0; --e4) {
-          const float4 d4 = Dbar4[e4];
-          const float dbr[4] = {d4.x, d4.y, d4.z, d4.w};
-          // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
-          //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
-          //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
-          // (element-wise parts two queries per instruction; the suffix itself is serial)
-#pragma unroll
-          for (int hh = 1; hh >= 0; --hh) {
-            const int e = e4 * 4 + 2 * hh;
-            const float2 p2 = make_float2(vs[e], vs[e + 1]), i2 = make_float2(inv[e], inv[e + 1]);
-            const float2 w2 = mul2(sub2(make_float2(vd[e], vd[e + 1]), make_float2(dbr[2 * hh], dbr[2 * hh + 1])), i2);
-            const float2 s2 = mul2(p2, i2);
-            const float r1 = fmaf(-w2.y, s2.y, R);
-            R = fmaf(-w2.x, s2.x, r1);
-            const float2 pd2 = mul2(p2, add2(w2, make_float2(R, r1)));
-            vd[e] = pd2.x;
-            vd[e + 1] = pd2.y;
-            shp[e4 * 2 + hh] = pack_bf16(s2.x, s2.y);
-          }
-        }
-      };
-      if (masked_tile) chunk(std::true_type{}); else chunk(std::false_type{});
-      // warpgroup 0: the suffix behind its first query; the others: their own sum of dk_share
-      sG[(odd * 4 + wg) * 128 + row] = R;
-      // the shares stay in TMEM, over score columns this thread has consumed
-      tmem_st8(tS0 + tcol, shp);
-      asm volatile("bar.sync 1, 512;" ::: "memory");   // the compute warps
-      // the suffix behind each segment: warpgroup 0's value carries the suffix behind the
-      // half-step, every later (earlier in query order) segment adds its own sum
-      const float r0 = sG[(odd * 4 + 0) * 128 + row], r1s = sG[(odd * 4 + 1) * 128 + row];
-      const float r2s = sG[(odd * 4 + 2) * 128 + row], r3s = sG[(odd * 4 + 3) * 128 + row];
-      const float fix = wg == 0 ? 0.f : (wg == 1 ? r0 : (wg == 2 ? r0 + r1s : (r0 + r1s) + r2s));
-      sigma = ((r0 + r1s) + r2s) + r3s;                // the suffix behind the next half-step
-      // the dQ MMAs of the previous 128 queries read the pdp buffer that is written next
-      if (!odd && s >= 1) {
-        mbar_wait(dqdone, (s - 1) & 1, ctl, &g_status, kErrWaitMma);
-      }
-      {
-        uint32_t pdt[8];                               // 16 pdp values as bf16 pairs
-#pragma unroll
-        for (int e8 = 0; e8 < 2; ++e8) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int e = e8 * 8 + 2 * u;
-            const float2 f2 = fma2(make_float2(vs[e], vs[e + 1]), make_float2(fix, fix), make_float2(vd[e], vd[e + 1]));
-            pdt[e8 * 4 + u] = pack_bf16(f2.x, f2.y);
-          }
-          // shared memory: the MN-major A operand of dQ | ghat (M = queries)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPd + share_chunk_offset(row, qc + e8 * 8)),
-                       "r"(pdt[e8 * 4]), "r"(pdt[e8 * 4 + 1]), "r"(pdt[e8 * 4 + 2]), "r"(pdt[e8 * 4 + 3])
-                       : "memory");
-        }
-        // TMEM, over consumed dOV^T columns: the A operand of dK (M = keys)
-        tmem_st8(tDOV0 + tcol, pdt);
-      }
-      if (fetch_stats) {
-        sLse[(b ^ 1) * 128 + row] = st_max + log2f(st_den);
-        sDbar[(b ^ 1) * 128 + row] = st_dbar;
-      }
-      incl = incl_next;
-      incl_next = incl_next2;
-      tmem_st_wait();
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tiles + 8 * odd);
-    }
-  }
-  mbar_wait(sdone + 8, nsteps & 1, ctl, &g_status, kErrWaitMma);
-  tc_fence_after();
-  if (warp < 8) {
-    // lane = key: each warpgroup stores 32 of the 64 columns of dk_main and dv
-    float a[32];
-    const int64_t o = ((int64_t)n * g.tk + ja) * kHeadDim + 32 * wg;
-    tmem_ld32(tDK + lane_base + 32 * wg, a);
-    tmem_ld_wait(a);
-    if (!dead) {
-#pragma unroll
-      for (int e = 0; e < 32; e += 4)
-        *reinterpret_cast<float4*>(dk_main + o + e) =
-            make_float4(a[e] * g.scale, a[e + 1] * g.scale, a[e + 2] * g.scale, a[e + 3] * g.scale);
-    }
-    tmem_ld32(tDV + lane_base + 32 * wg, a);
-    tmem_ld_wait(a);
-    if (!dead) {
-#pragma unroll
-      for (int e = 0; e < 32; e += 8)
-        *reinterpret_cast<uint4*>(dv + o + e) =
-            make_uint4(pack_bf16(a[e], a[e + 1]), pack_bf16(a[e + 2], a[e + 3]),
-                       pack_bf16(a[e + 4], a[e + 5]), pack_bf16(a[e + 6], a[e + 7]));
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, 512);
-}
-
-
 // Barrier of the 128 threads of one warpgroup (named barriers 1 and 2).
 __device__ __forceinline__ void wg_barrier(int wg) {
   if (wg == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -2058,10 +1432,16 @@ inline int colsum_scan(const void* q, const void* k, const Geom& g, const float*
   if (int rc = make_map(&mq, q, g.n, g.tq, err, errlen)) return rc;
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   constexpr int smem = kColsumSmem;
-  if (int rc = set_smem_attr((const void*)colsum_scan_kernel, smem, err, errlen)) return rc;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
-  colsum_scan_kernel<<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
-                                                             total);
+  if (g.carry_rows == 32) {
+    if (int rc = set_smem_attr((const void*)colsum_scan_kernel<32>, smem, err, errlen)) return rc;
+    colsum_scan_kernel<32><<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
+                                                                   total);
+  } else {
+    if (int rc = set_smem_attr((const void*)colsum_scan_kernel<64>, smem, err, errlen)) return rc;
+    colsum_scan_kernel<64><<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
+                                                                   total);
+  }
   return launch_status("tc colsum_scan", err, errlen);
 }
 
@@ -2075,16 +1455,9 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   constexpr int smem = kMainSmem;
   static_assert(2 * (smem + 1024) <= 233472 && 3 * (smem + 1024) > 233472, "exactly two CTAs of the main pass fit one SM");
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  static const bool two_warpgroups = getenv("DILUTION_FWD_WG2") != nullptr;     // A/B switch
-  if (g.carry_rows <= 32 && !two_warpgroups) {
-    if (int rc = set_smem_attr((const void*)forward_main4_kernel, smem, err, errlen)) return rc;
-    forward_main4_kernel<<<(unsigned)(g.n * nqb), 512, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
-                                                                 out, ssum);
-  } else {
-    if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
-    forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
-                                                                out, ssum);
-  }
+  if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
+  forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
+                                                              out, ssum);
   return launch_status("tc forward_main", err, errlen);
 }
 
@@ -2119,26 +1492,7 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   if (int rc = launch_status("tc backward_prep", err, errlen)) return rc;
   CUtensorMap mdq;
   if (int rc = make_map_f32(&mdq, dq_main, g.n, g.tq, err, errlen)) return rc;
-  if (g.carry_rows == 16) {
-    constexpr int smem_bwd = kBwd4Smem;
-    static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
-    if (int rc = set_smem_attr((const void*)backward_main4_kernel, smem_bwd, err, errlen)) return rc;
-    // the kernel redistributes registers between its warpgroups; that only works inside what the
-    // CTA was launched with, so make sure the compiled kernel has the allocation the split assumes
-    static const int launch_regs = [] {
-      cudaFuncAttributes a;
-      return cudaFuncGetAttributes(&a, backward_main4_kernel) == cudaSuccess ? a.numRegs : 0;
-    }();
-    if (launch_regs * kBwd4Threads < 512 * kBwd4ComputeRegs + 128 * kBwd4IssueRegs) {
-      snprintf(err, errlen, "backward_main4_kernel was compiled with %d registers per thread; its register "
-               "split needs %d", launch_regs, kBwd4LaunchRegs);
-      return 3;
-    }
-    mark("tc_backward_main", st, 0);
-    backward_main4_kernel<<<(unsigned)(g.n * nkb), kBwd4Threads, smem_bwd, st>>>(
-        mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
-        (__nv_bfloat16*)dv, ghat);
-  } else if (g.carry_rows == 32) {
+  if (g.carry_rows == 32) {
     constexpr int smem_bwd = kBwdSmem;
     static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
     if (int rc = set_smem_attr((const void*)backward_main_kernel, smem_bwd, err, errlen)) return rc;
@@ -2147,7 +1501,7 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
         mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
         (__nv_bfloat16*)dv, ghat);
   } else {
-    snprintf(err, errlen, "the tensor-core backward needs checkpoints every 16 or 32 query rows (got %d)", g.carry_rows);
+    snprintf(err, errlen, "the tensor-core backward needs checkpoints every 32 query rows (got %d)", g.carry_rows);
     return 1;
   }
   mark("tc_backward_main", st, 1);

@@ -137,9 +137,9 @@ def dilution_attention_forward(
     column totals of p, i.e. the decode accumulator after this prefix.
     `carry` holds one per-key demand checkpoint every aux["bwd_block_m"] query
     rows; entries for keys a row block cannot see are unwritten.  The spacing
-    follows the kernels that will read it: 16 rows when the autograd op will run
-    its backward on the tensor-core kernels, 64 for their forward-only calls, 32
-    on the fp32 kernels (the reference stores every 32 or 64, kernels.py:374-377).
+    follows the kernels that will read it: 32 rows when a backward will follow and
+    on the fp32 kernels, 64 for forward-only calls of the tensor-core kernels (the
+    reference stores every 32 or 64 in the same way, kernels.py:374-377).
 
     Without return_aux the (batch*head) rows are processed in slabs so that the
     quadratic carry scratch stays under scratch_budget_gib; rows are independent,

@@ -89,11 +89,11 @@ unsigned long long dilution_launch_count(void);
 int dilution_profile_enable(int on);
 int dilution_profile_collect(char* buf, size_t cap);
 
-/* Preferred checkpoint spacing for this case: 16 query rows when a backward will follow on the
- * tensor-core kernels (bf16, BF16 precision, d == 64: its main pass gives every thread 16
- * queries), 64 for their forward-only calls (a quarter of the scratch), 32 for the fp32
- * kernels (the reference's bwd_block_m).  The tensor-core kernels accept 16, 32 and 64 (the
- * backward 16 and 32), the fp32 kernels 32 only. */
+/* Preferred checkpoint spacing for this case: 32 query rows when a backward will follow (the
+ * reference's bwd_block_m; the reverse pass gives every thread 32 queries) and on the fp32
+ * kernels; 64 for forward-only calls of the tensor-core kernels (bf16, BF16 precision,
+ * d == 64): half the scratch.  The tensor-core forward kernels accept 32 and 64, everything
+ * else 32 only. */
 int dilution_carry_rows(int dtype, int precision, int d, int training);
 
 /* Pass 1 — causal-softmax row statistics for every query.

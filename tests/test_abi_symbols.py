@@ -37,7 +37,7 @@ def test_version_and_size_queries():
     lib = load_package()._lib.load()
     assert lib.dilution_version() == 3
     assert lib.dilution_backward_scratch_bytes(2, 100, 64) == 4 * (2 * 2 * 100 * 64 + 2 * 2 * 100) + 2 * 2 * 100 * 64
-    assert lib.dilution_carry_rows(1, 2, 64, 1) == 16 and lib.dilution_carry_rows(1, 2, 64, 0) == 64
+    assert lib.dilution_carry_rows(1, 2, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 64, 0) == 64
     assert lib.dilution_carry_rows(0, 0, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 128, 0) == 32
     a = lib.dilution_decode_scratch_bytes(4, 1000, 64)
     b = lib.dilution_decode_scratch_bytes(4, 2000, 64)
