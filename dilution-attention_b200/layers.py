@@ -32,13 +32,24 @@ from . import kernels as K
 _ROPE_DIMS = (32, 64, 128)
 
 
+_TABLE_CACHE: dict = {}
+
+
 def rope_tables(rope, seq: int, offset: int, device, dtype):
     """cos / sin tables (seq, dim/2) exactly as RopeModule.forward builds them (rope.py:33-39):
-    fp32 angles, cast to the activation dtype."""
+    fp32 angles, cast to the activation dtype.  The last table per (dim, theta, device, dtype) is
+    kept: every rotated layer of a model asks for the same positions within a forward pass or a
+    decode step."""
+    key = (rope.dim, float(rope.theta), str(device), dtype)
+    hit = _TABLE_CACHE.get(key)
+    if hit is not None and hit[0] == (seq, offset):
+        return hit[1], hit[2]
     positions = torch.arange(offset, offset + seq, device=device, dtype=torch.float32)
     inv_freq = 1.0 / (rope.theta ** (torch.arange(0, rope.dim, 2, device=device, dtype=torch.float32) / rope.dim))
     freqs = torch.outer(positions, inv_freq)
-    return freqs.cos().to(dtype).contiguous(), freqs.sin().to(dtype).contiguous()
+    cos, sin = freqs.cos().to(dtype).contiguous(), freqs.sin().to(dtype).contiguous()
+    _TABLE_CACHE[key] = ((seq, offset), cos, sin)
+    return cos, sin
 
 
 class _SplitHeadsRope(torch.autograd.Function):
