@@ -22,7 +22,8 @@ Also on the line:
   decode         cached decode tok/s at 131072 and 16384 cached keys (batch 64 x 16
                  heads, 256 steps, heads sharded over ranks) against the measured HBM
                  copy bandwidth;
-  other_shapes   (1 GPU) forward + backward at the smaller shapes the reference publishes;
+  other_shapes   (1 GPU) forward + backward at the smaller shapes the reference publishes, and at
+                 an fp32 and a head_dim-128 shape, which run on the exact-fp32 tile kernels;
   config1_fp32   (1 GPU) BASELINE config 1 on the exact-fp32 kernels, with the reference's
                  CPU operator at the same shape;
   lm             (1 GPU, when a copy of the reference package is installed under
@@ -297,9 +298,13 @@ def run_triton(args):
         torch.cuda.synchronize()
         dms = a.elapsed_time(b) / steps
         other = time_other_shapes(rk.dilution_attention, dev)
+        try:
+            other_ffma = time_shapes(rk.dilution_attention, dev, FFMA_SHAPES, iters=5)
+        except Exception as e:  # noqa: BLE001
+            other_ffma = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
         import triton
         print(json.dumps({
-            "impl": "triton", "other_shapes": other, "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
+            "impl": "triton", "other_shapes": other, "fp32_and_d128_shapes": other_ffma, "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
             "unit": "TFLOP/s", "ms_per_step": ms, "steps": len(times), "n_gpus": 1, "dtype": "bf16",
             "config": {"workload": f"train_fwd_bwd_B{B}_H{H}_T{T}_d{D}",
                        "path": "dilution.kernels.dilution_attention of the reference, Triton "
@@ -316,18 +321,23 @@ def run_triton(args):
 OTHER_SHAPES = ((32, 12, 1024), (8, 8, 4096), (2, 12, 16384))
 
 
-def time_other_shapes(op, dev, iters=10):
-    """Median CUDA-event ms of forward + backward of `op` at OTHER_SHAPES (warm-up 3)."""
+# Shapes that run on the exact-fp32 tile kernels here (fp32 tensors under "tf32", as the model's
+# non-autocast path passes them, and head_dim 128): (batch, heads, seq, head_dim, dtype, precision).
+FFMA_SHAPES = ((8, 8, 4096, 64, torch.float32, "tf32"), (4, 8, 4096, 128, torch.bfloat16, "bf16"))
+
+
+def time_shapes(op, dev, shapes, iters=10):
+    """Median CUDA-event ms of forward + backward of `op` at the given shapes (warm-up 3)."""
     out = {}
-    for b, h, t in OTHER_SHAPES:
-        g = torch.Generator(device=dev).manual_seed(b * t)
-        q, k, v = (torch.empty(b, h, t, 64, device=dev, dtype=torch.bfloat16).normal_(generator=g)
-                   .mul_(0.5 if i < 2 else 1.0).requires_grad_(True) for i in range(3))
-        dout = torch.empty(b, h, t, 64, device=dev).normal_(generator=g).mul_(1e-2)
+    for b, h, t, d, dtype, prec in shapes:
+        g = torch.Generator(device=dev).manual_seed(b * t + d)
+        q, k, v = (torch.empty(b, h, t, d, device=dev, dtype=torch.float32).normal_(generator=g)
+                   .mul_(0.5 if i < 2 else 1.0).to(dtype).requires_grad_(True) for i in range(3))
+        dout = torch.empty(b, h, t, d, device=dev).normal_(generator=g).mul_(1e-2)
 
         def step():
             q.grad = k.grad = v.grad = None
-            op(q, k, v, dot_precision="bf16").backward(dout)
+            op(q, k, v, dot_precision=prec).backward(dout)
 
         for _ in range(3):
             step()
@@ -341,10 +351,15 @@ def time_other_shapes(op, dev, iters=10):
             torch.cuda.synchronize()
             times.append(a.elapsed_time(e))
         ms = statistics.median(times)
-        out[f"B{b}_H{h}_T{t}"] = {"ms": ms, "tflops": causal_flops(b * h, t, 64, 7) / (ms * 1e-3) / 1e12}
+        name = f"B{b}_H{h}_T{t}" + ("" if (d, dtype) == (64, torch.bfloat16) else f"_d{d}_{str(dtype)[6:]}_{prec}")
+        out[name] = {"ms": ms, "tflops": causal_flops(b * h, t, d, 7) / (ms * 1e-3) / 1e12}
         del q, k, v, dout
     torch.cuda.empty_cache()
     return out
+
+
+def time_other_shapes(op, dev, iters=10):
+    return time_shapes(op, dev, [(b, h, t, 64, torch.bfloat16, "bf16") for b, h, t in OTHER_SHAPES], iters)
 
 
 # ------------------------------------------------------------------------------ our arm
@@ -490,6 +505,7 @@ def run_ours(args):
     other = fp32_c1 = None
     if c.world == 1 and not args.no_other:
         other = time_other_shapes(K.dilution_attention, c.dev)
+        other["exact_fp32_kernels"] = time_shapes(K.dilution_attention, c.dev, FFMA_SHAPES, iters=5)
         fp32_c1 = run_config1(c)
     sharded = None if args.no_sharded else run_train_sharded(c, args, devt)
     e2e = None if args.no_e2e else run_e2e(c, args, host, total_flops)
