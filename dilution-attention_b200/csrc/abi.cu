@@ -130,12 +130,19 @@ dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float s
   if ((dtype) == DILUTION_F32) { using T = float; DIL_DISPATCH_D(d, __VA_ARGS__) } \
   else { using T = __nv_bfloat16; DIL_DISPATCH_D(d, __VA_ARGS__) }
 
-// ---- exact-fp32 launches ---------------------------------------------------
-template <typename T, int D>
+// ---- fp32-tile launches ------------------------------------------------------
+// MMA = false: fp32 FMAs (precision IEEE); MMA = true: tf32 tensor-core products with fp32
+// accumulation (precision TF32 on fp32 tensors; every bf16-tensor case the tcgen05 kernels do
+// not take).
+#define DIL_DISPATCH_MMA(precision, ...)                          \
+  if ((precision) == DILUTION_PREC_IEEE) { constexpr bool MMA = false; __VA_ARGS__; } \
+  else { constexpr bool MMA = true; __VA_ARGS__; }
+
+template <typename T, int D, bool MMA>
 int launch_rowstats(const void* q, const void* k, const dil::Geom& g, float* rmax, float* rden,
                     cudaStream_t st) {
   using namespace dil::simt;
-  auto kern = rowstats_kernel<T, D>;
+  auto kern = rowstats_kernel<T, D, MMA>;
   if (int rc = set_smem(kern, smem_rowstats<D>())) return rc;
   const int nqb = (g.tq + TS - 1) / TS;
   {
@@ -145,12 +152,12 @@ int launch_rowstats(const void* q, const void* k, const dil::Geom& g, float* rma
   return check_launch("rowstats");
 }
 
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 int launch_colsum(const void* q, const void* k, const dil::Geom& g, const float* rmax,
                   const float* rden, const float* base, float* carry, float* total,
                   cudaStream_t st) {
   using namespace dil::simt;
-  auto kern = colsum_scan_kernel<T, D>;
+  auto kern = colsum_scan_kernel<T, D, MMA>;
   if (int rc = set_smem(kern, smem_colsum<D>())) return rc;
   const int nkb = (g.tk + TS - 1) / TS;
   {
@@ -161,7 +168,7 @@ int launch_colsum(const void* q, const void* k, const dil::Geom& g, const float*
   return check_launch("colsum_scan");
 }
 
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 int launch_main(const void* q, const void* k, const void* v, const dil::Geom& g, const float* rmax,
                 const float* rden, const float* carry, const float* base, float* out, float* ssum,
                 float* pk, cudaStream_t st) {
@@ -170,12 +177,12 @@ int launch_main(const void* q, const void* k, const void* v, const dil::Geom& g,
   const unsigned grid = (unsigned)(g.n * nqb);
   Prof prof("simt_forward_main", st);
   if (pk) {
-    auto kern = main_kernel<T, D, true>;
+    auto kern = main_kernel<T, D, true, MMA>;
     if (int rc = set_smem(kern, smem_main<D>())) return rc;
     kern<<<grid, NT, smem_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, rmax, rden,
                                             carry, base, out, ssum, pk);
   } else {
-    auto kern = main_kernel<T, D, false>;
+    auto kern = main_kernel<T, D, false, MMA>;
     if (int rc = set_smem(kern, smem_main<D>())) return rc;
     kern<<<grid, NT, smem_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, rmax, rden,
                                             carry, base, out, ssum, nullptr);
@@ -210,7 +217,7 @@ void mark_scope(const char* name, cudaStream_t st, int phase) {
   }
 }
 
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 int launch_backward(const void* q, const void* k, const void* v, const dil::Geom& g,
                     const float* dout, const float* out, const float* rmax, const float* rden,
                     const float* carry, const float* ssum, const float* pk, const BwdScratch& s,
@@ -225,7 +232,7 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
   const int nkb = (g.tk + TS - 1) / TS;
   const unsigned grid = (unsigned)(g.n * nkb);
   {
-    auto kern = backward_main_kernel<T, D>;
+    auto kern = backward_main_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_main<D>())) return rc;
     {
       Prof prof("simt_backward_main", st);
@@ -236,7 +243,7 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
     if (int rc = check_launch("backward_main")) return rc;
   }
   {
-    auto kern = backward_dk_correction_kernel<T, D>;
+    auto kern = backward_dk_correction_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
     {
       Prof prof("simt_backward_dk_correction", st);
@@ -445,7 +452,7 @@ int dilution_rowstats(const void* q, const void* k, int dtype, int precision, in
     return dil::tc::rowstats(q, k, g, rmax, rden, st, g_err, sizeof(g_err));
   }
 #endif
-  DIL_DISPATCH(dtype, d, return (launch_rowstats<T, D>(q, k, g, rmax, rden, st)))
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_rowstats<T, D, MMA>(q, k, g, rmax, rden, st))))
   return DILUTION_OK;
 }
 
@@ -500,7 +507,7 @@ int dilution_colsum_scan(const void* q, const void* k, int dtype, int precision,
     return dil::tc::colsum_scan(q, k, g, rmax, rden, carry_base, carry, total, st, g_err, sizeof(g_err));
   }
 #endif
-  DIL_DISPATCH(dtype, d, return (launch_colsum<T, D>(q, k, g, rmax, rden, carry_base, carry, total, st)))
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_colsum<T, D, MMA>(q, k, g, rmax, rden, carry_base, carry, total, st))))
   return DILUTION_OK;
 }
 
@@ -525,7 +532,7 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
   }
 #endif
 #endif
-  DIL_DISPATCH(dtype, d, return (launch_main<T, D>(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st)))
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_main<T, D, MMA>(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st))))
   return DILUTION_OK;
 }
 
@@ -560,8 +567,8 @@ int dilution_backward(const void* q, const void* k, const void* v, int dtype, in
 #endif
   if (dout_dtype != DILUTION_F32)
     return fail(DILUTION_ERR_UNSUPPORTED, "dilution_backward: the fp32 path takes an fp32 dout");
-  DIL_DISPATCH(dtype, d, return (launch_backward<T, D>(q, k, v, g, (const float*)dout, out, rmax, rden, carry, ssum,
-                                                       pk, s, dq, dk, dv, st)))
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_backward<T, D, MMA>(
+      q, k, v, g, (const float*)dout, out, rmax, rden, carry, ssum, pk, s, dq, dk, dv, st))))
   return DILUTION_OK;
 }
 

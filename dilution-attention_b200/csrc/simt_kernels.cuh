@@ -1,14 +1,17 @@
-// Exact-fp32 kernels for every pass of dilution attention (forward and backward).
+// fp32-tile kernels for every pass of dilution attention (forward and backward).
 //
-// These serve dot_precision "ieee"/"tf32" (fp32 products, as the reference's
-// tl.dot(input_precision="ieee"), kernels.py:81-92) and every head_dim the
-// tensor-core path is not built for.  Products are plain FFMA on 64x64 tiles
-// staged in shared memory; all softmax / cumsum / share arithmetic is fp32.
+// These serve dot_precision "ieee" and "tf32" (the reference's
+// tl.dot(input_precision=...), kernels.py:81-92) and every dtype / head_dim the
+// tcgen05 path is not built for.  Products run on 64x64 tiles staged in shared
+// memory as fp32, either as plain FFMA ("ieee") or as warp-level tf32 tensor-core
+// products with fp32 accumulation (everything else); all softmax / cumsum / share
+// arithmetic is fp32.
 //
 // Layout of one CTA: 256 threads, one 64x64 (query x key) tile at a time.
-//   thread (ty = tid/16, tx = tid%16) owns tile rows ty+16r, columns tx+16c.
+//   FFMA: thread (ty = tid/16, tx = tid%16) owns tile rows ty+16r, columns tx+16c;
+//   MMA:  warp w owns rows 16*(w%4).., columns (N/2)*(w/4).. of a [64 x N] result.
 // Shared tiles of operands are [64][D+4] fp32 (float4-aligned, conflict-free
-// for the access patterns below); score tiles are [64][65].
+// for the access patterns below); score tiles are [64][68].
 #pragma once
 
 #include "common.cuh"
@@ -19,9 +22,42 @@ namespace simt {
 constexpr int TS = 64;    // tile side
 static_assert(TS == 2 * kCarryRows, "two demand checkpoints per tile");
 constexpr int NT = 256;   // threads per CTA
-constexpr int SL = 65;    // leading dimension of score tiles
+constexpr int SL = 68;    // leading dimension of score tiles (4 mod 32: conflict-free MMA fragments)
 
 template <int D> __host__ __device__ constexpr int ld() { return D + 4; }
+
+// Products come in two flavours.  MMA = false: fp32 FMAs, exact (dot_precision "ieee").
+// MMA = true: warp-level tensor-core products on tf32 operands with fp32 accumulation
+// (mma.sync m16n8k8) — what the reference's "tf32" mode means for fp32 tensors
+// (kernels.py:318-325), and exact on bf16 tensors' values, which tf32 holds without loss.
+// The eight warps of a CTA tile a [64 x N] result as 4 row groups of 16 x 2 column groups of N/2.
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// Which element of a [64 x D] result a thread's accumulator acc[r][c] holds.
+template <bool MMA, int D> struct Frag {
+  static __device__ __forceinline__ int row(int r, int /*c*/) { return (threadIdx.x >> 4) + 16 * r; }
+  static __device__ __forceinline__ int col(int /*r*/, int c) { return (threadIdx.x & 15) + 16 * c; }
+};
+template <int D> struct Frag<true, D> {
+  // r = register of the m16n8 fragment, c = 8-column tile of the warp's D/2 columns
+  static __device__ __forceinline__ int row(int r, int /*c*/) {
+    return 16 * ((threadIdx.x >> 5) & 3) + ((threadIdx.x & 31) >> 2) + 8 * (r >> 1);
+  }
+  static __device__ __forceinline__ int col(int r, int c) {
+    return (D / 2) * (threadIdx.x >> 7) + 8 * c + 2 * (threadIdx.x & 3) + (r & 1);
+  }
+};
 
 // Rows [row0, row0+64) of a (rows_total, D) row-major matrix -> fp32 smem tile.
 // Rows past the end are zero.
@@ -36,10 +72,39 @@ __device__ __forceinline__ void load_tile(float* s, const T* __restrict__ g, int
   }
 }
 
-// C[i][j] = sum_d A[i][d] * B[j][d]   (A, B: [64][D+4]; C: [64][65])
-template <int D>
+// C[i][j] = sum_d A[i][d] * B[j][d]   (A, B: [64][D+4]; C: [64][SL])
+template <int D, bool MMA>
 __device__ __forceinline__ void score_tile(const float* A, const float* B, float* C) {
   constexpr int LD = ld<D>();
+  if (MMA) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3, r0 = 16 * (warp & 3), c0 = 32 * (warp >> 2);
+    float acc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+#pragma unroll 2
+    for (int k0 = 0; k0 < D; k0 += 8) {
+      const uint32_t a[4] = {to_tf32(A[(r0 + g) * LD + k0 + t]), to_tf32(A[(r0 + g + 8) * LD + k0 + t]),
+                             to_tf32(A[(r0 + g) * LD + k0 + t + 4]), to_tf32(A[(r0 + g + 8) * LD + k0 + t + 4])};
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float* brow = B + (c0 + 8 * nt + g) * LD + k0 + t;
+        const uint32_t b[2] = {to_tf32(brow[0]), to_tf32(brow[4])};
+        mma_tf32(acc[nt], a, b);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      float* c = C + (r0 + g) * SL + c0 + 8 * nt + 2 * t;
+      c[0] = acc[nt][0];
+      c[1] = acc[nt][1];
+      c[8 * SL] = acc[nt][2];
+      c[8 * SL + 1] = acc[nt][3];
+    }
+    return;
+  }
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4];
 #pragma unroll
@@ -69,12 +134,47 @@ __device__ __forceinline__ void score_tile(const float* A, const float* B, float
     for (int c = 0; c < 4; ++c) C[(ty + 16 * r) * SL + tx + 16 * c] = acc[r][c];
 }
 
-// acc[r][c] += sum_j A(i,j) * B[j][tx+16c],  i = ty+16r.
-// A is a [64][65] score tile, read transposed when TRANS_A (A(i,j) = A[j][i]).
-template <int D, bool TRANS_A>
+// acc[r][c] += sum_j A(i,j) * B[j][col],  (i, col) = Frag<MMA, D>::row / col (r, c).
+// A is a [64][SL] score tile, read transposed when TRANS_A (A(i,j) = A[j][i]).
+template <int D, bool TRANS_A, bool MMA>
 __device__ __forceinline__ void accum_tile(const float* A, const float* B, float (&acc)[4][D / 16]) {
   constexpr int LD = ld<D>();
   constexpr int DC = D / 16;
+  if (MMA) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3, r0 = 16 * (warp & 3), c0 = (D / 2) * (warp >> 2);
+    float c4[DC][4];
+#pragma unroll
+    for (int nt = 0; nt < DC; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c4[nt][i] = acc[i][nt];
+#pragma unroll 2
+    for (int k0 = 0; k0 < TS; k0 += 8) {
+      uint32_t a[4];
+      if (TRANS_A) {
+        a[0] = to_tf32(A[(k0 + t) * SL + r0 + g]);
+        a[1] = to_tf32(A[(k0 + t) * SL + r0 + g + 8]);
+        a[2] = to_tf32(A[(k0 + t + 4) * SL + r0 + g]);
+        a[3] = to_tf32(A[(k0 + t + 4) * SL + r0 + g + 8]);
+      } else {
+        a[0] = to_tf32(A[(r0 + g) * SL + k0 + t]);
+        a[1] = to_tf32(A[(r0 + g + 8) * SL + k0 + t]);
+        a[2] = to_tf32(A[(r0 + g) * SL + k0 + t + 4]);
+        a[3] = to_tf32(A[(r0 + g + 8) * SL + k0 + t + 4]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < DC; ++nt) {
+        const float* bcol = B + (k0 + t) * LD + c0 + 8 * nt + g;
+        const uint32_t b[2] = {to_tf32(bcol[0]), to_tf32(bcol[4 * LD])};
+        mma_tf32(c4[nt], a, b);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < DC; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i][nt] = c4[nt][i];
+    return;
+  }
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
 #pragma unroll 4
   for (int j = 0; j < TS; ++j) {
@@ -120,7 +220,7 @@ __device__ __forceinline__ int first_query_block(int jb, int q_off) {
 
 // ---------------------------------------------------------------- pass 1
 // grid = n * ceil(tq/64), longest rows first.
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
                                                       const T* __restrict__ k, Geom g,
                                                       float* __restrict__ rmax,
@@ -144,7 +244,7 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
     __syncthreads();
     load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
     __syncthreads();
-    score_tile<D>(sQ, sK, sS);
+    score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
     float z[16];
     float tmax = -INFINITY;
@@ -182,7 +282,7 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
 // Key-stationary: one CTA per (row n, 64-key block), query blocks in causal
 // order; the running per-key demand is the exclusive scan, written as a
 // checkpoint before each query block.  grid = n * ceil(tk/64).
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) colsum_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
     const float* __restrict__ rden, const float* __restrict__ carry_base,
@@ -210,7 +310,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
     load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
     load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
     __syncthreads();
-    score_tile<D>(sQ, sK, sS);
+    score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
     float part = 0.f;
 #pragma unroll 4
@@ -237,7 +337,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
 
 // ---------------------------------------------------------------- pass 3
 // Query-stationary main pass.  grid = n * ceil(tq/64), longest rows first.
-template <typename T, int D, bool PK>
+template <typename T, int D, bool PK, bool MMA>
 __global__ void __launch_bounds__(NT) main_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden,
@@ -277,7 +377,7 @@ __global__ void __launch_bounds__(NT) main_kernel(
     load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
     load_tile<T, D>(sV, v + n * g.tk * D, jb * TS, g.tk);
     __syncthreads();
-    score_tile<D>(sQ, sK, sP);
+    score_tile<D, MMA>(sQ, sK, sP);
     __syncthreads();
     scores_to_bids(sP, sM, sRinv, g, ib, jb);
     __syncthreads();
@@ -294,8 +394,8 @@ __global__ void __launch_bounds__(NT) main_kernel(
     __syncthreads();
 #pragma unroll
     for (int c = 0; c < 16; ++c) my_ssum += sSh[row * SL + part * 16 + c];
-    accum_tile<D, false>(sSh, sV, acc_o);
-    if (PK) accum_tile<D, false>(sP, sK, acc_pk);
+    accum_tile<D, false, MMA>(sSh, sV, acc_o);
+    if (PK) accum_tile<D, false, MMA>(sP, sK, acc_pk);
   }
   my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 1);
   my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 2);
@@ -306,15 +406,15 @@ __global__ void __launch_bounds__(NT) main_kernel(
     if (i < g.tq) ssum[n * g.tq + i] = my_ssum;
   }
   __syncthreads();
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  using F = Frag<MMA, D>;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int il = ty + 16 * r, i = ib * TS + il;
+    const int il = F::row(r, 0), i = ib * TS + il;
     if (i >= g.tq) continue;
     const float den = sRow[il] + g.eps;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
-      const int64_t o = (n * g.tq + i) * D + tx + 16 * c;
+      const int64_t o = (n * g.tq + i) * D + F::col(r, c);
       out[o] = acc_o[r][c] / den;
       if (PK) pk[o] = acc_pk[r][c] * g.scale;
     }
@@ -345,7 +445,7 @@ __global__ void dbar_kernel(const float* __restrict__ dout, const float* __restr
 // Heavy reverse pass (the reference's BA, kernels.py:677-775): key-stationary,
 // query blocks from last to first so the per-key suffix of dk_share is a
 // running sum.  grid = n * ceil(t/64).
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) backward_main_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, Geom g,
     const float* __restrict__ dout, const float* __restrict__ dbar,
@@ -381,7 +481,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
     for (int c = 0; c < DC; ++c) acc_dk[r][c] = acc_dv[r][c] = 0.f;
   float sufk = 0.f;
   const int row = threadIdx.x >> 2, part = threadIdx.x & 3;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  using F = Frag<MMA, D>;
 
   for (int ib = nqb - 1; ib >= first_query_block(jb, g.q_off); --ib) {
     __syncthreads();
@@ -395,8 +495,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       sSinv[threadIdx.x] = ok ? 1.f / (ssum[n * g.tq + i] + g.eps) : 0.f;
     }
     __syncthreads();
-    score_tile<D>(sQ, sK, sP);
-    score_tile<D>(sDO, sV, sDS);
+    score_tile<D, MMA>(sQ, sK, sP);
+    score_tile<D, MMA>(sDO, sV, sDS);
     __syncthreads();
     scores_to_bids(sP, sM, sRinv, g, ib, jb);
     for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
@@ -435,30 +535,30 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       const int i = ib * TS + row;
       if (part == 0 && i < g.tq) atomicAdd(&ghat[n * g.tq + i], gs);
     }
-    accum_tile<D, true>(sP, sDO, acc_dv);
-    accum_tile<D, true>(sDS, sQ, acc_dk);
+    accum_tile<D, true, MMA>(sP, sDO, acc_dv);
+    accum_tile<D, true, MMA>(sDS, sQ, acc_dk);
     float dqp[4][DC];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
       for (int c = 0; c < DC; ++c) dqp[r][c] = 0.f;
-    accum_tile<D, false>(sDS, sK, dqp);
+    accum_tile<D, false, MMA>(sDS, sK, dqp);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const int i = ib * TS + ty + 16 * r;
+      const int i = ib * TS + F::row(r, 0);
       if (i >= g.tq) continue;
 #pragma unroll
       for (int c = 0; c < DC; ++c)
-        atomicAdd(&dq_main[(n * g.tq + i) * D + tx + 16 * c], dqp[r][c] * g.scale);
+        atomicAdd(&dq_main[(n * g.tq + i) * D + F::col(r, c)], dqp[r][c] * g.scale);
     }
   }
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int j = jb * TS + ty + 16 * r;
+    const int j = jb * TS + F::row(r, 0);
     if (j >= g.tk) continue;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
-      const int64_t o = (n * g.tk + j) * D + tx + 16 * c;
+      const int64_t o = (n * g.tk + j) * D + F::col(r, c);
       dk_main[o] = acc_dk[r][c] * g.scale;
       dv[o] = from_f32<T>(acc_dv[r][c]);
     }
@@ -467,7 +567,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
 
 // Softmax-Jacobian correction for dk (the reference's BC, kernels.py:777-809):
 // dk = dk_main - scale * p^T (ghat q).  grid = n * ceil(t/64).
-template <typename T, int D>
+template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
     const float* __restrict__ rden, const float* __restrict__ ghat,
@@ -499,7 +599,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
       sG[threadIdx.x] = i < g.tq ? ghat[n * g.tq + i] : 0.f;
     }
     __syncthreads();
-    score_tile<D>(sQ, sK, sP);
+    score_tile<D, MMA>(sQ, sK, sP);
     __syncthreads();
     for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
       const int i = idx >> 6, j = idx & 63;
@@ -508,16 +608,16 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
       sP[i * SL + j] = (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] * sG[i] : 0.f;
     }
     __syncthreads();
-    accum_tile<D, true>(sP, sQ, acc);
+    accum_tile<D, true, MMA>(sP, sQ, acc);
   }
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  using F = Frag<MMA, D>;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int j = jb * TS + ty + 16 * r;
+    const int j = jb * TS + F::row(r, 0);
     if (j >= g.tk) continue;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
-      const int64_t o = (n * g.tk + j) * D + tx + 16 * c;
+      const int64_t o = (n * g.tk + j) * D + F::col(r, c);
       dk[o] = from_f32<T>(dk_main[o] - acc[r][c] * g.scale);
     }
   }

@@ -51,7 +51,7 @@ TC_SAVE_PK = os.environ.get("DILUTION_SAVE_PK", "1") != "0"
 
 
 def _resolve_precision(dot_precision: str) -> tuple[int, str]:
-    """"ieee" / "tf32": fp32 products; "bf16": bf16 tensor-core operands
+    """"ieee": fp32 products; "tf32": tf32 tensor-core products of fp32 operands; "bf16": bf16 tensor-core operands
     (kernels.py:318-325, same return values and error)."""
     if dot_precision == "bf16":
         return 1, "tf32"
@@ -252,7 +252,7 @@ def dilution_attention(
     """Differentiable fused dilution attention (kernels.py:906-930).
 
     "bf16" (default): bf16 tensor-core operands, fp32 accumulation and fp32
-    cumsum/share maths; "tf32"/"ieee": fp32 products.
+    cumsum/share maths; "tf32": tf32 tensor-core products of fp32 operands; "ieee": fp32 products.
     """
     _resolve_precision(dot_precision)
     return _DilutionAttentionFn.apply(q, k, v, dot_precision)

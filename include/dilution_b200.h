@@ -15,8 +15,11 @@
  *    the reference builds with reshape(n, seq, d).contiguous() (kernels.py:362-364);
  *  - `dtype` is the element type of q/k/v (and of the decode caches);
  *  - `precision` mirrors the reference's dot_precision (kernels.py:318-325):
- *    IEEE/TF32 keep fp32 products (exact fp32 FMA here, which satisfies both),
- *    BF16 uses bf16 tensor-core operands with fp32 accumulation;
+ *    IEEE keeps fp32 products (fp32 FMAs); TF32 rounds the operands of every
+ *    product to tf32 and accumulates in fp32 on the tensor cores, as tl.dot does
+ *    with input_precision="tf32" (kernels.py:81-92); BF16 uses bf16 tensor-core
+ *    operands with fp32 accumulation (tcgen05 for bf16 tensors of head_dim 64;
+ *    the tf32 tile kernels, which hold bf16 values without loss, otherwise);
  *  - row statistics are in the log2 domain as in kernels.py:159-184:
  *    rmax = max_j z_ij, rden = sum_j 2^(z_ij - rmax), z = q.k * scale * log2(e);
  *  - `q_offset`: absolute position of local query row 0 (0 for a whole sequence;

@@ -35,14 +35,47 @@ def test_backward_small_goldens(kernels, t):
         assert rel_err(got.cpu(), c[name]) < 1e-4, name
 
 
+# "ieee": fp32 FMAs, 1e-4 of the oracle.  "tf32": tensor-core products on operands rounded to
+# 10 mantissa bits with fp32 accumulation (the reference's own meaning of the mode,
+# kernels.py:318-325), within 5e-3 of the fp32 oracle.
+@pytest.mark.parametrize("prec,tol", [("ieee", 1e-4), ("tf32", 5e-3)])
 @pytest.mark.parametrize("head_dim", [16, 32, 128])
-def test_backward_other_head_dims(kernels, head_dim):
+def test_backward_other_head_dims(kernels, head_dim, prec, tol):
     q, k, v, dout = make_inputs(1, 2, 130, head_dim, 500 + head_dim)
-    _, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
+    ref, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
     qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
-    kernels.dilution_attention(qs, ks, vs, dot_precision="tf32").backward(dout.to(DEV))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision=prec)
+    out.backward(dout.to(DEV))
+    assert rel_err(out.detach().cpu(), ref) < tol
     for name, ref, got in (("dq", rdq, qs.grad), ("dk", rdk, ks.grad), ("dv", rdv, vs.grad)):
-        assert rel_err(got.cpu(), ref) < 1e-4, name
+        assert rel_err(got.cpu(), ref) < tol, name
+
+
+@pytest.mark.parametrize("seq", [64, 257, 1100])
+def test_tf32_products_head_dim_64(kernels, seq):
+    q, k, v, dout = make_inputs(2, 3, seq, 64, 900 + seq)
+    ref, rdq, rdk, rdv = O.dilution_backward(q, k, v, dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision="tf32")
+    out.backward(dout.to(DEV))
+    assert rel_err(out.detach().cpu(), ref) < 5e-3
+    for name, ref, got in (("dq", rdq, qs.grad), ("dk", rdk, ks.grad), ("dv", rdv, vs.grad)):
+        assert rel_err(got.cpu(), ref) < 5e-3, name
+
+
+@pytest.mark.parametrize("head_dim", [32, 128])
+def test_bf16_tensors_other_head_dims(kernels, head_dim):
+    """bf16 tensors whose head size the tcgen05 kernels do not take: tile kernels with
+    tensor-core products, against the oracle on the same bf16-rounded inputs."""
+    q, k, v, dout = make_inputs(1, 3, 300, head_dim, 70 + head_dim, scales=(0.5, 0.5, 1.0, 1.0))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref, rdq, rdk, rdv = O.dilution_backward(qb.float(), kb.float(), vb.float(), dout)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    out = kernels.dilution_attention(qs, ks, vs, dot_precision="bf16")
+    out.backward(dout.to(DEV).bfloat16())
+    assert (out.detach().float().cpu() - ref).abs().max().item() < 2e-2
+    for name, ref, got in (("dq", rdq, qs.grad), ("dk", rdk, ks.grad), ("dv", rdv, vs.grad)):
+        assert rel_err(got.float().cpu(), ref) < 2e-2, name
 
 
 def test_backward_finite_grads(kernels):
