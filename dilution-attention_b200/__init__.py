@@ -15,7 +15,7 @@ After the first import it is also registered as `dilution_attention_b200`.
 
 import sys as _sys
 
-from . import _lib, kernels, layers, partition  # noqa: F401
+from . import _lib, kernels, kernels_bid, layers, partition  # noqa: F401
 from .kernels import (  # noqa: F401
     dilution_attention,
     dilution_attention_forward,
@@ -32,7 +32,7 @@ from .layers import install_layers, softmax_decode_append_step, split_heads_rope
 _sys.modules.setdefault("dilution_attention_b200", _sys.modules[__name__])
 
 __all__ = [
-    "kernels", "partition", "dilution_attention", "dilution_attention_forward",
+    "kernels", "kernels_bid", "partition", "dilution_attention", "dilution_attention_forward",
     "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step",
     "dilution_decode_append_step", "softmax_attention_forward", "softmax_decode_append_step",
     "split_heads_rope", "install", "uninstall", "install_layers", "uninstall_layers", "layers",

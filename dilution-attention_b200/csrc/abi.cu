@@ -105,9 +105,12 @@ int check_common(const char* fn, int dtype, int precision, int64_t n, int64_t tq
 int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_offset, int carry_rows);
 
 dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps,
-                    int carry_rows = dil::kCarryRows) {
+                    int carry_rows = dil::kCarryRows, int bid = dil::kBidSoftmax,
+                    int share = dil::kShareInclusive) {
   dil::Geom g;
   g.carry_rows = carry_rows;
+  g.bid = bid;
+  g.share = share;
   g.n = n;
   g.tq = (int)tq;
   g.tk = (int)tk;
@@ -242,7 +245,8 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
     }
     if (int rc = check_launch("backward_main")) return rc;
   }
-  {
+  const int64_t total = rows * D;
+  if (g.bid == dil::kBidSoftmax) {
     auto kern = backward_dk_correction_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
     {
@@ -251,12 +255,17 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
                                                 s.dk_main, (T*)dk);
     }
     if (int rc = check_launch("backward_dk_correction")) return rc;
+  } else {
+    // a bid without row normalisation has no Jacobian correction: dk is dk_main in the input dtype
+    Prof prof("dk_store", st);
+    dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(s.dk_main, nullptr, nullptr, total, D,
+                                                                          (T*)dk);
+    if (int rc = check_launch("dk_store")) return rc;
   }
-  const int64_t total = rows * D;
   {
     Prof prof("dq_epilogue", st);
-    dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(s.dq_main, s.ghat, pk, total, D,
-                                                                          (T*)dq);
+    dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        s.dq_main, s.ghat, g.bid == dil::kBidSoftmax ? pk : nullptr, total, D, (T*)dq);
   }
   return check_launch("dq_epilogue");
 }
@@ -283,11 +292,11 @@ dil::decode::Scratch carve_decode(void* scratch, int64_t n, int64_t len, int d) 
   return s;
 }
 
-template <typename T, int D, bool DILUTE = true>
+template <typename T, int D, int MODE = dil::decode::kSweepDilution>
 int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
                   cudaStream_t st, bool timing = true, const void* knew = nullptr,
-                  const void* vnew = nullptr) {
+                  const void* vnew = nullptr, int bid = dil::kBidSoftmax, int share = dil::kShareInclusive) {
   using namespace dil::decode;
   const int chunk = decode_chunk(n, len);
   const int nch = (int)((len + chunk - 1) / chunk);
@@ -303,9 +312,9 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
   if (int rc = check_launch("decode scores")) return rc;
   {
     Prof prof("decode_sweep", st, timing);
-    sweep_kernel<T, D, DILUTE><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
-                                            committed, s.pout, s.psum, (const T*)vnew,
-                                            (T*)const_cast<void*>(vc));
+    sweep_kernel<T, D, MODE><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
+                                                  committed, s.pout, s.psum, (const T*)vnew,
+                                                  (T*)const_cast<void*>(vc), bid, share);
   }
   if (int rc = check_launch("decode sweep")) return rc;
   {
@@ -667,8 +676,85 @@ int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v
   if (((uintptr_t)q1 | (uintptr_t)k1 | (uintptr_t)v1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
     return fail(DILUTION_ERR_ARG, "dilution_softmax_decode_append: q1 / k1 / v1 / caches must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  DIL_DISPATCH(dtype, d, return (launch_decode<T, D, false>(q1, k_cache, v_cache, n, capacity, length, scale,
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D, dil::decode::kSweepSoftmax>(q1, k_cache, v_cache, n, capacity, length, scale,
                                                             0.f, nullptr, out, scratch, st, true, k1, v1)))
+  return DILUTION_OK;
+}
+
+// ---- share / bid variants (the tile kernels; kernels_bid.py of the reference) -------------
+static int check_variant(const char* fn, int bid, int share) {
+  if (bid != dil::kBidSoftmax && bid != dil::kBidSigmoid)
+    return fail(DILUTION_ERR_UNSUPPORTED, "%s: bid %d is not built (DILUTION_BID_SOFTMAX, DILUTION_BID_SIGMOID)", fn, bid);
+  if (share != dil::kShareNone && share != dil::kShareInclusive && share != dil::kShareExclusive)
+    return fail(DILUTION_ERR_ARG, "%s: share must be 0 (none), 1 (inclusive) or 2 (exclusive)", fn);
+  return DILUTION_OK;
+}
+
+int dilution_variant_forward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                             int64_t t, int d, float scale, float eps, int bid, int share, float* rmax,
+                             float* rden, float* carry, float* total, float* out, float* ssum, float* pk,
+                             void* stream) {
+  if (int rc = check_common("dilution_variant_forward", dtype, precision, n, t, t, 0, d)) return rc;
+  if (int rc = check_variant("dilution_variant_forward", bid, share)) return rc;
+  const bool stats = bid == dil::kBidSoftmax;
+  if (!q || !k || !v || !carry || !total || !out || !ssum || (stats && (!rmax || !rden)))
+    return fail(DILUTION_ERR_ARG, "dilution_variant_forward: null pointer");
+  if (!stats) rmax = rden = pk = nullptr;
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (stats) {
+    DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, {
+      if (int rc = launch_rowstats<T, D, MMA>(q, k, g, rmax, rden, st)) return rc;
+    }))
+  }
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, {
+    if (int rc = launch_colsum<T, D, MMA>(q, k, g, rmax, rden, nullptr, carry, total, st)) return rc;
+  }))
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_main<T, D, MMA>(q, k, v, g, rmax, rden, carry, nullptr, out, ssum, pk, st))))
+  return DILUTION_OK;
+}
+
+int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                              int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
+                              const float* out, const float* rmax, const float* rden, const float* carry,
+                              const float* ssum, const float* pk, void* scratch, void* dq, void* dk, void* dv,
+                              void* stream) {
+  if (int rc = check_common("dilution_variant_backward", dtype, precision, n, t, t, 0, d)) return rc;
+  if (int rc = check_variant("dilution_variant_backward", bid, share)) return rc;
+  const bool stats = bid == dil::kBidSoftmax;
+  if (!q || !k || !v || !dout || !out || !carry || !ssum || !scratch || !dq || !dk || !dv ||
+      (stats && (!rmax || !rden || !pk)))
+    return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
+  if (!stats) rmax = rden = pk = nullptr;
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
+  const BwdScratch s = carve_bwd(scratch, n, t, d);
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_backward<T, D, MMA>(
+      q, k, v, g, dout, out, rmax, rden, carry, ssum, pk, s, dq, dk, dv, st))))
+  return DILUTION_OK;
+}
+
+int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                            int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
+                            float eps, int bid, int share, float* committed, void* out, void* scratch,
+                            void* stream) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "dilution_variant_decode: dtype must be DILUTION_F32 or DILUTION_BF16");
+  if (int rc = check_variant("dilution_variant_decode", bid, share)) return rc;
+  if (!valid_d(d))
+    return fail(DILUTION_ERR_UNSUPPORTED, "dilution_variant_decode: head_dim %d not in {16, 32, 64, 128}", d);
+  if (n < 1 || n > 65535)
+    return fail(DILUTION_ERR_ARG, "dilution_variant_decode: n must be in [1, 65535] rows per call");
+  if (capacity < 1 || length < 1 || length > capacity || capacity > (1 << 30))
+    return fail(DILUTION_ERR_ARG, "dilution_variant_decode: length %lld outside cache capacity %lld",
+                (long long)length, (long long)capacity);
+  if (!q1 || !k_cache || !v_cache || !committed || !out || !scratch || ((k1 == nullptr) != (v1 == nullptr)))
+    return fail(DILUTION_ERR_ARG, "dilution_variant_decode: null pointer");
+  if (((uintptr_t)q1 | (uintptr_t)k1 | (uintptr_t)v1 | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+    return fail(DILUTION_ERR_ARG, "dilution_variant_decode: q1 / k1 / v1 / caches must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D, dil::decode::kSweepVariant>(
+      q1, k_cache, v_cache, n, capacity, length, scale, eps, committed, out, scratch, st, true, k1, v1, bid, share)))
   return DILUTION_OK;
 }
 

@@ -112,6 +112,11 @@ struct Geom {
   float scale;
   float eps;
   int carry_rows; // query rows per demand checkpoint (16, 32 or 64)
+  int bid;        // bid function (codes of kernels_bid.py:94): 0 softmax, 5 sigmoid; tile kernels only
+  int share;      // share step (kernels_bid.py:123-127): 1 inclusive, 2 exclusive history, 0 none
 };
+
+constexpr int kBidSoftmax = 0, kBidSigmoid = 5;
+constexpr int kShareNone = 0, kShareInclusive = 1, kShareExclusive = 2;
 
 }  // namespace dil

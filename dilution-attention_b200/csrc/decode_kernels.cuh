@@ -4,8 +4,9 @@
 // launches with no device-side waiting:
 //   scores_kernel  : stream K once; z_j = q.k_j (log2 domain) -> scratch, and
 //                    (max, sum) of each chunk;
-//   sweep_kernel   : combine the chunk statistics, p_j, share_j = p/(c+p+eps),
-//                    c_j += p_j in place, stream V once, partial share@V;
+//   sweep_kernel   : combine the chunk statistics, p_j, share_j = p/(c+p+eps) (or the
+//                    selected bid / share variant), c_j += p_j in place, stream V once,
+//                    partial share@V;
 //   finalize_kernel: out = sum(partials) / (sum(share) + eps).
 // Optionally the step also appends the new token (the model's _append_kv,
 // model.py:85-93): given its k and v rows, the CTA that owns position len-1 takes
@@ -151,10 +152,29 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   }
 }
 
-// grid = (chunks, n).  DILUTE = false turns the step into plain softmax attention of the new
-// token over the cache (share = p, no demand read or written): the cached step of the
-// reference's softmax layers (model.py:112-117).
-template <typename T, int D, bool DILUTE = true>
+// The share of one key (kernels_bid.py:925-945) and its demand advanced in place.
+//   MODE kSweepDilution: softmax bid, share = p / (c + p + eps)            (the operator)
+//   MODE kSweepSoftmax : share = p, no demand read or written: plain softmax attention of the
+//                        new token over the cache, the cached step of the reference's softmax
+//                        layers (model.py:112-117)
+//   MODE kSweepVariant : bid (softmax / sigmoid) and share step (inclusive / exclusive / none)
+//                        chosen at run time; the demand advances by p in every case
+constexpr int kSweepSoftmax = 0, kSweepDilution = 1, kSweepVariant = 2;
+
+template <int MODE>
+__device__ __forceinline__ float key_share(float a, float gmax, float rinv, float eps, float* c_ptr,
+                                           bool fresh, int bid, int share_step) {
+  float p = exp2f(a - gmax) * rinv;
+  if (MODE == kSweepSoftmax) return p;
+  if (MODE == kSweepVariant && bid == kBidSigmoid) p = 1.f / (1.f + exp2f(-a));
+  const float c = fresh ? 0.f : *c_ptr;     // a fresh key: no demand yet, whatever the buffer holds
+  *c_ptr = c + p;
+  if (MODE == kSweepDilution || share_step == kShareInclusive) return p / (c + p + eps);
+  return share_step == kShareExclusive ? p / (c + eps) : p;
+}
+
+// grid = (chunks, n)
+template <typename T, int D, int MODE = kSweepDilution>
 __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int64_t cap, int len,
                                                    int chunk, float eps, int64_t stride,
                                                    const float* __restrict__ aff,
@@ -162,7 +182,8 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
                                                    float* __restrict__ committed,
                                                    float* __restrict__ pout,
                                                    float* __restrict__ psum,
-                                                   const T* __restrict__ vnew, T* __restrict__ vc_out) {
+                                                   const T* __restrict__ vnew, T* __restrict__ vc_out,
+                                                   int bid, int share_step) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   const int64_t n = blockIdx.y;
   const int nch = gridDim.x;
@@ -214,15 +235,8 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     const int key = base + lane;
     float share = 0.f;
     if (key < k1) {
-      const float a = aff[n * stride + key];
-      const float p = exp2f(a - gmax) * rinv;
-      if (DILUTE) {
-        const float c = committed[n * cap + key];
-        share = p / (c + p + eps);
-        committed[n * cap + key] = c + p;
-      } else {
-        share = p;
-      }
+      share = key_share<MODE>(aff[n * stride + key], gmax, rinv, eps, committed + n * cap + key, false, bid,
+                              share_step);
       ssh += share;
     }
 #pragma unroll
@@ -238,9 +252,8 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     // the new token: no demand on it yet (whatever the buffer holds), its value row from vnew
     float share = 0.f;
     if (lane == 0) {
-      const float p = exp2f(aff[n * stride + len - 1] - gmax) * rinv;
-      share = DILUTE ? p / (p + eps) : p;
-      if (DILUTE) committed[n * cap + len - 1] = p;
+      share = key_share<MODE>(aff[n * stride + len - 1], gmax, rinv, eps, committed + n * cap + len - 1, true,
+                              bid, share_step);
       ssh += share;
     }
     share = __shfl_sync(0xffffffffu, share, 0);

@@ -192,14 +192,22 @@ __device__ __forceinline__ void accum_tile(const float* A, const float* B, float
 
 // Row statistics of local rows [ib*64, ib*64+64) into shared arrays (rinv = 1/rden;
 // both zero for rows past tq so that their p is exactly zero).
+// The sigmoid bid has no row statistics (kernels_bid.py:259-262): null pointers, unused values.
 __device__ __forceinline__ void load_stats(float* sM, float* sRinv, const float* rmax,
                                            const float* rden, int64_t n, int ib, int tq) {
   if (threadIdx.x < TS) {
     const int i = ib * TS + threadIdx.x;
-    const bool ok = i < tq;
+    const bool ok = i < tq && rmax != nullptr;
     sM[threadIdx.x] = ok ? rmax[n * tq + i] : 0.f;
     sRinv[threadIdx.x] = ok ? 1.f / rden[n * tq + i] : 0.f;
   }
+}
+
+// The bid of one raw score (kernels_bid.py:191-197): softmax from the row statistics, or the
+// element-wise sigmoid of the scaled score.
+__device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv) {
+  const float z = score * g.zscale;
+  return g.bid == kBidSigmoid ? 1.f / (1.f + exp2f(-z)) : exp2f(z - m) * rinv;
 }
 
 // Raw scores in S -> bids p in place (zero outside the causal/bounds mask).
@@ -207,9 +215,8 @@ __device__ __forceinline__ void scores_to_bids(float* S, const float* sM, const 
                                                const Geom& g, int ib, int jb) {
   for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
     const int i = idx >> 6, j = idx & 63;
-    const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
-    const float z = S[i * SL + j] * g.zscale;
-    S[i * SL + j] = (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] : 0.f;
+    const int ja = jb * TS + j, il = ib * TS + i, ia = g.q_off + il;
+    S[i * SL + j] = (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(S[i * SL + j], g, sM[i], sRinv[i]) : 0.f;
   }
 }
 
@@ -316,9 +323,8 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
 #pragma unroll 4
     for (int rr = 0; rr < 16; ++rr) {
       const int i = seg * 16 + rr;
-      const int ia = g.q_off + ib * TS + i;
-      const float z = sS[i * SL + col] * g.zscale;
-      part += (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] : 0.f;
+      const int il = ib * TS + i, ia = g.q_off + il;
+      part += (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(sS[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
     }
     sPart[seg * TS + col] = part;
     __syncthreads();
@@ -385,10 +391,20 @@ __global__ void __launch_bounds__(NT) main_kernel(
       const int col = threadIdx.x, ja = jb * TS + col;
       float c = (ja < g.tk) ? carry_row[ja] : 0.f;
       if (carry_base != nullptr && ja < g.tk) c += carry_base[n * g.tk + ja];
-      for (int i = 0; i < TS; ++i) {
-        const float p = sP[i * SL + col];
-        sSh[i * SL + col] = p / (c + p + g.eps);
-        c += p;
+      if (g.share == kShareInclusive) {
+        for (int i = 0; i < TS; ++i) {
+          const float p = sP[i * SL + col];
+          sSh[i * SL + col] = p / (c + p + g.eps);
+          c += p;
+        }
+      } else if (g.share == kShareExclusive) {      // earlier queries' demand only
+        for (int i = 0; i < TS; ++i) {
+          const float p = sP[i * SL + col];
+          sSh[i * SL + col] = p / (c + g.eps);
+          c += p;
+        }
+      } else {                                      // no share step: the bids themselves
+        for (int i = 0; i < TS; ++i) sSh[i * SL + col] = sP[i * SL + col];
       }
     }
     __syncthreads();
@@ -514,19 +530,41 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
         c += sP[i * SL + col];
       }
       float r = sufk;                          // reverse: suffix of dk_share
-      for (int i = TS - 1; i >= 0; --i) {
-        const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
-        const float inv = 1.f / (cc + p + g.eps);
-        const float inv2 = inv * inv;
-        const float dk_share = -ds * p * inv2;                       // :761
-        sDS[i * SL + col] = p * (ds * (cc + g.eps) * inv2 + r);      // pdp, :765
-        sP[i * SL + col] = p * inv * sSinv[i];                       // attn, :757
-        r += dk_share;
+      if (g.share == kShareInclusive && g.bid == kBidSoftmax) {
+        for (int i = TS - 1; i >= 0; --i) {
+          const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
+          const float inv = 1.f / (cc + p + g.eps);
+          const float inv2 = inv * inv;
+          const float dk_share = -ds * p * inv2;                       // :761
+          sDS[i * SL + col] = p * (ds * (cc + g.eps) * inv2 + r);      // pdp, :765
+          sP[i * SL + col] = p * inv * sSinv[i];                       // attn, :757
+          r += dk_share;
+        }
+      } else {
+        // the other share steps and the sigmoid bid (kernels_bid.py:735-754): inv, dk_share and
+        // the direct term follow the share step, the Jacobian factor follows the bid
+        for (int i = TS - 1; i >= 0; --i) {
+          const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
+          float inv = 1.f, dk_share = 0.f, direct = ds;
+          if (g.share == kShareInclusive) {
+            inv = 1.f / (cc + p + g.eps);
+            dk_share = -ds * p * inv * inv;
+            direct = ds * (cc + g.eps) * inv * inv;
+          } else if (g.share == kShareExclusive) {
+            inv = 1.f / (cc + g.eps);
+            dk_share = -ds * p * inv * inv;
+            direct = ds * inv;
+          }
+          const float jac = g.bid == kBidSigmoid ? p * (1.f - p) : p;
+          sDS[i * SL + col] = jac * (direct + r);
+          sP[i * SL + col] = p * inv * sSinv[i];
+          r += dk_share;
+        }
       }
       sufk = r;
     }
     __syncthreads();
-    {
+    if (g.bid == kBidSoftmax) {   // ghat: the row-normalised bid's Jacobian term; none for the sigmoid
       float gs = 0.f;
 #pragma unroll
       for (int c = 0; c < 16; ++c) gs += sDS[row * SL + part * 16 + c];
@@ -623,14 +661,15 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
   }
 }
 
-// dq = dq_main - ghat * pk  (kernels.py:814-826), stored in the input dtype.
+// dq = dq_main - ghat * pk  (kernels.py:814-826), stored in the input dtype.  Without pk
+// (a bid with no row normalisation has no such term) a plain store in the input dtype.
 template <typename T>
 __global__ void dq_epilogue_kernel(const float* __restrict__ dq_main,
                                    const float* __restrict__ ghat, const float* __restrict__ pk,
                                    int64_t total, int d, T* __restrict__ dq) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
-  dq[idx] = from_f32<T>(dq_main[idx] - ghat[idx / d] * pk[idx]);
+  dq[idx] = from_f32<T>(pk != nullptr ? dq_main[idx] - ghat[idx / d] * pk[idx] : dq_main[idx]);
 }
 
 // Shared-memory sizes (bytes) of the kernels above.

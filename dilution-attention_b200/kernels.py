@@ -551,6 +551,9 @@ def install(target=None, fused_decode: bool = False):
     for name in ("dilution_attention_forward", "dilution_attention", "dilution_decode_step"):
         setattr(target, name, globals()[name])
     target.HAS_TRITON = True   # the reference gates its kernel path on this flag
+    if getattr(target, "__name__", "") == "dilution.kernels":
+        from . import kernels_bid      # the module the model binds for the bid / share ablations
+        kernels_bid.install()
     if fused_decode:
         import dilution.model as model
         cls = model.DilutionAttention
@@ -571,6 +574,9 @@ def uninstall(target=None):
                 setattr(target, name, value)
         del target._b200_saved
     import sys
+    if getattr(target, "__name__", "") == "dilution.kernels":
+        from . import kernels_bid
+        kernels_bid.uninstall()
     model = sys.modules.get("dilution.model")
     if model is not None and hasattr(model.DilutionAttention, "_unfused_step_cache"):
         model.DilutionAttention.step_cache = model.DilutionAttention._unfused_step_cache

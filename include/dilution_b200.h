@@ -45,11 +45,13 @@
 extern "C" {
 #endif
 
-#define DILUTION_ABI_VERSION 3
+#define DILUTION_ABI_VERSION 4
 #define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint of the fp32 kernels */
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
 enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */
+enum { DILUTION_BID_SOFTMAX = 0, DILUTION_BID_SIGMOID = 5 };        /* bid codes of kernels_bid.py:94 */
+enum { DILUTION_SHARE_NONE = 0, DILUTION_SHARE_INCLUSIVE = 1, DILUTION_SHARE_EXCLUSIVE = 2 }; /* kernels_bid.py:123-127 */
 enum {
   DILUTION_OK = 0,
   DILUTION_ERR_ARG = 1,        /* bad size / dtype / null pointer / alignment */
@@ -253,6 +255,46 @@ int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* 
 int dilution_decode_static(const void* q1, const void* k_cache, const void* v_cache, int dtype,
                            int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
                            float* committed, void* out, void* stream);
+
+/* ---- share / bid variants ------------------------------------------------------------
+ * The ablations a model configuration can select besides the operator itself
+ * (config.py:68-72; kernels_bid.py of the reference, generated from kernels.py with
+ * three more arguments):
+ *   bid    DILUTION_BID_SOFTMAX  p = causal softmax of the scaled scores (the operator);
+ *          DILUTION_BID_SIGMOID  p = sigmoid of the scaled score, element-wise, no row
+ *                                statistics and no Jacobian correction (kernels_bid.py:194-196);
+ *   share  INCLUSIVE  share = p / (committed + p + eps)   (the operator);
+ *          EXCLUSIVE  share = p / (committed + eps)       (earlier queries' demand only);
+ *          NONE       share = p                           (no share step: out = p v / rowsum p).
+ * The other bid functions of kernels_bid.py (relu, relu2, softplus, minshift, expshift,
+ * sigshift) are not built: DILUTION_ERR_UNSUPPORTED.  These calls run the fp32 tile kernels
+ * for every dtype and head_dim (IEEE: fp32 FMAs; otherwise tf32 tensor-core products), with
+ * a checkpoint every DILUTION_CARRY_ROWS query rows.
+ *
+ * dilution_variant_forward: all forward passes of one call (kernels_bid.py:424-489):
+ * rmax, rden (n, t) — softmax bid only, may be NULL for the sigmoid; carry
+ * (n, ceil(t/32), t); total (n, t) = column totals of p (the decode accumulator after this
+ * prefix); out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
+ * which dilution_variant_backward needs for the softmax bid.
+ * dilution_variant_backward: dq, dk, dv in the input dtype from an fp32 dout
+ * (kernels_bid.py:731-815); scratch of dilution_backward_scratch_bytes(n, t, d).
+ * dilution_variant_decode: one cached token (kernels_bid.py:853-1012); k1 / v1 (n, d) are
+ * the new token's rows to append at position length-1, or both NULL when the caller has
+ * written them; committed advances by p in place for every variant; scratch of
+ * dilution_decode_scratch_bytes(n, length, d). */
+int dilution_variant_forward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                             int64_t t, int d, float scale, float eps, int bid, int share, float* rmax,
+                             float* rden, float* carry, float* total, float* out, float* ssum, float* pk,
+                             void* stream);
+int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                              int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
+                              const float* out, const float* rmax, const float* rden, const float* carry,
+                              const float* ssum, const float* pk, void* scratch, void* dq, void* dk, void* dv,
+                              void* stream);
+int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                            int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
+                            float eps, int bid, int share, float* committed, void* out, void* scratch,
+                            void* stream);
 
 #ifdef __cplusplus
 }

@@ -72,3 +72,17 @@ def _device_status_is_clean(request):
         lib = load_package()._lib.load()
         rc = lib.dilution_device_status()
         assert rc == 0, lib.dilution_last_error().decode()
+
+
+# The bid / share ablations stored in tests/golden/variants_b1h2t80d32.npz (key prefix, bid, share_cumsum).
+VARIANTS = [("softmax_exclusive", "softmax", "exclusive"), ("softmax_none", "softmax", False),
+            ("sigmoid_inclusive", "sigmoid", True), ("sigmoid_exclusive", "sigmoid", "exclusive"),
+            ("sigmoid_none", "sigmoid", False)]
+
+
+def variant_case(key):
+    """q, k, v, dout and the reference's out, dq, dk, dv, demand of one stored variant."""
+    g = golden("variants_b1h2t80d32.npz")
+    case = {n: torch.from_numpy(g[n]) for n in ("q", "k", "v", "dout")}
+    case.update({n: torch.from_numpy(g[f"{key}_{n}"]) for n in ("out", "dq", "dk", "dv", "demand")})
+    return case

@@ -18,6 +18,11 @@ Fixture layout (all fp32 unless noted):
   layers_b2t24h2d32.npz  the model's softmax layer pieces: RopeModule outputs at two offsets
                        (bf16 and fp32 inputs) and softmax-attention rows
                        (F.scaled_dot_product_attention, is_causal) for the same q, k, v
+  variants_b1h2t80d32.npz  the bid / share ablations of src/dilution/kernels_bid.py:130-166
+                       ("softmax" / "sigmoid" bids x inclusive / "exclusive" / no share step):
+                       q, k, v, dout and per variant out, dq, dk, dv and demand (= p.sum(-2))
+
+`--only variants` writes just the last one.
 """
 
 from __future__ import annotations
@@ -55,14 +60,42 @@ def ref_fwd_bwd(ref, q, k, v, dout):
     return out.detach(), qs.grad, ks.grad, vs.grad
 
 
+VARIANTS = [("softmax", "exclusive"), ("softmax", False), ("sigmoid", True), ("sigmoid", "exclusive"),
+            ("sigmoid", False)]
+
+
+def variant_key(bid, share):
+    return f"{bid}_{ {True: 'inclusive', False: 'none'}.get(share, share) }"
+
+
+def make_variants():
+    from dilution.kernels_bid import bids_from_affinity, dilution_attention_reference as ref_bid
+    b, h, t, d = 1, 2, 80, 32
+    q, k, v, dout = make_inputs(b, h, t, d, 7070)
+    data = dict(q=q.numpy(), k=k.numpy(), v=v.numpy(), dout=dout.numpy())
+    aff = (q @ k.transpose(-2, -1)) / math.sqrt(d)
+    causal = torch.ones(t, t, dtype=torch.bool).tril()
+    for bid, share in VARIANTS:
+        out, dq, dk, dv = ref_fwd_bwd(lambda a, b_, c: ref_bid(a, b_, c, bid=bid, share_cumsum=share), q, k, v, dout)
+        p = bids_from_affinity(aff, causal, bid)
+        for name, x in dict(out=out, dq=dq, dk=dk, dv=dv, demand=p.sum(-2)).items():
+            data[f"{variant_key(bid, share)}_{name}"] = x.numpy()
+    np.savez(os.path.join(HERE, "variants_b1h2t80d32.npz"), **data)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
+    ap.add_argument("--only", choices=("all", "variants"), default="all")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from dilution.kernels import dilution_attention_reference as ref
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    make_variants()
+    if args.only == "variants":
+        print("wrote the variants fixture to", HERE)
+        return
 
     # config 1: B1 H4 T512 d64, fp32 N(0,1), seed 1338 (1337 + config index)
     q, k, v, dout = make_inputs(1, 4, 512, 64, 1338)

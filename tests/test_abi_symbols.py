@@ -35,7 +35,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_version_and_size_queries():
     lib = load_package()._lib.load()
-    assert lib.dilution_version() == 3
+    assert lib.dilution_version() == 4
     assert lib.dilution_backward_scratch_bytes(2, 100, 64) == 4 * (2 * 2 * 100 * 64 + 2 * 2 * 100) + 2 * 2 * 100 * 64
     assert lib.dilution_carry_rows(1, 2, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 64, 0) == 64
     assert lib.dilution_carry_rows(0, 0, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 128, 0) == 32
@@ -58,3 +58,11 @@ def test_argument_validation_happens_before_any_launch():
     assert rc == 1 and b"capacity" in lib.dilution_last_error()
     with pytest.raises(ValueError):
         pkg._lib.check(rc, "dilution_decode")
+    # the bid / share variants: bid codes this build does not cover, share steps that do not exist
+    args = (one, one, one, 0, 0, 1, 8, 64, 0.125, 1e-9)
+    rc = lib.dilution_variant_forward(*args, 1, 1, one, one, one, one, one, one, None, None)
+    assert rc == 2 and b"not built" in lib.dilution_last_error()
+    rc = lib.dilution_variant_forward(*args, 5, 3, None, None, one, one, one, one, None, None)
+    assert rc == 1 and b"share" in lib.dilution_last_error()
+    rc = lib.dilution_variant_forward(*args, 0, 2, None, None, one, one, one, one, None, None)
+    assert rc == 1 and b"null" in lib.dilution_last_error()      # the softmax bid needs rmax / rden
