@@ -59,16 +59,29 @@ template <int D> struct Frag<true, D> {
   }
 };
 
-// Rows [row0, row0+64) of a (rows_total, D) row-major matrix -> fp32 smem tile.
-// Rows past the end are zero.
+// Rows [row0, row0+64) of a (rows_total, D) row-major matrix -> fp32 smem tile, 16 bytes per
+// load (rows start 16-byte aligned: D is a multiple of 16 elements).  Rows past the end are zero.
 template <typename T, int D>
 __device__ __forceinline__ void load_tile(float* s, const T* __restrict__ g, int row0,
                                           int rows_total) {
   constexpr int LD = ld<D>();
-  for (int idx = threadIdx.x; idx < TS * D; idx += NT) {
-    const int r = idx / D, c = idx % D;
+  constexpr int E = 16 / (int)sizeof(T);     // elements per load: 4 fp32 or 8 bf16
+  constexpr int PER_ROW = D / E;
+  for (int idx = threadIdx.x; idx < TS * PER_ROW; idx += NT) {
+    const int r = idx / PER_ROW, c = (idx % PER_ROW) * E;
     const int gr = row0 + r;
-    s[r * LD + c] = (gr < rows_total) ? to_f32(g[(int64_t)gr * D + c]) : 0.f;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (gr < rows_total) raw = *reinterpret_cast<const uint4*>(g + (int64_t)gr * D + c);
+    float* dst = s + r * LD + c;
+    if (sizeof(T) == 4) {
+      *reinterpret_cast<uint4*>(dst) = raw;
+    } else {
+      // bf16 -> fp32 is a 16-bit shift
+      *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
+                                                        __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
+    }
   }
 }
 
@@ -355,11 +368,11 @@ __global__ void __launch_bounds__(NT) main_kernel(
   float* sQ = smem;
   float* sK = sQ + TS * LD;
   float* sV = sK + TS * LD;
-  float* sP = sV + TS * LD;
-  float* sSh = sP + TS * SL;
-  float* sM = sSh + TS * SL;
+  float* sP = sV + TS * LD;   // scores, then bids, then shares, in place
+  float* sM = sP + TS * SL;
   float* sRinv = sM + TS;
   float* sRow = sRinv + TS;
+  float* sSeg = sRow + TS;   // [4][64] segment sums of the bids
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
@@ -385,33 +398,51 @@ __global__ void __launch_bounds__(NT) main_kernel(
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sP);
     __syncthreads();
-    scores_to_bids(sP, sM, sRinv, g, ib, jb);
-    __syncthreads();
-    if (threadIdx.x < TS) {
-      const int col = threadIdx.x, ja = jb * TS + col;
+    {
+      // thread = (key column, 16-query segment): bids in place and their segment sums, then the
+      // demand in front of the segment (checkpoint + earlier segments) and the shares
+      const int col = threadIdx.x & 63, seg = threadIdx.x >> 6;
+      const int ja = jb * TS + col;
+      float seg_sum = 0.f;
+#pragma unroll 4
+      for (int rr = 0; rr < 16; ++rr) {
+        const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
+        const float p =
+            (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+        sP[i * SL + col] = p;
+        seg_sum += p;
+      }
+      sSeg[seg * TS + col] = seg_sum;
+      __syncthreads();
+      if (PK) {                 // pk = p K while the tile still holds the bids
+        accum_tile<D, false, MMA>(sP, sK, acc_pk);
+        __syncthreads();
+      }
       float c = (ja < g.tk) ? carry_row[ja] : 0.f;
       if (carry_base != nullptr && ja < g.tk) c += carry_base[n * g.tk + ja];
+      for (int s2 = 0; s2 < seg; ++s2) c += sSeg[s2 * TS + col];
       if (g.share == kShareInclusive) {
-        for (int i = 0; i < TS; ++i) {
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+          const int i = seg * 16 + rr;
           const float p = sP[i * SL + col];
-          sSh[i * SL + col] = p / (c + p + g.eps);
+          sP[i * SL + col] = p / (c + p + g.eps);
           c += p;
         }
       } else if (g.share == kShareExclusive) {      // earlier queries' demand only
-        for (int i = 0; i < TS; ++i) {
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+          const int i = seg * 16 + rr;
           const float p = sP[i * SL + col];
-          sSh[i * SL + col] = p / (c + g.eps);
+          sP[i * SL + col] = p / (c + g.eps);
           c += p;
         }
-      } else {                                      // no share step: the bids themselves
-        for (int i = 0; i < TS; ++i) sSh[i * SL + col] = sP[i * SL + col];
-      }
+      }                                             // no share step: the bids themselves
     }
     __syncthreads();
 #pragma unroll
-    for (int c = 0; c < 16; ++c) my_ssum += sSh[row * SL + part * 16 + c];
-    accum_tile<D, false, MMA>(sSh, sV, acc_o);
-    if (PK) accum_tile<D, false, MMA>(sP, sK, acc_pk);
+    for (int c = 0; c < 16; ++c) my_ssum += sP[row * SL + part * 16 + c];
+    accum_tile<D, false, MMA>(sP, sV, acc_o);
   }
   my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 1);
   my_ssum += __shfl_xor_sync(0xffffffffu, my_ssum, 2);
@@ -478,11 +509,11 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   float* sDO = sQ + TS * LD;
   float* sP = sDO + TS * LD;
   float* sDS = sP + TS * SL;
-  float* sC = sDS + TS * SL;
-  float* sM = sC + TS * SL;
+  float* sM = sDS + TS * SL;
   float* sRinv = sM + TS;
   float* sDbar = sRinv + TS;
   float* sSinv = sDbar + TS;
+  float* sSeg = sSinv + TS;   // [8][64] segment sums: bids, then dk_share
   const int nqb = (g.tq + TS - 1) / TS;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
@@ -514,54 +545,70 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
     score_tile<D, MMA>(sQ, sK, sP);
     score_tile<D, MMA>(sDO, sV, sDS);
     __syncthreads();
-    scores_to_bids(sP, sM, sRinv, g, ib, jb);
-    for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
-      const int i = idx >> 6, j = idx & 63;
-      const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
-      const float ds = (sDS[i * SL + j] - sDbar[i]) * sSinv[i];   // kernels.py:463-464
-      sDS[i * SL + j] = (ja <= ia && ja < g.tk) ? ds : 0.f;
-    }
-    __syncthreads();
-    if (threadIdx.x < TS) {
-      const int col = threadIdx.x, ja = jb * TS + col;
-      float c = (ja < g.tk) ? carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] : 0.f;
-      for (int i = 0; i < TS; ++i) {          // forward: exclusive demand
-        sC[i * SL + col] = c;
-        c += sP[i * SL + col];
+    {
+      // thread = (key column, 16-query segment), three phases separated by barriers:
+      //  1. bids and ds in place, segment sums of the bids;
+      //  2. the demand in front of every query (checkpoint + earlier segments + running sum) and
+      //     the segment sums of dk_share;
+      //  3. the same walk again with the suffix of dk_share over later queries (as
+      //     kernels_bid.py:749: total minus prefix), the element-wise terms of kernels.py:757-765 /
+      //     kernels_bid.py:735-754 by share step and bid, pdp and attn in place.
+      const int col = threadIdx.x & 63, seg = threadIdx.x >> 6;
+      const int ja = jb * TS + col;
+      float seg_sum = 0.f;
+#pragma unroll 4
+      for (int rr = 0; rr < 16; ++rr) {
+        const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
+        const bool ok = ja <= ia && ja < g.tk && il < g.tq;
+        const float p = ok ? bid_value(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+        sP[i * SL + col] = p;
+        seg_sum += p;
+        sDS[i * SL + col] = ok ? (sDS[i * SL + col] - sDbar[i]) * sSinv[i] : 0.f;   // kernels.py:463-464
       }
-      float r = sufk;                          // reverse: suffix of dk_share
-      if (g.share == kShareInclusive && g.bid == kBidSoftmax) {
-        for (int i = TS - 1; i >= 0; --i) {
-          const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
-          const float inv = 1.f / (cc + p + g.eps);
+      sSeg[seg * TS + col] = seg_sum;
+      __syncthreads();
+      float c0 = (ja < g.tk) ? carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] : 0.f;
+      for (int s2 = 0; s2 < seg; ++s2) c0 += sSeg[s2 * TS + col];
+      // first walk: the segment's sum of dk_share
+      float c = c0, dk_sum = 0.f;
+      if (g.share != kShareNone) {
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+          const int i = seg * 16 + rr;
+          const float p = sP[i * SL + col], ds = sDS[i * SL + col];
+          const float inv = 1.f / (g.share == kShareInclusive ? c + p + g.eps : c + g.eps);
+          dk_sum -= ds * p * inv * inv;                    // :761
+          c += p;
+        }
+      }
+      sSeg[(4 + seg) * TS + col] = dk_sum;
+      __syncthreads();
+      // second walk, same order (the demand of every query is rebuilt bit for bit): the suffix of
+      // dk_share over later queries = later tiles + later segments + this segment - prefix
+      float r = sufk + dk_sum;
+      for (int s2 = 3; s2 > seg; --s2) r += sSeg[(4 + s2) * TS + col];
+      c = c0;
+#pragma unroll 4
+      for (int rr = 0; rr < 16; ++rr) {
+        const int i = seg * 16 + rr;
+        const float p = sP[i * SL + col], ds = sDS[i * SL + col];
+        float inv = 1.f, direct = ds;
+        if (g.share == kShareInclusive) {
+          inv = 1.f / (c + p + g.eps);
           const float inv2 = inv * inv;
-          const float dk_share = -ds * p * inv2;                       // :761
-          sDS[i * SL + col] = p * (ds * (cc + g.eps) * inv2 + r);      // pdp, :765
-          sP[i * SL + col] = p * inv * sSinv[i];                       // attn, :757
-          r += dk_share;
+          r += ds * p * inv2;                              // minus this query's dk_share
+          direct = ds * (c + g.eps) * inv2;                // :765
+        } else if (g.share == kShareExclusive) {
+          inv = 1.f / (c + g.eps);
+          r += ds * p * inv * inv;
+          direct = ds * inv;
         }
-      } else {
-        // the other share steps and the sigmoid bid (kernels_bid.py:735-754): inv, dk_share and
-        // the direct term follow the share step, the Jacobian factor follows the bid
-        for (int i = TS - 1; i >= 0; --i) {
-          const float p = sP[i * SL + col], cc = sC[i * SL + col], ds = sDS[i * SL + col];
-          float inv = 1.f, dk_share = 0.f, direct = ds;
-          if (g.share == kShareInclusive) {
-            inv = 1.f / (cc + p + g.eps);
-            dk_share = -ds * p * inv * inv;
-            direct = ds * (cc + g.eps) * inv * inv;
-          } else if (g.share == kShareExclusive) {
-            inv = 1.f / (cc + g.eps);
-            dk_share = -ds * p * inv * inv;
-            direct = ds * inv;
-          }
-          const float jac = g.bid == kBidSigmoid ? p * (1.f - p) : p;
-          sDS[i * SL + col] = jac * (direct + r);
-          sP[i * SL + col] = p * inv * sSinv[i];
-          r += dk_share;
-        }
+        const float jac = g.bid == kBidSigmoid ? p * (1.f - p) : p;
+        sDS[i * SL + col] = jac * (direct + r);            // pdp
+        sP[i * SL + col] = p * inv * sSinv[i];             // attn, :757
+        c += p;
       }
-      sufk = r;
+      sufk += (sSeg[4 * TS + col] + sSeg[5 * TS + col]) + (sSeg[6 * TS + col] + sSeg[7 * TS + col]);
     }
     __syncthreads();
     if (g.bid == kBidSoftmax) {   // ghat: the row-normalised bid's Jacobian term; none for the sigmoid
@@ -675,8 +722,8 @@ __global__ void dq_epilogue_kernel(const float* __restrict__ dq_main,
 // Shared-memory sizes (bytes) of the kernels above.
 template <int D> constexpr size_t smem_rowstats() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL); }
 template <int D> constexpr size_t smem_colsum() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 2 * TS + 4 * TS); }
-template <int D> constexpr size_t smem_main() { return sizeof(float) * (3 * TS * ld<D>() + 2 * TS * SL + 3 * TS); }
-template <int D> constexpr size_t smem_bwd_main() { return sizeof(float) * (4 * TS * ld<D>() + 3 * TS * SL + 4 * TS); }
+template <int D> constexpr size_t smem_main() { return sizeof(float) * (3 * TS * ld<D>() + TS * SL + 7 * TS); }
+template <int D> constexpr size_t smem_bwd_main() { return sizeof(float) * (4 * TS * ld<D>() + 2 * TS * SL + 12 * TS); }
 template <int D> constexpr size_t smem_bwd_dk() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 3 * TS); }
 
 }  // namespace simt
