@@ -44,6 +44,17 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// Element-wise arithmetic follows the product flavour: exact division and exp2f next to the fp32
+// FMAs, the special-function unit's approximations (about 2^-22 relative) next to tf32 products.
+// An MMA operand is rounded to tf32 once, where it is written to shared memory, so that fragment
+// loads are plain loads.
+template <bool MMA> __device__ __forceinline__ float op_round(float x) {
+  return MMA ? __uint_as_float(to_tf32(x)) : x;
+}
+template <bool MMA> __device__ __forceinline__ float recip(float x) { return MMA ? fast_rcp(x) : 1.f / x; }
+template <bool MMA> __device__ __forceinline__ float ratio(float a, float b) { return MMA ? a * fast_rcp(b) : a / b; }
+template <bool MMA> __device__ __forceinline__ float pow2(float x) { return MMA ? fast_exp2(x) : exp2f(x); }
+
 // Which element of a [64 x D] result a thread's accumulator acc[r][c] holds.
 template <bool MMA, int D> struct Frag {
   static __device__ __forceinline__ int row(int r, int /*c*/) { return (threadIdx.x >> 4) + 16 * r; }
@@ -61,7 +72,8 @@ template <int D> struct Frag<true, D> {
 
 // Rows [row0, row0+64) of a (rows_total, D) row-major matrix -> fp32 smem tile, 16 bytes per
 // load (rows start 16-byte aligned: D is a multiple of 16 elements).  Rows past the end are zero.
-template <typename T, int D>
+// ROUND: fp32 values are rounded to tf32 on the way (bf16 values are tf32 values already).
+template <typename T, int D, bool ROUND = false>
 __device__ __forceinline__ void load_tile(float* s, const T* __restrict__ g, int row0,
                                           int rows_total) {
   constexpr int LD = ld<D>();
@@ -74,6 +86,12 @@ __device__ __forceinline__ void load_tile(float* s, const T* __restrict__ g, int
     if (gr < rows_total) raw = *reinterpret_cast<const uint4*>(g + (int64_t)gr * D + c);
     float* dst = s + r * LD + c;
     if (sizeof(T) == 4) {
+      if (ROUND) {
+        raw.x = to_tf32(__uint_as_float(raw.x));
+        raw.y = to_tf32(__uint_as_float(raw.y));
+        raw.z = to_tf32(__uint_as_float(raw.z));
+        raw.w = to_tf32(__uint_as_float(raw.w));
+      }
       *reinterpret_cast<uint4*>(dst) = raw;
     } else {
       // bf16 -> fp32 is a 16-bit shift
@@ -99,12 +117,14 @@ __device__ __forceinline__ void score_tile(const float* A, const float* B, float
       for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
 #pragma unroll 2
     for (int k0 = 0; k0 < D; k0 += 8) {
-      const uint32_t a[4] = {to_tf32(A[(r0 + g) * LD + k0 + t]), to_tf32(A[(r0 + g + 8) * LD + k0 + t]),
-                             to_tf32(A[(r0 + g) * LD + k0 + t + 4]), to_tf32(A[(r0 + g + 8) * LD + k0 + t + 4])};
+      // both tiles hold tf32 values (load_tile)
+      const uint32_t a[4] = {__float_as_uint(A[(r0 + g) * LD + k0 + t]), __float_as_uint(A[(r0 + g + 8) * LD + k0 + t]),
+                             __float_as_uint(A[(r0 + g) * LD + k0 + t + 4]),
+                             __float_as_uint(A[(r0 + g + 8) * LD + k0 + t + 4])};
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const float* brow = B + (c0 + 8 * nt + g) * LD + k0 + t;
-        const uint32_t b[2] = {to_tf32(brow[0]), to_tf32(brow[4])};
+        const uint32_t b[2] = {__float_as_uint(brow[0]), __float_as_uint(brow[4])};
         mma_tf32(acc[nt], a, b);
       }
     }
@@ -148,8 +168,9 @@ __device__ __forceinline__ void score_tile(const float* A, const float* B, float
 }
 
 // acc[r][c] += sum_j A(i,j) * B[j][col],  (i, col) = Frag<MMA, D>::row / col (r, c).
-// A is a [64][SL] score tile, read transposed when TRANS_A (A(i,j) = A[j][i]).
-template <int D, bool TRANS_A, bool MMA>
+// A is a [64][SL] score tile, read transposed when TRANS_A (A(i,j) = A[j][i]).  With tf32 products B
+// holds tf32 values (load_tile) and so does A unless CVT_A asks for the rounding here.
+template <int D, bool TRANS_A, bool MMA, bool CVT_A = false>
 __device__ __forceinline__ void accum_tile(const float* A, const float* B, float (&acc)[4][D / 16]) {
   constexpr int LD = ld<D>();
   constexpr int DC = D / 16;
@@ -163,22 +184,25 @@ __device__ __forceinline__ void accum_tile(const float* A, const float* B, float
       for (int i = 0; i < 4; ++i) c4[nt][i] = acc[i][nt];
 #pragma unroll 2
     for (int k0 = 0; k0 < TS; k0 += 8) {
-      uint32_t a[4];
+      float af[4];
       if (TRANS_A) {
-        a[0] = to_tf32(A[(k0 + t) * SL + r0 + g]);
-        a[1] = to_tf32(A[(k0 + t) * SL + r0 + g + 8]);
-        a[2] = to_tf32(A[(k0 + t + 4) * SL + r0 + g]);
-        a[3] = to_tf32(A[(k0 + t + 4) * SL + r0 + g + 8]);
+        af[0] = A[(k0 + t) * SL + r0 + g];
+        af[1] = A[(k0 + t) * SL + r0 + g + 8];
+        af[2] = A[(k0 + t + 4) * SL + r0 + g];
+        af[3] = A[(k0 + t + 4) * SL + r0 + g + 8];
       } else {
-        a[0] = to_tf32(A[(r0 + g) * SL + k0 + t]);
-        a[1] = to_tf32(A[(r0 + g + 8) * SL + k0 + t]);
-        a[2] = to_tf32(A[(r0 + g) * SL + k0 + t + 4]);
-        a[3] = to_tf32(A[(r0 + g + 8) * SL + k0 + t + 4]);
+        af[0] = A[(r0 + g) * SL + k0 + t];
+        af[1] = A[(r0 + g + 8) * SL + k0 + t];
+        af[2] = A[(r0 + g) * SL + k0 + t + 4];
+        af[3] = A[(r0 + g + 8) * SL + k0 + t + 4];
       }
+      uint32_t a[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = CVT_A ? to_tf32(af[i]) : __float_as_uint(af[i]);
 #pragma unroll
       for (int nt = 0; nt < DC; ++nt) {
         const float* bcol = B + (k0 + t) * LD + c0 + 8 * nt + g;
-        const uint32_t b[2] = {to_tf32(bcol[0]), to_tf32(bcol[4 * LD])};
+        const uint32_t b[2] = {__float_as_uint(bcol[0]), __float_as_uint(bcol[4 * LD])};
         mma_tf32(c4[nt], a, b);
       }
     }
@@ -218,19 +242,10 @@ __device__ __forceinline__ void load_stats(float* sM, float* sRinv, const float*
 
 // The bid of one raw score (kernels_bid.py:191-197): softmax from the row statistics, or the
 // element-wise sigmoid of the scaled score.
+template <bool MMA>
 __device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv) {
   const float z = score * g.zscale;
-  return g.bid == kBidSigmoid ? 1.f / (1.f + exp2f(-z)) : exp2f(z - m) * rinv;
-}
-
-// Raw scores in S -> bids p in place (zero outside the causal/bounds mask).
-__device__ __forceinline__ void scores_to_bids(float* S, const float* sM, const float* sRinv,
-                                               const Geom& g, int ib, int jb) {
-  for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
-    const int i = idx >> 6, j = idx & 63;
-    const int ja = jb * TS + j, il = ib * TS + i, ia = g.q_off + il;
-    S[i * SL + j] = (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(S[i * SL + j], g, sM[i], sRinv[i]) : 0.f;
-  }
+  return g.bid == kBidSigmoid ? recip<MMA>(1.f + pow2<MMA>(-z)) : pow2<MMA>(z - m) * rinv;
 }
 
 __device__ __forceinline__ int first_query_block(int jb, int q_off) {
@@ -253,7 +268,7 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
-  load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+  load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
 
   const int r = threadIdx.x >> 2, part = threadIdx.x & 3;
   const int ia = g.q_off + ib * TS + r;
@@ -262,7 +277,7 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
   const int njb = last_key / TS + 1;
   for (int jb = 0; jb < njb; ++jb) {
     __syncthreads();
-    load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+    load_tile<T, D, MMA>(sK, k + n * g.tk * D, jb * TS, g.tk);
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
@@ -282,12 +297,12 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
     float ps = 0.f;
     if (nm > -INFINITY) {
 #pragma unroll
-      for (int c = 0; c < 16; ++c) ps += exp2f(z[c] - nm);
+      for (int c = 0; c < 16; ++c) ps += pow2<MMA>(z[c] - nm);
     }
     ps += __shfl_xor_sync(0xffffffffu, ps, 1);
     ps += __shfl_xor_sync(0xffffffffu, ps, 2);
     if (nm > -INFINITY) {
-      s = s * exp2f(m - nm) + ps;
+      s = s * pow2<MMA>(m - nm) + ps;
       m = nm;
     }
   }
@@ -319,7 +334,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
-  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+  load_tile<T, D, MMA>(sK, k + n * g.tk * D, jb * TS, g.tk);
 
   const int col = threadIdx.x & 63, seg = threadIdx.x >> 6;
   const int ja = jb * TS + col;
@@ -327,7 +342,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   float local = 0.f;
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
-    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
     load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sS);
@@ -337,7 +352,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
     for (int rr = 0; rr < 16; ++rr) {
       const int i = seg * 16 + rr;
       const int il = ib * TS + i, ia = g.q_off + il;
-      part += (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(sS[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+      part += (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sS[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
     }
     sPart[seg * TS + col] = part;
     __syncthreads();
@@ -376,7 +391,7 @@ __global__ void __launch_bounds__(NT) main_kernel(
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
-  load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+  load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
   load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
 
   float acc_o[4][DC], acc_pk[4][DC];
@@ -393,8 +408,8 @@ __global__ void __launch_bounds__(NT) main_kernel(
   const float* carry_row = carry + (n * ncb + 2 * ib) * (int64_t)g.tk;
   for (int jb = 0; jb < njb; ++jb) {
     __syncthreads();
-    load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
-    load_tile<T, D>(sV, v + n * g.tk * D, jb * TS, g.tk);
+    load_tile<T, D, MMA>(sK, k + n * g.tk * D, jb * TS, g.tk);
+    load_tile<T, D, MMA>(sV, v + n * g.tk * D, jb * TS, g.tk);
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sP);
     __syncthreads();
@@ -408,14 +423,14 @@ __global__ void __launch_bounds__(NT) main_kernel(
       for (int rr = 0; rr < 16; ++rr) {
         const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
         const float p =
-            (ja <= ia && ja < g.tk && il < g.tq) ? bid_value(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+            (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
         sP[i * SL + col] = p;
         seg_sum += p;
       }
       sSeg[seg * TS + col] = seg_sum;
       __syncthreads();
       if (PK) {                 // pk = p K while the tile still holds the bids
-        accum_tile<D, false, MMA>(sP, sK, acc_pk);
+        accum_tile<D, false, MMA, true>(sP, sK, acc_pk);
         __syncthreads();
       }
       float c = (ja < g.tk) ? carry_row[ja] : 0.f;
@@ -426,7 +441,7 @@ __global__ void __launch_bounds__(NT) main_kernel(
         for (int rr = 0; rr < 16; ++rr) {
           const int i = seg * 16 + rr;
           const float p = sP[i * SL + col];
-          sP[i * SL + col] = p / (c + p + g.eps);
+          sP[i * SL + col] = op_round<MMA>(ratio<MMA>(p, c + p + g.eps));
           c += p;
         }
       } else if (g.share == kShareExclusive) {      // earlier queries' demand only
@@ -434,10 +449,14 @@ __global__ void __launch_bounds__(NT) main_kernel(
         for (int rr = 0; rr < 16; ++rr) {
           const int i = seg * 16 + rr;
           const float p = sP[i * SL + col];
-          sP[i * SL + col] = p / (c + g.eps);
+          sP[i * SL + col] = op_round<MMA>(ratio<MMA>(p, c + g.eps));
           c += p;
         }
-      }                                             // no share step: the bids themselves
+      } else if (MMA) {                             // no share step: the bids themselves
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr)
+          sP[(seg * 16 + rr) * SL + col] = op_round<MMA>(sP[(seg * 16 + rr) * SL + col]);
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -518,8 +537,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
-  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
-  load_tile<T, D>(sV, v + n * g.tk * D, jb * TS, g.tk);
+  load_tile<T, D, MMA>(sK, k + n * g.tk * D, jb * TS, g.tk);
+  load_tile<T, D, MMA>(sV, v + n * g.tk * D, jb * TS, g.tk);
 
   float acc_dk[4][DC], acc_dv[4][DC];
 #pragma unroll
@@ -532,8 +551,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
 
   for (int ib = nqb - 1; ib >= first_query_block(jb, g.q_off); --ib) {
     __syncthreads();
-    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-    load_tile<float, D>(sDO, dout + n * g.tq * D, ib * TS, g.tq);
+    load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_tile<float, D, MMA>(sDO, dout + n * g.tq * D, ib * TS, g.tq);
     load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
@@ -560,7 +579,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       for (int rr = 0; rr < 16; ++rr) {
         const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
         const bool ok = ja <= ia && ja < g.tk && il < g.tq;
-        const float p = ok ? bid_value(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+        const float p = ok ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
         sP[i * SL + col] = p;
         seg_sum += p;
         sDS[i * SL + col] = ok ? (sDS[i * SL + col] - sDbar[i]) * sSinv[i] : 0.f;   // kernels.py:463-464
@@ -576,7 +595,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
         for (int rr = 0; rr < 16; ++rr) {
           const int i = seg * 16 + rr;
           const float p = sP[i * SL + col], ds = sDS[i * SL + col];
-          const float inv = 1.f / (g.share == kShareInclusive ? c + p + g.eps : c + g.eps);
+          const float inv = recip<MMA>(g.share == kShareInclusive ? c + p + g.eps : c + g.eps);
           dk_sum -= ds * p * inv * inv;                    // :761
           c += p;
         }
@@ -594,18 +613,18 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
         const float p = sP[i * SL + col], ds = sDS[i * SL + col];
         float inv = 1.f, direct = ds;
         if (g.share == kShareInclusive) {
-          inv = 1.f / (c + p + g.eps);
+          inv = recip<MMA>(c + p + g.eps);
           const float inv2 = inv * inv;
           r += ds * p * inv2;                              // minus this query's dk_share
           direct = ds * (c + g.eps) * inv2;                // :765
         } else if (g.share == kShareExclusive) {
-          inv = 1.f / (c + g.eps);
+          inv = recip<MMA>(c + g.eps);
           r += ds * p * inv * inv;
           direct = ds * inv;
         }
         const float jac = g.bid == kBidSigmoid ? p * (1.f - p) : p;
-        sDS[i * SL + col] = jac * (direct + r);            // pdp
-        sP[i * SL + col] = p * inv * sSinv[i];             // attn, :757
+        sDS[i * SL + col] = op_round<MMA>(jac * (direct + r));            // pdp
+        sP[i * SL + col] = op_round<MMA>(p * inv * sSinv[i]);             // attn, :757
         c += p;
       }
       sufk += (sSeg[4 * TS + col] + sSeg[5 * TS + col]) + (sSeg[6 * TS + col] + sSeg[7 * TS + col]);
@@ -669,7 +688,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
-  load_tile<T, D>(sK, k + n * g.tk * D, jb * TS, g.tk);
+  load_tile<T, D, MMA>(sK, k + n * g.tk * D, jb * TS, g.tk);
   float acc[4][DC];
 #pragma unroll
   for (int r = 0; r < 4; ++r)
@@ -677,7 +696,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     for (int c = 0; c < DC; ++c) acc[r][c] = 0.f;
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
-    load_tile<T, D>(sQ, q + n * g.tq * D, ib * TS, g.tq);
+    load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
     load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
@@ -690,7 +709,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
       const int i = idx >> 6, j = idx & 63;
       const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
       const float z = sP[i * SL + j] * g.zscale;
-      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? exp2f(z - sM[i]) * sRinv[i] * sG[i] : 0.f;
+      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? op_round<MMA>(pow2<MMA>(z - sM[i]) * sRinv[i] * sG[i]) : 0.f;
     }
     __syncthreads();
     accum_tile<D, true, MMA>(sP, sQ, acc);
