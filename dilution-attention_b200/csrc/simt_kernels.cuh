@@ -184,25 +184,31 @@ __device__ __forceinline__ void accum_tile(const float* A, const float* B, float
       for (int i = 0; i < 4; ++i) c4[nt][i] = acc[i][nt];
 #pragma unroll 2
     for (int k0 = 0; k0 < TS; k0 += 8) {
+      // The eight k of a step are taken in the order 0,2,4,6,1,3,5,7 (fragment index t holds
+      // rows k0+2t and k0+2t+1) in A and B alike, which leaves the sum unchanged and makes the
+      // loads below fall on distinct banks: row strides are 4 mod 32 words, so 2t rows apart is
+      // 8t banks apart and the eight columns g fill the gap.
       float af[4];
       if (TRANS_A) {
-        af[0] = A[(k0 + t) * SL + r0 + g];
-        af[1] = A[(k0 + t) * SL + r0 + g + 8];
-        af[2] = A[(k0 + t + 4) * SL + r0 + g];
-        af[3] = A[(k0 + t + 4) * SL + r0 + g + 8];
+        af[0] = A[(k0 + 2 * t) * SL + r0 + g];
+        af[1] = A[(k0 + 2 * t) * SL + r0 + g + 8];
+        af[2] = A[(k0 + 2 * t + 1) * SL + r0 + g];
+        af[3] = A[(k0 + 2 * t + 1) * SL + r0 + g + 8];
       } else {
-        af[0] = A[(r0 + g) * SL + k0 + t];
-        af[1] = A[(r0 + g + 8) * SL + k0 + t];
-        af[2] = A[(r0 + g) * SL + k0 + t + 4];
-        af[3] = A[(r0 + g + 8) * SL + k0 + t + 4];
+        const float2 lo = *reinterpret_cast<const float2*>(&A[(r0 + g) * SL + k0 + 2 * t]);
+        const float2 hi = *reinterpret_cast<const float2*>(&A[(r0 + g + 8) * SL + k0 + 2 * t]);
+        af[0] = lo.x;
+        af[1] = hi.x;
+        af[2] = lo.y;
+        af[3] = hi.y;
       }
       uint32_t a[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) a[i] = CVT_A ? to_tf32(af[i]) : __float_as_uint(af[i]);
 #pragma unroll
       for (int nt = 0; nt < DC; ++nt) {
-        const float* bcol = B + (k0 + t) * LD + c0 + 8 * nt + g;
-        const uint32_t b[2] = {__float_as_uint(bcol[0]), __float_as_uint(bcol[4 * LD])};
+        const float* bcol = B + (k0 + 2 * t) * LD + c0 + 8 * nt + g;
+        const uint32_t b[2] = {__float_as_uint(bcol[0]), __float_as_uint(bcol[LD])};
         mma_tf32(c4[nt], a, b);
       }
     }
