@@ -23,8 +23,9 @@ Also on the line:
                  heads, 256 steps, heads sharded over ranks) against the measured HBM
                  copy bandwidth;
   other_shapes   (1 GPU) forward + backward at the smaller shapes the reference publishes, and at
-                 an fp32 and a head_dim-128 shape, which run on the exact-fp32 tile kernels;
-  config1_fp32   (1 GPU) BASELINE config 1 on the exact-fp32 kernels, with the reference's
+                 an fp32 ("tf32") and a head_dim-128 shape, which run on the fp32 tile kernels with tf32
+                 tensor-core products;
+  config1_fp32   (1 GPU) BASELINE config 1 on the tile kernels with fp32 FMA products, with the reference's
                  CPU operator at the same shape;
   lm             (1 GPU, when a copy of the reference package is installed under
                  baseline/_ref) the reference's unmodified DilutionLM on these kernels:
@@ -299,7 +300,7 @@ def run_triton(args):
         dms = a.elapsed_time(b) / steps
         other = time_other_shapes(rk.dilution_attention, dev)
         try:
-            other_ffma = time_shapes(rk.dilution_attention, dev, FFMA_SHAPES, iters=5)
+            other_ffma = time_shapes(rk.dilution_attention, dev, TILE_SHAPES, iters=5)
         except Exception as e:  # noqa: BLE001
             other_ffma = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
         import triton
@@ -321,9 +322,10 @@ def run_triton(args):
 OTHER_SHAPES = ((32, 12, 1024), (8, 8, 4096), (2, 12, 16384))
 
 
-# Shapes that run on the exact-fp32 tile kernels here (fp32 tensors under "tf32", as the model's
-# non-autocast path passes them, and head_dim 128): (batch, heads, seq, head_dim, dtype, precision).
-FFMA_SHAPES = ((8, 8, 4096, 64, torch.float32, "tf32"), (4, 8, 4096, 128, torch.bfloat16, "bf16"))
+# Shapes that run on the fp32 tile kernels here, with tf32 tensor-core products (fp32 tensors under
+# "tf32", as the model's non-autocast path passes them, and head_dim 128):
+# (batch, heads, seq, head_dim, dtype, precision).
+TILE_SHAPES = ((8, 8, 4096, 64, torch.float32, "tf32"), (4, 8, 4096, 128, torch.bfloat16, "bf16"))
 
 
 def time_shapes(op, dev, shapes, iters=10):
@@ -505,7 +507,7 @@ def run_ours(args):
     other = fp32_c1 = None
     if c.world == 1 and not args.no_other:
         other = time_other_shapes(K.dilution_attention, c.dev)
-        other["exact_fp32_kernels"] = time_shapes(K.dilution_attention, c.dev, FFMA_SHAPES, iters=5)
+        other["tile_kernels"] = time_shapes(K.dilution_attention, c.dev, TILE_SHAPES, iters=5)
         fp32_c1 = run_config1(c)
     sharded = None if args.no_sharded else run_train_sharded(c, args, devt)
     e2e = None if args.no_e2e else run_e2e(c, args, host, total_flops)
@@ -538,7 +540,7 @@ def run_ours(args):
 
 def run_config1(c, iters=10):
     """BASELINE config 1 (B1 H4 T512 d64 fp32, forward + autograd backward of
-    dilution_attention_reference): this library's exact-fp32 kernels on the GPU, and the reference's
+    dilution_attention_reference): this library's fp32 tile kernels (FMA products) on the GPU, and the reference's
     CPU operator at the same shape on the host cores."""
     g = torch.Generator().manual_seed(1338)
     hq, hk, hv, hd = (torch.randn(1, 4, 512, 64, generator=g) for _ in range(4))
@@ -561,7 +563,7 @@ def run_config1(c, iters=10):
         torch.cuda.synchronize()
         times.append(a.elapsed_time(e))
     res = {"workload": "B1_H4_T512_d64 fp32 forward + backward", "gpu_ms": statistics.median(times),
-           "gpu_path": "exact-fp32 FFMA kernels (dot_precision ieee)"}
+           "gpu_path": "fp32 tile kernels, FMA products (dot_precision ieee)"}
     if reference_package() is not None:
         from dilution.kernels import dilution_attention_reference as ref
         cpu = []
