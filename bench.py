@@ -303,9 +303,14 @@ def run_triton(args):
             other_ffma = time_shapes(rk.dilution_attention, dev, TILE_SHAPES, iters=5)
         except Exception as e:  # noqa: BLE001
             other_ffma = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+        try:
+            import dilution.kernels_bid as rkb
+            variants = time_variants(rkb.dilution_attention, dev)
+        except Exception as e:  # noqa: BLE001
+            variants = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
         import triton
         print(json.dumps({
-            "impl": "triton", "other_shapes": other, "fp32_and_d128_shapes": other_ffma, "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
+            "impl": "triton", "other_shapes": other, "fp32_and_d128_shapes": other_ffma, "variants": variants, "metric": METRIC, "value": causal_flops(B * H, T, D, 7) / (ms * 1e-3) / 1e12,
             "unit": "TFLOP/s", "ms_per_step": ms, "steps": len(times), "n_gpus": 1, "dtype": "bf16",
             "config": {"workload": f"train_fwd_bwd_B{B}_H{H}_T{T}_d{D}",
                        "path": "dilution.kernels.dilution_attention of the reference, Triton "
@@ -357,6 +362,26 @@ def time_shapes(op, dev, shapes, iters=10):
         out[name] = {"ms": ms, "tflops": causal_flops(b * h, t, d, 7) / (ms * 1e-3) / 1e12}
         del q, k, v, dout
     torch.cuda.empty_cache()
+    return out
+
+
+# The bid / share ablations at the shape the reference's ablation configurations train at
+# (configs/bid_8192: context 8192, 8 heads of 64, bf16): (bid, share_cumsum).
+VARIANTS = (("sigmoid", True), ("softmax", "exclusive"), ("softmax", False), ("sigmoid", False))
+VARIANT_SHAPE = (4, 8, 8192, 64, torch.bfloat16, "bf16")
+
+
+def time_variants(op_bid, dev, iters=5):
+    """Forward + backward of the kernels_bid entry point `op_bid` under each variant."""
+    out = {}
+    for bid, share in VARIANTS:
+        def op(q, k, v, dot_precision):
+            return op_bid(q, k, v, dot_precision=dot_precision, bid=bid, share_cumsum=share)
+        r = time_shapes(op, dev, [VARIANT_SHAPE], iters)
+        key = f"{bid}_{ {True: 'inclusive', False: 'none'}.get(share, share) }"
+        out[key] = next(iter(r.values()))
+    b, h, t, d = VARIANT_SHAPE[:4]
+    out["shape"] = f"B{b}_H{h}_T{t}_d{d}_bf16"
     return out
 
 
@@ -508,6 +533,7 @@ def run_ours(args):
     if c.world == 1 and not args.no_other:
         other = time_other_shapes(K.dilution_attention, c.dev)
         other["tile_kernels"] = time_shapes(K.dilution_attention, c.dev, TILE_SHAPES, iters=5)
+        other["variants"] = time_variants(c.pkg.kernels_bid.dilution_attention, c.dev)
         fp32_c1 = run_config1(c)
     sharded = None if args.no_sharded else run_train_sharded(c, args, devt)
     e2e = None if args.no_e2e else run_e2e(c, args, host, total_flops)

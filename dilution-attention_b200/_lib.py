@@ -45,7 +45,7 @@ SIGNATURES = {
     "dilution_variant_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I,
                                       _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_variant_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I,
-                                       _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+                                       _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_variant_decode": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _I, _I, _P, _P, _P, _P]),
 }
 BID = {"softmax": 0, "sigmoid": 5}          # codes of the reference's BID_TYPES (kernels_bid.py:84)

@@ -702,6 +702,24 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
   if (!stats) rmax = rden = pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
   cudaStream_t st = (cudaStream_t)stream;
+#if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_MAIN
+  if (dil::tc::supported(dtype, precision, d, 0)) {
+    // bf16 tensors, head_dim 64: the tcgen05 kernels, instantiated for the bid and share step
+    if (stats && pk) {
+      Prof prof("tc_rowstats_pk", st);
+      if (int rc = dil::tc::rowstats_pk(q, k, g, rmax, rden, pk, st, g_err, sizeof(g_err))) return rc;
+    } else if (stats) {
+      Prof prof("tc_rowstats", st);
+      if (int rc = dil::tc::rowstats(q, k, g, rmax, rden, st, g_err, sizeof(g_err))) return rc;
+    }
+    {
+      Prof prof("tc_colsum_scan", st);
+      if (int rc = dil::tc::colsum_scan(q, k, g, rmax, rden, nullptr, carry, total, st, g_err, sizeof(g_err))) return rc;
+    }
+    Prof prof("tc_forward_main", st);
+    return dil::tc::forward_main(q, k, v, g, rmax, rden, carry, nullptr, out, ssum, st, g_err, sizeof(g_err));
+  }
+#endif
   if (stats) {
     DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, {
       if (int rc = launch_rowstats<T, D, MMA>(q, k, g, rmax, rden, st)) return rc;
@@ -717,18 +735,23 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
 int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
                               int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
                               const float* out, const float* rmax, const float* rden, const float* carry,
-                              const float* ssum, const float* pk, void* scratch, void* dq, void* dk, void* dv,
-                              void* stream) {
+                              const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
+                              void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_variant_backward", dtype, precision, n, t, t, 0, d)) return rc;
   if (int rc = check_variant("dilution_variant_backward", bid, share)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
-  if (!q || !k || !v || !dout || !out || !carry || !ssum || !scratch || !dq || !dk || !dv ||
+  if (!q || !k || !v || !dout || !out || !carry || !total || !ssum || !scratch || !dq || !dk || !dv ||
       (stats && (!rmax || !rden || !pk)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
   if (!stats) rmax = rden = pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
+#if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_BACKWARD
+  if (dil::tc::supported(dtype, precision, d, 0))
+    return dil::tc::backward(q, k, v, g, dout, DILUTION_F32, out, rmax, rden, carry, total, ssum, pk, s.dq_main,
+                             s.dk_main, s.ghat, s.dbar, s.dop, dq, dk, dv, st, g_err, sizeof(g_err), mark_scope);
+#endif
   DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_backward<T, D, MMA>(
       q, k, v, g, dout, out, rmax, rden, carry, ssum, pk, s, dq, dk, dv, st))))
   return DILUTION_OK;

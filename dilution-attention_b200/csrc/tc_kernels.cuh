@@ -172,10 +172,21 @@ __device__ __forceinline__ uint32_t share_chunk_offset(int key, int q) {
   return (uint32_t)((q >> 6) * (int)kTileBytes + key * 128 + ((((q & 63) >> 3) ^ (key & 7)) << 4));
 }
 
-// log2-domain log-sum-exp of query i (+inf past the end, so that its p is 0)
+// log2-domain log-sum-exp of query i (+inf past the end, so that its p is 0).  The sigmoid bid
+// has no row statistics: its "lse" is 0 for a query that exists and +inf past the end.
+template <int BID = kBidSoftmax>
 __device__ __forceinline__ float load_lse(const float* __restrict__ rmax, const float* __restrict__ rden,
                                           int64_t row_base, int i, int tq) {
+  if (BID == kBidSigmoid) return i < tq ? 0.f : INFINITY;
   return i < tq ? rmax[row_base + i] + log2f(rden[row_base + i]) : INFINITY;
+}
+
+// The bid of one raw score s (kernels_bid.py:191-197) given the row's lse l:
+// softmax 2^(s*zscale - l); sigmoid 1 / (1 + 2^(l - s*zscale)), which is 0 for l = +inf.
+template <int BID>
+__device__ __forceinline__ float bid_p(float s, float zscale, float l) {
+  if (BID == kBidSigmoid) return fast_rcp(1.f + fast_exp2(fmaf(s, -zscale, l)));
+  return fast_exp2(fmaf(s, zscale, -l));
 }
 
 // ---------------------------------------------------------------- pass 1: row statistics
@@ -306,7 +317,7 @@ __global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant_
 // 0 and 64 of a tile): half the scratch and half the checkpoint stores.
 constexpr int kColsumSmem = 3 * kTileBytes + 1024 + 2048 + 1024 + 256;
 
-template <int CR>
+template <int CR, int BID = kBidSoftmax>
 __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Geom g,
     const float* __restrict__ rmax, const float* __restrict__ rden,
@@ -339,7 +350,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 128);
-  if (nib > 0 && wg == 0) sL[row] = load_lse(rmax, rden, row_base, ib0 * kTileRows + row, g.tq);
+  if (nib > 0 && wg == 0) sL[row] = load_lse<BID>(rmax, rden, row_base, ib0 * kTileRows + row, g.tq);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -389,7 +400,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     __syncwarp();
     // while the MMA runs: next tile's statistics, and the checkpoints of the previous tile
     float lse_next = 0.f;
-    if (wg == 1 && it + 1 < nib) lse_next = load_lse(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq);
+    if (wg == 1 && it + 1 < nib) lse_next = load_lse<BID>(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq);
     if (wg == 0 && it > 0) store_checkpoints(ib - 1, sCs[((it - 1) & 1) * 128 + row]);
     mbar_wait(sdone, it & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
@@ -416,7 +427,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
           const float ls[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
+            float p = bid_p<BID>(v[e4 * 4 + u], g.zscale, ls[u]);
             if (EDGE && ja > i0 + c * 32 + e4 * 4 + u) p = 0.f;
             part[u] += p;
           }
@@ -458,6 +469,9 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
 // TMEM: S^T 128 columns, O 64, rs 16 (256 allocated; two CTAs per SM).
 constexpr int kMainSmem = 7 * kTileBytes + 512 + 128;   // exact: the base must already be 1024-aligned
 
+// BID / SHARE select the ablations of kernels_bid.py (sigmoid bid; exclusive or absent share step,
+// :254-262); the default instantiation is the operator.
+template <int BID = kBidSoftmax, int SHARE = kShareInclusive>
 __global__ void __launch_bounds__(256, 2) forward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, Geom g, const float* __restrict__ rmax,
@@ -494,7 +508,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  if (wg == 0) sL[row] = load_lse(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
+  if (wg == 0) sL[row] = load_lse<BID>(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
   else {
 #pragma unroll
     for (int c = 0; c < 8; ++c)
@@ -586,10 +600,17 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e8 * 8 + h * 4 + u;
-            float p = fast_exp2(fmaf(v[e], g.zscale, -ls[u]));
+            float p = bid_p<BID>(v[e], g.zscale, ls[u]);
             if (MASK && (dead || ja > qh + c * 32 + e)) p = 0.f;
-            den += p;
-            sh[u] = p * fast_rcp(den);
+            if (SHARE == kShareInclusive) {
+              den += p;
+              sh[u] = p * fast_rcp(den);
+            } else if (SHARE == kShareExclusive) {     // earlier queries' demand only
+              sh[u] = p * fast_rcp(den);
+              den += p;
+            } else {                                   // no share step
+              sh[u] = p;
+            }
           }
           packed[h * 2 + 0] = pack_bf16(sh[0], sh[1]);
           packed[h * 2 + 1] = pack_bf16(sh[2], sh[3]);
@@ -714,6 +735,7 @@ __global__ void backward_prep_kernel(const TD* __restrict__ dout, const float* _
 constexpr int kBwdThreads = 384;
 constexpr int kBwdSmem = 12 * kTileBytes + 2048 + 2048 + 256 + 1024;
 
+template <int BID = kBidSoftmax, int SHARE = kShareInclusive>
 __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq, Geom g,
@@ -755,7 +777,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   auto load_stats = [&](int ib) {
     const int i = ib * kTileRows + row;
     float2 st = make_float2(INFINITY, 0.f);
-    if (i < g.tq) st = make_float2(rmax[row_base + i] + log2f(rden[row_base + i]), dbarp[row_base + i]);
+    if (i < g.tq) st = make_float2(load_lse<BID>(rmax, rden, row_base, i, g.tq), dbarp[row_base + i]);
     return st;
   };
 
@@ -979,8 +1001,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       const bool fetch_stats = !odd && wg == 0 && s + 1 < nsteps;
       if (fetch_stats) {
         const int i = (ib - 1) * kTileRows + row;     // ib >= 1 here, so i < tq
-        st_max = rmax[row_base + i];
-        st_den = rden[row_base + i];
+        if (BID == kBidSoftmax) {
+          st_max = rmax[row_base + i];
+          st_den = rden[row_base + i];
+        } else {
+          st_max = 0.f;                               // no row statistics: lse = 0 + log2(1)
+        }
         st_dbar = dbarp[row_base + i];
       }
       mbar_wait(sdone + 8 * odd, s & 1, ctl, &g_status, kErrWaitMma);
@@ -1014,19 +1040,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
         for (int e4 = 0; e4 < 8; ++e4) {
           const float4 l4 = Lse4[e4];
           const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float2 zs = make_float2(g.zscale, g.zscale);
-          const float2 z01 = fma2(make_float2(vs[e4 * 4], vs[e4 * 4 + 1]), zs, make_float2(-lse[0], -lse[1]));
-          const float2 z23 = fma2(make_float2(vs[e4 * 4 + 2], vs[e4 * 4 + 3]), zs, make_float2(-lse[2], -lse[3]));
+          // softmax: z = s*zscale - lse, p = 2^z;  sigmoid: z = lse - s*zscale, p = 1/(1 + 2^z)
+          const float zsign = BID == kBidSigmoid ? -g.zscale : g.zscale;
+          const float lsign = BID == kBidSigmoid ? 1.f : -1.f;
+          const float2 zs = make_float2(zsign, zsign);
+          const float2 z01 = fma2(make_float2(vs[e4 * 4], vs[e4 * 4 + 1]), zs, make_float2(lsign * lse[0], lsign * lse[1]));
+          const float2 z23 = fma2(make_float2(vs[e4 * 4 + 2], vs[e4 * 4 + 3]), zs, make_float2(lsign * lse[2], lsign * lse[3]));
           const float z[4] = {z01.x, z01.y, z23.x, z23.y};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e4 * 4 + u;
             float p = fast_exp2(z[u]);
+            if (BID == kBidSigmoid) p = fast_rcp(1.f + p);
             if (MASK) {
               if (dead || ja > iq0 + e) p = 0.f;
             }
-            incle += p;
-            inv[e] = fast_rcp(incle);
+            if (SHARE == kShareInclusive) {
+              incle += p;
+              inv[e] = fast_rcp(incle);
+            } else if (SHARE == kShareExclusive) {     // the demand of earlier queries only
+              inv[e] = fast_rcp(incle);
+              incle += p;
+            } else {
+              inv[e] = 1.f;
+            }
             vs[e] = p;
           }
         }
@@ -1037,18 +1074,37 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
           // with inv = 1/(committed+p+eps), share = p*inv and w = ds*inv:
           //   ds*(committed+eps)*inv^2 = w*(1-share),  dk_share = -w*share,
           //   dp = w - w*share + (suffix before this query) = w + (suffix after it)
-          // (element-wise parts two queries per instruction; the suffix itself is serial)
+          // (element-wise parts two queries per instruction; the suffix itself is serial).
+          // Exclusive share step (inv = 1/(committed+eps)): the direct term is w itself, so
+          // dp = w + (suffix BEFORE this query); no share step: dp = ds, no suffix at all.
+          // The Jacobian factor is p for the softmax bid and p(1-p) for the sigmoid
+          // (kernels_bid.py:194-196, 735-754); vs keeps it for the later suffix fix-up.
 #pragma unroll
           for (int h = 1; h >= 0; --h) {
             const int e = e4 * 4 + 2 * h;
             const float2 p2 = make_float2(vs[e], vs[e + 1]), i2 = make_float2(inv[e], inv[e + 1]);
             const float2 w2 = mul2(sub2(make_float2(vd[e], vd[e + 1]), make_float2(dbr[2 * h], dbr[2 * h + 1])), i2);
             const float2 s2 = mul2(p2, i2);
-            const float r1 = fmaf(-w2.y, s2.y, R);
-            R = fmaf(-w2.x, s2.x, r1);
-            const float2 pd2 = mul2(p2, add2(w2, make_float2(R, r1)));
+            float2 jac2 = p2;
+            if (BID == kBidSigmoid) jac2 = mul2(p2, sub2(make_float2(1.f, 1.f), p2));
+            float2 pd2;
+            if (SHARE == kShareInclusive) {
+              const float r1 = fmaf(-w2.y, s2.y, R);
+              R = fmaf(-w2.x, s2.x, r1);
+              pd2 = mul2(jac2, add2(w2, make_float2(R, r1)));
+            } else if (SHARE == kShareExclusive) {
+              const float r1 = fmaf(-w2.y, s2.y, R);
+              pd2 = mul2(jac2, add2(w2, make_float2(r1, R)));
+              R = fmaf(-w2.x, s2.x, r1);
+            } else {
+              pd2 = mul2(jac2, w2);
+            }
             vd[e] = pd2.x;
             vd[e + 1] = pd2.y;
+            if (BID == kBidSigmoid) {
+              vs[e] = jac2.x;
+              vs[e + 1] = jac2.y;
+            }
             shp[e4 * 2 + h] = pack_bf16(s2.x, s2.y);
           }
         }
@@ -1413,6 +1469,15 @@ constexpr int kTwoPerSm = 100 * 1024;
 static_assert(5 * (kRowstatsSmem + 1024) > 233472 && 5 * (kColsumSmem + 1024) > 233472,
               "at most four CTAs of a 128-column kernel may share an SM");
 
+// Compile-time bid / share of a launch from the run-time fields of its geometry.
+#define DIL_TC_SHARE(g, ...)                                                                       \
+  if ((g).share == kShareInclusive) { constexpr int SHARE = kShareInclusive; __VA_ARGS__; }        \
+  else if ((g).share == kShareExclusive) { constexpr int SHARE = kShareExclusive; __VA_ARGS__; }   \
+  else { constexpr int SHARE = kShareNone; __VA_ARGS__; }
+#define DIL_TC_BID(g, ...)                                                     \
+  if ((g).bid == kBidSigmoid) { constexpr int BID = kBidSigmoid; __VA_ARGS__; } \
+  else { constexpr int BID = kBidSoftmax; __VA_ARGS__; }
+
 inline int rowstats(const void* q, const void* k, const Geom& g, float* rmax, float* rden,
                     cudaStream_t st, char* err, size_t errlen) {
   CUtensorMap mq, mk;
@@ -1433,14 +1498,17 @@ inline int colsum_scan(const void* q, const void* k, const Geom& g, const float*
   if (int rc = make_map(&mk, k, g.n, g.tk, err, errlen)) return rc;
   constexpr int smem = kColsumSmem;
   const int nkb = (g.tk + kTileRows - 1) / kTileRows;
+  const unsigned grid = (unsigned)(g.n * nkb);
   if (g.carry_rows == 32) {
-    if (int rc = set_smem_attr((const void*)colsum_scan_kernel<32>, smem, err, errlen)) return rc;
-    colsum_scan_kernel<32><<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
-                                                                   total);
+    DIL_TC_BID(g, {
+      if (int rc = set_smem_attr((const void*)colsum_scan_kernel<32, BID>, smem, err, errlen)) return rc;
+      colsum_scan_kernel<32, BID><<<grid, 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry, total);
+    })
   } else {
-    if (int rc = set_smem_attr((const void*)colsum_scan_kernel<64>, smem, err, errlen)) return rc;
-    colsum_scan_kernel<64><<<(unsigned)(g.n * nkb), 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry,
-                                                                   total);
+    DIL_TC_BID(g, {
+      if (int rc = set_smem_attr((const void*)colsum_scan_kernel<64, BID>, smem, err, errlen)) return rc;
+      colsum_scan_kernel<64, BID><<<grid, 256, smem, st>>>(mq, mk, g, rmax, rden, carry_base, carry, total);
+    })
   }
   return launch_status("tc colsum_scan", err, errlen);
 }
@@ -1455,9 +1523,11 @@ inline int forward_main(const void* q, const void* k, const void* v, const Geom&
   constexpr int smem = kMainSmem;
   static_assert(2 * (smem + 1024) <= 233472 && 3 * (smem + 1024) > 233472, "exactly two CTAs of the main pass fit one SM");
   const int nqb = (g.tq + kTileRows - 1) / kTileRows;
-  if (int rc = set_smem_attr((const void*)forward_main_kernel, smem, err, errlen)) return rc;
-  forward_main_kernel<<<(unsigned)(g.n * nqb), 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base,
-                                                              out, ssum);
+  const unsigned grid = (unsigned)(g.n * nqb);
+  DIL_TC_BID(g, DIL_TC_SHARE(g, {
+    if (int rc = set_smem_attr((const void*)forward_main_kernel<BID, SHARE>, smem, err, errlen)) return rc;
+    forward_main_kernel<BID, SHARE><<<grid, 256, smem, st>>>(mq, mk, mv, g, rmax, rden, carry, carry_base, out, ssum);
+  }))
   return launch_status("tc forward_main", err, errlen);
 }
 
@@ -1495,17 +1565,29 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   if (g.carry_rows == 32) {
     constexpr int smem_bwd = kBwdSmem;
     static_assert(smem_bwd <= 232448 && 2 * smem_bwd > 233472, "the backward main pass runs one CTA per SM");
-    if (int rc = set_smem_attr((const void*)backward_main_kernel, smem_bwd, err, errlen)) return rc;
     mark("tc_backward_main", st, 0);
-    backward_main_kernel<<<(unsigned)(g.n * nkb), kBwdThreads, smem_bwd, st>>>(
-        mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
-        (__nv_bfloat16*)dv, ghat);
+    const unsigned grid = (unsigned)(g.n * nkb);
+    DIL_TC_BID(g, DIL_TC_SHARE(g, {
+      if (int rc = set_smem_attr((const void*)backward_main_kernel<BID, SHARE>, smem_bwd, err, errlen)) return rc;
+      backward_main_kernel<BID, SHARE><<<grid, kBwdThreads, smem_bwd, st>>>(
+          mq, mk, md, mdq, g, (const __nv_bfloat16*)v, rmax, rden, dbarp, carry, total, dq_main, dk_main,
+          (__nv_bfloat16*)dv, ghat);
+    }))
   } else {
     snprintf(err, errlen, "the tensor-core backward needs checkpoints every 32 query rows (got %d)", g.carry_rows);
     return 1;
   }
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
+  if (g.bid == kBidSigmoid) {
+    // no row normalisation in the bid: no Jacobian correction, dk and dq are dk_main and dq_main
+    const int64_t n4 = rows * kHeadDim / 4;
+    mark("tc_cast_dk_dq", st, 0);
+    cast_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk_main, (__nv_bfloat16*)dk, n4);
+    cast_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_main, (__nv_bfloat16*)dq, n4);
+    mark("tc_cast_dk_dq", st, 1);
+    return launch_status("tc cast_dk_dq", err, errlen);
+  }
   if (pk != nullptr)
     return backward_tail_with_pk(mq, mk, g, rmax, rden, ghat, dk_main, dq_main, pk, dq, dk, st, err, errlen, mark);
   constexpr int smem = kCorrSmem > kTwoPerSm ? kCorrSmem : kTwoPerSm;

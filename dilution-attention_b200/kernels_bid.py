@@ -13,8 +13,9 @@ Same entry points and keyword arguments as the reference module (`bid`, `share_c
 `shift` after the arguments of `dilution.kernels`); `shift` only matters to bids that are not
 built here.  The six other bid functions of the reference (relu, relu2, softplus, minshift,
 expshift, sigshift) raise ValueError.  The operator itself (softmax, True) is handed to
-`kernels.py`, tensor-core path included; every other combination runs the fp32 tile kernels of
-the C ABI's dilution_variant_* calls: fp32 FMAs for "ieee", tf32 tensor-core products otherwise.
+`kernels.py`; every other combination goes through the C ABI's dilution_variant_* calls: the
+tcgen05 kernels instantiated for the bid and share step for bf16 tensors of head_dim 64 under
+"bf16", the fp32 tile kernels otherwise (fp32 FMAs for "ieee", tf32 tensor-core products else).
 """
 
 from __future__ import annotations
@@ -135,12 +136,12 @@ class _VariantFn(torch.autograd.Function):
         ctx.args = (dot_precision, bid, share)
         stats = [x for x in (aux["rmax"], aux["rden"], aux["pk"]) if x is not None]
         ctx.n_stats = len(stats)
-        ctx.save_for_backward(q, k, v, out, aux["carry"], aux["ssum"], *stats)
+        ctx.save_for_backward(q, k, v, out, aux["carry"], aux["ssum"], aux["total"], *stats)
         return out.reshape(q.shape)
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, carry, ssum, *stats = ctx.saved_tensors
+        q, k, v, out, carry, ssum, total, *stats = ctx.saved_tensors
         rmax, rden, pk = stats if ctx.n_stats == 3 else (None, None, None)
         dot_precision, bid, share = ctx.args
         lib = _lib.load()
@@ -154,7 +155,7 @@ class _VariantFn(torch.autograd.Function):
         _lib.check(lib.dilution_variant_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim, 1.0 / math.sqrt(head_dim),
             EPS, bid, share, dof.data_ptr(), out.data_ptr(), K._ptr(rmax), K._ptr(rden), carry.data_ptr(),
-            ssum.data_ptr(), K._ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            total.data_ptr(), ssum.data_ptr(), K._ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             K._stream(q.device)), "dilution_variant_backward")
         shape4 = (batch, heads, seq, head_dim)
         return (dq.reshape(shape4).to(q.dtype), dk.reshape(shape4).to(k.dtype), dv.reshape(shape4).to(v.dtype),

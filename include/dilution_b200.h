@@ -267,9 +267,10 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  *          EXCLUSIVE  share = p / (committed + eps)       (earlier queries' demand only);
  *          NONE       share = p                           (no share step: out = p v / rowsum p).
  * The other bid functions of kernels_bid.py (relu, relu2, softplus, minshift, expshift,
- * sigshift) are not built: DILUTION_ERR_UNSUPPORTED.  These calls run the fp32 tile kernels
- * for every dtype and head_dim (IEEE: fp32 FMAs; otherwise tf32 tensor-core products), with
- * a checkpoint every DILUTION_CARRY_ROWS query rows.
+ * sigshift) are not built: DILUTION_ERR_UNSUPPORTED.  bf16 tensors of head_dim 64 under
+ * DILUTION_PREC_BF16 run on the tcgen05 kernels, instantiated for the bid and share step;
+ * every other dtype, precision and head_dim on the fp32 tile kernels (IEEE: fp32 FMAs;
+ * otherwise tf32 tensor-core products).  Checkpoints every DILUTION_CARRY_ROWS query rows.
  *
  * dilution_variant_forward: all forward passes of one call (kernels_bid.py:424-489):
  * rmax, rden (n, t) — softmax bid only, may be NULL for the sigmoid; carry
@@ -277,7 +278,8 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * prefix); out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
  * which dilution_variant_backward needs for the softmax bid.
  * dilution_variant_backward: dq, dk, dv in the input dtype from an fp32 dout
- * (kernels_bid.py:731-815); scratch of dilution_backward_scratch_bytes(n, t, d).
+ * (kernels_bid.py:731-815), given what the forward wrote; scratch of
+ * dilution_backward_scratch_bytes(n, t, d).
  * dilution_variant_decode: one cached token (kernels_bid.py:853-1012); k1 / v1 (n, d) are
  * the new token's rows to append at position length-1, or both NULL when the caller has
  * written them; committed advances by p in place for every variant; scratch of
@@ -289,8 +291,8 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
 int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
                               int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
                               const float* out, const float* rmax, const float* rden, const float* carry,
-                              const float* ssum, const float* pk, void* scratch, void* dq, void* dk, void* dv,
-                              void* stream);
+                              const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
+                              void* dk, void* dv, void* stream);
 int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
                             int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
                             float eps, int bid, int share, float* committed, void* out, void* scratch,

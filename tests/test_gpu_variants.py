@@ -88,6 +88,35 @@ def test_bf16_tensors(KB, key, bid, share):
     check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
 
 
+@pytest.mark.parametrize("seq", [300, 1100, 2049])
+@pytest.mark.parametrize("key,bid,share", VARIANTS)
+def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, seq):
+    """bf16 tensors with heads of 64 under "bf16": the tcgen05 kernels instantiated for the bid and
+    share step (not the tile kernels), forward and backward, at ragged lengths."""
+    pkg = load_package()
+    q, k, v, dout = make_inputs(2, 2, seq, 64, 31 + seq, scales=(0.5, 0.5, 1.0, 1.0))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    pkg._lib.profile(True)
+    pkg._lib.profile_collect()
+    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share)
+    out.backward(dout.to(DEV))
+    torch.cuda.synchronize()
+    names = set(pkg._lib.profile_collect())
+    pkg._lib.profile(False)
+    assert {"tc_colsum_scan", "tc_forward_main", "tc_backward_main"} <= names, names
+    assert not any(n.startswith("simt_") for n in names), names
+    assert ("tc_rowstats_pk" in names) == (bid == "softmax")
+    assert (out.detach().cpu() - ref).abs().max().item() < 2e-2
+    check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
+    # forward only, with the demand totals
+    out2, aux = KB.dilution_attention_forward(qs.detach(), ks.detach(), vs.detach(), dot_precision="bf16",
+                                              return_aux=True, bid=bid, share_cumsum=share)
+    assert (out2.cpu() - ref).abs().max().item() < 2e-2
+    assert rel_err(aux["committed_total"].cpu(), O.variant_bids(qb.float(), kb.float(), bid).sum(-2)) < 2e-2
+
+
 def test_the_operator_itself_goes_to_the_production_kernels(KB):
     pkg = load_package()
     q, k, v, _ = make_inputs(1, 2, 300, 64, 5, scales=(0.5, 0.5, 1.0, 1.0))
