@@ -697,7 +697,10 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
   if (int rc = check_common("dilution_variant_forward", dtype, precision, n, t, t, 0, d)) return rc;
   if (int rc = check_variant("dilution_variant_forward", bid, share)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
-  if (!q || !k || !v || !carry || !total || !out || !ssum || (stats && (!rmax || !rden)))
+  // without a share step nothing downstream reads the checkpoints: carry and total may both be
+  // NULL, and the column-sum pass is skipped
+  const bool scan = !(share == dil::kShareNone && carry == nullptr && total == nullptr);
+  if (!q || !k || !v || (scan && (!carry || !total)) || !out || !ssum || (stats && (!rmax || !rden)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_forward: null pointer");
   if (!stats) rmax = rden = pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
@@ -712,7 +715,7 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
       Prof prof("tc_rowstats", st);
       if (int rc = dil::tc::rowstats(q, k, g, rmax, rden, st, g_err, sizeof(g_err))) return rc;
     }
-    {
+    if (scan) {
       Prof prof("tc_colsum_scan", st);
       if (int rc = dil::tc::colsum_scan(q, k, g, rmax, rden, nullptr, carry, total, st, g_err, sizeof(g_err))) return rc;
     }
@@ -725,9 +728,11 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
       if (int rc = launch_rowstats<T, D, MMA>(q, k, g, rmax, rden, st)) return rc;
     }))
   }
-  DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, {
-    if (int rc = launch_colsum<T, D, MMA>(q, k, g, rmax, rden, nullptr, carry, total, st)) return rc;
-  }))
+  if (scan) {
+    DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, {
+      if (int rc = launch_colsum<T, D, MMA>(q, k, g, rmax, rden, nullptr, carry, total, st)) return rc;
+    }))
+  }
   DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_main<T, D, MMA>(q, k, v, g, rmax, rden, carry, nullptr, out, ssum, pk, st))))
   return DILUTION_OK;
 }
@@ -740,8 +745,8 @@ int dilution_variant_backward(const void* q, const void* k, const void* v, int d
   if (int rc = check_common("dilution_variant_backward", dtype, precision, n, t, t, 0, d)) return rc;
   if (int rc = check_variant("dilution_variant_backward", bid, share)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
-  if (!q || !k || !v || !dout || !out || !carry || !total || !ssum || !scratch || !dq || !dk || !dv ||
-      (stats && (!rmax || !rden || !pk)))
+  if (!q || !k || !v || !dout || !out || !ssum || !scratch || !dq || !dk || !dv ||
+      (share != dil::kShareNone && (!carry || !total)) || (stats && (!rmax || !rden || !pk)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
   if (!stats) rmax = rden = pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);

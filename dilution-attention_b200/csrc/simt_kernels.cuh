@@ -439,9 +439,12 @@ __global__ void __launch_bounds__(NT) main_kernel(
         accum_tile<D, false, MMA, true>(sP, sK, acc_pk);
         __syncthreads();
       }
-      float c = (ja < g.tk) ? carry_row[ja] : 0.f;
-      if (carry_base != nullptr && ja < g.tk) c += carry_base[n * g.tk + ja];
-      for (int s2 = 0; s2 < seg; ++s2) c += sSeg[s2 * TS + col];
+      float c = 0.f;
+      if (g.share != kShareNone) {                  // no share step: no demand is read
+        c = (ja < g.tk) ? carry_row[ja] : 0.f;
+        if (carry_base != nullptr && ja < g.tk) c += carry_base[n * g.tk + ja];
+        for (int s2 = 0; s2 < seg; ++s2) c += sSeg[s2 * TS + col];
+      }
       if (g.share == kShareInclusive) {
 #pragma unroll 4
         for (int rr = 0; rr < 16; ++rr) {
@@ -592,8 +595,11 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       }
       sSeg[seg * TS + col] = seg_sum;
       __syncthreads();
-      float c0 = (ja < g.tk) ? carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] : 0.f;
-      for (int s2 = 0; s2 < seg; ++s2) c0 += sSeg[s2 * TS + col];
+      float c0 = 0.f;
+      if (g.share != kShareNone) {                  // no share step: no demand is read
+        c0 = (ja < g.tk) ? carry[(n * ncb + 2 * ib) * (int64_t)g.tk + ja] : 0.f;
+        for (int s2 = 0; s2 < seg; ++s2) c0 += sSeg[s2 * TS + col];
+      }
       // first walk: the segment's sum of dk_share
       float c = c0, dk_sum = 0.f;
       if (g.share != kShareNone) {

@@ -548,7 +548,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   auto load_den = [&](int jbx) {
     const int jx = jbx * kTileRows + row;
     float d = g.eps;
-    if (jx < g.tk && have_rows) {
+    if (SHARE != kShareNone && jx < g.tk && have_rows) {      // no share step: no demand is read
       d += carry[carry_row + jx];
       if (carry_base != nullptr) d += carry_base[(int64_t)n * g.tk + jx];
     }
@@ -983,7 +983,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
     // demand of this thread's key in front of its 32 queries of half-step h (exclusive of the
     // first): the stored checkpoint of that 32-row block (past the end: any value, p is 0 there)
     auto load_edge = [&](int h) {
-      if (dead) return 0.f;
+      if (dead || SHARE == kShareNone) return 0.f;         // no share step: no demand is read
       const int rb = 4 * (nqb - 1 - (h >> 1)) + ((h & 1) ? 0 : 2) + (wg == 0 ? 1 : 0);
       return rb < ncb ? carry[((int64_t)n * ncb + rb) * g.tk + ja] : total[(int64_t)n * g.tk + ja];
     };

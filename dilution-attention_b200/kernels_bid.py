@@ -57,9 +57,11 @@ def _is_operator(bid: str, share_cumsum) -> bool:
     return bid == "softmax" and _share_code(share_cumsum) == 1
 
 
-def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget_gib=16.0, keep_carry=False):
-    """All forward passes on the tile kernels, (batch*head) rows in slabs under the scratch
-    budget unless the checkpoints are kept for a backward."""
+def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget_gib=16.0, keep_carry=False,
+                     need_total=True):
+    """All forward passes of one call, (batch*head) rows in slabs under the scratch budget unless
+    the checkpoints are kept for a backward.  Without a share step nothing reads the checkpoints:
+    unless the demand totals are asked for, the column-sum pass is skipped altogether."""
     lib = _lib.load()
     (qf, kf, vf), code, prec, n = K._prepare(q, k, v, dot_precision)
     batch, heads, seq, head_dim = q.shape
@@ -67,7 +69,8 @@ def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget
     stats = bid == _lib.BID["softmax"]
     out = torch.empty(n, seq, head_dim, **f32)
     ssum = torch.empty(n, seq, **f32)
-    total = torch.empty(n, seq, **f32)
+    scan = share != 0 or need_total
+    total = torch.empty(n, seq, **f32) if scan else None
     rmax = torch.empty(n, seq, **f32) if stats else None
     rden = torch.empty(n, seq, **f32) if stats else None
     pk = torch.empty(n, seq, head_dim, **f32) if (save_pk and stats) else None
@@ -75,7 +78,7 @@ def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget
     rows = n
     if not keep_carry:
         rows = max(1, min(n, int(scratch_budget_gib * 2**30) // max(ncb * seq * 4, 1)))
-    carry = torch.empty(rows, ncb, seq, **f32)
+    carry = torch.empty(rows, ncb, seq, **f32) if scan else None
     scale = 1.0 / math.sqrt(head_dim)
     st = K._stream(q.device)
     part = lambda x, a, b: None if x is None else x[a:b].data_ptr()
@@ -83,7 +86,7 @@ def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget
         b = min(a + rows, n)
         _lib.check(lib.dilution_variant_forward(
             qf[a:b].data_ptr(), kf[a:b].data_ptr(), vf[a:b].data_ptr(), code, prec, b - a, seq, head_dim,
-            scale, EPS, bid, share, part(rmax, a, b), part(rden, a, b), carry.data_ptr(), total[a:b].data_ptr(),
+            scale, EPS, bid, share, part(rmax, a, b), part(rden, a, b), K._ptr(carry), part(total, a, b),
             out[a:b].data_ptr(), ssum[a:b].data_ptr(), part(pk, a, b), st), "dilution_variant_forward")
     return out, dict(rmax=rmax, rden=rden, carry=carry, ssum=ssum, pk=pk, total=total)
 
@@ -115,7 +118,8 @@ def dilution_attention_forward(
             res[1].update(bid=bid, share_cumsum=share_cumsum, shift=shift)
         return res
     batch, heads, seq, head_dim = q.shape
-    out, aux = _variant_forward(q, k, v, dot_precision, code_b, code_s, save_pk=False, keep_carry=return_aux)
+    out, aux = _variant_forward(q, k, v, dot_precision, code_b, code_s, save_pk=False, keep_carry=return_aux,
+                                need_total=return_aux)
     result = out.reshape(batch, heads, seq, head_dim)
     if return_aux:
         return result, dict(rmax=aux["rmax"], rden=aux["rden"], carry=aux["carry"], ssum=aux["ssum"],
@@ -132,16 +136,21 @@ class _VariantFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, dot_precision, bid, share):
         training = any(ctx.needs_input_grad[:3])
-        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, save_pk=training, keep_carry=True)
+        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, save_pk=training, keep_carry=True,
+                                    need_total=False)
         ctx.args = (dot_precision, bid, share)
         stats = [x for x in (aux["rmax"], aux["rden"], aux["pk"]) if x is not None]
         ctx.n_stats = len(stats)
-        ctx.save_for_backward(q, k, v, out, aux["carry"], aux["ssum"], aux["total"], *stats)
+        scan = [x for x in (aux["carry"], aux["total"]) if x is not None]
+        ctx.n_scan = len(scan)
+        ctx.save_for_backward(q, k, v, out, aux["ssum"], *scan, *stats)
         return out.reshape(q.shape)
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, carry, ssum, total, *stats = ctx.saved_tensors
+        q, k, v, out, ssum, *rest = ctx.saved_tensors
+        carry, total = rest[:2] if ctx.n_scan == 2 else (None, None)
+        stats = rest[ctx.n_scan:]
         rmax, rden, pk = stats if ctx.n_stats == 3 else (None, None, None)
         dot_precision, bid, share = ctx.args
         lib = _lib.load()
@@ -154,8 +163,8 @@ class _VariantFn(torch.autograd.Function):
                               dtype=torch.uint8)
         _lib.check(lib.dilution_variant_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim, 1.0 / math.sqrt(head_dim),
-            EPS, bid, share, dof.data_ptr(), out.data_ptr(), K._ptr(rmax), K._ptr(rden), carry.data_ptr(),
-            total.data_ptr(), ssum.data_ptr(), K._ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            EPS, bid, share, dof.data_ptr(), out.data_ptr(), K._ptr(rmax), K._ptr(rden), K._ptr(carry),
+            K._ptr(total), ssum.data_ptr(), K._ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             K._stream(q.device)), "dilution_variant_backward")
         shape4 = (batch, heads, seq, head_dim)
         return (dq.reshape(shape4).to(q.dtype), dk.reshape(shape4).to(k.dtype), dv.reshape(shape4).to(v.dtype),

@@ -275,7 +275,8 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * dilution_variant_forward: all forward passes of one call (kernels_bid.py:424-489):
  * rmax, rden (n, t) — softmax bid only, may be NULL for the sigmoid; carry
  * (n, ceil(t/32), t); total (n, t) = column totals of p (the decode accumulator after this
- * prefix); out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
+ * prefix) — with DILUTION_SHARE_NONE carry and total may both be NULL and the column-sum
+ * pass is skipped; out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
  * which dilution_variant_backward needs for the softmax bid.
  * dilution_variant_backward: dq, dk, dv in the input dtype from an fp32 dout
  * (kernels_bid.py:731-815), given what the forward wrote; scratch of
