@@ -42,13 +42,14 @@ SIGNATURES = {
     "dilution_softmax_decode_append": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _P, _P, _P]),
     "dilution_split_heads_rope": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _I, _P]),
     "dilution_decode_static": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P]),
-    "dilution_variant_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I,
+    "dilution_variant_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I, _F,
                                       _P, _P, _P, _P, _P, _P, _P, _P]),
-    "dilution_variant_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I,
+    "dilution_variant_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I, _F,
                                        _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "dilution_variant_decode": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _I, _I, _P, _P, _P, _P]),
+    "dilution_variant_decode": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _I, _I, _F, _P, _P, _P, _P]),
 }
-BID = {"softmax": 0, "sigmoid": 5}          # codes of the reference's BID_TYPES (kernels_bid.py:84)
+# codes of the reference's BID_TYPES (kernels_bid.py:84) for the bids that are built
+BID = {"softmax": 0, "sigmoid": 5, "expshift": 6, "sigshift": 7}
 
 _lib = None
 

@@ -106,11 +106,13 @@ int check_carry_rows(const char* fn, int dtype, int precision, int d, int64_t q_
 
 dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float scale, float eps,
                     int carry_rows = dil::kCarryRows, int bid = dil::kBidSoftmax,
-                    int share = dil::kShareInclusive) {
+                    int share = dil::kShareInclusive, float shift = 1.f) {
   dil::Geom g;
   g.carry_rows = carry_rows;
-  g.bid = bid;
+  g.bid = dil::bid_form(bid);
   g.share = share;
+  g.normalised = bid == dil::kBidSoftmax;
+  g.lshift = (bid == dil::kBidExpshift || bid == dil::kBidSigshift) ? log2f(shift) : 0.f;
   g.n = n;
   g.tq = (int)tq;
   g.tk = (int)tk;
@@ -246,7 +248,7 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
     if (int rc = check_launch("backward_main")) return rc;
   }
   const int64_t total = rows * D;
-  if (g.bid == dil::kBidSoftmax) {
+  if (g.normalised) {
     auto kern = backward_dk_correction_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
     {
@@ -265,7 +267,7 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
   {
     Prof prof("dq_epilogue", st);
     dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-        s.dq_main, s.ghat, g.bid == dil::kBidSoftmax ? pk : nullptr, total, D, (T*)dq);
+        s.dq_main, s.ghat, g.normalised ? pk : nullptr, total, D, (T*)dq);
   }
   return check_launch("dq_epilogue");
 }
@@ -296,7 +298,8 @@ template <typename T, int D, int MODE = dil::decode::kSweepDilution>
 int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int64_t cap,
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
                   cudaStream_t st, bool timing = true, const void* knew = nullptr,
-                  const void* vnew = nullptr, int bid = dil::kBidSoftmax, int share = dil::kShareInclusive) {
+                  const void* vnew = nullptr, int bid = dil::kBidSoftmax, int share = dil::kShareInclusive,
+                  float lshift = 0.f) {
   using namespace dil::decode;
   const int chunk = decode_chunk(n, len);
   const int nch = (int)((len + chunk - 1) / chunk);
@@ -314,7 +317,7 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
     Prof prof("decode_sweep", st, timing);
     sweep_kernel<T, D, MODE><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
                                                   committed, s.pout, s.psum, (const T*)vnew,
-                                                  (T*)const_cast<void*>(vc), bid, share);
+                                                  (T*)const_cast<void*>(vc), bid, share, lshift);
   }
   if (int rc = check_launch("decode sweep")) return rc;
   {
@@ -682,20 +685,22 @@ int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v
 }
 
 // ---- share / bid variants (the tile kernels; kernels_bid.py of the reference) -------------
-static int check_variant(const char* fn, int bid, int share) {
-  if (bid != dil::kBidSoftmax && bid != dil::kBidSigmoid)
-    return fail(DILUTION_ERR_UNSUPPORTED, "%s: bid %d is not built (DILUTION_BID_SOFTMAX, DILUTION_BID_SIGMOID)", fn, bid);
+static int check_variant(const char* fn, int bid, int share, float shift) {
+  if (bid != dil::kBidSoftmax && bid != dil::kBidSigmoid && bid != dil::kBidExpshift && bid != dil::kBidSigshift)
+    return fail(DILUTION_ERR_UNSUPPORTED, "%s: bid %d is not built (softmax 0, sigmoid 5, expshift 6, sigshift 7)", fn, bid);
+  if ((bid == dil::kBidExpshift || bid == dil::kBidSigshift) && !(shift > 0.f))
+    return fail(DILUTION_ERR_ARG, "%s: shift must be positive", fn);
   if (share != dil::kShareNone && share != dil::kShareInclusive && share != dil::kShareExclusive)
     return fail(DILUTION_ERR_ARG, "%s: share must be 0 (none), 1 (inclusive) or 2 (exclusive)", fn);
   return DILUTION_OK;
 }
 
 int dilution_variant_forward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
-                             int64_t t, int d, float scale, float eps, int bid, int share, float* rmax,
+                             int64_t t, int d, float scale, float eps, int bid, int share, float shift, float* rmax,
                              float* rden, float* carry, float* total, float* out, float* ssum, float* pk,
                              void* stream) {
   if (int rc = check_common("dilution_variant_forward", dtype, precision, n, t, t, 0, d)) return rc;
-  if (int rc = check_variant("dilution_variant_forward", bid, share)) return rc;
+  if (int rc = check_variant("dilution_variant_forward", bid, share, shift)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
   // without a share step nothing downstream reads the checkpoints: carry and total may both be
   // NULL, and the column-sum pass is skipped
@@ -703,7 +708,7 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
   if (!q || !k || !v || (scan && (!carry || !total)) || !out || !ssum || (stats && (!rmax || !rden)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_forward: null pointer");
   if (!stats) rmax = rden = pk = nullptr;
-  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share, shift);
   cudaStream_t st = (cudaStream_t)stream;
 #if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_MAIN
   if (dil::tc::supported(dtype, precision, d, 0)) {
@@ -738,18 +743,18 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
 }
 
 int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
-                              int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
+                              int64_t t, int d, float scale, float eps, int bid, int share, float shift, const float* dout,
                               const float* out, const float* rmax, const float* rden, const float* carry,
                               const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
                               void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_variant_backward", dtype, precision, n, t, t, 0, d)) return rc;
-  if (int rc = check_variant("dilution_variant_backward", bid, share)) return rc;
+  if (int rc = check_variant("dilution_variant_backward", bid, share, shift)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
   if (!q || !k || !v || !dout || !out || !ssum || !scratch || !dq || !dk || !dv ||
       (share != dil::kShareNone && (!carry || !total)) || (stats && (!rmax || !rden || !pk)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
   if (!stats) rmax = rden = pk = nullptr;
-  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share);
+  const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share, shift);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
 #if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_BACKWARD
@@ -764,11 +769,11 @@ int dilution_variant_backward(const void* q, const void* k, const void* v, int d
 
 int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
                             int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
-                            float eps, int bid, int share, float* committed, void* out, void* scratch,
+                            float eps, int bid, int share, float shift, float* committed, void* out, void* scratch,
                             void* stream) {
   if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
     return fail(DILUTION_ERR_ARG, "dilution_variant_decode: dtype must be DILUTION_F32 or DILUTION_BF16");
-  if (int rc = check_variant("dilution_variant_decode", bid, share)) return rc;
+  if (int rc = check_variant("dilution_variant_decode", bid, share, shift)) return rc;
   if (!valid_d(d))
     return fail(DILUTION_ERR_UNSUPPORTED, "dilution_variant_decode: head_dim %d not in {16, 32, 64, 128}", d);
   if (n < 1 || n > 65535)
@@ -782,7 +787,8 @@ int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void
     return fail(DILUTION_ERR_ARG, "dilution_variant_decode: q1 / k1 / v1 / caches must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   DIL_DISPATCH(dtype, d, return (launch_decode<T, D, dil::decode::kSweepVariant>(
-      q1, k_cache, v_cache, n, capacity, length, scale, eps, committed, out, scratch, st, true, k1, v1, bid, share)))
+      q1, k_cache, v_cache, n, capacity, length, scale, eps, committed, out, scratch, st, true, k1, v1, bid, share,
+      (bid == dil::kBidExpshift || bid == dil::kBidSigshift) ? log2f(shift) * 1.f : 0.f)))
   return DILUTION_OK;
 }
 

@@ -112,11 +112,19 @@ struct Geom {
   float scale;
   float eps;
   int carry_rows; // query rows per demand checkpoint (16, 32 or 64)
-  int bid;        // bid function (codes of kernels_bid.py:94): 0 softmax, 5 sigmoid; tile kernels only
+  int bid;        // FORM of the bid: kBidSoftmax 2^(z - l) or kBidSigmoid 1/(1 + 2^(l - z))
   int share;      // share step (kernels_bid.py:123-127): 1 inclusive, 2 exclusive history, 0 none
+  int normalised; // the bid divides by its row sum (softmax): l is the row's log-sum-exp and the
+                  // backward has the Jacobian correction ghat; otherwise l = lshift for every row
+  float lshift;   // log2 of the shift of expshift / sigshift (kernels_bid.py:19-26); 0 for the sigmoid
 };
 
-constexpr int kBidSoftmax = 0, kBidSigmoid = 5;
+// Bid codes of the reference (kernels_bid.py:84) that are built, and the form each one takes:
+// expshift = the softmax form without the row sum, sigshift = the sigmoid form, both with l = log2(shift).
+constexpr int kBidSoftmax = 0, kBidSigmoid = 5, kBidExpshift = 6, kBidSigshift = 7;
+__host__ __device__ constexpr int bid_form(int bid) {
+  return (bid == kBidSigmoid || bid == kBidSigshift) ? kBidSigmoid : kBidSoftmax;
+}
 constexpr int kShareNone = 0, kShareInclusive = 1, kShareExclusive = 2;
 
 }  // namespace dil

@@ -157,16 +157,17 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
 //   MODE kSweepSoftmax : share = p, no demand read or written: plain softmax attention of the
 //                        new token over the cache, the cached step of the reference's softmax
 //                        layers (model.py:112-117)
-//   MODE kSweepVariant : bid (softmax / sigmoid) and share step (inclusive / exclusive / none)
+//   MODE kSweepVariant : bid (softmax / sigmoid / expshift / sigshift) and share step (inclusive / exclusive / none)
 //                        chosen at run time; the demand advances by p in every case
 constexpr int kSweepSoftmax = 0, kSweepDilution = 1, kSweepVariant = 2;
 
 template <int MODE>
 __device__ __forceinline__ float key_share(float a, float gmax, float rinv, float eps, float* c_ptr,
-                                           bool fresh, int bid, int share_step) {
+                                           bool fresh, int bid, int share_step, float lshift) {
   float p = exp2f(a - gmax) * rinv;
   if (MODE == kSweepSoftmax) return p;
-  if (MODE == kSweepVariant && bid == kBidSigmoid) p = 1.f / (1.f + exp2f(-a));
+  if (MODE == kSweepVariant && bid != kBidSoftmax)      // bids without a row sum
+    p = bid_form(bid) == kBidSigmoid ? 1.f / (1.f + exp2f(lshift - a)) : exp2f(a - lshift);
   const float c = fresh ? 0.f : *c_ptr;     // a fresh key: no demand yet, whatever the buffer holds
   *c_ptr = c + p;
   if (MODE == kSweepDilution || share_step == kShareInclusive) return p / (c + p + eps);
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
                                                    float* __restrict__ pout,
                                                    float* __restrict__ psum,
                                                    const T* __restrict__ vnew, T* __restrict__ vc_out,
-                                                   int bid, int share_step) {
+                                                   int bid, int share_step, float lshift) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   const int64_t n = blockIdx.y;
   const int nch = gridDim.x;
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (key < k1) {
       share = key_share<MODE>(aff[n * stride + key], gmax, rinv, eps, committed + n * cap + key, false, bid,
-                              share_step);
+                              share_step, lshift);
       ssh += share;
     }
 #pragma unroll
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (lane == 0) {
       share = key_share<MODE>(aff[n * stride + len - 1], gmax, rinv, eps, committed + n * cap + len - 1, true,
-                              bid, share_step);
+                              bid, share_step, lshift);
       ssh += share;
     }
     share = __shfl_sync(0xffffffffu, share, 0);

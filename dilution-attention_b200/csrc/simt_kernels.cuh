@@ -235,23 +235,29 @@ __device__ __forceinline__ void accum_tile(const float* A, const float* B, float
 
 // Row statistics of local rows [ib*64, ib*64+64) into shared arrays (rinv = 1/rden;
 // both zero for rows past tq so that their p is exactly zero).
-// The sigmoid bid has no row statistics (kernels_bid.py:259-262): null pointers, unused values.
+// A bid without a row sum has no row statistics (kernels_bid.py:259-262): null pointers, and
+// every row's exponent is log2 of the shift.
 __device__ __forceinline__ void load_stats(float* sM, float* sRinv, const float* rmax,
-                                           const float* rden, int64_t n, int ib, int tq) {
+                                           const float* rden, int64_t n, int ib, int tq, float lshift) {
   if (threadIdx.x < TS) {
     const int i = ib * TS + threadIdx.x;
-    const bool ok = i < tq && rmax != nullptr;
-    sM[threadIdx.x] = ok ? rmax[n * tq + i] : 0.f;
-    sRinv[threadIdx.x] = ok ? 1.f / rden[n * tq + i] : 0.f;
+    const bool ok = i < tq;
+    if (rmax != nullptr) {
+      sM[threadIdx.x] = ok ? rmax[n * tq + i] : 0.f;
+      sRinv[threadIdx.x] = ok ? 1.f / rden[n * tq + i] : 0.f;
+    } else {
+      sM[threadIdx.x] = lshift;
+      sRinv[threadIdx.x] = ok ? 1.f : 0.f;
+    }
   }
 }
 
-// The bid of one raw score (kernels_bid.py:191-197): softmax from the row statistics, or the
-// element-wise sigmoid of the scaled score.
+// The bid of one raw score (kernels_bid.py:191-204): softmax from the row statistics, or the
+// element-wise sigmoid of the scaled score (m = log2 of the shift, 0 for the plain sigmoid).
 template <bool MMA>
 __device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv) {
   const float z = score * g.zscale;
-  return g.bid == kBidSigmoid ? recip<MMA>(1.f + pow2<MMA>(-z)) : pow2<MMA>(z - m) * rinv;
+  return g.bid == kBidSigmoid ? recip<MMA>(1.f + pow2<MMA>(m - z)) : pow2<MMA>(z - m) * rinv;
 }
 
 __device__ __forceinline__ int first_query_block(int jb, int q_off) {
@@ -349,7 +355,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
@@ -398,7 +404,7 @@ __global__ void __launch_bounds__(NT) main_kernel(
   const int64_t n = blockIdx.x % g.n;
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
   load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-  load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+  load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
 
   float acc_o[4][DC], acc_pk[4][DC];
 #pragma unroll
@@ -562,7 +568,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
     load_tile<float, D, MMA>(sDO, dout + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
       const bool ok = i < g.tq;
@@ -642,7 +648,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       sufk += (sSeg[4 * TS + col] + sSeg[5 * TS + col]) + (sSeg[6 * TS + col] + sSeg[7 * TS + col]);
     }
     __syncthreads();
-    if (g.bid == kBidSoftmax) {   // ghat: the row-normalised bid's Jacobian term; none for the sigmoid
+    if (g.normalised) {   // ghat: the row-normalised bid's Jacobian term
       float gs = 0.f;
 #pragma unroll
       for (int c = 0; c < 16; ++c) gs += sDS[row * SL + part * 16 + c];
@@ -709,7 +715,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq);
+    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
       sG[threadIdx.x] = i < g.tq ? ghat[n * g.tq + i] : 0.f;

@@ -173,15 +173,16 @@ __device__ __forceinline__ uint32_t share_chunk_offset(int key, int q) {
 }
 
 // log2-domain log-sum-exp of query i (+inf past the end, so that its p is 0).  The sigmoid bid
-// has no row statistics: its "lse" is 0 for a query that exists and +inf past the end.
+// and the shifted bids have no row statistics: their "lse" is log2 of the shift (0 for the plain
+// sigmoid) for a query that exists and +inf past the end.
 template <int BID = kBidSoftmax>
 __device__ __forceinline__ float load_lse(const float* __restrict__ rmax, const float* __restrict__ rden,
-                                          int64_t row_base, int i, int tq) {
-  if (BID == kBidSigmoid) return i < tq ? 0.f : INFINITY;
+                                          int64_t row_base, int i, int tq, float lshift = 0.f) {
+  if (BID == kBidSigmoid || rmax == nullptr) return i < tq ? lshift : INFINITY;   // no row statistics
   return i < tq ? rmax[row_base + i] + log2f(rden[row_base + i]) : INFINITY;
 }
 
-// The bid of one raw score s (kernels_bid.py:191-197) given the row's lse l:
+// The bid of one raw score s (kernels_bid.py:191-204) given the row's lse l:
 // softmax 2^(s*zscale - l); sigmoid 1 / (1 + 2^(l - s*zscale)), which is 0 for l = +inf.
 template <int BID>
 __device__ __forceinline__ float bid_p(float s, float zscale, float l) {
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 128);
-  if (nib > 0 && wg == 0) sL[row] = load_lse<BID>(rmax, rden, row_base, ib0 * kTileRows + row, g.tq);
+  if (nib > 0 && wg == 0) sL[row] = load_lse<BID>(rmax, rden, row_base, ib0 * kTileRows + row, g.tq, g.lshift);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -400,7 +401,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     __syncwarp();
     // while the MMA runs: next tile's statistics, and the checkpoints of the previous tile
     float lse_next = 0.f;
-    if (wg == 1 && it + 1 < nib) lse_next = load_lse<BID>(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq);
+    if (wg == 1 && it + 1 < nib) lse_next = load_lse<BID>(rmax, rden, row_base, (ib + 1) * kTileRows + row, g.tq, g.lshift);
     if (wg == 0 && it > 0) store_checkpoints(ib - 1, sCs[((it - 1) & 1) * 128 + row]);
     mbar_wait(sdone, it & 1, ctl, &g_status, kErrWaitMma);
     tc_fence_after();
@@ -508,7 +509,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(&ctl->tmem), 256);
-  if (wg == 0) sL[row] = load_lse<BID>(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq);
+  if (wg == 0) sL[row] = load_lse<BID>(rmax, rden, (int64_t)n * g.tq, ib * kTileRows + row, g.tq, g.lshift);
   else {
 #pragma unroll
     for (int c = 0; c < 8; ++c)
@@ -777,7 +778,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
   auto load_stats = [&](int ib) {
     const int i = ib * kTileRows + row;
     float2 st = make_float2(INFINITY, 0.f);
-    if (i < g.tq) st = make_float2(load_lse<BID>(rmax, rden, row_base, i, g.tq), dbarp[row_base + i]);
+    if (i < g.tq) st = make_float2(load_lse<BID>(rmax, rden, row_base, i, g.tq, g.lshift), dbarp[row_base + i]);
     return st;
   };
 
@@ -1001,11 +1002,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
       const bool fetch_stats = !odd && wg == 0 && s + 1 < nsteps;
       if (fetch_stats) {
         const int i = (ib - 1) * kTileRows + row;     // ib >= 1 here, so i < tq
-        if (BID == kBidSoftmax) {
+        if (BID == kBidSoftmax && rmax != nullptr) {
           st_max = rmax[row_base + i];
           st_den = rden[row_base + i];
         } else {
-          st_max = 0.f;                               // no row statistics: lse = 0 + log2(1)
+          st_max = g.lshift;                          // no row statistics: lse = log2(shift) + log2(1)
         }
         st_dbar = dbarp[row_base + i];
       }
@@ -1078,7 +1079,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
           // Exclusive share step (inv = 1/(committed+eps)): the direct term is w itself, so
           // dp = w + (suffix BEFORE this query); no share step: dp = ds, no suffix at all.
           // The Jacobian factor is p for the softmax bid and p(1-p) for the sigmoid
-          // (kernels_bid.py:194-196, 735-754); vs keeps it for the later suffix fix-up.
+          // (kernels_bid.py:196-204, 735-754); vs keeps it for the later suffix fix-up.
 #pragma unroll
           for (int h = 1; h >= 0; --h) {
             const int e = e4 * 4 + 2 * h;
@@ -1579,7 +1580,7 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   }
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
-  if (g.bid == kBidSigmoid) {
+  if (!g.normalised) {
     // no row normalisation in the bid: no Jacobian correction, dk and dq are dk_main and dq_main
     const int64_t n4 = rows * kHeadDim / 4;
     mark("tc_cast_dk_dq", st, 0);

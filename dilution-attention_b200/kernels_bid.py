@@ -3,16 +3,18 @@ selectable bid function and share step (kernels_bid.py:1-43), the module the ref
 model binds instead of `dilution.kernels` whenever its configuration selects an ablation
 (model.py:142-156).
 
-    bid           "softmax"  p = causal softmax of the scaled scores       (the operator)
-                  "sigmoid"  p = sigmoid of the scaled score, element-wise, no row sum
+    bid           "softmax"   p = causal softmax of the scaled scores       (the operator)
+                  "sigmoid"   p = sigmoid of the scaled score, element-wise, no row sum
+                  "expshift"  p = exp(a) / shift: softmax's exponential without the row sum
+                  "sigshift"  p = exp(a) / (exp(a) + shift) = sigmoid(a - log shift)
     share_cumsum  True         share = p / (committed + p + eps)           (the operator)
                   "exclusive"  share = p / (committed + eps): earlier queries' demand only
                   False        no share step: out = p v / rowsum(p)
 
 Same entry points and keyword arguments as the reference module (`bid`, `share_cumsum`,
-`shift` after the arguments of `dilution.kernels`); `shift` only matters to bids that are not
-built here.  The six other bid functions of the reference (relu, relu2, softplus, minshift,
-expshift, sigshift) raise ValueError.  The operator itself (softmax, True) is handed to
+`shift` after the arguments of `dilution.kernels`); `shift` is read by the two shifted bids only
+(the model passes its context length, model.py:152-156).  The four bid functions of the reference
+that divide by a row sum of their own (relu, relu2, softplus, minshift) raise ValueError.  The operator itself (softmax, True) is handed to
 `kernels.py`; every other combination goes through the C ABI's dilution_variant_* calls: the
 tcgen05 kernels instantiated for the bid and share step for bf16 tensors of head_dim 64 under
 "bf16", the fp32 tile kernels otherwise (fp32 FMAs for "ieee", tf32 tensor-core products else).
@@ -30,7 +32,7 @@ from . import kernels as K
 EPS = K.EPS
 HAS_TRITON = False
 BID_TYPES = ("softmax", "relu", "relu2", "softplus", "minshift", "sigmoid", "expshift", "sigshift")
-BUILT_BIDS = ("softmax", "sigmoid")
+BUILT_BIDS = ("softmax", "sigmoid", "expshift", "sigshift")
 
 _resolve_precision = K._resolve_precision
 
@@ -57,8 +59,8 @@ def _is_operator(bid: str, share_cumsum) -> bool:
     return bid == "softmax" and _share_code(share_cumsum) == 1
 
 
-def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget_gib=16.0, keep_carry=False,
-                     need_total=True):
+def _variant_forward(q, k, v, dot_precision, bid, share, shift, save_pk, scratch_budget_gib=16.0,
+                     keep_carry=False, need_total=True):
     """All forward passes of one call, (batch*head) rows in slabs under the scratch budget unless
     the checkpoints are kept for a backward.  Without a share step nothing reads the checkpoints:
     unless the demand totals are asked for, the column-sum pass is skipped altogether."""
@@ -66,7 +68,7 @@ def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget
     (qf, kf, vf), code, prec, n = K._prepare(q, k, v, dot_precision)
     batch, heads, seq, head_dim = q.shape
     f32 = dict(device=q.device, dtype=torch.float32)
-    stats = bid == _lib.BID["softmax"]
+    stats = bid == _lib.BID["softmax"]     # the only built bid with row statistics
     out = torch.empty(n, seq, head_dim, **f32)
     ssum = torch.empty(n, seq, **f32)
     scan = share != 0 or need_total
@@ -86,7 +88,7 @@ def _variant_forward(q, k, v, dot_precision, bid, share, save_pk, scratch_budget
         b = min(a + rows, n)
         _lib.check(lib.dilution_variant_forward(
             qf[a:b].data_ptr(), kf[a:b].data_ptr(), vf[a:b].data_ptr(), code, prec, b - a, seq, head_dim,
-            scale, EPS, bid, share, part(rmax, a, b), part(rden, a, b), K._ptr(carry), part(total, a, b),
+            scale, EPS, bid, share, float(shift), part(rmax, a, b), part(rden, a, b), K._ptr(carry), part(total, a, b),
             out[a:b].data_ptr(), ssum[a:b].data_ptr(), part(pk, a, b), st), "dilution_variant_forward")
     return out, dict(rmax=rmax, rden=rden, carry=carry, ssum=ssum, pk=pk, total=total)
 
@@ -118,8 +120,8 @@ def dilution_attention_forward(
             res[1].update(bid=bid, share_cumsum=share_cumsum, shift=shift)
         return res
     batch, heads, seq, head_dim = q.shape
-    out, aux = _variant_forward(q, k, v, dot_precision, code_b, code_s, save_pk=False, keep_carry=return_aux,
-                                need_total=return_aux)
+    out, aux = _variant_forward(q, k, v, dot_precision, code_b, code_s, shift, save_pk=False,
+                                keep_carry=return_aux, need_total=return_aux)
     result = out.reshape(batch, heads, seq, head_dim)
     if return_aux:
         return result, dict(rmax=aux["rmax"], rden=aux["rden"], carry=aux["carry"], ssum=aux["ssum"],
@@ -134,11 +136,11 @@ class _VariantFn(torch.autograd.Function):
     input dtypes."""
 
     @staticmethod
-    def forward(ctx, q, k, v, dot_precision, bid, share):
+    def forward(ctx, q, k, v, dot_precision, bid, share, shift):
         training = any(ctx.needs_input_grad[:3])
-        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, save_pk=training, keep_carry=True,
+        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, shift, save_pk=training, keep_carry=True,
                                     need_total=False)
-        ctx.args = (dot_precision, bid, share)
+        ctx.args = (dot_precision, bid, share, shift)
         stats = [x for x in (aux["rmax"], aux["rden"], aux["pk"]) if x is not None]
         ctx.n_stats = len(stats)
         scan = [x for x in (aux["carry"], aux["total"]) if x is not None]
@@ -152,7 +154,7 @@ class _VariantFn(torch.autograd.Function):
         carry, total = rest[:2] if ctx.n_scan == 2 else (None, None)
         stats = rest[ctx.n_scan:]
         rmax, rden, pk = stats if ctx.n_stats == 3 else (None, None, None)
-        dot_precision, bid, share = ctx.args
+        dot_precision, bid, share, shift = ctx.args
         lib = _lib.load()
         batch, heads, seq, head_dim = q.shape
         (qf, kf, vf), code, prec, n = K._prepare(q, k, v, dot_precision)
@@ -163,12 +165,12 @@ class _VariantFn(torch.autograd.Function):
                               dtype=torch.uint8)
         _lib.check(lib.dilution_variant_backward(
             qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, seq, head_dim, 1.0 / math.sqrt(head_dim),
-            EPS, bid, share, dof.data_ptr(), out.data_ptr(), K._ptr(rmax), K._ptr(rden), K._ptr(carry),
+            EPS, bid, share, float(shift), dof.data_ptr(), out.data_ptr(), K._ptr(rmax), K._ptr(rden), K._ptr(carry),
             K._ptr(total), ssum.data_ptr(), K._ptr(pk), scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             K._stream(q.device)), "dilution_variant_backward")
         shape4 = (batch, heads, seq, head_dim)
         return (dq.reshape(shape4).to(q.dtype), dk.reshape(shape4).to(k.dtype), dv.reshape(shape4).to(v.dtype),
-                None, None, None)
+                None, None, None, None)
 
 
 def dilution_attention(
@@ -194,7 +196,7 @@ def dilution_attention(
     _resolve_precision(dot_precision)
     if _is_operator(bid, share_cumsum):
         return K.dilution_attention(q, k, v, dot_precision=dot_precision)
-    return _VariantFn.apply(q, k, v, dot_precision, code_b, code_s)
+    return _VariantFn.apply(q, k, v, dot_precision, code_b, code_s, shift)
 
 
 def dilution_attention_reference(q, k, v, bid: str = "softmax", share_cumsum=True, shift: float = 1.0):
@@ -203,7 +205,7 @@ def dilution_attention_reference(q, k, v, bid: str = "softmax", share_cumsum=Tru
     code_b, code_s = _bid_code(bid), _share_code(share_cumsum)
     if _is_operator(bid, share_cumsum):
         return K.dilution_attention_reference(q, k, v)
-    return _VariantFn.apply(q.float(), k.float(), v.float(), "ieee", code_b, code_s)
+    return _VariantFn.apply(q.float(), k.float(), v.float(), "ieee", code_b, code_s, shift)
 
 
 def dilution_decode_step(
@@ -239,7 +241,8 @@ def dilution_decode_step(
     _lib.check(lib.dilution_variant_decode(
         qf.data_ptr(), None, None, k_cache.view(n, capacity, head_dim).data_ptr(),
         v_cache.view(n, capacity, head_dim).data_ptr(), code, n, capacity, length, head_dim,
-        1.0 / math.sqrt(head_dim), EPS, code_b, code_s, committed.view(n, capacity).data_ptr(), out.data_ptr(),
+        1.0 / math.sqrt(head_dim), EPS, code_b, code_s, float(shift), committed.view(n, capacity).data_ptr(),
+        out.data_ptr(),
         scratch.data_ptr(), K._stream(q1.device)), "dilution_variant_decode")
     return out.view(batch, heads, 1, head_dim)
 

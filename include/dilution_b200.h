@@ -50,7 +50,8 @@ extern "C" {
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
 enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */
-enum { DILUTION_BID_SOFTMAX = 0, DILUTION_BID_SIGMOID = 5 };        /* bid codes of kernels_bid.py:94 */
+enum { DILUTION_BID_SOFTMAX = 0, DILUTION_BID_SIGMOID = 5, DILUTION_BID_EXPSHIFT = 6,
+       DILUTION_BID_SIGSHIFT = 7 };                                 /* bid codes of kernels_bid.py:84 */
 enum { DILUTION_SHARE_NONE = 0, DILUTION_SHARE_INCLUSIVE = 1, DILUTION_SHARE_EXCLUSIVE = 2 }; /* kernels_bid.py:123-127 */
 enum {
   DILUTION_OK = 0,
@@ -262,12 +263,17 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * three more arguments):
  *   bid    DILUTION_BID_SOFTMAX  p = causal softmax of the scaled scores (the operator);
  *          DILUTION_BID_SIGMOID  p = sigmoid of the scaled score, element-wise, no row
- *                                statistics and no Jacobian correction (kernels_bid.py:194-196);
+ *                                statistics and no Jacobian correction (kernels_bid.py:196-198);
+ *          DILUTION_BID_EXPSHIFT p = exp(a) / shift, softmax's exponential without the row sum
+ *                                (kernels_bid.py:199-201);
+ *          DILUTION_BID_SIGSHIFT p = exp(a) / (exp(a) + shift) = sigmoid(a - log shift)
+ *                                (kernels_bid.py:202-204); `shift` > 0 is read by these two only
+ *                                (the model passes its context length, model.py:152-156);
  *   share  INCLUSIVE  share = p / (committed + p + eps)   (the operator);
  *          EXCLUSIVE  share = p / (committed + eps)       (earlier queries' demand only);
  *          NONE       share = p                           (no share step: out = p v / rowsum p).
- * The other bid functions of kernels_bid.py (relu, relu2, softplus, minshift, expshift,
- * sigshift) are not built: DILUTION_ERR_UNSUPPORTED.  bf16 tensors of head_dim 64 under
+ * The bid functions of kernels_bid.py that divide by a row sum of their own (relu, relu2,
+ * softplus, minshift) are not built: DILUTION_ERR_UNSUPPORTED.  bf16 tensors of head_dim 64 under
  * DILUTION_PREC_BF16 run on the tcgen05 kernels, instantiated for the bid and share step;
  * every other dtype, precision and head_dim on the fp32 tile kernels (IEEE: fp32 FMAs;
  * otherwise tf32 tensor-core products).  Checkpoints every DILUTION_CARRY_ROWS query rows.
@@ -286,17 +292,17 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * written them; committed advances by p in place for every variant; scratch of
  * dilution_decode_scratch_bytes(n, length, d). */
 int dilution_variant_forward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
-                             int64_t t, int d, float scale, float eps, int bid, int share, float* rmax,
+                             int64_t t, int d, float scale, float eps, int bid, int share, float shift, float* rmax,
                              float* rden, float* carry, float* total, float* out, float* ssum, float* pk,
                              void* stream);
 int dilution_variant_backward(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
-                              int64_t t, int d, float scale, float eps, int bid, int share, const float* dout,
+                              int64_t t, int d, float scale, float eps, int bid, int share, float shift, const float* dout,
                               const float* out, const float* rmax, const float* rden, const float* carry,
                               const float* total, const float* ssum, const float* pk, void* scratch, void* dq,
                               void* dk, void* dv, void* stream);
 int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
                             int dtype, int64_t n, int64_t capacity, int64_t length, int d, float scale,
-                            float eps, int bid, int share, float* committed, void* out, void* scratch,
+                            float eps, int bid, int share, float shift, float* committed, void* out, void* scratch,
                             void* stream);
 
 #ifdef __cplusplus

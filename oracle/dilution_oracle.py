@@ -2,8 +2,8 @@
 
 This module is a plain restatement, on the CPU, of the reference operator in
 `src/dilution/kernels.py:40-68` (the fp32 spec `dilution_attention_reference`),
-of its bid / share variants in `src/dilution/kernels_bid.py:94-166` (softmax and
-sigmoid bids; inclusive, exclusive and absent share step) and of the eager
+of its bid / share variants in `src/dilution/kernels_bid.py:94-166` (softmax,
+sigmoid, expshift and sigshift bids; inclusive, exclusive and absent share step) and of the eager
 cached-decode step in `src/dilution/model.py:242-257`.  Only
 the test-suite, the smoke check and the CPU-baseline leg of the benchmark may
 import it; the product path never does, and it raises when the CUDA library is
@@ -257,25 +257,30 @@ def decode_step(q1, k_cache, v_cache, committed, length: int) -> torch.Tensor:
     return y
 
 
-def variant_bids(q, k, bid: str = "softmax") -> torch.Tensor:
-    """Bids under a selectable bid function, the two branches of bids_from_affinity this build
-    covers (kernels_bid.py:94-102): "softmax" as kernels.py:60-64, "sigmoid" element-wise with
-    zeros outside the causal window.  (..., T, T) fp32."""
+def variant_bids(q, k, bid: str = "softmax", shift: float = 1.0) -> torch.Tensor:
+    """Bids under a selectable bid function, the four branches of bids_from_affinity this build
+    covers (kernels_bid.py:94-104): "softmax" as kernels.py:60-64; "sigmoid", "expshift"
+    (exp(a) / shift) and "sigshift" (sigmoid(a - log shift)) element-wise with zeros outside the
+    causal window.  (..., T, T) fp32."""
     seq, head_dim = q.shape[-2], q.shape[-1]
     aff = (q.float() @ k.float().transpose(-2, -1)) / math.sqrt(head_dim)        # kernels_bid.py:153
     causal = torch.tril(torch.ones(seq, seq, dtype=torch.bool))                  # :154
     if bid == "softmax":
-        return aff.masked_fill(~causal, torch.finfo(torch.float32).min).softmax(dim=-1)   # :98-99
+        return aff.masked_fill(~causal, torch.finfo(torch.float32).min).softmax(dim=-1)   # :97-98
     if bid == "sigmoid":
-        return torch.sigmoid(aff).masked_fill(~causal, 0.0)                      # :100-101
-    raise ValueError("the oracle restates the softmax and sigmoid bids only")
+        return torch.sigmoid(aff).masked_fill(~causal, 0.0)                      # :99-100
+    if bid == "expshift":
+        return (torch.exp(aff) / float(shift)).masked_fill(~causal, 0.0)         # :101-102
+    if bid == "sigshift":
+        return torch.sigmoid(aff - math.log(float(shift))).masked_fill(~causal, 0.0)   # :103-104
+    raise ValueError("the oracle restates the softmax, sigmoid, expshift and sigshift bids only")
 
 
-def variant_dense(q, k, v, bid: str = "softmax", share_cumsum=True) -> torch.Tensor:
+def variant_dense(q, k, v, bid: str = "softmax", share_cumsum=True, shift: float = 1.0) -> torch.Tensor:
     """The operator with a selectable bid and share step, as the dense spec of
     kernels_bid.py:152-166: share_cumsum True (inclusive, the operator), "exclusive"
     (earlier queries' demand only) or False (no share step).  Differentiable by autograd."""
-    p = variant_bids(q, k, bid)                                                  # :155
+    p = variant_bids(q, k, bid, shift)                                           # :155
     if not share_cumsum:
         return (p / p.sum(dim=-1, keepdim=True)) @ v.float()                     # :156-157
     committed = p.cumsum(dim=-2) - p                                             # :158
@@ -287,15 +292,16 @@ def variant_dense(q, k, v, bid: str = "softmax", share_cumsum=True) -> torch.Ten
     return attn @ v.float()                                                      # :164
 
 
-def variant_backward(q, k, v, dout, bid: str = "softmax", share_cumsum=True):
+def variant_backward(q, k, v, dout, bid: str = "softmax", share_cumsum=True, shift: float = 1.0):
     """out, dq, dk, dv by autograd through `variant_dense`."""
     qs, ks, vs = (t.detach().clone().float().requires_grad_(True) for t in (q, k, v))
-    out = variant_dense(qs, ks, vs, bid, share_cumsum)
+    out = variant_dense(qs, ks, vs, bid, share_cumsum, shift)
     out.backward(dout.float())
     return out.detach(), qs.grad, ks.grad, vs.grad
 
 
-def variant_decode_step(q1, k_cache, v_cache, committed, length: int, bid: str = "softmax", share_cumsum=True):
+def variant_decode_step(q1, k_cache, v_cache, committed, length: int, bid: str = "softmax", share_cumsum=True,
+                        shift: float = 1.0):
     """One cached decode step under a bid / share variant: the maths of the reference's decode
     kernel (kernels_bid.py:905-950), which is the eager step of model.py:242-257 except that
     with no share step the kernel still divides by the row sum of the bids (:948) where the
@@ -306,7 +312,12 @@ def variant_decode_step(q1, k_cache, v_cache, committed, length: int, bid: str =
     v = v_cache[:, :, :length].float()
     c = committed[:, :, :length]
     aff = (q1.float() @ k.transpose(-2, -1)).squeeze(2) / math.sqrt(head_dim)   # :873, :887
-    p = aff.softmax(dim=-1) if bid == "softmax" else torch.sigmoid(aff)         # :913-916
+    if bid == "softmax":                                                         # :913-920
+        p = aff.softmax(dim=-1)
+    elif bid == "expshift":
+        p = torch.exp(aff) / float(shift)
+    else:
+        p = torch.sigmoid(aff - (math.log(float(shift)) if bid == "sigshift" else 0.0))
     if share_cumsum == "exclusive":
         share = p / (c + EPS)                                                   # :937-938
     elif share_cumsum:

@@ -77,7 +77,9 @@ def _device_status_is_clean(request):
 # The bid / share ablations stored in tests/golden/variants_b1h2t80d32.npz (key prefix, bid, share_cumsum).
 VARIANTS = [("softmax_exclusive", "softmax", "exclusive"), ("softmax_none", "softmax", False),
             ("sigmoid_inclusive", "sigmoid", True), ("sigmoid_exclusive", "sigmoid", "exclusive"),
-            ("sigmoid_none", "sigmoid", False)]
+            ("sigmoid_none", "sigmoid", False), ("expshift_inclusive", "expshift", True),
+            ("sigshift_inclusive", "sigshift", True), ("sigshift_none", "sigshift", False)]
+SHIFT = 80.0      # the divisor of the shifted bids in that fixture; the other bids ignore it
 
 
 def variant_case(key):

@@ -19,7 +19,8 @@ Fixture layout (all fp32 unless noted):
                        (bf16 and fp32 inputs) and softmax-attention rows
                        (F.scaled_dot_product_attention, is_causal) for the same q, k, v
   variants_b1h2t80d32.npz  the bid / share ablations of src/dilution/kernels_bid.py:130-166
-                       ("softmax" / "sigmoid" bids x inclusive / "exclusive" / no share step):
+                       ("softmax" / "sigmoid" / "expshift" / "sigshift" bids x inclusive / "exclusive" /
+                       no share step, shift 80):
                        q, k, v, dout and per variant out, dq, dk, dv and demand (= p.sum(-2))
 
 `--only variants` writes just the last one.
@@ -61,7 +62,8 @@ def ref_fwd_bwd(ref, q, k, v, dout):
 
 
 VARIANTS = [("softmax", "exclusive"), ("softmax", False), ("sigmoid", True), ("sigmoid", "exclusive"),
-            ("sigmoid", False)]
+            ("sigmoid", False), ("expshift", True), ("sigshift", True), ("sigshift", False)]
+SHIFT = 80.0      # the shifted bids' divisor: the model passes its context length (model.py:152-156)
 
 
 def variant_key(bid, share):
@@ -72,12 +74,12 @@ def make_variants():
     from dilution.kernels_bid import bids_from_affinity, dilution_attention_reference as ref_bid
     b, h, t, d = 1, 2, 80, 32
     q, k, v, dout = make_inputs(b, h, t, d, 7070)
-    data = dict(q=q.numpy(), k=k.numpy(), v=v.numpy(), dout=dout.numpy())
+    data = dict(q=q.numpy(), k=k.numpy(), v=v.numpy(), dout=dout.numpy(), shift=np.array(SHIFT))
     aff = (q @ k.transpose(-2, -1)) / math.sqrt(d)
     causal = torch.ones(t, t, dtype=torch.bool).tril()
     for bid, share in VARIANTS:
-        out, dq, dk, dv = ref_fwd_bwd(lambda a, b_, c: ref_bid(a, b_, c, bid=bid, share_cumsum=share), q, k, v, dout)
-        p = bids_from_affinity(aff, causal, bid)
+        out, dq, dk, dv = ref_fwd_bwd(lambda a, b_, c: ref_bid(a, b_, c, bid=bid, share_cumsum=share, shift=SHIFT), q, k, v, dout)
+        p = bids_from_affinity(aff, causal, bid, SHIFT)
         for name, x in dict(out=out, dq=dq, dk=dk, dv=dv, demand=p.sum(-2)).items():
             data[f"{variant_key(bid, share)}_{name}"] = x.numpy()
     np.savez(os.path.join(HERE, "variants_b1h2t80d32.npz"), **data)

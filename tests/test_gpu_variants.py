@@ -12,7 +12,7 @@ import sys
 import pytest
 import torch
 
-from conftest import ROOT, VARIANTS, load_package, make_inputs, rel_err, variant_case
+from conftest import ROOT, SHIFT, VARIANTS, load_package, make_inputs, rel_err, variant_case
 from oracle import dilution_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -43,7 +43,7 @@ def check_grads(share, got, want, tol):
 def test_goldens_forward_and_backward_fp32(KB, key, bid, share):
     c = variant_case(key)
     qs, ks, vs = (c[n].to(DEV).requires_grad_(True) for n in "qkv")
-    out = KB.dilution_attention(qs, ks, vs, dot_precision="ieee", bid=bid, share_cumsum=share)
+    out = KB.dilution_attention(qs, ks, vs, dot_precision="ieee", bid=bid, share_cumsum=share, shift=SHIFT)
     out.backward(c["dout"].to(DEV))
     assert out.dtype == torch.float32 and rel_err(out.detach().cpu(), c["out"]) < 1e-4
     check_grads(share, (qs.grad, ks.grad, vs.grad), (c["dq"], c["dk"], c["dv"]), 1e-4)
@@ -53,23 +53,23 @@ def test_goldens_forward_and_backward_fp32(KB, key, bid, share):
 def test_reference_signature_and_demand_totals(KB, key, bid, share):
     c = variant_case(key)
     q, k, v = (c[n].to(DEV) for n in "qkv")
-    out = KB.dilution_attention_reference(q, k, v, bid=bid, share_cumsum=share)
+    out = KB.dilution_attention_reference(q, k, v, bid=bid, share_cumsum=share, shift=SHIFT)
     assert rel_err(out.cpu(), c["out"]) < 1e-4
-    out2, aux = KB.dilution_attention_forward(q, k, v, return_aux=True, bid=bid, share_cumsum=share)
+    out2, aux = KB.dilution_attention_forward(q, k, v, return_aux=True, bid=bid, share_cumsum=share, shift=SHIFT)
     assert rel_err(out2.cpu(), c["out"]) < 1e-4
     assert rel_err(aux["committed_total"].cpu(), c["demand"]) < 1e-5
     assert aux["bid"] == bid and aux["share_cumsum"] == share
-    assert (aux["rmax"] is None) == (bid == "sigmoid")
+    assert (aux["rmax"] is None) == (bid != "softmax")
 
 
 @pytest.mark.parametrize("key,bid,share", VARIANTS)
 @pytest.mark.parametrize("seq,head_dim", [(257, 64), (700, 32), (130, 128)])
 def test_ragged_lengths_against_oracle(KB, key, bid, share, seq, head_dim):
     q, k, v, dout = make_inputs(2, 2, seq, head_dim, 300 + seq)
-    ref, rdq, rdk, rdv = O.variant_backward(q, k, v, dout, bid, share)
+    ref, rdq, rdk, rdv = O.variant_backward(q, k, v, dout, bid, share, SHIFT)
     for prec, tol in (("ieee", 1e-4), ("tf32", 5e-3)):
         qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
-        out = KB.dilution_attention(qs, ks, vs, dot_precision=prec, bid=bid, share_cumsum=share)
+        out = KB.dilution_attention(qs, ks, vs, dot_precision=prec, bid=bid, share_cumsum=share, shift=SHIFT)
         out.backward(dout.to(DEV))
         assert rel_err(out.detach().cpu(), ref) < tol, prec
         check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), tol)
@@ -79,9 +79,9 @@ def test_ragged_lengths_against_oracle(KB, key, bid, share, seq, head_dim):
 def test_bf16_tensors(KB, key, bid, share):
     q, k, v, dout = make_inputs(1, 3, 300, 64, 77, scales=(0.5, 0.5, 1.0, 1.0))
     qb, kb, vb = (x.bfloat16() for x in (q, k, v))
-    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share)
+    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share, SHIFT)
     qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
-    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share)
+    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share, shift=SHIFT)
     out.backward(dout.to(DEV))
     assert (out.detach().cpu() - ref).abs().max().item() < 2e-2
     assert qs.grad.dtype == ks.grad.dtype == vs.grad.dtype == torch.bfloat16
@@ -96,11 +96,11 @@ def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, s
     pkg = load_package()
     q, k, v, dout = make_inputs(2, 2, seq, 64, 31 + seq, scales=(0.5, 0.5, 1.0, 1.0))
     qb, kb, vb = (x.bfloat16() for x in (q, k, v))
-    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share)
+    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share, SHIFT)
     qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
     pkg._lib.profile(True)
     pkg._lib.profile_collect()
-    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share)
+    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share, shift=SHIFT)
     out.backward(dout.to(DEV))
     torch.cuda.synchronize()
     names = set(pkg._lib.profile_collect())
@@ -113,9 +113,9 @@ def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, s
     check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
     # forward only, with the demand totals
     out2, aux = KB.dilution_attention_forward(qs.detach(), ks.detach(), vs.detach(), dot_precision="bf16",
-                                              return_aux=True, bid=bid, share_cumsum=share)
+                                              return_aux=True, bid=bid, share_cumsum=share, shift=SHIFT)
     assert (out2.cpu() - ref).abs().max().item() < 2e-2
-    assert rel_err(aux["committed_total"].cpu(), O.variant_bids(qb.float(), kb.float(), bid).sum(-2)) < 2e-2
+    assert rel_err(aux["committed_total"].cpu(), O.variant_bids(qb.float(), kb.float(), bid, SHIFT).sum(-2)) < 2e-2
 
 
 def test_the_operator_itself_goes_to_the_production_kernels(KB):
@@ -153,8 +153,8 @@ def test_decode_steps_from_a_prefilled_cache(KB, key, bid, share, dtype, tol):
     q, k, v = (x.to(dtype) for x in (q, k, v))
     _, aux = KB.dilution_attention_forward(q[:, :, :prefix].to(DEV), k[:, :, :prefix].to(DEV), v[:, :, :prefix].to(DEV),
                                            dot_precision="ieee" if dtype == torch.float32 else "bf16",
-                                           return_aux=True, bid=bid, share_cumsum=share)
-    demand = O.variant_bids(q[:, :, :prefix], k[:, :, :prefix], bid).sum(-2)
+                                           return_aux=True, bid=bid, share_cumsum=share, shift=SHIFT)
+    demand = O.variant_bids(q[:, :, :prefix], k[:, :, :prefix], bid, SHIFT).sum(-2)
     assert rel_err(aux["committed_total"].cpu(), demand) < (1e-5 if dtype == torch.float32 else 2e-2)
     kc = torch.zeros(b, h, cap, d, dtype=dtype)
     vc = torch.zeros(b, h, cap, d, dtype=dtype)
@@ -165,8 +165,8 @@ def test_decode_steps_from_a_prefilled_cache(KB, key, bid, share, dtype, tol):
     for s in range(steps):
         length = prefix + s + 1
         q1 = q[:, :, length - 1:length]
-        want = O.variant_decode_step(q1, kc, vc, committed, length, bid, share)
-        got = KB.dilution_decode_step(q1.to(DEV), kd, vd, cd, length, bid=bid, share_cumsum=share)
+        want = O.variant_decode_step(q1, kc, vc, committed, length, bid, share, SHIFT)
+        got = KB.dilution_decode_step(q1.to(DEV), kd, vd, cd, length, bid=bid, share_cumsum=share, shift=SHIFT)
         assert got.dtype == dtype and got.shape == (b, h, 1, d)
         assert rel_err(got.float().cpu(), want) < tol, s
     assert rel_err(cd.cpu(), committed) < 1e-5
@@ -195,7 +195,7 @@ def test_variant_decode_appends_through_the_c_abi():
     scratch = torch.empty(lib.dilution_decode_scratch_bytes(n, length, d), device=DEV, dtype=torch.uint8)
     qd, k1, v1 = q1.reshape(n, d).to(DEV), k_new.reshape(n, d).to(DEV), v_new.reshape(n, d).to(DEV)
     L.check(lib.dilution_variant_decode(qd.data_ptr(), k1.data_ptr(), v1.data_ptr(), kd.data_ptr(), vd.data_ptr(),
-                                        L.F32, n, cap, length, d, d ** -0.5, 1e-9, L.BID["sigmoid"], 2,
+                                        L.F32, n, cap, length, d, d ** -0.5, 1e-9, L.BID["sigmoid"], 2, 1.0,
                                         cd.data_ptr(), out.data_ptr(), scratch.data_ptr(),
                                         torch.cuda.current_stream().cuda_stream), "dilution_variant_decode")
     assert rel_err(out.cpu().view(1, n, 1, d), want) < 1e-4
@@ -207,7 +207,7 @@ REF = os.path.join(ROOT, "baseline", "_ref")
 
 
 @pytest.mark.parametrize("bid,share", [("sigmoid", True), ("sigmoid", "exclusive"), ("softmax", "exclusive"),
-                                       ("softmax", False)])
+                                       ("softmax", False), ("sigshift", True), ("expshift", True)])
 def test_reference_model_with_a_variant_configuration(bid, share):
     """The unmodified DilutionLM configured with an ablation binds dilution.kernels_bid
     (model.py:145-156): after install() its kernel path runs here and must reproduce the eager

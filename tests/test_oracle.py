@@ -170,7 +170,7 @@ def test_rope_and_softmax_attention_match_reference_modules():
     assert torch.equal(sk, O.rope(k, 9, theta))
 
 
-from conftest import VARIANTS, variant_case  # noqa: E402
+from conftest import SHIFT, VARIANTS, variant_case  # noqa: E402
 
 
 @pytest.mark.parametrize("key,bid,share", VARIANTS)
@@ -178,11 +178,11 @@ def test_variants_match_reference_goldens(key, bid, share):
     """The bid / share restatements against kernels_bid.dilution_attention_reference and its
     autograd gradients (stored by tests/golden/make_golden.py)."""
     c = variant_case(key)
-    out, dq, dk, dv = O.variant_backward(c["q"], c["k"], c["v"], c["dout"], bid, share)
+    out, dq, dk, dv = O.variant_backward(c["q"], c["k"], c["v"], c["dout"], bid, share, SHIFT)
     assert rel_err(out, c["out"]) < 1e-5
     for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
         assert rel_err(got, c[name]) < 1e-4, name
-    assert rel_err(O.variant_bids(c["q"], c["k"], bid).sum(-2), c["demand"]) < 1e-6
+    assert rel_err(O.variant_bids(c["q"], c["k"], bid, SHIFT).sum(-2), c["demand"]) < 1e-6
 
 
 def test_variant_operator_is_the_operator():
@@ -199,7 +199,7 @@ def test_variant_decode_steps_reproduce_dense_rows(key, bid, share):
     q, k, v = c["q"], c["k"], c["v"]
     seq = q.shape[2]
     committed = torch.zeros(*q.shape[:2], seq)
-    rows = [O.variant_decode_step(q[:, :, t:t + 1], k, v, committed, t + 1, bid, share) for t in range(seq)]
+    rows = [O.variant_decode_step(q[:, :, t:t + 1], k, v, committed, t + 1, bid, share, SHIFT) for t in range(seq)]
     got = torch.cat(rows, dim=2)
     assert rel_err(got, c["out"]) < 1e-4
     assert rel_err(committed, c["demand"]) < 1e-5
