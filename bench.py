@@ -498,7 +498,9 @@ def run_ours(args):
     c = Ctx()
     K, L = c.K, c.L
     if args.only:
-        blocks = {"decode": run_decode, "prefill": run_prefill, "lm": run_lm}
+        blocks = {"decode": run_decode, "prefill": run_prefill, "lm": run_lm,
+                  "tile": lambda c_, a_: time_shapes(c_.K.dilution_attention, c_.dev, TILE_SHAPES, iters=3),
+                  "variants": lambda c_, a_: time_variants(c_.pkg.kernels_bid.dilution_attention, c_.dev, iters=3)}
         res = blocks[args.only](c, args)
         if c.rank == 0:
             print(json.dumps({args.only: res}), flush=True)
@@ -979,7 +981,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
-    ap.add_argument("--only", default=None, choices=["decode", "prefill", "lm"],
+    ap.add_argument("--only", default=None, choices=["decode", "prefill", "lm", "tile", "variants"],
                     help="run one block alone and print it")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
