@@ -88,3 +88,46 @@ def test_equal_area_bounds_balance_and_agree_with_oracle():
     b = P.equal_area_bounds(131072, 8)
     areas = [b[i + 1] ** 2 - b[i] ** 2 for i in range(8)]
     assert max(areas) / (sum(areas) / 8) < 1.03   # speed-up ceiling > 7.7x, not 4.27x
+
+
+def test_variant_codes_and_errors_follow_the_reference_module():
+    """kernels_bid.py:84-91, 123-127 of the reference: bid names, share codes, ValueError."""
+    KB = load_package().kernels_bid
+    assert KB.BID_TYPES == ("softmax", "relu", "relu2", "softplus", "minshift", "sigmoid", "expshift", "sigshift")
+    assert [KB._bid_code(b) for b in KB.BUILT_BIDS] == [KB.BID_TYPES.index(b) for b in KB.BUILT_BIDS]
+    assert KB._share_code(True) == 1 and KB._share_code(False) == 0 and KB._share_code("exclusive") == 2
+    with pytest.raises(ValueError, match="bid must be one of"):
+        KB._bid_code("tanh")
+    with pytest.raises(ValueError, match="not built"):
+        KB._bid_code("softplus")
+    q = torch.randn(1, 1, 8, 64)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):          # the variants have none either
+        KB.dilution_attention_forward(q, q, q, bid="sigmoid")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        KB.dilution_attention(q, q, q, dot_precision="ieee", bid="softmax", share_cumsum="exclusive")
+    with pytest.raises(ValueError, match="exactly one query row"):
+        KB.dilution_decode_step(torch.randn(1, 1, 2, 32), torch.zeros(1, 1, 8, 32), torch.zeros(1, 1, 8, 32),
+                                torch.zeros(1, 1, 8), 1, bid="sigmoid")
+
+
+def test_variant_install_keeps_the_module_s_own_code_for_unbuilt_bids():
+    """After install() a bid this backend does not build still reaches the module's original
+    function; the built ones reach this backend; uninstall() puts everything back."""
+    KB = load_package().kernels_bid
+    calls = []
+
+    def original(*args, bid="softmax", **kwargs):
+        calls.append(bid)
+        return "original"
+
+    fake = types.SimpleNamespace(HAS_TRITON=False, dilution_attention_forward=original,
+                                 dilution_attention=original, dilution_decode_step=original)
+    KB.install(fake)
+    assert fake.HAS_TRITON is True
+    assert fake.dilution_attention("q", "k", "v", bid="relu2") == "original" and calls == ["relu2"]
+    q = torch.randn(1, 1, 8, 64)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):          # a built bid: this backend, which needs CUDA
+        fake.dilution_attention_forward(q, q, q, bid="sigshift", shift=8.0)
+    assert calls == ["relu2"]
+    KB.uninstall(fake)
+    assert fake.dilution_attention is original and fake.HAS_TRITON is False
