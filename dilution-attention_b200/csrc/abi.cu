@@ -248,7 +248,8 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
     if (int rc = check_launch("backward_main")) return rc;
   }
   const int64_t total = rows * D;
-  if (g.normalised) {
+  const bool corrected = g.normalised && g.share != dil::kShareNone;   // without a share step ghat is identically 0
+  if (corrected) {
     auto kern = backward_dk_correction_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
     {
@@ -267,7 +268,7 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
   {
     Prof prof("dq_epilogue", st);
     dq_epilogue_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-        s.dq_main, s.ghat, g.normalised ? pk : nullptr, total, D, (T*)dq);
+        s.dq_main, s.ghat, corrected ? pk : nullptr, total, D, (T*)dq);
   }
   return check_launch("dq_epilogue");
 }
@@ -751,9 +752,11 @@ int dilution_variant_backward(const void* q, const void* k, const void* v, int d
   if (int rc = check_variant("dilution_variant_backward", bid, share, shift)) return rc;
   const bool stats = bid == dil::kBidSoftmax;
   if (!q || !k || !v || !dout || !out || !ssum || !scratch || !dq || !dk || !dv ||
-      (share != dil::kShareNone && (!carry || !total)) || (stats && (!rmax || !rden || !pk)))
+      (share != dil::kShareNone && (!carry || !total)) || (stats && (!rmax || !rden)) ||
+      (stats && share != dil::kShareNone && !pk))
     return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
-  if (!stats) rmax = rden = pk = nullptr;
+  if (!stats) rmax = rden = nullptr;
+  if (!stats || share == dil::kShareNone) pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share, shift);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;

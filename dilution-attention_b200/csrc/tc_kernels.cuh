@@ -1580,8 +1580,10 @@ inline int backward(const void* q, const void* k, const void* v, const Geom& g, 
   }
   mark("tc_backward_main", st, 1);
   if (int rc = launch_status("tc backward_main", err, errlen)) return rc;
-  if (!g.normalised) {
-    // no row normalisation in the bid: no Jacobian correction, dk and dq are dk_main and dq_main
+  if (!g.normalised || g.share == kShareNone) {
+    // no row normalisation in the bid: no Jacobian correction, dk and dq are dk_main and dq_main.
+    // Without a share step the correction of the softmax bid vanishes identically:
+    // ghat_i = sum_j p_ij (do_i.v_j - do_i.out_i) = do_i.out_i - do_i.out_i = 0 (out_i = sum_j p_ij v_j).
     const int64_t n4 = rows * kHeadDim / 4;
     mark("tc_cast_dk_dq", st, 0);
     cast_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk_main, (__nv_bfloat16*)dk, n4);

@@ -138,11 +138,15 @@ class _VariantFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, dot_precision, bid, share, shift):
         training = any(ctx.needs_input_grad[:3])
-        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, shift, save_pk=training, keep_carry=True,
-                                    need_total=False)
+        # without a share step the softmax bid's Jacobian correction is identically zero: no pk
+        out, aux = _variant_forward(q, k, v, dot_precision, bid, share, shift, save_pk=training and share != 0,
+                                    keep_carry=True, need_total=False)
         ctx.args = (dot_precision, bid, share, shift)
-        stats = [x for x in (aux["rmax"], aux["rden"], aux["pk"]) if x is not None]
+        stats = [x for x in (aux["rmax"], aux["rden"]) if x is not None]
         ctx.n_stats = len(stats)
+        ctx.has_pk = aux["pk"] is not None
+        if ctx.has_pk:
+            stats.append(aux["pk"])
         scan = [x for x in (aux["carry"], aux["total"]) if x is not None]
         ctx.n_scan = len(scan)
         ctx.save_for_backward(q, k, v, out, aux["ssum"], *scan, *stats)
@@ -153,7 +157,8 @@ class _VariantFn(torch.autograd.Function):
         q, k, v, out, ssum, *rest = ctx.saved_tensors
         carry, total = rest[:2] if ctx.n_scan == 2 else (None, None)
         stats = rest[ctx.n_scan:]
-        rmax, rden, pk = stats if ctx.n_stats == 3 else (None, None, None)
+        rmax, rden = stats[:2] if ctx.n_stats == 2 else (None, None)
+        pk = stats[-1] if ctx.has_pk else None
         dot_precision, bid, share, shift = ctx.args
         lib = _lib.load()
         batch, heads, seq, head_dim = q.shape

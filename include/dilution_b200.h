@@ -283,7 +283,8 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * (n, ceil(t/32), t); total (n, t) = column totals of p (the decode accumulator after this
  * prefix) — with DILUTION_SHARE_NONE carry and total may both be NULL and the column-sum
  * pass is skipped; out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
- * which dilution_variant_backward needs for the softmax bid.
+ * which dilution_variant_backward needs for the softmax bid with a share step (without one
+ * the softmax bid's Jacobian correction vanishes identically and pk is not read).
  * dilution_variant_backward: dq, dk, dv in the input dtype from an fp32 dout
  * (kernels_bid.py:731-815), given what the forward wrote; scratch of
  * dilution_backward_scratch_bytes(n, t, d).

@@ -108,7 +108,8 @@ def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, s
     assert {"tc_forward_main", "tc_backward_main"} <= names, names
     assert not any(n.startswith("simt_") for n in names), names
     assert ("tc_colsum_scan" in names) == (share is not False)      # nothing reads checkpoints without a share step
-    assert ("tc_rowstats_pk" in names) == (bid == "softmax")
+    assert ("tc_rowstats_pk" in names) == (bid == "softmax" and share is not False)
+    assert ("tc_backward_key_correction" in names) == (bid == "softmax" and share is not False)
     assert (out.detach().cpu() - ref).abs().max().item() < 2e-2
     check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
     # forward only, with the demand totals
