@@ -468,7 +468,7 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
     """Roofline block of the dominant kernel of the training step."""
     # algorithmic matmuls per kernel: the backward main pass carries all five backward products,
     # the forward main pass QK^T and share@V; the other passes are recomputation overhead
-    share = {"backward_main": 5, "forward_main": 2}
+    share = {"backward_main": 5, "forward_main": 2, "forward_fused": 2}
     dom = max(kernels_ms, key=kernels_ms.get) if kernels_ms else None
     if dom is None:
         return None
@@ -478,6 +478,7 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
     # ncu capture at T=4096 (64 rows, 528 causal 128x128 tiles per row: 1341.02 MB), scaled by the
     # number of causal tiles this launch processes -- the dQ tile reductions dominate it and grow
     # with the tile count.  Only the backward main pass has a captured figure.
+    executed = 11 if any("forward_fused" in name for name in kernels_ms) else 12
     tiles = n_rows * (T // 128) * (T // 128 + 1) // 2
     traffic = 1341.02e6 / (64 * 528) * tiles if "backward_main" in dom else None
     return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
@@ -486,12 +487,13 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
                               "128x128 tiles per launch; bytes",
             "peak_source": f"{peaks['source']} sustained bf16", "matmuls_in_kernel": mm,
             "step_frac_of_peak": value_per_gpu / peaks["tensor"],
-            # matmul-equivalents the tensor cores actually run per step: QK^T in the row,
-            # column-sum, main, reverse and key-correction passes (5), share@V, dO V^T, dV, dQ,
-            # dK (5), the pk product of the row pass and the key-correction product W Q (2);
-            # the ones columns that give row sums and ghat (N = 80 instead of 64) are not counted
-            "executed": {"matmuls_per_step": 12, "value": value_per_gpu * 12 / 7, "unit": "TFLOP/s",
-                         "frac": value_per_gpu * 12 / 7 / peaks["tensor"]}}
+            # matmul-equivalents the tensor cores actually run per step: QK^T in the row, key-
+            # stationary forward, reverse and key-correction passes (4; 5 when the forward runs as
+            # column-sum pass + main pass), share@V, dO V^T, dV, dQ, dK (5), the pk product of the
+            # row pass and the key-correction product W Q (2); the ones columns that give row sums
+            # and ghat (N = 80 instead of 64) are not counted
+            "executed": {"matmuls_per_step": executed, "value": value_per_gpu * executed / 7, "unit": "TFLOP/s",
+                         "frac": value_per_gpu * executed / 7 / peaks["tensor"]}}
 
 
 def run_ours(args):

@@ -33,6 +33,7 @@ SIGNATURES = {
     "dilution_colsum_scan": (_I, [_P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _P, _P, _P, _I, _P, _P, _P]),
     "dilution_forward_main": (_I, [_P, _P, _P, _I, _I, _L, _L, _L, _L, _I, _F, _F,
                                    _P, _P, _P, _I, _P, _P, _P, _P, _P]),
+    "dilution_forward_fused": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_backward_scratch_bytes": (_Z, [_L, _L, _I]),
     "dilution_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F,
                                _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P]),

@@ -16,6 +16,7 @@
 #if __has_include("tc_kernels.cuh")
 #include "tc_kernels.cuh"
 #include "tc_rowpass_kernels.cuh"
+#include "tc_fused_forward.cuh"
 #define DILUTION_TENSOR_PATH 1
 #endif
 
@@ -547,6 +548,24 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
 #endif
   DIL_DISPATCH(dtype, d, DIL_DISPATCH_MMA(precision, return (launch_main<T, D, MMA>(q, k, v, g, rmax, rden, carry, carry_base, out, ssum, pk, st))))
   return DILUTION_OK;
+}
+
+int dilution_forward_fused(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                           int64_t t, int d, float scale, float eps, const float* rmax, const float* rden,
+                           float* carry, float* total, float* out, float* ssum, void* stream) {
+  if (int rc = check_common("dilution_forward_fused", dtype, precision, n, t, t, 0, d)) return rc;
+  if (!q || !k || !v || !rmax || !rden || !carry || !total || !out || !ssum)
+    return fail(DILUTION_ERR_ARG, "dilution_forward_fused: null pointer");
+#if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_MAIN
+  if (dil::tc::supported(dtype, precision, d, 0)) {
+    const dil::Geom g = make_geom(n, t, t, 0, scale, eps, 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    Prof prof("tc_forward_fused", st);
+    return dil::tc::forward_fused(q, k, v, g, rmax, rden, carry, total, out, ssum, st, g_err, sizeof(g_err));
+  }
+#endif
+  return fail(DILUTION_ERR_UNSUPPORTED, "dilution_forward_fused: bf16 inputs, BF16 precision and head_dim 64 only "
+              "(other cases run dilution_colsum_scan and dilution_forward_main)");
 }
 
 size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d) {

@@ -48,6 +48,9 @@ HAS_CUDA_LIB = _lib.available()
 # key half left.  False (or DILUTION_SAVE_PK=0 in the environment): nothing is saved and the
 # correction pass recomputes the query half.
 TC_SAVE_PK = os.environ.get("DILUTION_SAVE_PK", "1") != "0"
+# Training forward on the tensor-core path: one key-stationary sweep for passes 2 and 3
+# (dilution_forward_fused) instead of the column-sum pass plus the query-stationary main pass.
+TC_FUSED_FORWARD = os.environ.get("DILUTION_FUSED_FORWARD", "1") != "0"
 
 
 def _resolve_precision(dot_precision: str) -> tuple[int, str]:
@@ -105,6 +108,13 @@ def _forward_rows(lib, qf, kf, vf, code, prec, scale, out, ssum, rmax, rden, car
     else:
         _lib.check(lib.dilution_rowstats(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
                                          d, scale, rmax.data_ptr(), rden.data_ptr(), st), "dilution_rowstats")
+    if (TC_FUSED_FORWARD and carry_rows == 32 and carry_base is None and q_offset == 0 and tq == tk
+            and _lib.tensor_core_path(code, prec, d)):
+        _lib.check(lib.dilution_forward_fused(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), code, prec, n, tq, d,
+                                              scale, EPS, rmax.data_ptr(), rden.data_ptr(), carry.data_ptr(),
+                                              total.data_ptr(), out.data_ptr(), ssum.data_ptr(), st),
+                   "dilution_forward_fused")
+        return
     _lib.check(lib.dilution_colsum_scan(qf.data_ptr(), kf.data_ptr(), code, prec, n, tq, tk, q_offset,
                                         d, scale, rmax.data_ptr(), rden.data_ptr(), None, carry_rows,
                                         carry.data_ptr(), total.data_ptr(), st), "dilution_colsum_scan")

@@ -158,6 +158,20 @@ int dilution_forward_main(const void* q, const void* k, const void* v, int dtype
 
 /* Bytes of scratch dilution_backward needs (fp32 dq_main, dk_main, ghat, dbar and a
  * bf16 copy of dout). */
+/* Passes 2 and 3 of a TRAINING forward in one key-stationary sweep (the reference's training
+ * forward does the same: _dilution_key_forward + _dilution_normalize, kernels.py:200-248):
+ * after dilution_rowstats[_pk], writes the checkpoints every 32 query rows (carry:
+ * (n, ceil(t/32), t)), the demand totals, out (n, t, d) fp32 and ssum (n, t) that
+ * dilution_colsum_scan + dilution_forward_main would write, with one QK^T sweep and one
+ * exponential per score less.  The per-key demand is a register for the whole sweep; the
+ * output tiles of the key blocks are added to `out` by tensor reductions (out and ssum are
+ * zeroed first, on the stream), so the summation order of `out` across key blocks is not
+ * fixed.  bf16 tensors, DILUTION_PREC_BF16, head_dim 64, whole sequences (tq = tk, no offset)
+ * only: DILUTION_ERR_UNSUPPORTED otherwise. */
+int dilution_forward_fused(const void* q, const void* k, const void* v, int dtype, int precision, int64_t n,
+                           int64_t t, int d, float scale, float eps, const float* rmax, const float* rden,
+                           float* carry, float* total, float* out, float* ssum, void* stream);
+
 size_t dilution_backward_scratch_bytes(int64_t n, int64_t t, int d);
 
 /* Pass 4 — backward of the whole operator.

@@ -134,12 +134,13 @@ def test_bf16_training_step_runs_on_the_tensor_core_kernels(pkg, kernels):
     torch.cuda.synchronize()
     names = set(pkg._lib.profile_collect())
     pkg._lib.profile(False)
+    # passes 2 and 3: one key-stationary sweep, or the column-sum pass plus the main pass
+    fwd = {"tc_forward_fused"} if kernels.TC_FUSED_FORWARD else {"tc_colsum_scan", "tc_forward_main"}
     if kernels.TC_SAVE_PK:      # pass 1 saves pk; the correction pass has only its key half left
-        want = {"tc_rowstats_pk", "tc_colsum_scan", "tc_forward_main", "tc_backward_prep",
-                "tc_backward_main", "tc_backward_key_correction", "tc_dq_from_pk"}
+        want = {"tc_rowstats_pk", "tc_backward_prep", "tc_backward_main", "tc_backward_key_correction",
+                "tc_dq_from_pk"} | fwd
     else:
-        want = {"tc_rowstats", "tc_colsum_scan", "tc_forward_main", "tc_backward_prep",
-                "tc_backward_main", "tc_backward_correction", "tc_cast_dq"}
+        want = {"tc_rowstats", "tc_backward_prep", "tc_backward_main", "tc_backward_correction", "tc_cast_dq"} | fwd
     assert names == want, names
     ref = O.dilution_backward(qs.detach().float().cpu(), ks.detach().float().cpu(), vs.detach().float().cpu(), dout)
     for name, gr, t in (("dq", ref[1], qs), ("dk", ref[2], ks), ("dv", ref[3], vs)):

@@ -134,7 +134,8 @@ def test_alternating_model_bf16_autocast_trains_on_the_tensor_core_kernels(ref):
     torch.cuda.synchronize()
     names = set(pkg._lib.profile_collect())
     pkg._lib.profile(False)
-    assert {"tc_colsum_scan", "tc_forward_main", "tc_backward_main"} <= names, names
+    assert "tc_backward_main" in names and \
+        ({"tc_forward_fused"} <= names or {"tc_colsum_scan", "tc_forward_main"} <= names), names
     assert names & {"tc_rowstats", "tc_rowstats_pk"} and \
         names & {"tc_backward_correction", "tc_backward_key_correction"}, names
     assert not any(n.startswith("simt_") for n in names), names
