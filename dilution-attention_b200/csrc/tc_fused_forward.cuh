@@ -233,7 +233,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) forward_fused_kernel(
             float sh[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              float p = fast_exp2(fmaf(v[e4 * 4 + u], g.zscale, -ls[u]));
+              // two special-function ops per score on two warps per scheduler: every fourth
+              // exponential is a degree-4 polynomial on the FMA pipe instead (7.30 -> 7.08 ms)
+              const float z = fmaf(v[e4 * 4 + u], g.zscale, -ls[u]);
+              float p = u == 3 ? poly_exp2<4>(z) : fast_exp2(z);
               if (MASK && (dead || ja > q0 + e4 * 4 + u)) p = 0.f;
               den += p;
               sh[u] = p * fast_rcp(den);
