@@ -549,6 +549,8 @@ def run_ours(args):
     if not args.no_lm:
         lm = run_lm(c, args) if c.world == 1 else {"skipped": "measured on 1 GPU only (no tensor-parallel model)"}
 
+    # 0 unless a kernel of this run gave up one of its bounded waits (rank 0's device)
+    device_status = c.L.load().dilution_device_status()
     if c.rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": c.world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -559,7 +561,7 @@ def run_ours(args):
                            "l2": "inputs exceed L2 (q,k,v 134 MB each, dout/out 268 MB at T=16384)",
                            "flop_count": "7*N*T*(T+1)*D"},
                 "roofline": roofline, "kernels_ms": kernels_ms, "e2e": e2e, "gpu_launches": launches,
-                "clocks": clocks.summary(), "other_shapes": other, "config1_fp32": fp32_c1,
+                "device_status": device_status, "clocks": clocks.summary(), "other_shapes": other, "config1_fp32": fp32_c1,
                 "train_sharded": sharded, "prefill": prefill,
                 "decode": decode, "lm": lm}
         if c.world == 1 and not args.no_cpu:

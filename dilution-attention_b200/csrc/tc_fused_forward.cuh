@@ -78,6 +78,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) forward_fused_kernel(
     for (int c = 0; c < 8; ++c)
       reinterpret_cast<uint4*>(ones_ptr)[row * 8 + c] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // only now: the barriers these copies complete on were initialised by thread 0, and nothing but
+  // the CTA-wide barrier above orders that against another warp's use of them
   if (tid == 256) {
     mbar_expect_tx(kfull, 4 * kTileBytes);
     tma_load_tile(sK, &map_k, k0, n, kfull);
@@ -89,10 +95,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) forward_fused_kernel(
       tma_load_tile(sQ + kTileBytes * s, &map_q, (ib0 + s) * kTileRows, n, qfull + 8 * s);
     }
   }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+  __syncwarp();
   const uint32_t tmem = ctl->tmem;
   const uint32_t tS = tmem, tO = tmem + 256;              // O | rs tile b at tO + 128 b
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
