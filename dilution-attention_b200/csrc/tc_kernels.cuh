@@ -11,6 +11,8 @@
 //                                          per-query statistics it needs are
 //                                          warp-uniform and come from shared
 //                                          memory as broadcasts.
+// A training forward runs passes 2 and 3 as one key-stationary sweep (tc_fused_forward.cuh);
+// forward-only calls, sequence-parallel prefill and the bid / share variants run them separately.
 // Warp w of a CTA reads TMEM lanes 32*(w%4)..32*(w%4)+31.  The forward passes and the
 // correction pass run 256 threads (two warpgroups that split a tile's columns), thread 0
 // issuing TMA and MMA, two to four CTAs per SM hiding each other's MMA/TMA latency; the
