@@ -468,7 +468,7 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
     """Roofline block of the dominant kernel of the training step."""
     # algorithmic matmuls per kernel: the backward main pass carries all five backward products,
     # the forward main pass QK^T and share@V; the other passes are recomputation overhead
-    share = {"backward_main": 5, "forward_main": 2, "forward_fused": 2}
+    share = {"backward_main": 5, "forward_main": 2, "forward_fused": 2}      # longest launch of the step
     dom = max(kernels_ms, key=kernels_ms.get) if kernels_ms else None
     if dom is None:
         return None

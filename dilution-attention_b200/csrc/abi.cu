@@ -560,8 +560,13 @@ int dilution_forward_fused(const void* q, const void* k, const void* v, int dtyp
   if (dil::tc::supported(dtype, precision, d, 0)) {
     const dil::Geom g = make_geom(n, t, t, 0, scale, eps, 32);
     cudaStream_t st = (cudaStream_t)stream;
-    Prof prof("tc_forward_fused", st);
-    return dil::tc::forward_fused(q, k, v, g, rmax, rden, carry, total, out, ssum, st, g_err, sizeof(g_err));
+    {
+      Prof prof("tc_forward_fused", st);
+      if (int rc = dil::tc::forward_fused(q, k, v, g, rmax, rden, carry, total, out, ssum, st, g_err, sizeof(g_err)))
+        return rc;
+    }
+    Prof prof("tc_normalize_out", st);
+    return dil::tc::normalize_out(g, out, ssum, st, g_err, sizeof(g_err));
   }
 #endif
   return fail(DILUTION_ERR_UNSUPPORTED, "dilution_forward_fused: bf16 inputs, BF16 precision and head_dim 64 only "

@@ -333,8 +333,12 @@ inline int forward_fused(const void* q, const void* k, const void* v, const Geom
   const int nsb = (g.tk + kFusedKeys - 1) / kFusedKeys;
   forward_fused_kernel<<<(unsigned)(g.n * nsb), kFusedThreads, smem, st>>>(mq, mk, mv, mo, g, rmax, rden, carry,
                                                                          total, ssum);
-  if (int rc = launch_status("tc forward_fused", err, errlen)) return rc;
-  const int64_t n4 = rows * kHeadDim / 4;
+  return launch_status("tc forward_fused", err, errlen);
+}
+
+// The division that ends the fused forward: out = O / (rs + eps), in place.
+inline int normalize_out(const Geom& g, float* out, const float* ssum, cudaStream_t st, char* err, size_t errlen) {
+  const int64_t n4 = g.n * g.tq * kHeadDim / 4;
   normalize_out_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(out, ssum, g.eps, n4);
   return launch_status("tc normalize_out", err, errlen);
 }

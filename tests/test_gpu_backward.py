@@ -135,7 +135,7 @@ def test_bf16_training_step_runs_on_the_tensor_core_kernels(pkg, kernels):
     names = set(pkg._lib.profile_collect())
     pkg._lib.profile(False)
     # passes 2 and 3: one key-stationary sweep, or the column-sum pass plus the main pass
-    fwd = {"tc_forward_fused"} if kernels.TC_FUSED_FORWARD else {"tc_colsum_scan", "tc_forward_main"}
+    fwd = {"tc_forward_fused", "tc_normalize_out"} if kernels.TC_FUSED_FORWARD else {"tc_colsum_scan", "tc_forward_main"}
     if kernels.TC_SAVE_PK:      # pass 1 saves pk; the correction pass has only its key half left
         want = {"tc_rowstats_pk", "tc_backward_prep", "tc_backward_main", "tc_backward_key_correction",
                 "tc_dq_from_pk"} | fwd
