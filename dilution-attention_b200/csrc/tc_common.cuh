@@ -83,6 +83,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
   return true;
 }
 
+// After a wait has given up, the CTA runs to its end without waiting for anything, so copies and
+// MMAs it issued may still be in flight when it gets there.  Every kernel calls this in front of its
+// last CTA-wide barrier: a CTA that gave up idles for a fixed grace period (about 0.2 ms, three
+// orders of magnitude above a copy's or an MMA's latency) before it frees its TMEM and returns.
+__device__ __forceinline__ void drain_if_aborted(const Ctl* ctl) {
+  if (ctl->abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000LL) {
+    }
+  }
+}
+
 // ---- fences -------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

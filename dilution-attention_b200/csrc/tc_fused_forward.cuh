@@ -298,6 +298,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) forward_fused_kernel(
     }
     if (!dead) total[(int64_t)n * g.tk + ja] = den - g.eps;
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 512);

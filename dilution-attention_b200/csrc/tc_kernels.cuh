@@ -305,6 +305,7 @@ __global__ void __launch_bounds__(256, 4) rowstats_kernel(const __grid_constant_
     rmax[(int64_t)n * g.tq + i] = nm;
     rden[(int64_t)n * g.tq + i] = tot;
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 128);
@@ -455,6 +456,7 @@ __global__ void __launch_bounds__(256, 4) colsum_scan_kernel(
     if (nib > 0) store_checkpoints(nqb - 1, sCs[((nib - 1) & 1) * 128 + row]);
     total[(int64_t)n * g.tk + ja] = local;
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 128);
@@ -670,6 +672,7 @@ __global__ void __launch_bounds__(256, 2) forward_main_kernel(
       if (wg == 0) ssum[(int64_t)n * g.tq + i] = r[0];
     }
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 256);
@@ -1183,6 +1186,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) backward_main_kernel(
                        pack_bf16(a[e + 4], a[e + 5]), pack_bf16(a[e + 6], a[e + 7]));
     }
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 512);
@@ -1413,6 +1417,7 @@ __global__ void __launch_bounds__(256, 2) backward_correction_kernel(
                        pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
     }
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 256);

@@ -286,6 +286,7 @@ __global__ void __launch_bounds__(256, 2) rowpass_product_kernel(
     }
   };
   if (wg == 0) merge(std::integral_constant<int, 0>{}); else merge(std::integral_constant<int, 1>{});
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 256);
@@ -457,6 +458,7 @@ __global__ void __launch_bounds__(256, 4) backward_key_correction64_kernel(
                        pack_bf16(m[e + 4], m[e + 5]), pack_bf16(m[e + 6], m[e + 7]));
     }
   }
+  drain_if_aborted(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_free(tmem, 128);
