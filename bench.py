@@ -898,7 +898,7 @@ def run_lm(c, args):
         nb, prompt, new = LM["gen_batch"], args.lm_prompt or LM["gen_prompt"], LM["gen_new"]
         g = torch.Generator().manual_seed(1344)
         idx_h = torch.randint(0, LM["vocab"], (B, T + 1), generator=g).pin_memory()
-        idx_gen = torch.randint(0, LM["vocab"], (nb, prompt), generator=g).to(dev)
+        idx_gen_full = torch.randint(0, LM["vocab"], (nb, prompt), generator=g).to(dev)
 
         def train(steps):
             """forward, loss, backward, gradient clipping, fused AdamW; token ids come from the host
@@ -929,8 +929,9 @@ def run_lm(c, args):
             torch.cuda.empty_cache()
             return out
 
-        def generate(new_tokens):
+        def generate(new_tokens, graphed=False, prompt=prompt):
             """DilutionLM.prefill + greedy decode_step loop (model.py:451-470, 498-509)"""
+            idx_gen = idx_gen_full[:, :prompt]
             torch.manual_seed(1345)
             model = DilutionLM(config(prompt + new)).to(dev).eval()
             model.enable_dilution_kernel()
@@ -950,18 +951,42 @@ def run_lm(c, args):
                 ev[2].record()
                 torch.cuda.synchronize()
             pre_ms, dec_ms = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+            out = {"decode_tok_s": nb * (new_tokens - 1) / (dec_ms * 1e-3),
+                   "decode_ms_per_token": dec_ms / (new_tokens - 1), "prefill_ms": pre_ms,
+                   "prefill_tok_s": nb * prompt / (pre_ms * 1e-3), "batch": nb, "prompt": prompt,
+                   "new_tokens": new_tokens}
+            if graphed:
+                # the same greedy loop with the per-token layer loop replayed from one CUDA graph
+                # (layers.GraphedDecode): first step eager, second recorded, the rest timed
+                del caches
+                with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                    logits, caches = model.prefill(idx_gen, capacity=prompt + new)
+                dec = c.pkg.GraphedDecode(model, caches)
+                tok = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+                for s in range(2):
+                    tok = dec.step(tok)[:, -1, :].float().argmax(dim=-1, keepdim=True)
+                torch.cuda.synchronize()
+                ev[0].record()
+                for s in range(new_tokens - 3):
+                    tok = dec.step(tok)[:, -1, :].float().argmax(dim=-1, keepdim=True)
+                ev[1].record()
+                torch.cuda.synchronize()
+                g_ms = ev[0].elapsed_time(ev[1])
+                out["graphed"] = {"decode_tok_s": nb * (new_tokens - 3) / (g_ms * 1e-3),
+                                  "decode_ms_per_token": g_ms / (new_tokens - 3), "timed_tokens": new_tokens - 3,
+                                  "path": "layers.GraphedDecode: DilutionLM.decode_step recorded once, replayed per token"}
+                dec.close()
             del model, caches
             torch.cuda.empty_cache()
-            return {"decode_tok_s": nb * (new_tokens - 1) / (dec_ms * 1e-3),
-                    "decode_ms_per_token": dec_ms / (new_tokens - 1), "prefill_ms": pre_ms,
-                    "prefill_tok_s": nb * prompt / (pre_ms * 1e-3), "batch": nb, "prompt": prompt,
-                    "new_tokens": new_tokens}
+            return out
 
         steps = max(1, min(args.steps, 3))
         c.pkg.install(fused_decode=True)
         c.pkg.install_layers()
         res["train"] = train(steps)
-        res["generate"] = generate(new)
+        res["generate"] = generate(new, graphed=True)
+        # a short context, where a token's ~200 launches cost more than the bytes they move
+        res["generate_short_context"] = generate(min(new, 256), graphed=True, prompt=min(prompt, 1024))
         c.pkg.uninstall_layers()
         c.pkg.uninstall()
         c.pkg.install()

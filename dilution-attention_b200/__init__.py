@@ -27,7 +27,13 @@ from .kernels import (  # noqa: F401
     softmax_attention_forward,
     uninstall,
 )
-from .layers import install_layers, softmax_decode_append_step, split_heads_rope, uninstall_layers  # noqa: F401
+from .layers import (  # noqa: F401
+    GraphedDecode,
+    install_layers,
+    softmax_decode_append_step,
+    split_heads_rope,
+    uninstall_layers,
+)
 
 _sys.modules.setdefault("dilution_attention_b200", _sys.modules[__name__])
 
@@ -35,5 +41,5 @@ __all__ = [
     "kernels", "kernels_bid", "partition", "dilution_attention", "dilution_attention_forward",
     "dilution_attention_reference", "dilution_attention_host", "dilution_decode_step",
     "dilution_decode_append_step", "softmax_attention_forward", "softmax_decode_append_step",
-    "split_heads_rope", "install", "uninstall", "install_layers", "uninstall_layers", "layers",
+    "split_heads_rope", "install", "uninstall", "install_layers", "uninstall_layers", "layers", "GraphedDecode",
 ]

@@ -301,25 +301,28 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
                   int64_t len, float scale, float eps, float* committed, void* out, void* scratch,
                   cudaStream_t st, bool timing = true, const void* knew = nullptr,
                   const void* vnew = nullptr, int bid = dil::kBidSoftmax, int share = dil::kShareInclusive,
-                  float lshift = 0.f) {
+                  float lshift = 0.f, const int* pos_dev = nullptr) {
   using namespace dil::decode;
-  const int chunk = decode_chunk(n, len);
-  const int nch = (int)((len + chunk - 1) / chunk);
-  const Scratch s = carve_decode(scratch, n, len, D);
-  const int64_t stride = decode_stride(len);
+  // with the length on the device (pos_dev) the launch geometry cannot follow it: the grid, the
+  // chunking and the scratch layout are those of a full cache
+  const int64_t geo = pos_dev != nullptr ? cap : len;
+  const int chunk = decode_chunk(n, geo);
+  const int nch = (int)((geo + chunk - 1) / chunk);
+  const Scratch s = carve_decode(scratch, n, geo, D);
+  const int64_t stride = decode_stride(geo);
   const dim3 grid((unsigned)nch, (unsigned)n);
   {
     Prof prof("decode_scores", st, timing);
     scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
                                              scale * dil::kLog2e, stride, s.aff, s.part,
-                                             (const T*)knew, (T*)const_cast<void*>(kc));
+                                             (const T*)knew, (T*)const_cast<void*>(kc), pos_dev);
   }
   if (int rc = check_launch("decode scores")) return rc;
   {
     Prof prof("decode_sweep", st, timing);
     sweep_kernel<T, D, MODE><<<grid, NT, 0, st>>>((const T*)vc, cap, (int)len, chunk, eps, stride, s.aff, s.part,
                                                   committed, s.pout, s.psum, (const T*)vnew,
-                                                  (T*)const_cast<void*>(vc), bid, share, lshift);
+                                                  (T*)const_cast<void*>(vc), bid, share, lshift, pos_dev);
   }
   if (int rc = check_launch("decode sweep")) return rc;
   {
@@ -657,9 +660,9 @@ int dilution_decode_append(const void* q1, const void* k1, const void* v1, void*
   return DILUTION_OK;
 }
 
-int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* cos_table,
-                              const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
-                              int inverse, void* stream) {
+static int split_heads_rope_impl(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                                 const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
+                                 int inverse, const int* pos_dev, void* stream) {
   if (!qkv || !q || !k || !v) return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: null pointer");
   if ((cos_table == nullptr) != (sin_table == nullptr))
     return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: cos and sin tables go together");
@@ -678,13 +681,28 @@ int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* 
 #define DIL_ROPE(DD)                                                                                           \
   if (inverse)                                                                                                 \
     dil::layer::split_heads_rope_kernel<false, DD><<<grid, 256, 0, st>>>(                                      \
-        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads);      \
+        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads,      \
+        pos_dev);                                                                                              \
   else                                                                                                         \
     dil::layer::split_heads_rope_kernel<true, DD><<<grid, 256, 0, st>>>(                                       \
-        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads);
+        (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads,      \
+        pos_dev);
   if (d == 32) { DIL_ROPE(32) } else if (d == 64) { DIL_ROPE(64) } else { DIL_ROPE(128) }
 #undef DIL_ROPE
   return check_launch("split_heads_rope");
+}
+
+int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                              const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
+                              int inverse, void* stream) {
+  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, seq, heads, d, inverse, nullptr, stream);
+}
+
+int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                                 const void* sin_table, int64_t batch, int heads, int d,
+                                 const int* position_dev, void* stream) {
+  if (!position_dev) return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope_at: null position");
+  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, 1, heads, d, 0, position_dev, stream);
 }
 
 int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache,
@@ -816,6 +834,48 @@ int dilution_variant_decode(const void* q1, const void* k1, const void* v1, void
   DIL_DISPATCH(dtype, d, return (launch_decode<T, D, dil::decode::kSweepVariant>(
       q1, k_cache, v_cache, n, capacity, length, scale, eps, committed, out, scratch, st, true, k1, v1, bid, share,
       (bid == dil::kBidExpshift || bid == dil::kBidSigshift) ? log2f(shift) * 1.f : 0.f)))
+  return DILUTION_OK;
+}
+
+// ---- cached steps whose length lives on the device (for a captured graph) ------------------
+static int check_decode_at(const char* fn, int dtype, int64_t n, int64_t capacity, int d, const void* q1,
+                           const void* k1, const void* v1, const void* kc, const void* vc, const void* pos,
+                           const void* out, const void* scratch) {
+  if (dtype != DILUTION_F32 && dtype != DILUTION_BF16)
+    return fail(DILUTION_ERR_ARG, "%s: dtype must be DILUTION_F32 or DILUTION_BF16", fn);
+  if (!valid_d(d)) return fail(DILUTION_ERR_UNSUPPORTED, "%s: head_dim %d not in {16, 32, 64, 128}", fn, d);
+  if (n < 1 || n > 65535) return fail(DILUTION_ERR_ARG, "%s: n must be in [1, 65535] rows per call", fn);
+  if (capacity < 1 || capacity > (1 << 30)) return fail(DILUTION_ERR_ARG, "%s: capacity out of range", fn);
+  if (!q1 || !k1 || !v1 || !kc || !vc || !pos || !out || !scratch) return fail(DILUTION_ERR_ARG, "%s: null pointer", fn);
+  if (((uintptr_t)q1 | (uintptr_t)k1 | (uintptr_t)v1 | (uintptr_t)kc | (uintptr_t)vc) & 15)
+    return fail(DILUTION_ERR_ARG, "%s: q1 / k1 / v1 / caches must be 16-byte aligned", fn);
+  return DILUTION_OK;
+}
+
+int dilution_decode_append_at(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                              int dtype, int64_t n, int64_t capacity, const int* position_dev, int d,
+                              float scale, float eps, float* committed, void* out, void* scratch,
+                              void* stream) {
+  if (int rc = check_decode_at("dilution_decode_append_at", dtype, n, capacity, d, q1, k1, v1, k_cache, v_cache,
+                               position_dev, out, scratch)) return rc;
+  if (!committed) return fail(DILUTION_ERR_ARG, "dilution_decode_append_at: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D>(q1, k_cache, v_cache, n, capacity, 0, scale, eps, committed, out,
+                                                     scratch, st, true, k1, v1, dil::kBidSoftmax,
+                                                     dil::kShareInclusive, 0.f, position_dev)))
+  return DILUTION_OK;
+}
+
+int dilution_softmax_decode_append_at(const void* q1, const void* k1, const void* v1, void* k_cache,
+                                      void* v_cache, int dtype, int64_t n, int64_t capacity,
+                                      const int* position_dev, int d, float scale, void* out, void* scratch,
+                                      void* stream) {
+  if (int rc = check_decode_at("dilution_softmax_decode_append_at", dtype, n, capacity, d, q1, k1, v1, k_cache,
+                               v_cache, position_dev, out, scratch)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  DIL_DISPATCH(dtype, d, return (launch_decode<T, D, dil::decode::kSweepSoftmax>(
+      q1, k_cache, v_cache, n, capacity, 0, scale, 0.f, nullptr, out, scratch, st, true, k1, v1, dil::kBidSoftmax,
+      dil::kShareInclusive, 0.f, position_dev)))
   return DILUTION_OK;
 }
 

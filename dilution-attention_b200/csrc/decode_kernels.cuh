@@ -68,11 +68,15 @@ struct Scratch {
 template <typename T, int D>
 __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
                                                     const T* __restrict__ kc, int64_t cap,
-                                                    int len, int chunk, float zscale,
+                                                    int len_arg, int chunk, float zscale,
                                                     int64_t stride, float* __restrict__ aff,
                                                     float2* __restrict__ part,
-                                                    const T* __restrict__ knew, T* __restrict__ kc_out) {
+                                                    const T* __restrict__ knew, T* __restrict__ kc_out,
+                                                    const int* __restrict__ pos_dev) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
+  // the number of valid keys: a launch argument, or (a step inside a captured graph, whose
+  // arguments are frozen) the new token's position read from device memory, plus one
+  const int len = pos_dev != nullptr ? *pos_dev + 1 : len_arg;
   const int64_t n = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = lane % TPK, grp = lane / TPK;
@@ -86,7 +90,8 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   const int k0 = blockIdx.x * chunk;
   // with an append, position len-1 (the last key of the last chunk) is not read from the cache:
   // the streaming loop stops in front of it and warp 0 takes its row from knew afterwards
-  const bool appends = knew != nullptr && k0 + chunk >= len;
+  // (a grid sized for the capacity has chunks behind the last key: they write neutral statistics)
+  const bool appends = knew != nullptr && len - 1 >= k0 && len - 1 < k0 + chunk;
   const int k1 = min(len, k0 + chunk) - (appends ? 1 : 0);
   const T* krow = kc + n * cap * D + t * E;
   float m = -INFINITY, s = 0.f;
@@ -176,7 +181,7 @@ __device__ __forceinline__ float key_share(float a, float gmax, float rinv, floa
 
 // grid = (chunks, n)
 template <typename T, int D, int MODE = kSweepDilution>
-__global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int64_t cap, int len,
+__global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int64_t cap, int len_arg,
                                                    int chunk, float eps, int64_t stride,
                                                    const float* __restrict__ aff,
                                                    const float2* __restrict__ part,
@@ -184,8 +189,10 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
                                                    float* __restrict__ pout,
                                                    float* __restrict__ psum,
                                                    const T* __restrict__ vnew, T* __restrict__ vc_out,
-                                                   int bid, int share_step, float lshift) {
+                                                   int bid, int share_step, float lshift,
+                                                   const int* __restrict__ pos_dev) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
+  const int len = pos_dev != nullptr ? *pos_dev + 1 : len_arg;      // as in scores_kernel
   const int64_t n = blockIdx.y;
   const int nch = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -219,7 +226,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
   const float gmax = sstat[0], rinv = sstat[1];
 
   const int k0 = blockIdx.x * chunk;
-  const bool appends = vnew != nullptr && k0 + chunk >= len;     // as in scores_kernel
+  const bool appends = vnew != nullptr && len - 1 >= k0 && len - 1 < k0 + chunk;     // as in scores_kernel
   const int k1 = min(len, k0 + chunk) - (appends ? 1 : 0);
   const T* vrow = vc + n * cap * D + t * E;
   float acc[E];

@@ -51,7 +51,7 @@ __global__ void split_heads_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bf
                                         __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
                                         const __nv_bfloat16* __restrict__ cos_t,
                                         const __nv_bfloat16* __restrict__ sin_t, int64_t batch, int64_t seq,
-                                        int heads) {
+                                        int heads, const int* __restrict__ pos_dev) {
   constexpr int SL = D / 8;                                  // 16-byte slices per head row
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = batch * seq * heads * SL;
@@ -65,8 +65,11 @@ __global__ void split_heads_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bf
   float c[4] = {1.f, 1.f, 1.f, 1.f}, s[4] = {0.f, 0.f, 0.f, 0.f};
   const bool rot = cos_t != nullptr;
   if (rot) {
-    const uint2 cr = *reinterpret_cast<const uint2*>(cos_t + t * (D / 2) + sl * 4);
-    const uint2 sr = *reinterpret_cast<const uint2*>(sin_t + t * (D / 2) + sl * 4);
+    // table row = position of the token: its row in this call, plus (a step inside a captured
+    // graph, whose arguments are frozen) the first row's position read from device memory
+    const int64_t tr = t + (pos_dev != nullptr ? *pos_dev : 0);
+    const uint2 cr = *reinterpret_cast<const uint2*>(cos_t + tr * (D / 2) + sl * 4);
+    const uint2 sr = *reinterpret_cast<const uint2*>(sin_t + tr * (D / 2) + sl * 4);
     c[0] = __uint_as_float(cr.x << 16); c[1] = __uint_as_float(cr.x & 0xffff0000u);
     c[2] = __uint_as_float(cr.y << 16); c[3] = __uint_as_float(cr.y & 0xffff0000u);
     s[0] = __uint_as_float(sr.x << 16); s[1] = __uint_as_float(sr.x & 0xffff0000u);

@@ -400,6 +400,10 @@ def dilution_decode_append_step(
     position len are written by the kernels, committed is advanced in place and
     cache["len"] grows by one.  Raises ValueError past the capacity, as
     _append_kv does.  Returns (B, H, 1, D) in q1.dtype.
+
+    A cache that carries "pos_dev" (a one-element int32 device tensor holding the new token's
+    position, see layers.GraphedDecode) takes the length from there: the launches then have
+    the geometry of a full cache and can be recorded into a CUDA graph.
     """
     lib = _lib.load()
     t = cache["len"]
@@ -414,16 +418,23 @@ def dilution_decode_append_step(
     kf = k_cache.view(n, capacity, head_dim)
     vf = v_cache.view(n, capacity, head_dim)
     cf = committed.view(n, capacity)
+    pos_dev = cache.get("pos_dev")
     if out is None:
         out = torch.empty(n, head_dim, device=q1.device, dtype=q1.dtype)
-    need = lib.dilution_decode_scratch_bytes(n, t + 1, head_dim)
+    need = lib.dilution_decode_scratch_bytes(n, capacity if pos_dev is not None else t + 1, head_dim)
     if scratch is None or scratch.numel() * scratch.element_size() < need:
         scratch = torch.empty(need, device=q1.device, dtype=torch.uint8)
     code = _lib.BF16 if q1.dtype == torch.bfloat16 else _lib.F32
-    _lib.check(lib.dilution_decode_append(qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), kf.data_ptr(),
-                                          vf.data_ptr(), code, n, capacity, t + 1, head_dim,
-                                          1.0 / math.sqrt(head_dim), EPS, cf.data_ptr(), out.data_ptr(),
-                                          scratch.data_ptr(), _stream(q1.device)), "dilution_decode_append")
+    if pos_dev is not None:
+        _lib.check(lib.dilution_decode_append_at(qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), kf.data_ptr(),
+                                                 vf.data_ptr(), code, n, capacity, pos_dev.data_ptr(), head_dim,
+                                                 1.0 / math.sqrt(head_dim), EPS, cf.data_ptr(), out.data_ptr(),
+                                                 scratch.data_ptr(), _stream(q1.device)), "dilution_decode_append_at")
+    else:
+        _lib.check(lib.dilution_decode_append(qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), kf.data_ptr(),
+                                              vf.data_ptr(), code, n, capacity, t + 1, head_dim,
+                                              1.0 / math.sqrt(head_dim), EPS, cf.data_ptr(), out.data_ptr(),
+                                              scratch.data_ptr(), _stream(q1.device)), "dilution_decode_append")
     cache["len"] = t + 1
     return out.view(batch, heads, 1, head_dim)
 
@@ -531,7 +542,11 @@ def _fused_step_cache(self, x1, cache):
     if not self._kernel_ok(x1) or not self._standard():
         return self._unfused_step_cache(x1, cache)
     batch = x1.shape[0]
-    q1, k1, v1 = self._split_heads(x1, offset=cache["len"])
+    if cache.get("pos_dev") is not None:       # the position lives on the device (a captured step)
+        from . import layers
+        q1, k1, v1 = layers.split_heads_at(self, x1, cache)
+    else:
+        q1, k1, v1 = self._split_heads(x1, offset=cache["len"])
     y = dilution_decode_append_step(q1, k1, v1, cache).to(q1.dtype)
     return self._merge_heads(y, batch, 1)
 

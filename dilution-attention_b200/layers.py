@@ -96,11 +96,38 @@ def split_heads_rope(qkv: torch.Tensor, n_heads: int, rope=None, offset: int = 0
     return _SplitHeadsRope.apply(qkv, n_heads, cos, sin)
 
 
+def split_heads_at(layer, x1, cache):
+    """`_split_heads` of ONE token per batch row whose position is read from the device
+    (cache["pos_dev"], a one-element int32 tensor): the launch takes no host-side position, so
+    it can be recorded into a CUDA graph.  layer: the attention module; x1: (B, 1, C).
+    bf16 projections only."""
+    lib = _lib.load()
+    qkv = layer.c_attn(x1)
+    if qkv.dtype != torch.bfloat16:
+        raise ValueError("a step with the position on the device takes bfloat16 activations (autocast)")
+    batch, one, width = qkv.shape
+    heads = layer.n_heads
+    d = width // (3 * heads)
+    if one != 1 or d not in _ROPE_DIMS:
+        raise ValueError(f"one token per row and head_dim in {_ROPE_DIMS}")
+    qkv = qkv.contiguous()
+    q, k, v = (torch.empty(batch, heads, 1, d, device=qkv.device, dtype=qkv.dtype) for _ in range(3))
+    cos = sin = None
+    if layer.rope is not None:          # tables for every position the cache can hold
+        cos, sin = rope_tables(layer.rope, cache["k"].shape[2], 0, qkv.device, qkv.dtype)
+    _lib.check(lib.dilution_split_heads_rope_at(qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                K._ptr(cos), K._ptr(sin), batch, heads, d,
+                                                cache["pos_dev"].data_ptr(), K._stream(qkv.device)),
+               "dilution_split_heads_rope_at")
+    return q, k, v
+
+
 def softmax_decode_append_step(q1, k1, v1, cache: dict, scratch=None, out=None):
     """One cached token of a softmax layer: `_append_kv(cache, k1, v1)` followed by attention of
     q1 over the first len+1 cache rows (model.py:112-117), as three launches that stream K and V
     once.  q1, k1, v1: (B, H, 1, D); cache: the model's dict {"k", "v", "len"}.  Returns
-    (B, H, 1, D) in q1.dtype; cache["len"] grows by one."""
+    (B, H, 1, D) in q1.dtype; cache["len"] grows by one.  With cache["pos_dev"] the length is
+    read from the device (see GraphedDecode)."""
     lib = _lib.load()
     t = cache["len"]
     k_cache, v_cache = cache["k"], cache["v"]
@@ -115,16 +142,102 @@ def softmax_decode_append_step(q1, k1, v1, cache: dict, scratch=None, out=None):
     qf, kn, vn = (K._rows(x, n, d) for x in (q1, k1, v1))
     if out is None:
         out = torch.empty(n, d, device=q1.device, dtype=q1.dtype)
-    need = lib.dilution_decode_scratch_bytes(n, t + 1, d)
+    pos_dev = cache.get("pos_dev")
+    need = lib.dilution_decode_scratch_bytes(n, capacity if pos_dev is not None else t + 1, d)
     if scratch is None or scratch.numel() * scratch.element_size() < need:
         scratch = torch.empty(need, device=q1.device, dtype=torch.uint8)
     code = _lib.BF16 if q1.dtype == torch.bfloat16 else _lib.F32
-    _lib.check(lib.dilution_softmax_decode_append(
-        qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), k_cache.view(n, capacity, d).data_ptr(),
-        v_cache.view(n, capacity, d).data_ptr(), code, n, capacity, t + 1, d, 1.0 / math.sqrt(d),
-        out.data_ptr(), scratch.data_ptr(), K._stream(q1.device)), "dilution_softmax_decode_append")
+    if pos_dev is not None:
+        _lib.check(lib.dilution_softmax_decode_append_at(
+            qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), k_cache.view(n, capacity, d).data_ptr(),
+            v_cache.view(n, capacity, d).data_ptr(), code, n, capacity, pos_dev.data_ptr(), d, 1.0 / math.sqrt(d),
+            out.data_ptr(), scratch.data_ptr(), K._stream(q1.device)), "dilution_softmax_decode_append_at")
+    else:
+        _lib.check(lib.dilution_softmax_decode_append(
+            qf.data_ptr(), kn.data_ptr(), vn.data_ptr(), k_cache.view(n, capacity, d).data_ptr(),
+            v_cache.view(n, capacity, d).data_ptr(), code, n, capacity, t + 1, d, 1.0 / math.sqrt(d),
+            out.data_ptr(), scratch.data_ptr(), K._stream(q1.device)), "dilution_softmax_decode_append")
     cache["len"] = t + 1
     return out.view(batch, heads, 1, d)
+
+
+class GraphedDecode:
+    """The model's per-token layer loop (`DilutionLM.decode_step`, model.py:464-470) recorded ONCE
+    into a CUDA graph and replayed per token.
+
+    A step's launches normally take the cache length and the token's position as host scalars,
+    which a graph would freeze.  Here every cache of the model shares one int32 device scalar
+    (`cache["pos_dev"]`, the new token's position); the decode and head-split launches read it
+    (`dilution_decode_append_at`, `dilution_softmax_decode_append_at`,
+    `dilution_split_heads_rope_at`), and the recorded step ends by adding one to it.
+
+    Needs `install(fused_decode=True)` and `install_layers()` (every attention layer's cached
+    step on this library's kernels), bf16 autocast, and a model whose embedding does not use the
+    position (positional "none", "rope" or "rope_alt": `_embed`, model.py:386-393).  Usage:
+
+        logits, caches = model.prefill(prompt, capacity=...)
+        dec = GraphedDecode(model, caches)
+        logits = dec.step(token)          # (B, 1) int64 -> (B, 1, vocab); the first call records
+
+    The caches stay the model's own dicts; their "len" entries are kept in step with the device
+    scalar, so `model.decode_step` can take over again after `dec.close()`.
+    """
+
+    def __init__(self, model, caches, autocast_dtype=torch.bfloat16):
+        if model.config.positional == "learned":
+            raise ValueError("GraphedDecode needs a model whose embedding ignores the position")
+        self.model, self.caches, self.dtype = model, caches, autocast_dtype
+        dev = caches[0]["k"].device
+        self.capacity = min(c["k"].shape[2] for c in caches)
+        self.position = caches[0]["len"]
+        if any(c["len"] != self.position for c in caches):
+            raise ValueError("all layers' caches must hold the same number of tokens")
+        self.pos_dev = torch.tensor([self.position], device=dev, dtype=torch.int32)
+        for c in caches:
+            c["pos_dev"] = self.pos_dev
+        self.graph = None
+        self.token = None
+        self.logits = None
+
+    def _one_step(self):
+        with torch.no_grad(), torch.autocast("cuda", dtype=self.dtype):
+            logits = self.model.decode_step(self.token, 0, self.caches)
+        self.pos_dev.add_(1)
+        return logits
+
+    def step(self, token):
+        """One token for every sequence: (B, 1) int64 ids -> (B, 1, vocab) logits (a view of a
+        buffer that the next call overwrites)."""
+        if self.position >= self.capacity:
+            raise ValueError("decode step past the cache capacity (context_length)")
+        if self.graph is None:
+            # the first step runs eagerly (it also warms up every library this step touches), the
+            # second is recorded; recording executes nothing, so it is replayed right away
+            if self.token is None:
+                self.token = token.clone()
+                logits = self._one_step()
+                self.position += 1
+                return logits
+            self.token.copy_(token)
+            for c in self.caches:                 # the recorded step must not move the host-side lengths
+                c["len"] = self.position
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._one_step()
+        else:
+            self.token.copy_(token)
+        self.graph.replay()
+        self.position += 1
+        for c in self.caches:
+            c["len"] = self.position
+        return self.logits
+
+    def close(self):
+        """Detach the device-side position: the caches are the model's plain dicts again."""
+        for c in self.caches:
+            c.pop("pos_dev", None)
+            c["len"] = self.position
+        self.graph = None
 
 
 # ---- patches of dilution.model -------------------------------------------------------------
@@ -180,6 +293,9 @@ def _softmax_step_cache(self, x1, cache):
     if not x1.is_cuda or (self.d_model // self.n_heads) not in (16, 32, 64, 128):
         return self._b200_step_cache(x1, cache)
     batch = x1.shape[0]
+    if cache.get("pos_dev") is not None:       # the position lives on the device (a captured step)
+        q1, k1, v1 = split_heads_at(self, x1, cache)
+        return self._merge_heads(softmax_decode_append_step(q1, k1, v1, cache), batch, 1)
     q1, k1, v1 = self._split_heads(x1, offset=cache["len"])
     if q1.dtype not in (torch.float32, torch.bfloat16) or cache["k"].dtype != q1.dtype:
         t = self._append_kv(cache, k1, v1)

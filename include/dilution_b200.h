@@ -45,7 +45,7 @@
 extern "C" {
 #endif
 
-#define DILUTION_ABI_VERSION 4
+#define DILUTION_ABI_VERSION 5
 #define DILUTION_CARRY_ROWS 32      /* query rows per carry checkpoint of the fp32 kernels */
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
@@ -270,6 +270,33 @@ int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* 
 int dilution_decode_static(const void* q1, const void* k_cache, const void* v_cache, int dtype,
                            int64_t n, int64_t capacity, int64_t length, int d, float scale, float eps,
                            float* committed, void* out, void* stream);
+
+/* ---- cached steps for a captured graph -------------------------------------------------
+ * A CUDA graph freezes the arguments of the launches it records, and a decode step's launches
+ * take the cache length (grid, chunking) and the token's position (RoPE table row) as host
+ * scalars.  These three entries read both from ONE int in device memory instead —
+ * *position_dev = the new token's position = the number of keys already cached — so the
+ * per-token layer loop of the model (model.py:464-470) can be captured once and replayed per
+ * token, with a one-element increment of that int recorded at the end of the step.  The launch
+ * geometry is that of a full cache: the scratch is dilution_decode_scratch_bytes(n, capacity, d),
+ * chunks behind the last key write neutral statistics and return.  The caller guarantees
+ * *position_dev < capacity.
+ *   dilution_decode_append_at          dilution_decode_append with length = *position_dev + 1
+ *   dilution_softmax_decode_append_at  dilution_softmax_decode_append likewise (k1, v1 required)
+ *   dilution_split_heads_rope_at       the head split of ONE token per batch row (seq = 1) whose
+ *                                      rotation uses row *position_dev of cos / sin tables that
+ *                                      cover every position up to the capacity */
+int dilution_decode_append_at(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                              int dtype, int64_t n, int64_t capacity, const int* position_dev, int d,
+                              float scale, float eps, float* committed, void* out, void* scratch,
+                              void* stream);
+int dilution_softmax_decode_append_at(const void* q1, const void* k1, const void* v1, void* k_cache,
+                                      void* v_cache, int dtype, int64_t n, int64_t capacity,
+                                      const int* position_dev, int d, float scale, void* out, void* scratch,
+                                      void* stream);
+int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const void* cos_table,
+                                 const void* sin_table, int64_t batch, int heads, int d,
+                                 const int* position_dev, void* stream);
 
 /* ---- share / bid variants ------------------------------------------------------------
  * The ablations a model configuration can select besides the operator itself

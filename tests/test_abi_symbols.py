@@ -35,7 +35,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_version_and_size_queries():
     lib = load_package()._lib.load()
-    assert lib.dilution_version() == 4
+    assert lib.dilution_version() == 5
     assert lib.dilution_backward_scratch_bytes(2, 100, 64) == 4 * (2 * 2 * 100 * 64 + 2 * 2 * 100) + 2 * 2 * 100 * 64
     assert lib.dilution_carry_rows(1, 2, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 64, 0) == 64
     assert lib.dilution_carry_rows(0, 0, 64, 1) == 32 and lib.dilution_carry_rows(1, 2, 128, 0) == 32

@@ -136,3 +136,60 @@ def test_patched_alternating_model_matches_eager(pkg):
     for n, gr in eager_grads.items():
         err = (grads[n] - gr).abs().max().item() / (gr.abs().max().item() + 1e-12)
         assert err < 1e-1, (n, err)
+
+
+def test_graphed_decode_replays_the_layer_loop(pkg):
+    """GraphedDecode: the model's decode_step recorded once into a CUDA graph (length and position
+    read from the device) against the same model stepping launch by launch — same logits, same
+    caches, same demand; and the model's own decode_step takes over again after close()."""
+    if not os.path.isdir(os.path.join(REF, "dilution")):
+        pytest.skip("no installed copy of the reference under baseline/_ref")
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from dilution.config import ModelConfig
+    from dilution.model import DilutionLM
+    cfg = ModelConfig(context_length=400, vocab_size=512, n_layers=4, n_heads=4, d_model=256,
+                      layer_attention=["softmax", "dilution"] * 2, positional="rope_alt", mlp="swiglu",
+                      ffn_hidden=512)
+    torch.manual_seed(5)
+    model = DilutionLM(cfg).to(DEV).eval()
+    tokens = torch.randint(0, cfg.vocab_size, (3, 340), device=DEV)
+    prefix, graphed_until = 300, 330
+    pkg.install(fused_decode=True)
+    pkg.layers.install_layers()
+    try:
+        model.enable_dilution_kernel()
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            # launch by launch
+            logits, caches = model.prefill(tokens[:, :prefix], capacity=360)
+            want = []
+            for pos in range(prefix, tokens.shape[1]):
+                want.append(model.decode_step(tokens[:, pos:pos + 1], pos, caches)[:, -1].float())
+            # recorded
+            logits, caches_g = model.prefill(tokens[:, :prefix], capacity=360)
+        dec = pkg.GraphedDecode(model, caches_g)
+        before = pkg._lib.launch_count()
+        got = [dec.step(tokens[:, pos:pos + 1])[:, -1].float().clone() for pos in range(prefix, graphed_until)]
+        assert dec.graph is not None and int(dec.pos_dev.item()) == graphed_until == dec.position
+        # replays launch nothing through the library's host code: the eager step and the recorded one only
+        assert pkg._lib.launch_count() - before <= 2 * 4 * 5
+        dec.close()
+        assert all("pos_dev" not in c and c["len"] == graphed_until for c in caches_g)
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            for pos in range(graphed_until, tokens.shape[1]):       # the model's own loop again
+                got.append(model.decode_step(tokens[:, pos:pos + 1], pos, caches_g)[:, -1].float())
+        torch.cuda.synchronize()
+    finally:
+        pkg.layers.uninstall_layers()
+        pkg.uninstall()
+    got, want = torch.stack(got, 1), torch.stack(want, 1)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() < 2e-2
+    for c, e in zip(caches_g, caches):
+        assert c["len"] == e["len"] == tokens.shape[1]
+        assert (c["k"].float() - e["k"].float()).abs().max().item() < 2e-2
+        if "committed" in c:
+            assert (c["committed"] - e["committed"]).abs().max().item() < 1e-2
+    with pytest.raises(ValueError, match="ignores the position"):
+        pkg.GraphedDecode(DilutionLM(ModelConfig(context_length=64, vocab_size=64, n_layers=1, n_heads=2, d_model=64,
+                                                 positional="learned")), [{"k": caches[0]["k"], "len": 1}])
