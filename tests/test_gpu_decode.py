@@ -125,3 +125,33 @@ def test_fused_append_equals_append_then_step(kernels, dtype, d):
     assert rel_err(a["committed"][:, :, :n], f["committed"][:, :, :n]) < 1e-5
     assert (f["committed"][:, :, n:] == 7.0).all()          # rows past the length stay untouched
     assert rel_err(f["committed"][:, :, :n].cpu(), cc[:, :, :n]) < 1e-5
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("position", [0, 31, 32, 2047, 2048, 4095, 4998])
+def test_step_with_the_length_on_the_device(kernels, dtype, tol, position):
+    """cache["pos_dev"]: the launches read the new token's position from device memory and run with
+    the geometry of the full cache (dilution_decode_append_at) — against the oracle's step, with
+    the spare rows of the caches and of the demand untouched, at positions around chunk edges."""
+    b, h, d, cap = 1, 3, 64, 5000
+    g = torch.Generator().manual_seed(700 + position)
+    kc = torch.randn(b, h, cap, d, generator=g).mul(0.5).to(dtype)
+    vc = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    kc[:, :, position + 1:], vc[:, :, position + 1:] = 0, 0
+    q1 = torch.randn(b, h, 1, d, generator=g).mul(0.5).to(dtype)
+    committed = torch.rand(b, h, cap, generator=g)
+    committed[:, :, position:] = 0
+    want_c = committed.clone()
+    want = O.decode_step(q1, kc, vc, want_c, position + 1)
+    k1, v1 = kc[:, :, position:position + 1].clone(), vc[:, :, position:position + 1].clone()
+    kd, vd = kc.clone(), vc.clone()
+    kd[:, :, position], vd[:, :, position] = 3.0, 3.0            # stale rows the step must overwrite
+    cache = {"k": kd.to(DEV), "v": vd.to(DEV), "len": position, "committed": committed.clone().to(DEV),
+             "pos_dev": torch.tensor([position], device=DEV, dtype=torch.int32)}
+    cache["committed"][:, :, position] = 9.0                     # stale demand the step must ignore
+    got = kernels.dilution_decode_append_step(q1.to(DEV), k1.to(DEV), v1.to(DEV), cache)
+    assert got.dtype == dtype and cache["len"] == position + 1
+    assert rel_err(got.float().cpu(), want) < tol
+    assert rel_err(cache["committed"].cpu(), want_c) < 1e-5
+    assert torch.equal(cache["k"].cpu()[:, :, position], k1[:, :, 0]) and torch.equal(cache["v"].cpu()[:, :, position], v1[:, :, 0])
+    assert cache["k"][:, :, position + 1:].abs().max().item() == 0 and cache["committed"][:, :, position + 1:].abs().max().item() == 0
