@@ -45,7 +45,7 @@ SIGNATURES = {
     "dilution_decode_static": (_I, [_P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _P, _P, _P]),
     "dilution_decode_append_at": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _P, _I, _F, _F, _P, _P, _P, _P]),
     "dilution_softmax_decode_append_at": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _P, _I, _F, _P, _P, _P]),
-    "dilution_split_heads_rope_at": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _P]),
+    "dilution_split_heads_rope_at": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P, _P]),
     "dilution_variant_forward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I, _F,
                                       _P, _P, _P, _P, _P, _P, _P, _P]),
     "dilution_variant_backward": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _F, _F, _I, _I, _F,

@@ -662,7 +662,7 @@ int dilution_decode_append(const void* q1, const void* k1, const void* v1, void*
 
 static int split_heads_rope_impl(void* qkv, void* q, void* k, void* v, const void* cos_table,
                                  const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
-                                 int inverse, const int* pos_dev, void* stream) {
+                                 int inverse, const int* pos_dev, int64_t table_rows, void* stream) {
   if (!qkv || !q || !k || !v) return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: null pointer");
   if ((cos_table == nullptr) != (sin_table == nullptr))
     return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope: cos and sin tables go together");
@@ -682,11 +682,11 @@ static int split_heads_rope_impl(void* qkv, void* q, void* k, void* v, const voi
   if (inverse)                                                                                                 \
     dil::layer::split_heads_rope_kernel<false, DD><<<grid, 256, 0, st>>>(                                      \
         (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads,      \
-        pos_dev);                                                                                              \
+        pos_dev, table_rows);                                                                                  \
   else                                                                                                         \
     dil::layer::split_heads_rope_kernel<true, DD><<<grid, 256, 0, st>>>(                                       \
         (bf*)qkv, (bf*)q, (bf*)k, (bf*)v, (const bf*)cos_table, (const bf*)sin_table, batch, seq, heads,      \
-        pos_dev);
+        pos_dev, table_rows);
   if (d == 32) { DIL_ROPE(32) } else if (d == 64) { DIL_ROPE(64) } else { DIL_ROPE(128) }
 #undef DIL_ROPE
   return check_launch("split_heads_rope");
@@ -695,14 +695,17 @@ static int split_heads_rope_impl(void* qkv, void* q, void* k, void* v, const voi
 int dilution_split_heads_rope(void* qkv, void* q, void* k, void* v, const void* cos_table,
                               const void* sin_table, int64_t batch, int64_t seq, int heads, int d,
                               int inverse, void* stream) {
-  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, seq, heads, d, inverse, nullptr, stream);
+  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, seq, heads, d, inverse, nullptr, 0, stream);
 }
 
 int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const void* cos_table,
-                                 const void* sin_table, int64_t batch, int heads, int d,
+                                 const void* sin_table, int64_t table_rows, int64_t batch, int heads, int d,
                                  const int* position_dev, void* stream) {
   if (!position_dev) return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope_at: null position");
-  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, 1, heads, d, 0, position_dev, stream);
+  if (cos_table != nullptr && table_rows < 1)
+    return fail(DILUTION_ERR_ARG, "dilution_split_heads_rope_at: table_rows must be the tables' row count");
+  return split_heads_rope_impl(qkv, q, k, v, cos_table, sin_table, batch, 1, heads, d, 0, position_dev,
+                               table_rows, stream);
 }
 
 int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v1, void* k_cache,

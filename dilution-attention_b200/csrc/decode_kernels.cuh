@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   // the number of valid keys: a launch argument, or (a step inside a captured graph, whose
   // arguments are frozen) the new token's position read from device memory, plus one
-  const int len = pos_dev != nullptr ? *pos_dev + 1 : len_arg;
+  // (held inside the cache: a position past the capacity rewrites the last row instead of
+  // writing behind the cache; the caller owns the count)
+  const int len = pos_dev != nullptr ? min(max(*pos_dev + 1, 1), (int)cap) : len_arg;
   const int64_t n = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = lane % TPK, grp = lane / TPK;
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
                                                    int bid, int share_step, float lshift,
                                                    const int* __restrict__ pos_dev) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
-  const int len = pos_dev != nullptr ? *pos_dev + 1 : len_arg;      // as in scores_kernel
+  const int len = pos_dev != nullptr ? min(max(*pos_dev + 1, 1), (int)cap) : len_arg;   // as in scores_kernel
   const int64_t n = blockIdx.y;
   const int nch = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -51,7 +51,8 @@ __global__ void split_heads_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bf
                                         __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
                                         const __nv_bfloat16* __restrict__ cos_t,
                                         const __nv_bfloat16* __restrict__ sin_t, int64_t batch, int64_t seq,
-                                        int heads, const int* __restrict__ pos_dev) {
+                                        int heads, const int* __restrict__ pos_dev,
+                                        int64_t table_rows) {
   constexpr int SL = D / 8;                                  // 16-byte slices per head row
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = batch * seq * heads * SL;
@@ -67,7 +68,9 @@ __global__ void split_heads_rope_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bf
   if (rot) {
     // table row = position of the token: its row in this call, plus (a step inside a captured
     // graph, whose arguments are frozen) the first row's position read from device memory
-    const int64_t tr = t + (pos_dev != nullptr ? *pos_dev : 0);
+    // (a position outside the table is held at its nearest row: wrong angles, no stray read)
+    int64_t tr = t;
+    if (pos_dev != nullptr) tr = min(max(t + (int64_t)*pos_dev, (int64_t)0), table_rows - 1);
     const uint2 cr = *reinterpret_cast<const uint2*>(cos_t + tr * (D / 2) + sl * 4);
     const uint2 sr = *reinterpret_cast<const uint2*>(sin_t + tr * (D / 2) + sl * 4);
     c[0] = __uint_as_float(cr.x << 16); c[1] = __uint_as_float(cr.x & 0xffff0000u);

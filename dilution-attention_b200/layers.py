@@ -113,10 +113,16 @@ def split_heads_at(layer, x1, cache):
     qkv = qkv.contiguous()
     q, k, v = (torch.empty(batch, heads, 1, d, device=qkv.device, dtype=qkv.dtype) for _ in range(3))
     cos = sin = None
-    if layer.rope is not None:          # tables for every position the cache can hold
-        cos, sin = rope_tables(layer.rope, cache["k"].shape[2], 0, qkv.device, qkv.dtype)
+    if layer.rope is not None:
+        # tables for every position the cache can hold, kept with the cache: a recorded graph
+        # holds their addresses, so they must live as long as the cache does
+        tables = cache.get("rope_tables")
+        if tables is None:
+            tables = cache["rope_tables"] = rope_tables(layer.rope, cache["k"].shape[2], 0, qkv.device, qkv.dtype)
+        cos, sin = tables
     _lib.check(lib.dilution_split_heads_rope_at(qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                                K._ptr(cos), K._ptr(sin), batch, heads, d,
+                                                K._ptr(cos), K._ptr(sin),
+                                                0 if cos is None else cos.shape[0], batch, heads, d,
                                                 cache["pos_dev"].data_ptr(), K._stream(qkv.device)),
                "dilution_split_heads_rope_at")
     return q, k, v
@@ -236,6 +242,7 @@ class GraphedDecode:
         """Detach the device-side position: the caches are the model's plain dicts again."""
         for c in self.caches:
             c.pop("pos_dev", None)
+            c.pop("rope_tables", None)
             c["len"] = self.position
         self.graph = None
 

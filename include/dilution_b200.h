@@ -280,12 +280,13 @@ int dilution_decode_static(const void* q1, const void* k_cache, const void* v_ca
  * token, with a one-element increment of that int recorded at the end of the step.  The launch
  * geometry is that of a full cache: the scratch is dilution_decode_scratch_bytes(n, capacity, d),
  * chunks behind the last key write neutral statistics and return.  The caller guarantees
- * *position_dev < capacity.
+ * 0 <= *position_dev < capacity; a value outside is held at the nearest row (the step then
+ * rewrites that row: a wrong result, never an access outside the cache or the tables).
  *   dilution_decode_append_at          dilution_decode_append with length = *position_dev + 1
  *   dilution_softmax_decode_append_at  dilution_softmax_decode_append likewise (k1, v1 required)
  *   dilution_split_heads_rope_at       the head split of ONE token per batch row (seq = 1) whose
- *                                      rotation uses row *position_dev of cos / sin tables that
- *                                      cover every position up to the capacity */
+ *                                      rotation uses row *position_dev of cos / sin tables of
+ *                                      table_rows rows (every position up to the capacity) */
 int dilution_decode_append_at(const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
                               int dtype, int64_t n, int64_t capacity, const int* position_dev, int d,
                               float scale, float eps, float* committed, void* out, void* scratch,
@@ -295,8 +296,8 @@ int dilution_softmax_decode_append_at(const void* q1, const void* k1, const void
                                       const int* position_dev, int d, float scale, void* out, void* scratch,
                                       void* stream);
 int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const void* cos_table,
-                                 const void* sin_table, int64_t batch, int heads, int d,
-                                 const int* position_dev, void* stream);
+                                 const void* sin_table, int64_t table_rows, int64_t batch, int heads,
+                                 int d, const int* position_dev, void* stream);
 
 /* ---- share / bid variants ------------------------------------------------------------
  * The ablations a model configuration can select besides the operator itself

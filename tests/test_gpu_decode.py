@@ -155,3 +155,46 @@ def test_step_with_the_length_on_the_device(kernels, dtype, tol, position):
     assert rel_err(cache["committed"].cpu(), want_c) < 1e-5
     assert torch.equal(cache["k"].cpu()[:, :, position], k1[:, :, 0]) and torch.equal(cache["v"].cpu()[:, :, position], v1[:, :, 0])
     assert cache["k"][:, :, position + 1:].abs().max().item() == 0 and cache["committed"][:, :, position + 1:].abs().max().item() == 0
+
+
+def test_position_past_the_capacity_stays_inside_the_cache(kernels, pkg):
+    """The C-ABI step with the position on the device holds a position outside [0, capacity) at the
+    nearest row: the result is the caller's problem, the memory around the caches is not touched
+    (dilution_decode_append_at, dilution_softmax_decode_append_at)."""
+    from importlib import import_module
+    _lib = import_module(pkg.__name__ + "._lib")
+    lib = _lib.load()
+    n, d, cap, pad = 3, 64, 300, 64
+    g = torch.Generator().manual_seed(77)
+
+    def guarded(rows, width, dtype):            # a cache with sentinel rows on both sides
+        buf = torch.full((pad + rows + pad, width), 7.0, dtype=dtype, device=DEV)
+        buf[pad:pad + rows] = torch.randn(rows, width, generator=g).to(dtype).to(DEV)
+        return buf, buf[pad:pad + rows]
+
+    kbuf, kc = guarded(n * cap, d, torch.bfloat16)
+    vbuf, vc = guarded(n * cap, d, torch.bfloat16)
+    cbuf, committed = guarded(n * cap, 1, torch.float32)
+    committed.copy_(torch.rand(n * cap, 1, generator=g).to(DEV))
+    q1, k1, v1 = (torch.randn(n, d, generator=g).to(torch.bfloat16).to(DEV) for _ in range(3))
+    out = torch.empty(n, d, device=DEV, dtype=torch.bfloat16)
+    scratch = kernels.decode_scratch(n, cap, d, DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    for position in (cap, cap + 5, 1 << 20, -3):
+        pos = torch.tensor([position], device=DEV, dtype=torch.int32)
+        rc = lib.dilution_decode_append_at(q1.data_ptr(), k1.data_ptr(), v1.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                           _lib.BF16, n, cap, pos.data_ptr(), d, d ** -0.5, 1e-9, committed.data_ptr(),
+                                           out.data_ptr(), scratch.data_ptr(), stream)
+        assert rc == 0
+        rc = lib.dilution_softmax_decode_append_at(q1.data_ptr(), k1.data_ptr(), v1.data_ptr(), kc.data_ptr(),
+                                                   vc.data_ptr(), _lib.BF16, n, cap, pos.data_ptr(), d, d ** -0.5,
+                                                   out.data_ptr(), scratch.data_ptr(), stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.isfinite(out.float()).all()
+        for buf, rows in ((kbuf, n * cap), (vbuf, n * cap), (cbuf, n * cap)):
+            assert (buf[:pad] == 7.0).all() and (buf[pad + rows:] == 7.0).all()
+        # the row the step wrote is the nearest one inside the cache
+        row = cap - 1 if position >= cap else 0
+        got_k = kc.view(n, cap, d)[:, row]
+        assert torch.equal(got_k, k1)
