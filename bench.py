@@ -547,7 +547,7 @@ def run_ours(args):
     decode = None if args.no_decode else run_decode(c, args)
     lm = None
     if not args.no_lm:
-        lm = run_lm(c, args) if c.world == 1 else {"skipped": "measured on 1 GPU only (no tensor-parallel model)"}
+        lm = run_lm(c, args)
 
     # 0 unless a kernel of this run gave up one of its bounded waits (rank 0's device)
     device_status = c.L.load().dilution_device_status()
@@ -900,11 +900,16 @@ def run_lm(c, args):
         idx_h = torch.randint(0, LM["vocab"], (B, T + 1), generator=g).pin_memory()
         idx_gen_full = torch.randint(0, LM["vocab"], (nb, prompt), generator=g).to(dev)
 
+        def shard(model):
+            """more than one rank: every rank builds the same weights (same seed), keeps 16 / N heads
+            and 1 / N of each MLP, and feeds the same tokens (partition.shard_lm_heads)"""
+            return c.pkg.partition.shard_lm_heads(model) if c.world > 1 else model
+
         def train(steps):
             """forward, loss, backward, gradient clipping, fused AdamW; token ids come from the host
             and the loss is read back every step"""
             torch.manual_seed(1344)
-            model = DilutionLM(config(T)).to(dev).train()
+            model = shard(DilutionLM(config(T)).to(dev)).train()
             model.enable_dilution_kernel()
             opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
 
@@ -913,7 +918,10 @@ def run_lm(c, args):
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     _, loss = model(tok[:, :-1], tok[:, 1:])
                 loss.backward()
-                torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                if c.world > 1:
+                    c.pkg.partition.clip_grad_norm_(model, 1.0)
+                else:
+                    torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
                 opt.step()
                 opt.zero_grad(set_to_none=True)
                 return loss.item()
@@ -933,7 +941,7 @@ def run_lm(c, args):
             """DilutionLM.prefill + greedy decode_step loop (model.py:451-470, 498-509)"""
             idx_gen = idx_gen_full[:, :prompt]
             torch.manual_seed(1345)
-            model = DilutionLM(config(prompt + new)).to(dev).eval()
+            model = shard(DilutionLM(config(prompt + new)).to(dev)).eval()
             model.enable_dilution_kernel()
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
@@ -983,6 +991,18 @@ def run_lm(c, args):
         steps = max(1, min(args.steps, 3))
         c.pkg.install(fused_decode=True)
         c.pkg.install_layers()
+        if c.world > 1:
+            # the same global batch with the model's heads over the ranks: strong scaling; two
+            # all-reduces per block and direction (after c_proj and after the MLP) are the only
+            # exchanges (in the graphed decode loop they are recorded with the rest of the step)
+            res["parallelism"] = (f"heads sharded over {c.world} ranks (partition.shard_lm_heads): "
+                                  f"{LM['heads'] // c.world} heads and 1/{c.world} of each MLP per rank, NCCL "
+                                  "all-reduce after c_proj and after the MLP; embedding, LayerNorms, lm_head replicated")
+            res["scaling"] = "strong"
+            res["train"] = train(steps)
+            res["generate"] = generate(new, graphed=True)
+            res["gpu_launches"] = c.L.launch_count() - launches0
+            return res
         res["train"] = train(steps)
         res["generate"] = generate(new, graphed=True)
         # a short context, where a token's ~200 launches cost more than the bytes they move

@@ -201,3 +201,152 @@ def sequence_parallel_prefill(q_local, k_local, v_local, seq: int, bounds: list[
 
     out, _ = prefill_chunk(q_local, k_seen, v_seen, bounds[rank], dot_precision, exchange=exchange, mark=mark)
     return out, result["demand"]
+
+
+# ---- the LM with its heads sharded over ranks ------------------------------------------------
+# The attention operator shards by (batch, head) rows with no exchange; a model gets those rows
+# onto different GPUs by giving each rank a slice of the heads.  What follows is the usual
+# tensor-parallel split of a transformer block around that: the projections that produce heads
+# (c_attn; the MLP's up / gate projections) are split by output features, the ones that consume
+# them (c_proj; the MLP's down projection) by input features, and ONE all-reduce follows each of
+# the latter.  Embedding, LayerNorms and lm_head stay replicated.
+class _CopyToRanks(torch.autograd.Function):
+    """Identity forward; the backward sums the input's gradient over the ranks (every rank holds
+    only its heads' contribution to it)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _SumOverRanks(torch.autograd.Function):
+    """All-reduce forward (partial products of the row-split projection); identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous().clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class HeadParallelInput(torch.nn.Module):
+    """`inner(x)` for an `inner` whose output features are split over the ranks."""
+
+    def __init__(self, inner, group):
+        super().__init__()
+        self.inner, self.group = inner, group
+
+    def forward(self, x):
+        return self.inner(_CopyToRanks.apply(x, self.group))
+
+
+class HeadParallelOutput(torch.nn.Module):
+    """A projection whose INPUT features are split over the ranks: local product, all-reduce,
+    then the (replicated) bias once."""
+
+    def __init__(self, weight, bias, group):
+        super().__init__()
+        self.weight = torch.nn.Parameter(weight)
+        self.weight.head_sharded = True
+        self.bias = None if bias is None else torch.nn.Parameter(bias)
+        self.group = group
+
+    def forward(self, x):
+        y = _SumOverRanks.apply(torch.nn.functional.linear(x, self.weight), self.group)
+        return y if self.bias is None else y + self.bias.to(y.dtype)
+
+
+def _rows_of(linear, index):
+    """nn.Linear keeping the output features `index` of `linear`."""
+    out = torch.nn.Linear(linear.in_features, index.numel(), bias=linear.bias is not None,
+                          device=linear.weight.device, dtype=linear.weight.dtype)
+    with torch.no_grad():
+        out.weight.copy_(linear.weight[index])
+        if linear.bias is not None:
+            out.bias.copy_(linear.bias[index])
+    for p in out.parameters():
+        p.head_sharded = True                      # a slice: its gradient norm is a partial one
+    return out
+
+
+def _columns_of(linear, index, group):
+    """HeadParallelOutput keeping the input features `index` of `linear`."""
+    with torch.no_grad():
+        weight = linear.weight[:, index].clone()
+        bias = None if linear.bias is None else linear.bias.detach().clone()
+    return HeadParallelOutput(weight, bias, group)
+
+
+def shard_lm_heads(model, group=None):
+    """Split an initialised `DilutionLM` (model.py:342-512) over the ranks of `group` IN PLACE:
+    every attention layer keeps n_heads / world of its heads (the rows of `c_attn` that produce
+    them, the columns of `c_proj` that consume them), every MLP hidden / world of its units, and
+    one all-reduce follows `c_proj` and the MLP's last projection.  All ranks must hold the same
+    weights when this is called (same seed, or a broadcast), and must feed the same tokens; every
+    rank then computes the same logits and loss as the unsplit model, with 1 / world of the
+    attention rows, the projection FLOPs and the KV cache.  Gradients of the replicated
+    parameters (embedding, LayerNorms, biases behind an all-reduce) come out identical on every
+    rank; the split weights' gradients are the matching slices of the unsplit ones.  The layers'
+    `n_heads` / `d_model` attributes become the local ones, which is all `_split_heads`,
+    `_merge_heads`, the caches and this library's kernels read (model.py:59-93)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if world == 1:
+        return model
+    for block in model.transformer.h:
+        attn = block.attn
+        if not hasattr(attn, "c_attn"):
+            raise ValueError(f"cannot shard a {type(attn).__name__} layer by heads")
+        heads, width = attn.n_heads, attn.d_model
+        if heads % world:
+            raise ValueError(f"{heads} heads do not divide over {world} ranks")
+        local = width // world                                     # features of this rank's heads
+        dev = attn.c_attn.weight.device
+        mine = torch.arange(rank * local, (rank + 1) * local, device=dev)
+        attn.c_attn = HeadParallelInput(
+            _rows_of(attn.c_attn, torch.cat([mine, width + mine, 2 * width + mine])), group)
+        attn.c_proj = _columns_of(attn.c_proj, mine, group)
+        attn.n_heads, attn.d_model = heads // world, local
+        mlp = block.mlp
+        ups = [name for name in ("gate_proj", "up_proj", "c_fc") if hasattr(mlp, name)]
+        down = "down_proj" if hasattr(mlp, "down_proj") else "c_proj"
+        hidden = getattr(mlp, down).in_features
+        if hidden % world:
+            raise ValueError(f"MLP width {hidden} does not divide over {world} ranks")
+        units = torch.arange(rank * (hidden // world), (rank + 1) * (hidden // world), device=dev)
+        for name in ups:
+            setattr(mlp, name, _rows_of(getattr(mlp, name), units))
+        setattr(mlp, down, _columns_of(getattr(mlp, down), units, group))
+        block.mlp = HeadParallelInput(mlp, group)
+    return model
+
+
+def clip_grad_norm_(model, max_norm: float, group=None) -> torch.Tensor:
+    """`torch.nn.utils.clip_grad_norm_` for a model split by `shard_lm_heads`: the squared norms
+    of the split weights' gradients are summed over the ranks, the replicated parameters count
+    once, and every rank scales by the same factor.  Returns the total norm (of the whole model)."""
+    sharded = [p.grad for p in model.parameters() if p.grad is not None and getattr(p, "head_sharded", False)]
+    whole = [p.grad for p in model.parameters() if p.grad is not None and not getattr(p, "head_sharded", False)]
+    ref = (sharded or whole)[0]
+    part = ref.new_zeros((), dtype=torch.float32)
+    if sharded:
+        part = torch.stack([g.float().pow(2).sum() for g in sharded]).sum()
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(part, group=group)
+    rest = torch.stack([g.float().pow(2).sum() for g in whole]).sum() if whole else part.new_zeros(())
+    total = (part + rest).sqrt()
+    factor = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+    for g in sharded + whole:
+        g.mul_(factor.to(g.dtype))
+    return total
