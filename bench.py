@@ -480,7 +480,7 @@ def train_roofline(kernels_ms, n_rows, T, D, value_per_gpu, peaks):
     # with the tile count.  Only the backward main pass has a captured figure.
     executed = 11 if any("forward_fused" in name for name in kernels_ms) else 12
     tiles = n_rows * (T // 128) * (T // 128 + 1) // 2
-    traffic = 1341.02e6 / (64 * 528) * tiles if "backward_main" in dom else None
+    traffic = 1341.92e6 / (64 * 528) * tiles if "backward_main" in dom else None
     return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tensor"],
             "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
             "traffic_source": "constant from one ncu capture of this kernel at T=4096, scaled by causal "
