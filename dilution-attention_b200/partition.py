@@ -304,6 +304,10 @@ def shard_lm_heads(model, group=None):
     rank = dist.get_rank(group)
     if world == 1:
         return model
+    if getattr(model.config, "dropout", 0.0) > 0.0:
+        # the replicated activations (residual stream, MLP output) would draw a different mask on
+        # every rank, and the ranks' copies of the model would drift apart
+        raise ValueError("a model with dropout cannot be split by heads: the ranks' dropout masks differ")
     for block in model.transformer.h:
         attn = block.attn
         if not hasattr(attn, "c_attn"):

@@ -105,6 +105,11 @@ def _lm_worker(rank, world, port, variant, q):
                         p.add_(0.1 * torch.randn(p.shape, generator=torch.Generator().manual_seed(p.numel())))
         split = P.shard_lm_heads(copy.deepcopy(whole))
         assert split.transformer.h[0].attn.n_heads == 4 // world
+        try:                                       # dropout masks would differ between the ranks
+            P.shard_lm_heads(DilutionLM(ModelConfig(**dict(kw, dropout=0.1))))
+            raise AssertionError("a model with dropout was split")
+        except ValueError:
+            pass
         idx = torch.randint(0, 96, (2, 41), generator=torch.Generator().manual_seed(6))
         # training step: logits, loss, gradients
         lw, loss_w = whole(idx[:, :-1], idx[:, 1:])
