@@ -53,7 +53,8 @@ SIGNATURES = {
     "dilution_variant_decode": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _F, _F, _I, _I, _F, _P, _P, _P, _P]),
 }
 # codes of the reference's BID_TYPES (kernels_bid.py:84) for the bids that are built
-BID = {"softmax": 0, "sigmoid": 5, "expshift": 6, "sigshift": 7}
+BID = {"softmax": 0, "relu": 1, "relu2": 2, "softplus": 3, "minshift": 4, "sigmoid": 5, "expshift": 6, "sigshift": 7}
+ROW_SUM_BIDS = (0, 1, 2, 3, 4)      # bids with row statistics and a Jacobian correction in the backward
 
 _lib = None
 

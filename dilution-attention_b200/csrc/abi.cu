@@ -112,8 +112,9 @@ dil::Geom make_geom(int64_t n, int64_t tq, int64_t tk, int64_t q_offset, float s
   g.carry_rows = carry_rows;
   g.bid = dil::bid_form(bid);
   g.share = share;
-  g.normalised = bid == dil::kBidSoftmax;
+  g.normalised = bid == dil::kBidSoftmax || dil::row_sum_bid(bid);
   g.lshift = (bid == dil::kBidExpshift || bid == dil::kBidSigshift) ? log2f(shift) : 0.f;
+  g.ghat_pass = 0;
   g.n = n;
   g.tq = (int)tq;
   g.tk = (int)tk;
@@ -237,19 +238,26 @@ int launch_backward(const void* q, const void* k, const void* v, const dil::Geom
   if (int rc = check_launch("dbar")) return rc;
   const int nkb = (g.tk + TS - 1) / TS;
   const unsigned grid = (unsigned)(g.n * nkb);
-  {
+  // an f(a) / rowsum(f) bid under a share step: its Jacobian factor 1 / (row mass) is unbounded, so
+  // ghat is found first and subtracted before the factor multiplies (two sweeps, as the reference's
+  // B1-B2 then B4, kernels_bid.py:513-612, 659-728); everything else: one sweep, correction afterwards
+  const bool two_sweeps = dil::row_sum_bid(g.bid) && g.share != dil::kShareNone;
+  for (int sweep = two_sweeps ? 1 : 0; sweep <= (two_sweeps ? 2 : 0); ++sweep) {
+    dil::Geom gs = g;
+    gs.ghat_pass = sweep;
     auto kern = backward_main_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_main<D>())) return rc;
     {
-      Prof prof("simt_backward_main", st);
-      kern<<<grid, NT, smem_bwd_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, g, dout, s.dbar,
+      Prof prof(sweep == 1 ? "simt_backward_ghat" : "simt_backward_main", st);
+      kern<<<grid, NT, smem_bwd_main<D>(), st>>>((const T*)q, (const T*)k, (const T*)v, gs, dout, s.dbar,
                                                   ssum, rmax, rden, carry, s.dq_main, s.dk_main,
                                                   (T*)dv, s.ghat);
     }
     if (int rc = check_launch("backward_main")) return rc;
   }
   const int64_t total = rows * D;
-  const bool corrected = g.normalised && g.share != dil::kShareNone;   // without a share step ghat is identically 0
+  // without a share step ghat is identically 0; with two sweeps it is already inside dk_main / dq_main
+  const bool corrected = g.normalised && g.share != dil::kShareNone && !two_sweeps;
   if (corrected) {
     auto kern = backward_dk_correction_kernel<T, D, MMA>;
     if (int rc = set_smem(kern, smem_bwd_dk<D>())) return rc;
@@ -313,9 +321,14 @@ int launch_decode(const void* q1, const void* kc, const void* vc, int64_t n, int
   const dim3 grid((unsigned)nch, (unsigned)n);
   {
     Prof prof("decode_scores", st, timing);
-    scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
-                                             scale * dil::kLog2e, stride, s.aff, s.part,
-                                             (const T*)knew, (T*)const_cast<void*>(kc), pos_dev);
+    if (MODE == dil::decode::kSweepVariant && dil::row_sum_bid(bid))
+      scores_kernel<T, D, true><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
+                                                     scale * dil::kLog2e, stride, s.aff, s.part,
+                                                     (const T*)knew, (T*)const_cast<void*>(kc), pos_dev, bid);
+    else
+      scores_kernel<T, D><<<grid, NT, 0, st>>>((const T*)q1, (const T*)kc, cap, (int)len, chunk,
+                                               scale * dil::kLog2e, stride, s.aff, s.part,
+                                               (const T*)knew, (T*)const_cast<void*>(kc), pos_dev);
   }
   if (int rc = check_launch("decode scores")) return rc;
   {
@@ -732,8 +745,9 @@ int dilution_softmax_decode_append(const void* q1, const void* k1, const void* v
 
 // ---- share / bid variants (the tile kernels; kernels_bid.py of the reference) -------------
 static int check_variant(const char* fn, int bid, int share, float shift) {
-  if (bid != dil::kBidSoftmax && bid != dil::kBidSigmoid && bid != dil::kBidExpshift && bid != dil::kBidSigshift)
-    return fail(DILUTION_ERR_UNSUPPORTED, "%s: bid %d is not built (softmax 0, sigmoid 5, expshift 6, sigshift 7)", fn, bid);
+  if (bid < 0 || bid > 7)
+    return fail(DILUTION_ERR_ARG, "%s: bid %d is not one of softmax 0, relu 1, relu2 2, softplus 3, minshift 4, "
+                "sigmoid 5, expshift 6, sigshift 7", fn, bid);
   if ((bid == dil::kBidExpshift || bid == dil::kBidSigshift) && !(shift > 0.f))
     return fail(DILUTION_ERR_ARG, "%s: shift must be positive", fn);
   if (share != dil::kShareNone && share != dil::kShareInclusive && share != dil::kShareExclusive)
@@ -747,17 +761,18 @@ int dilution_variant_forward(const void* q, const void* k, const void* v, int dt
                              void* stream) {
   if (int rc = check_common("dilution_variant_forward", dtype, precision, n, t, t, 0, d)) return rc;
   if (int rc = check_variant("dilution_variant_forward", bid, share, shift)) return rc;
-  const bool stats = bid == dil::kBidSoftmax;
+  const bool stats = bid == dil::kBidSoftmax || dil::row_sum_bid(bid);   // bids with row statistics
   // without a share step nothing downstream reads the checkpoints: carry and total may both be
   // NULL, and the column-sum pass is skipped
   const bool scan = !(share == dil::kShareNone && carry == nullptr && total == nullptr);
   if (!q || !k || !v || (scan && (!carry || !total)) || !out || !ssum || (stats && (!rmax || !rden)))
     return fail(DILUTION_ERR_ARG, "dilution_variant_forward: null pointer");
-  if (!stats) rmax = rden = pk = nullptr;
+  if (!stats) rmax = rden = nullptr;
+  if (bid != dil::kBidSoftmax) pk = nullptr;       // only the softmax bid's backward reads pk
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share, shift);
   cudaStream_t st = (cudaStream_t)stream;
 #if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_MAIN
-  if (dil::tc::supported(dtype, precision, d, 0)) {
+  if (dil::tc::supported(dtype, precision, d, 0) && !dil::row_sum_bid(bid)) {
     // bf16 tensors, head_dim 64: the tcgen05 kernels, instantiated for the bid and share step
     if (stats && pk) {
       Prof prof("tc_rowstats_pk", st);
@@ -795,18 +810,18 @@ int dilution_variant_backward(const void* q, const void* k, const void* v, int d
                               void* dk, void* dv, void* stream) {
   if (int rc = check_common("dilution_variant_backward", dtype, precision, n, t, t, 0, d)) return rc;
   if (int rc = check_variant("dilution_variant_backward", bid, share, shift)) return rc;
-  const bool stats = bid == dil::kBidSoftmax;
+  const bool stats = bid == dil::kBidSoftmax || dil::row_sum_bid(bid);
   if (!q || !k || !v || !dout || !out || !ssum || !scratch || !dq || !dk || !dv ||
       (share != dil::kShareNone && (!carry || !total)) || (stats && (!rmax || !rden)) ||
-      (stats && share != dil::kShareNone && !pk))
+      (bid == dil::kBidSoftmax && share != dil::kShareNone && !pk))
     return fail(DILUTION_ERR_ARG, "dilution_variant_backward: null pointer");
   if (!stats) rmax = rden = nullptr;
-  if (!stats || share == dil::kShareNone) pk = nullptr;
+  if (bid != dil::kBidSoftmax || share == dil::kShareNone) pk = nullptr;
   const dil::Geom g = make_geom(n, t, t, 0, scale, eps, dil::kCarryRows, bid, share, shift);
   const BwdScratch s = carve_bwd(scratch, n, t, d);
   cudaStream_t st = (cudaStream_t)stream;
 #if defined(DILUTION_TENSOR_PATH) && DILUTION_TC_HAS_BACKWARD
-  if (dil::tc::supported(dtype, precision, d, 0))
+  if (dil::tc::supported(dtype, precision, d, 0) && !dil::row_sum_bid(bid))
     return dil::tc::backward(q, k, v, g, dout, DILUTION_F32, out, rmax, rden, carry, total, ssum, pk, s.dq_main,
                              s.dk_main, s.ghat, s.dbar, s.dop, dq, dk, dv, st, g_err, sizeof(g_err), mark_scope);
 #endif

@@ -8,6 +8,7 @@
 namespace dil {
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 constexpr int kCarryRows = 32;  // query rows per demand checkpoint of the fp32 kernels
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
@@ -112,19 +113,38 @@ struct Geom {
   float scale;
   float eps;
   int carry_rows; // query rows per demand checkpoint (16, 32 or 64)
-  int bid;        // FORM of the bid: kBidSoftmax 2^(z - l) or kBidSigmoid 1/(1 + 2^(l - z))
+  int bid;        // FORM of the bid: kBidSoftmax 2^(z - l), kBidSigmoid 1/(1 + 2^(l - z)), or one of the
+                  // four f(a) / rowsum(f) bids (fp32 tile kernels only)
   int share;      // share step (kernels_bid.py:123-127): 1 inclusive, 2 exclusive history, 0 none
-  int normalised; // the bid divides by its row sum (softmax): l is the row's log-sum-exp and the
-                  // backward has the Jacobian correction ghat; otherwise l = lshift for every row
+  int normalised; // the bid divides by its row sum (softmax, relu, relu2, softplus, minshift): there are
+                  // row statistics and the backward has the Jacobian correction ghat; otherwise
+                  // l = lshift for every row
   float lshift;   // log2 of the shift of expshift / sigshift (kernels_bid.py:19-26); 0 for the sigmoid
+  int ghat_pass;  // reverse pass of an f(a) / rowsum(f) bid, whose Jacobian factor is unbounded (1 / row mass):
+                  // 1 = accumulate ghat only, 2 = ghat is known and is subtracted BEFORE the factor
+                  // multiplies (kernels_bid.py:718); 0 = one pass, correction afterwards (softmax: jac = p <= 1)
 };
 
 // Bid codes of the reference (kernels_bid.py:84) that are built, and the form each one takes:
 // expshift = the softmax form without the row sum, sigshift = the sigmoid form, both with l = log2(shift).
 constexpr int kBidSoftmax = 0, kBidSigmoid = 5, kBidExpshift = 6, kBidSigshift = 7;
+// f(a) / rowsum(f) bids (kernels_bid.py:5-10, 206-225): relu(a), relu(a)^2, softplus(a), a - rowmin(a).
+// Row statistics: rmax holds the row minimum for minshift (0 otherwise), rden the row sum of f;
+// a row without mass (rden = 0) bids uniformly over its causal window, with a zero Jacobian.
+constexpr int kBidRelu = 1, kBidRelu2 = 2, kBidSoftplus = 3, kBidMinshift = 4;
+__host__ __device__ constexpr bool row_sum_bid(int bid) { return bid >= kBidRelu && bid <= kBidMinshift; }
 __host__ __device__ constexpr int bid_form(int bid) {
-  return (bid == kBidSigmoid || bid == kBidSigshift) ? kBidSigmoid : kBidSoftmax;
+  return row_sum_bid(bid) ? bid : (bid == kBidSigmoid || bid == kBidSigshift) ? kBidSigmoid : kBidSoftmax;
 }
 constexpr int kShareNone = 0, kShareInclusive = 1, kShareExclusive = 2;
+
+// f of the scaled score a for the f(a) / rowsum(f) bids (minshift: the caller subtracts the row minimum).
+__device__ __forceinline__ float bid_mass(float a, int bid) {
+  if (bid == kBidMinshift) return a;
+  const float f = fmaxf(a, 0.f);
+  if (bid == kBidRelu) return f;
+  if (bid == kBidRelu2) return f * f;
+  return f + log1pf(expf(-fabsf(a)));                     // stable softplus
+}
 
 }  // namespace dil

@@ -65,14 +65,16 @@ struct Scratch {
 };
 
 // grid = (chunks, n)
-template <typename T, int D>
+// MASS: an f(a) / rowsum(f) bid (kernels_bid.py:880-911) — the chunk statistics are (minimum of
+// the scaled scores, sum of f) instead of the softmax's (maximum, sum of exponentials).
+template <typename T, int D, bool MASS = false>
 __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
                                                     const T* __restrict__ kc, int64_t cap,
                                                     int len_arg, int chunk, float zscale,
                                                     int64_t stride, float* __restrict__ aff,
                                                     float2* __restrict__ part,
                                                     const T* __restrict__ knew, T* __restrict__ kc_out,
-                                                    const int* __restrict__ pos_dev) {
+                                                    const int* __restrict__ pos_dev, int bid = kBidSoftmax) {
   constexpr int E = Cfg<T, D>::E, TPK = Cfg<T, D>::TPK;
   // the number of valid keys: a launch argument, or (a step inside a captured graph, whose
   // arguments are frozen) the new token's position read from device memory, plus one
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
   const bool appends = knew != nullptr && len - 1 >= k0 && len - 1 < k0 + chunk;
   const int k1 = min(len, k0 + chunk) - (appends ? 1 : 0);
   const T* krow = kc + n * cap * D + t * E;
-  float m = -INFINITY, s = 0.f;
+  float m = MASS ? INFINITY : -INFINITY, s = 0.f;
   for (int base = k0 + warp * 32; base < k1; base += ROUND) {
     float mine = -INFINITY;
     uint4 raw[TPK];
@@ -119,9 +121,15 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
     const int key = base + lane;   // == base + grp*TPK + t
     if (key < k1) {
       aff[n * stride + key] = mine;
-      const float nm = fmaxf(m, mine);
-      s = s * exp2f(m - nm) + exp2f(mine - nm);
-      m = nm;
+      if (MASS) {
+        const float a = mine * kLn2;             // the scores are kept in the log2 domain
+        s += bid_mass(a, bid);
+        m = fminf(m, a);
+      } else {
+        const float nm = fmaxf(m, mine);
+        s = s * exp2f(m - nm) + exp2f(mine - nm);
+        m = nm;
+      }
     }
   }
   if (appends && warp == 0) {
@@ -139,13 +147,29 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
     for (int o = TPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     if (lane == 0) {
       aff[n * stride + len - 1] = dot;
-      const float nm = fmaxf(m, dot);
-      s = s * exp2f(m - nm) + exp2f(dot - nm);
-      m = nm;
+      if (MASS) {
+        s += bid_mass(dot * kLn2, bid);
+        m = fminf(m, dot * kLn2);
+      } else {
+        const float nm = fmaxf(m, dot);
+        s = s * exp2f(m - nm) + exp2f(dot - nm);
+        m = nm;
+      }
     }
   }
   // chunk statistics
   __shared__ float sm[WARPS], ss[WARPS];
+  if (MASS) {
+    const float wmin = -warp_max(-m), wsum = warp_sum(s);
+    if (lane == 0) { sm[warp] = wmin; ss[warp] = wsum; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float cm = INFINITY, cs = 0.f;
+      for (int w = 0; w < WARPS; ++w) { cm = fminf(cm, sm[w]); cs += ss[w]; }
+      part[n * MAX_CHUNKS + blockIdx.x] = make_float2(cm, cs);
+    }
+    return;
+  }
   const float wm = warp_max(m);
   const float ws = warp_sum(wm > -INFINITY ? s * exp2f(m - wm) : 0.f);
   if (lane == 0) { sm[warp] = wm; ss[warp] = ws; }
@@ -164,17 +188,23 @@ __global__ void __launch_bounds__(NT) scores_kernel(const T* __restrict__ q1,
 //   MODE kSweepSoftmax : share = p, no demand read or written: plain softmax attention of the
 //                        new token over the cache, the cached step of the reference's softmax
 //                        layers (model.py:112-117)
-//   MODE kSweepVariant : bid (softmax / sigmoid / expshift / sigshift) and share step (inclusive / exclusive / none)
-//                        chosen at run time; the demand advances by p in every case
+//   MODE kSweepVariant : bid (any of the eight) and share step (inclusive / exclusive / none)
+//                        chosen at run time; the demand advances by p in every case.  For an
+//                        f(a) / rowsum(f) bid gmax is the row minimum (minshift) or 0, rinv the
+//                        reciprocal of the row's mass (0 for a row without mass, which bids unif).
 constexpr int kSweepSoftmax = 0, kSweepDilution = 1, kSweepVariant = 2;
 
 template <int MODE>
 __device__ __forceinline__ float key_share(float a, float gmax, float rinv, float eps, float* c_ptr,
-                                           bool fresh, int bid, int share_step, float lshift) {
+                                           bool fresh, int bid, int share_step, float lshift, float unif = 0.f) {
   float p = exp2f(a - gmax) * rinv;
   if (MODE == kSweepSoftmax) return p;
-  if (MODE == kSweepVariant && bid != kBidSoftmax)      // bids without a row sum
+  if (MODE == kSweepVariant && row_sum_bid(bid)) {
+    const float an = a * kLn2;
+    p = fmaf(bid == kBidMinshift ? fmaxf(an - gmax, 0.f) : bid_mass(an, bid), rinv, unif);
+  } else if (MODE == kSweepVariant && bid != kBidSoftmax) {      // bids without a row sum
     p = bid_form(bid) == kBidSigmoid ? 1.f / (1.f + exp2f(lshift - a)) : exp2f(a - lshift);
+  }
   const float c = fresh ? 0.f : *c_ptr;     // a fresh key: no demand yet, whatever the buffer holds
   *c_ptr = c + p;
   if (MODE == kSweepDilution || share_step == kShareInclusive) return p / (c + p + eps);
@@ -201,10 +231,27 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
   const int t = lane % TPK, grp = lane / TPK;
   __shared__ float sred[WARPS];
   __shared__ float sacc[WARPS][D];
-  __shared__ float sstat[2];
+  __shared__ float sstat[3];
 
   // combine the per-chunk statistics of this row (nch <= MAX_CHUNKS <= NT)
-  {
+  if (MODE == kSweepVariant && row_sum_bid(bid)) {
+    // (minimum, mass) per chunk -> the row's minimum, 1 / mass and the uniform fall-back
+    float2 pr = make_float2(INFINITY, 0.f);
+    if (threadIdx.x < nch) pr = part[n * MAX_CHUNKS + threadIdx.x];
+    const float wmin = -warp_max(-pr.x), wsum = warp_sum(pr.y);
+    if (lane == 0) { sred[warp] = wmin; sacc[0][warp] = wsum; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float rmin = INFINITY, mass = 0.f;
+      for (int w = 0; w < WARPS; ++w) { rmin = fminf(rmin, sred[w]); mass += sacc[0][w]; }
+      if (bid == kBidMinshift) mass = fmaxf(mass - (float)len * rmin, 0.f);   // sum(a - rmin)
+      else rmin = 0.f;
+      sstat[0] = rmin;
+      sstat[1] = mass > 0.f ? 1.f / mass : 0.f;
+      sstat[2] = mass > 0.f ? 0.f : 1.f / (float)len;
+    }
+    __syncthreads();
+  } else {
     float2 pr = make_float2(-INFINITY, 0.f);
     if (threadIdx.x < nch) pr = part[n * MAX_CHUNKS + threadIdx.x];
     const float wm = warp_max(pr.x);
@@ -222,10 +269,11 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
       for (int w = 0; w < WARPS; ++w) den += sred[w];
       sstat[0] = gm;
       sstat[1] = 1.f / den;
+      sstat[2] = 0.f;
     }
     __syncthreads();
   }
-  const float gmax = sstat[0], rinv = sstat[1];
+  const float gmax = sstat[0], rinv = sstat[1], unif = sstat[2];
 
   const int k0 = blockIdx.x * chunk;
   const bool appends = vnew != nullptr && len - 1 >= k0 && len - 1 < k0 + chunk;     // as in scores_kernel
@@ -246,7 +294,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (key < k1) {
       share = key_share<MODE>(aff[n * stride + key], gmax, rinv, eps, committed + n * cap + key, false, bid,
-                              share_step, lshift);
+                              share_step, lshift, unif);
       ssh += share;
     }
 #pragma unroll
@@ -263,7 +311,7 @@ __global__ void __launch_bounds__(NT) sweep_kernel(const T* __restrict__ vc, int
     float share = 0.f;
     if (lane == 0) {
       share = key_share<MODE>(aff[n * stride + len - 1], gmax, rinv, eps, committed + n * cap + len - 1, true,
-                              bid, share_step, lshift);
+                              bid, share_step, lshift, unif);
       ssh += share;
     }
     share = __shfl_sync(0xffffffffu, share, 0);

@@ -236,28 +236,67 @@ __device__ __forceinline__ void accum_tile(const float* A, const float* B, float
 // Row statistics of local rows [ib*64, ib*64+64) into shared arrays (rinv = 1/rden;
 // both zero for rows past tq so that their p is exactly zero).
 // A bid without a row sum has no row statistics (kernels_bid.py:259-262): null pointers, and
-// every row's exponent is log2 of the shift.
-__device__ __forceinline__ void load_stats(float* sM, float* sRinv, const float* rmax,
-                                           const float* rden, int64_t n, int ib, int tq, float lshift) {
+// every row's exponent is log2 of the shift.  For the f(a) / rowsum(f) bids sM is the row minimum
+// (minshift) or 0, a row without mass gets rinv = 0 and sU = 1 / (keys in its causal window), the
+// uniform bid it falls back to (kernels_bid.py:206-225); sU is 0 everywhere else.
+__device__ __forceinline__ void load_stats(float* sM, float* sRinv, float* sU, const float* rmax,
+                                           const float* rden, int64_t n, int ib, const Geom& g) {
   if (threadIdx.x < TS) {
     const int i = ib * TS + threadIdx.x;
-    const bool ok = i < tq;
+    const bool ok = i < g.tq;
+    float m = g.lshift, r = ok ? 1.f : 0.f, u = 0.f;
     if (rmax != nullptr) {
-      sM[threadIdx.x] = ok ? rmax[n * tq + i] : 0.f;
-      sRinv[threadIdx.x] = ok ? 1.f / rden[n * tq + i] : 0.f;
-    } else {
-      sM[threadIdx.x] = lshift;
-      sRinv[threadIdx.x] = ok ? 1.f : 0.f;
+      m = ok ? rmax[n * g.tq + i] : 0.f;
+      const float den = ok ? rden[n * g.tq + i] : 0.f;
+      if (row_sum_bid(g.bid)) {
+        r = den > 0.f ? 1.f / den : 0.f;
+        u = (ok && !(den > 0.f)) ? 1.f / (float)(min(g.q_off + i, g.tk - 1) + 1) : 0.f;
+      } else {
+        r = ok ? 1.f / den : 0.f;
+      }
     }
+    sM[threadIdx.x] = m;
+    sRinv[threadIdx.x] = r;
+    sU[threadIdx.x] = u;
   }
 }
 
-// The bid of one raw score (kernels_bid.py:191-204): softmax from the row statistics, or the
-// element-wise sigmoid of the scaled score (m = log2 of the shift, 0 for the plain sigmoid).
+// The bid of one raw score (kernels_bid.py:191-225): softmax from the row statistics, the
+// element-wise sigmoid of the scaled score (m = log2 of the shift, 0 for the plain sigmoid), or
+// f(a) * rinv (+ the uniform fall-back of a row without mass).
 template <bool MMA>
-__device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv) {
+__device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv, float unif) {
+  if (row_sum_bid(g.bid)) {
+    const float a = score * g.scale;
+    const float f = g.bid == kBidMinshift ? fmaxf(a - m, 0.f) : bid_mass(a, g.bid);
+    return fmaf(f, rinv, unif);
+  }
   const float z = score * g.zscale;
   return g.bid == kBidSigmoid ? recip<MMA>(1.f + pow2<MMA>(m - z)) : pow2<MMA>(z - m) * rinv;
+}
+
+// jac, the diagonal factor of dp/da (da = jac * (dp - ghat)), from the raw score
+// (kernels_bid.py:187-225) ...
+template <bool MMA>
+__device__ __forceinline__ float bid_jac_of_score(float score, const Geom& g, float m, float rinv) {
+  const float a = score * g.scale;
+  if (g.bid == kBidRelu) return a > 0.f ? rinv : 0.f;
+  if (g.bid == kBidRelu2) return 2.f * fmaxf(a, 0.f) * rinv;
+  if (g.bid == kBidSoftplus) return rinv / (1.f + expf(-a));
+  if (g.bid == kBidMinshift) return rinv;
+  const float p = bid_value<MMA>(score, g, m, rinv, 0.f);
+  return g.bid == kBidSigmoid ? p * (1.f - p) : p;
+}
+// ... and from the bid itself, where the score is gone: relu p > 0 <=> a > 0; relu2 p = f^2 r so
+// 2 f r = 2 sqrt(p r); softplus f = p / r and sigmoid(a) = 1 - e^-f; minshift r inside the causal
+// window (`inside`).  A row without mass has rinv = 0 and with it a zero Jacobian.
+__device__ __forceinline__ float bid_jac_of_bid(float p, const Geom& g, float rinv, bool inside) {
+  if (g.bid == kBidSoftmax) return p;
+  if (g.bid == kBidSigmoid) return p * (1.f - p);
+  if (g.bid == kBidRelu) return p > 0.f ? rinv : 0.f;
+  if (g.bid == kBidRelu2) return 2.f * sqrtf(p * rinv);
+  if (g.bid == kBidSoftplus) return rinv > 0.f ? -expm1f(-p / rinv) * rinv : 0.f;
+  return inside ? rinv : 0.f;
 }
 
 __device__ __forceinline__ int first_query_block(int jb, int q_off) {
@@ -284,7 +323,8 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
 
   const int r = threadIdx.x >> 2, part = threadIdx.x & 3;
   const int ia = g.q_off + ib * TS + r;
-  float m = -INFINITY, s = 0.f;
+  const bool mass = row_sum_bid(g.bid);          // f(a) / rowsum(f): the sum of f, and the row minimum
+  float m = mass ? INFINITY : -INFINITY, s = 0.f;
   const int last_key = min(g.tk - 1, g.q_off + ib * TS + TS - 1);
   const int njb = last_key / TS + 1;
   for (int jb = 0; jb < njb; ++jb) {
@@ -293,6 +333,17 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
+    if (mass) {                                  // kernels_bid.py:326-338
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const int ja = jb * TS + part * 16 + c;
+        if (ja > ia || ja >= g.tk) continue;
+        const float a = sS[r * SL + part * 16 + c] * g.scale;
+        s += bid_mass(a, g.bid);
+        m = fminf(m, a);
+      }
+      continue;
+    }
     float z[16];
     float tmax = -INFINITY;
 #pragma unroll
@@ -319,6 +370,18 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
     }
   }
   const int i = ib * TS + r;
+  if (mass) {
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    m = fminf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fminf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (g.bid == kBidMinshift) {
+      // sum(a - rmin) over the window (kernels_bid.py:338-340); the rmax buffer holds rmin
+      s = fmaxf(s - (float)(min(ia, g.tk - 1) + 1) * m, 0.f);
+    } else {
+      m = 0.f;
+    }
+  }
   if (part == 0 && i < g.tq) {
     rmax[n * g.tq + i] = m;
     rden[n * g.tq + i] = s;
@@ -341,7 +404,8 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   float* sS = sQ + TS * LD;
   float* sM = sS + TS * SL;
   float* sRinv = sM + TS;
-  float* sPart = sRinv + TS;  // [4][64]
+  float* sU = sRinv + TS;
+  float* sPart = sU + TS;  // [4][64]
   const int nqb = (g.tq + TS - 1) / TS;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
@@ -355,7 +419,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
+    load_stats(sM, sRinv, sU, rmax, rden, n, ib, g);
     __syncthreads();
     score_tile<D, MMA>(sQ, sK, sS);
     __syncthreads();
@@ -364,7 +428,7 @@ __global__ void __launch_bounds__(NT) colsum_scan_kernel(
     for (int rr = 0; rr < 16; ++rr) {
       const int i = seg * 16 + rr;
       const int il = ib * TS + i, ia = g.q_off + il;
-      part += (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sS[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+      part += (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sS[i * SL + col], g, sM[i], sRinv[i], sU[i]) : 0.f;
     }
     sPart[seg * TS + col] = part;
     __syncthreads();
@@ -400,11 +464,12 @@ __global__ void __launch_bounds__(NT) main_kernel(
   float* sRinv = sM + TS;
   float* sRow = sRinv + TS;
   float* sSeg = sRow + TS;   // [4][64] segment sums of the bids
+  float* sU = sSeg + 4 * TS;
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int ib = nqb - 1 - (int)(blockIdx.x / g.n);
   load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-  load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
+  load_stats(sM, sRinv, sU, rmax, rden, n, ib, g);
 
   float acc_o[4][DC], acc_pk[4][DC];
 #pragma unroll
@@ -435,7 +500,7 @@ __global__ void __launch_bounds__(NT) main_kernel(
       for (int rr = 0; rr < 16; ++rr) {
         const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
         const float p =
-            (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+            (ja <= ia && ja < g.tk && il < g.tq) ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i], sU[i]) : 0.f;
         sP[i * SL + col] = p;
         seg_sum += p;
       }
@@ -548,6 +613,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   float* sDbar = sRinv + TS;
   float* sSinv = sDbar + TS;
   float* sSeg = sSinv + TS;   // [8][64] segment sums: bids, then dk_share
+  float* sU = sSeg + 8 * TS;
+  float* sGh = sU + TS;       // f(a) / rowsum(f) bids: the tile's part of ghat_i (pass 1), or ghat_i (pass 2)
   const int nqb = (g.tq + TS - 1) / TS;
   const int ncb = (g.tq + kCarryRows - 1) / kCarryRows;
   const int64_t n = blockIdx.x % g.n;
@@ -568,10 +635,11 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
     load_tile<float, D, MMA>(sDO, dout + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
+    load_stats(sM, sRinv, sU, rmax, rden, n, ib, g);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
       const bool ok = i < g.tq;
+      sGh[threadIdx.x] = (g.ghat_pass == 2 && ok) ? ghat[n * g.tq + i] : 0.f;
       sDbar[threadIdx.x] = ok ? dbar[n * g.tq + i] : 0.f;
       sSinv[threadIdx.x] = ok ? 1.f / (ssum[n * g.tq + i] + g.eps) : 0.f;
     }
@@ -594,7 +662,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
       for (int rr = 0; rr < 16; ++rr) {
         const int i = seg * 16 + rr, il = ib * TS + i, ia = g.q_off + il;
         const bool ok = ja <= ia && ja < g.tk && il < g.tq;
-        const float p = ok ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i]) : 0.f;
+        const float p = ok ? bid_value<MMA>(sP[i * SL + col], g, sM[i], sRinv[i], sU[i]) : 0.f;
         sP[i * SL + col] = p;
         seg_sum += p;
         sDS[i * SL + col] = ok ? (sDS[i * SL + col] - sDbar[i]) * sSinv[i] : 0.f;   // kernels.py:463-464
@@ -640,23 +708,35 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
           r += ds * p * inv * inv;
           direct = ds * inv;
         }
-        const float jac = g.bid == kBidSigmoid ? p * (1.f - p) : p;
-        sDS[i * SL + col] = op_round<MMA>(jac * (direct + r));            // pdp
+        const int il = ib * TS + i;
+        const float jac = bid_jac_of_bid(p, g, sRinv[i], ja <= g.q_off + il && ja < g.tk && il < g.tq);
+        float dp = direct + r;
+        if (g.ghat_pass == 1) {
+          // ghat_i = sum_j p_ij dp_ij (not the row sum of the tile below: jac != p): the 32 columns
+          // of a warp are summed here, two shared atomics per query row and tile
+          const float part_g = warp_sum(p * dp);
+          if ((threadIdx.x & 31) == 0) atomicAdd(&sGh[i], part_g);
+        } else if (g.ghat_pass == 2) {
+          dp -= sGh[i];
+        }
+        sDS[i * SL + col] = op_round<MMA>(jac * dp);                      // pdp
         sP[i * SL + col] = op_round<MMA>(p * inv * sSinv[i]);             // attn, :757
         c += p;
       }
       sufk += (sSeg[4 * TS + col] + sSeg[5 * TS + col]) + (sSeg[6 * TS + col] + sSeg[7 * TS + col]);
     }
     __syncthreads();
-    if (g.normalised) {   // ghat: the row-normalised bid's Jacobian term
+    if (g.normalised && g.ghat_pass != 2) {   // ghat: the row-normalised bid's Jacobian term
       float gs = 0.f;
 #pragma unroll
       for (int c = 0; c < 16; ++c) gs += sDS[row * SL + part * 16 + c];
       gs += __shfl_xor_sync(0xffffffffu, gs, 1);
       gs += __shfl_xor_sync(0xffffffffu, gs, 2);
+      if (g.ghat_pass == 1) gs = sGh[row];
       const int i = ib * TS + row;
       if (part == 0 && i < g.tq) atomicAdd(&ghat[n * g.tq + i], gs);
     }
+    if (g.ghat_pass == 1) continue;           // this pass is for ghat alone
     accum_tile<D, true, MMA>(sP, sDO, acc_dv);
     accum_tile<D, true, MMA>(sDS, sQ, acc_dk);
     float dqp[4][DC];
@@ -687,8 +767,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   }
 }
 
-// Softmax-Jacobian correction for dk (the reference's BC, kernels.py:777-809):
-// dk = dk_main - scale * p^T (ghat q).  grid = n * ceil(t/64).
+// Jacobian correction of a row-normalised bid for dk (the reference's BC, kernels.py:777-809):
+// dk = dk_main - scale * jac^T (ghat q), jac = p for the softmax.  grid = n * ceil(t/64).
 template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
@@ -703,6 +783,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
   float* sM = sP + TS * SL;
   float* sRinv = sM + TS;
   float* sG = sRinv + TS;
+  float* sU = sG + TS;
   const int nqb = (g.tq + TS - 1) / TS;
   const int64_t n = blockIdx.x % g.n;
   const int jb = (int)(blockIdx.x / g.n);
@@ -715,7 +796,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
   for (int ib = first_query_block(jb, g.q_off); ib < nqb; ++ib) {
     __syncthreads();
     load_tile<T, D, MMA>(sQ, q + n * g.tq * D, ib * TS, g.tq);
-    load_stats(sM, sRinv, rmax, rden, n, ib, g.tq, g.lshift);
+    load_stats(sM, sRinv, sU, rmax, rden, n, ib, g);
     if (threadIdx.x < TS) {
       const int i = ib * TS + threadIdx.x;
       sG[threadIdx.x] = i < g.tq ? ghat[n * g.tq + i] : 0.f;
@@ -726,8 +807,7 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
       const int i = idx >> 6, j = idx & 63;
       const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
-      const float z = sP[i * SL + j] * g.zscale;
-      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? op_round<MMA>(pow2<MMA>(z - sM[i]) * sRinv[i] * sG[i]) : 0.f;
+      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? op_round<MMA>(bid_jac_of_score<MMA>(sP[i * SL + j], g, sM[i], sRinv[i]) * sG[i]) : 0.f;
     }
     __syncthreads();
     accum_tile<D, true, MMA>(sP, sQ, acc);
@@ -758,10 +838,10 @@ __global__ void dq_epilogue_kernel(const float* __restrict__ dq_main,
 
 // Shared-memory sizes (bytes) of the kernels above.
 template <int D> constexpr size_t smem_rowstats() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL); }
-template <int D> constexpr size_t smem_colsum() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 2 * TS + 4 * TS); }
-template <int D> constexpr size_t smem_main() { return sizeof(float) * (3 * TS * ld<D>() + TS * SL + 7 * TS); }
-template <int D> constexpr size_t smem_bwd_main() { return sizeof(float) * (4 * TS * ld<D>() + 2 * TS * SL + 12 * TS); }
-template <int D> constexpr size_t smem_bwd_dk() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 3 * TS); }
+template <int D> constexpr size_t smem_colsum() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 3 * TS + 4 * TS); }
+template <int D> constexpr size_t smem_main() { return sizeof(float) * (3 * TS * ld<D>() + TS * SL + 8 * TS); }
+template <int D> constexpr size_t smem_bwd_main() { return sizeof(float) * (4 * TS * ld<D>() + 2 * TS * SL + 14 * TS); }
+template <int D> constexpr size_t smem_bwd_dk() { return sizeof(float) * (2 * TS * ld<D>() + TS * SL + 4 * TS); }
 
 }  // namespace simt
 }  // namespace dil

@@ -4,6 +4,9 @@ model binds instead of `dilution.kernels` whenever its configuration selects an 
 (model.py:142-156).
 
     bid           "softmax"   p = causal softmax of the scaled scores       (the operator)
+                  "relu", "relu2", "softplus", "minshift"
+                              p = f(a) / rowsum(f) with f = relu(a), relu(a)^2, softplus(a),
+                              a - rowmin(a); a row without mass bids uniformly
                   "sigmoid"   p = sigmoid of the scaled score, element-wise, no row sum
                   "expshift"  p = exp(a) / shift: softmax's exponential without the row sum
                   "sigshift"  p = exp(a) / (exp(a) + shift) = sigmoid(a - log shift)
@@ -13,11 +16,11 @@ model binds instead of `dilution.kernels` whenever its configuration selects an 
 
 Same entry points and keyword arguments as the reference module (`bid`, `share_cumsum`,
 `shift` after the arguments of `dilution.kernels`); `shift` is read by the two shifted bids only
-(the model passes its context length, model.py:152-156).  The four bid functions of the reference
-that divide by a row sum of their own (relu, relu2, softplus, minshift) raise ValueError.  The operator itself (softmax, True) is handed to
+(the model passes its context length, model.py:152-156).  The operator itself (softmax, True) is handed to
 `kernels.py`; every other combination goes through the C ABI's dilution_variant_* calls: the
 tcgen05 kernels instantiated for the bid and share step for bf16 tensors of head_dim 64 under
-"bf16", the fp32 tile kernels otherwise (fp32 FMAs for "ieee", tf32 tensor-core products else).
+"bf16" (softmax and the three element-wise bids), the fp32 tile kernels otherwise (fp32 FMAs for
+"ieee", tf32 tensor-core products else; the four f(a) / rowsum(f) bids always).
 """
 
 from __future__ import annotations
@@ -32,14 +35,14 @@ from . import kernels as K
 EPS = K.EPS
 HAS_TRITON = False
 BID_TYPES = ("softmax", "relu", "relu2", "softplus", "minshift", "sigmoid", "expshift", "sigshift")
-BUILT_BIDS = ("softmax", "sigmoid", "expshift", "sigshift")
+BUILT_BIDS = BID_TYPES
 
 _resolve_precision = K._resolve_precision
 
 
 def _bid_code(bid: str) -> int:
     """Code of a bid function (kernels_bid.py:88-91); ValueError for names the reference does not
-    know and for the ones this backend does not build."""
+    know."""
     if bid not in BID_TYPES:
         raise ValueError(f"bid must be one of {BID_TYPES}")
     if bid not in BUILT_BIDS:
@@ -68,14 +71,14 @@ def _variant_forward(q, k, v, dot_precision, bid, share, shift, save_pk, scratch
     (qf, kf, vf), code, prec, n = K._prepare(q, k, v, dot_precision)
     batch, heads, seq, head_dim = q.shape
     f32 = dict(device=q.device, dtype=torch.float32)
-    stats = bid == _lib.BID["softmax"]     # the only built bid with row statistics
+    stats = bid in _lib.ROW_SUM_BIDS       # bids that divide by a row sum have row statistics
     out = torch.empty(n, seq, head_dim, **f32)
     ssum = torch.empty(n, seq, **f32)
     scan = share != 0 or need_total
     total = torch.empty(n, seq, **f32) if scan else None
     rmax = torch.empty(n, seq, **f32) if stats else None
     rden = torch.empty(n, seq, **f32) if stats else None
-    pk = torch.empty(n, seq, head_dim, **f32) if (save_pk and stats) else None
+    pk = torch.empty(n, seq, head_dim, **f32) if (save_pk and bid == _lib.BID["softmax"]) else None
     ncb = (seq + _lib.CARRY_ROWS - 1) // _lib.CARRY_ROWS
     rows = n
     if not keep_carry:
@@ -255,19 +258,6 @@ def dilution_decode_step(
 _PATCHED = ("dilution_attention_forward", "dilution_attention", "dilution_decode_step")
 
 
-def _or_original(name, ours, original):
-    """The installed entry point: this backend for the bids it builds, the module's own function
-    (the reference's Triton kernels) for the rest, so that a configuration this backend does
-    not cover keeps working exactly as before the install."""
-    def entry(*args, bid: str = "softmax", **kwargs):
-        if bid in BUILT_BIDS or original is None:
-            return ours(*args, bid=bid, **kwargs)
-        return original(*args, bid=bid, **kwargs)
-    entry.__name__ = name
-    entry.__doc__ = ours.__doc__
-    return entry
-
-
 def install(target=None):
     """Assign the entry points above onto `dilution.kernels_bid` (or `target`): the module the
     reference's DilutionAttention binds when its configuration selects a bid or share step other
@@ -277,7 +267,7 @@ def install(target=None):
     if getattr(target, "_b200_saved", None) is None:
         target._b200_saved = {name: getattr(target, name, None) for name in _PATCHED + ("HAS_TRITON",)}
     for name in _PATCHED:
-        setattr(target, name, _or_original(name, globals()[name], target._b200_saved[name]))
+        setattr(target, name, globals()[name])
     target.HAS_TRITON = True
     return target
 

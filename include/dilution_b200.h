@@ -50,7 +50,8 @@ extern "C" {
 
 enum { DILUTION_F32 = 0, DILUTION_BF16 = 1 };                       /* dtype */
 enum { DILUTION_PREC_IEEE = 0, DILUTION_PREC_TF32 = 1, DILUTION_PREC_BF16 = 2 }; /* precision */
-enum { DILUTION_BID_SOFTMAX = 0, DILUTION_BID_SIGMOID = 5, DILUTION_BID_EXPSHIFT = 6,
+enum { DILUTION_BID_SOFTMAX = 0, DILUTION_BID_RELU = 1, DILUTION_BID_RELU2 = 2, DILUTION_BID_SOFTPLUS = 3,
+       DILUTION_BID_MINSHIFT = 4, DILUTION_BID_SIGMOID = 5, DILUTION_BID_EXPSHIFT = 6,
        DILUTION_BID_SIGSHIFT = 7 };                                 /* bid codes of kernels_bid.py:84 */
 enum { DILUTION_SHARE_NONE = 0, DILUTION_SHARE_INCLUSIVE = 1, DILUTION_SHARE_EXCLUSIVE = 2 }; /* kernels_bid.py:123-127 */
 enum {
@@ -304,6 +305,11 @@ int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const voi
  * (config.py:68-72; kernels_bid.py of the reference, generated from kernels.py with
  * three more arguments):
  *   bid    DILUTION_BID_SOFTMAX  p = causal softmax of the scaled scores (the operator);
+ *          DILUTION_BID_RELU, _RELU2, _SOFTPLUS, _MINSHIFT
+ *                                p = f(a) / rowsum(f) with f = relu(a), relu(a)^2, softplus(a),
+ *                                a - rowmin(a) (the minimum is a constant in the backward); a row
+ *                                without mass bids uniformly over its causal window, with a zero
+ *                                Jacobian (kernels_bid.py:5-10, 27-33, 206-225);
  *          DILUTION_BID_SIGMOID  p = sigmoid of the scaled score, element-wise, no row
  *                                statistics and no Jacobian correction (kernels_bid.py:196-198);
  *          DILUTION_BID_EXPSHIFT p = exp(a) / shift, softmax's exponential without the row sum
@@ -314,19 +320,23 @@ int dilution_split_heads_rope_at(void* qkv, void* q, void* k, void* v, const voi
  *   share  INCLUSIVE  share = p / (committed + p + eps)   (the operator);
  *          EXCLUSIVE  share = p / (committed + eps)       (earlier queries' demand only);
  *          NONE       share = p                           (no share step: out = p v / rowsum p).
- * The bid functions of kernels_bid.py that divide by a row sum of their own (relu, relu2,
- * softplus, minshift) are not built: DILUTION_ERR_UNSUPPORTED.  bf16 tensors of head_dim 64 under
- * DILUTION_PREC_BF16 run on the tcgen05 kernels, instantiated for the bid and share step;
- * every other dtype, precision and head_dim on the fp32 tile kernels (IEEE: fp32 FMAs;
- * otherwise tf32 tensor-core products).  Checkpoints every DILUTION_CARRY_ROWS query rows.
+ * bf16 tensors of head_dim 64 under DILUTION_PREC_BF16 run on the tcgen05 kernels, instantiated
+ * for the bid and share step (softmax and the three element-wise bids); every other dtype,
+ * precision and head_dim, and the four f(a) / rowsum(f) bids always, on the fp32 tile kernels
+ * (IEEE: fp32 FMAs; otherwise tf32 tensor-core products).  Checkpoints every
+ * DILUTION_CARRY_ROWS query rows.
  *
  * dilution_variant_forward: all forward passes of one call (kernels_bid.py:424-489):
- * rmax, rden (n, t) — softmax bid only, may be NULL for the sigmoid; carry
+ * rmax, rden (n, t) — row statistics of the bids that divide by a row sum (softmax: exponent and
+ * sum; f(a) / rowsum(f): the row minimum for minshift, else 0, and the row's mass), may be NULL
+ * for the element-wise bids; carry
  * (n, ceil(t/32), t); total (n, t) = column totals of p (the decode accumulator after this
  * prefix) — with DILUTION_SHARE_NONE carry and total may both be NULL and the column-sum
  * pass is skipped; out (n, t, d) fp32; ssum (n, t); pk (n, t, d) fp32 or NULL — sum_j p_ij k_j * scale,
  * which dilution_variant_backward needs for the softmax bid with a share step (without one
- * the softmax bid's Jacobian correction vanishes identically and pk is not read).
+ * the Jacobian correction vanishes identically and pk is not read; the f(a) / rowsum(f) bids,
+ * whose Jacobian factor 1 / mass is unbounded, find ghat in a sweep of its own and subtract it
+ * before the factor multiplies, kernels_bid.py:718, so they read no pk either).
  * dilution_variant_backward: dq, dk, dv in the input dtype from an fp32 dout
  * (kernels_bid.py:731-815), given what the forward wrote; scratch of
  * dilution_backward_scratch_bytes(n, t, d).

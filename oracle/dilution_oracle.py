@@ -258,10 +258,11 @@ def decode_step(q1, k_cache, v_cache, committed, length: int) -> torch.Tensor:
 
 
 def variant_bids(q, k, bid: str = "softmax", shift: float = 1.0) -> torch.Tensor:
-    """Bids under a selectable bid function, the four branches of bids_from_affinity this build
-    covers (kernels_bid.py:94-104): "softmax" as kernels.py:60-64; "sigmoid", "expshift"
+    """Bids under a selectable bid function, the branches of bids_from_affinity
+    (kernels_bid.py:94-120): "softmax" as kernels.py:60-64; "sigmoid", "expshift"
     (exp(a) / shift) and "sigshift" (sigmoid(a - log shift)) element-wise with zeros outside the
-    causal window.  (..., T, T) fp32."""
+    causal window; "relu", "relu2", "softplus", "minshift" as f(a) / rowsum(f) with the row
+    minimum held constant and a uniform row where there is no mass.  (..., T, T) fp32."""
     seq, head_dim = q.shape[-2], q.shape[-1]
     aff = (q.float() @ k.float().transpose(-2, -1)) / math.sqrt(head_dim)        # kernels_bid.py:153
     causal = torch.tril(torch.ones(seq, seq, dtype=torch.bool))                  # :154
@@ -273,7 +274,21 @@ def variant_bids(q, k, bid: str = "softmax", shift: float = 1.0) -> torch.Tensor
         return (torch.exp(aff) / float(shift)).masked_fill(~causal, 0.0)         # :101-102
     if bid == "sigshift":
         return torch.sigmoid(aff - math.log(float(shift))).masked_fill(~causal, 0.0)   # :103-104
-    raise ValueError("the oracle restates the softmax, sigmoid, expshift and sigshift bids only")
+    if bid == "relu":
+        f = aff.clamp_min(0.0)                                                   # :105-106
+    elif bid == "relu2":
+        f = aff.clamp_min(0.0) ** 2                                              # :107-108
+    elif bid == "softplus":
+        f = torch.nn.functional.softplus(aff)                                    # :109-110
+    elif bid == "minshift":
+        rmin = aff.masked_fill(~causal, float("inf")).amin(dim=-1, keepdim=True).detach()   # :111-113
+        f = aff - rmin
+    else:
+        raise ValueError(f"unknown bid {bid!r}")
+    f = f.masked_fill(~causal, 0.0)                                              # :116
+    rsum = f.sum(dim=-1, keepdim=True)                                           # :117
+    uniform = causal.to(f.dtype) / causal.sum(dim=-1, keepdim=True).to(f.dtype)  # :118-119
+    return torch.where(rsum > 0, f / rsum.clamp_min(1e-30), uniform)             # :120
 
 
 def variant_dense(q, k, v, bid: str = "softmax", share_cumsum=True, shift: float = 1.0) -> torch.Tensor:
@@ -316,8 +331,17 @@ def variant_decode_step(q1, k_cache, v_cache, committed, length: int, bid: str =
         p = aff.softmax(dim=-1)
     elif bid == "expshift":
         p = torch.exp(aff) / float(shift)
-    else:
+    elif bid in ("sigmoid", "sigshift"):
         p = torch.sigmoid(aff - (math.log(float(shift)) if bid == "sigshift" else 0.0))
+    else:                                                                        # :880-911, :929-945
+        if bid == "minshift":
+            f = aff - aff.amin(dim=-1, keepdim=True)
+        elif bid == "softplus":
+            f = torch.nn.functional.softplus(aff)
+        else:
+            f = aff.clamp_min(0.0) ** (2 if bid == "relu2" else 1)
+        mass = f.sum(dim=-1, keepdim=True)
+        p = torch.where(mass > 0, f / mass.clamp_min(1e-30), torch.full_like(f, 1.0 / length))
     if share_cumsum == "exclusive":
         share = p / (c + EPS)                                                   # :937-938
     elif share_cumsum:

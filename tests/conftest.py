@@ -78,7 +78,10 @@ def _device_status_is_clean(request):
 VARIANTS = [("softmax_exclusive", "softmax", "exclusive"), ("softmax_none", "softmax", False),
             ("sigmoid_inclusive", "sigmoid", True), ("sigmoid_exclusive", "sigmoid", "exclusive"),
             ("sigmoid_none", "sigmoid", False), ("expshift_inclusive", "expshift", True),
-            ("sigshift_inclusive", "sigshift", True), ("sigshift_none", "sigshift", False)]
+            ("sigshift_inclusive", "sigshift", True), ("sigshift_none", "sigshift", False),
+            ("relu_inclusive", "relu", True), ("relu2_inclusive", "relu2", True),
+            ("softplus_inclusive", "softplus", True), ("minshift_inclusive", "minshift", True),
+            ("relu_none", "relu", False), ("softplus_exclusive", "softplus", "exclusive")]
 SHIFT = 80.0      # the divisor of the shifted bids in that fixture; the other bids ignore it
 
 

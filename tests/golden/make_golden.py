@@ -62,7 +62,9 @@ def ref_fwd_bwd(ref, q, k, v, dout):
 
 
 VARIANTS = [("softmax", "exclusive"), ("softmax", False), ("sigmoid", True), ("sigmoid", "exclusive"),
-            ("sigmoid", False), ("expshift", True), ("sigshift", True), ("sigshift", False)]
+            ("sigmoid", False), ("expshift", True), ("sigshift", True), ("sigshift", False),
+            ("relu", True), ("relu2", True), ("softplus", True), ("minshift", True), ("relu", False),
+            ("softplus", "exclusive")]
 SHIFT = 80.0      # the shifted bids' divisor: the model passes its context length (model.py:152-156)
 
 

@@ -58,10 +58,12 @@ def test_argument_validation_happens_before_any_launch():
     assert rc == 1 and b"capacity" in lib.dilution_last_error()
     with pytest.raises(ValueError):
         pkg._lib.check(rc, "dilution_decode")
-    # the bid / share variants: bid codes this build does not cover, share steps that do not exist
+    # the bid / share variants: bid codes and share steps that do not exist
     args = (one, one, one, 0, 0, 1, 8, 64, 0.125, 1e-9)
-    rc = lib.dilution_variant_forward(*args, 1, 1, 1.0, one, one, one, one, one, one, None, None)
-    assert rc == 2 and b"not built" in lib.dilution_last_error()
+    rc = lib.dilution_variant_forward(*args, 8, 1, 1.0, one, one, one, one, one, one, None, None)
+    assert rc == 1 and b"bid" in lib.dilution_last_error()
+    rc = lib.dilution_variant_forward(*args, 3, 1, 1.0, None, None, one, one, one, one, None, None)
+    assert rc == 1 and b"null" in lib.dilution_last_error()      # a bid with a row sum needs rmax / rden
     rc = lib.dilution_variant_forward(*args, 5, 3, 1.0, None, None, one, one, one, one, None, None)
     assert rc == 1 and b"share" in lib.dilution_last_error()
     rc = lib.dilution_variant_forward(*args, 0, 2, 1.0, None, None, one, one, one, one, None, None)

@@ -17,6 +17,7 @@ from oracle import dilution_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+REF = os.path.join(ROOT, "baseline", "_ref")
 
 
 @pytest.fixture(scope="module")
@@ -59,20 +60,31 @@ def test_reference_signature_and_demand_totals(KB, key, bid, share):
     assert rel_err(out2.cpu(), c["out"]) < 1e-4
     assert rel_err(aux["committed_total"].cpu(), c["demand"]) < 1e-5
     assert aux["bid"] == bid and aux["share_cumsum"] == share
-    assert (aux["rmax"] is None) == (bid != "softmax")
+    assert (aux["rmax"] is None) == (bid in ("sigmoid", "expshift", "sigshift"))
 
 
 @pytest.mark.parametrize("key,bid,share", VARIANTS)
 @pytest.mark.parametrize("seq,head_dim", [(257, 64), (700, 32), (130, 128)])
 def test_ragged_lengths_against_oracle(KB, key, bid, share, seq, head_dim):
+    """fp32 tensors under "ieee" and "tf32".  The f(a) / rowsum(f) bids carry a Jacobian factor
+    1 / (row mass) that is unbounded where a row has one barely positive key; the reference bounds
+    their "ieee" gradients at 2e-3 (relu2, which squares the affinities: 5e-3) and does not test
+    them under "tf32" (tests/test_kernels.py:296-316).  Same bounds here; under "tf32", where a
+    rounded product can land on the other side of relu's kink and a row whose only positive
+    affinities are small sees them move by several percent (twice that after relu2's square), relu
+    is held to the output within 2e-2, relu2 within 1e-1, and their gradients within 1e-1."""
     q, k, v, dout = make_inputs(2, 2, seq, head_dim, 300 + seq)
     ref, rdq, rdk, rdv = O.variant_backward(q, k, v, dout, bid, share, SHIFT)
-    for prec, tol in (("ieee", 1e-4), ("tf32", 5e-3)):
+    row_sum = bid in ("relu", "relu2", "softplus", "minshift")
+    kinked = bid in ("relu", "relu2")
+    ieee_grad = 5e-3 if bid == "relu2" else 2e-3 if row_sum else 1e-4
+    for prec, tol, gtol in (("ieee", 1e-4, ieee_grad),
+                            ("tf32", 1e-1 if bid == "relu2" else 2e-2 if kinked else 5e-3, 1e-1 if kinked else 5e-3)):
         qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
         out = KB.dilution_attention(qs, ks, vs, dot_precision=prec, bid=bid, share_cumsum=share, shift=SHIFT)
         out.backward(dout.to(DEV))
         assert rel_err(out.detach().cpu(), ref) < tol, prec
-        check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), tol)
+        check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), gtol)
 
 
 @pytest.mark.parametrize("key,bid,share", VARIANTS)
@@ -88,8 +100,11 @@ def test_bf16_tensors(KB, key, bid, share):
     check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
 
 
+ROW_SUM = ("relu", "relu2", "softplus", "minshift")     # f(a) / rowsum(f): the tile kernels, always
+
+
 @pytest.mark.parametrize("seq", [300, 1100, 2049])
-@pytest.mark.parametrize("key,bid,share", VARIANTS)
+@pytest.mark.parametrize("key,bid,share", [x for x in VARIANTS if x[1] not in ROW_SUM])
 def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, seq):
     """bf16 tensors with heads of 64 under "bf16": the tcgen05 kernels instantiated for the bid and
     share step (not the tile kernels), forward and backward, at ragged lengths."""
@@ -119,6 +134,32 @@ def test_bf16_head_dim_64_runs_on_the_tensor_core_kernels(KB, key, bid, share, s
     assert rel_err(aux["committed_total"].cpu(), O.variant_bids(qb.float(), kb.float(), bid, SHIFT).sum(-2)) < 2e-2
 
 
+@pytest.mark.parametrize("key,bid,share", [x for x in VARIANTS if x[1] in ROW_SUM])
+def test_row_sum_bids_on_bf16_heads_of_64_take_the_tile_kernels(KB, key, bid, share):
+    """The four f(a) / rowsum(f) bids have no tcgen05 instantiation: bf16 tensors with heads of 64
+    run on the tile kernels (tf32 products, exact on bf16 values), with the row statistics, the
+    saved jac K product and the key correction of a row-normalised bid."""
+    pkg = load_package()
+    q, k, v, dout = make_inputs(2, 2, 520, 64, 71, scales=(0.5, 0.5, 1.0, 1.0))
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    ref, rdq, rdk, rdv = O.variant_backward(qb.float(), kb.float(), vb.float(), dout, bid, share, SHIFT)
+    qs, ks, vs = (x.to(DEV).requires_grad_(True) for x in (qb, kb, vb))
+    pkg._lib.profile(True)
+    pkg._lib.profile_collect()
+    out = KB.dilution_attention(qs, ks, vs, dot_precision="bf16", bid=bid, share_cumsum=share, shift=SHIFT)
+    out.backward(dout.to(DEV))
+    torch.cuda.synchronize()
+    names = set(pkg._lib.profile_collect())
+    pkg._lib.profile(False)
+    assert "simt_backward_main" in names and not any(n.startswith("tc_") for n in names), names
+    # under a share step ghat comes from a sweep of its own and is subtracted before the (unbounded)
+    # Jacobian factor multiplies: no correction pass afterwards
+    assert ("simt_backward_ghat" in names) == (share is not False)
+    assert "simt_backward_dk_correction" not in names
+    assert (out.detach().cpu() - ref).abs().max().item() < 2e-2
+    check_grads(share, (qs.grad, ks.grad, vs.grad), (rdq, rdk, rdv), 2e-2)
+
+
 def test_the_operator_itself_goes_to_the_production_kernels(KB):
     pkg = load_package()
     q, k, v, _ = make_inputs(1, 2, 300, 64, 5, scales=(0.5, 0.5, 1.0, 1.0))
@@ -133,11 +174,9 @@ def test_the_operator_itself_goes_to_the_production_kernels(KB):
     assert torch.equal(got, pkg.kernels.dilution_attention_forward(qb, kb, vb, dot_precision="bf16"))
 
 
-def test_unbuilt_and_unknown_bids_raise(KB):
+def test_unknown_bids_raise(KB):
     q, k, v, _ = make_inputs(1, 1, 16, 32, 1)
     q, k, v = (x.to(DEV) for x in (q, k, v))
-    with pytest.raises(ValueError, match="not built"):
-        KB.dilution_attention_forward(q, k, v, bid="relu")
     with pytest.raises(ValueError, match="bid must be one of"):
         KB.dilution_attention(q, k, v, bid="tanh")
     with pytest.raises(ValueError, match="dot_precision must be one of"):
@@ -174,6 +213,35 @@ def test_decode_steps_from_a_prefilled_cache(KB, key, bid, share, dtype, tol):
     assert cd[:, :, prefix + steps:].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("bid", ["relu", "relu2", "softplus", "minshift", "sigmoid", "expshift", "sigshift"])
+def test_bid_model_kernel_matches_eager(bid):
+    """tests/test_kernels.py:361-376 of the reference, as it stands there: an fp32 model with a
+    dilution layer under each bid and a softmax layer, eager logits against the kernel path."""
+    if not os.path.isdir(os.path.join(REF, "dilution")):
+        pytest.skip("no installed copy of the reference under baseline/_ref")
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from dilution.config import ModelConfig
+    from dilution.model import DilutionLM
+    pkg = load_package()
+    torch.manual_seed(7)
+    cfg = ModelConfig(vocab_size=128, n_layers=2, d_model=64, n_heads=2, context_length=96,
+                      layer_attention=["dilution", "softmax"], bid=bid)
+    model = DilutionLM(cfg).to(DEV).eval()
+    idx = torch.randint(0, 128, (2, 96), device=DEV)
+    pkg.install()
+    try:
+        with torch.no_grad():
+            eager, _ = model(idx)
+            before = pkg._lib.launch_count()
+            model.enable_dilution_kernel()
+            fused, _ = model(idx)
+        assert pkg._lib.launch_count() > before
+        assert (eager - fused).abs().max().item() < 5e-2
+    finally:
+        pkg.uninstall()
+
+
 def test_variant_decode_appends_through_the_c_abi():
     """k1 / v1 given: the call writes the new token's rows and treats its demand as zero."""
     pkg = load_package()
@@ -204,15 +272,16 @@ def test_variant_decode_appends_through_the_c_abi():
     assert torch.equal(kd.cpu()[:, :, length - 1], k_new) and torch.equal(vd.cpu()[:, :, length - 1], v_new)
 
 
-REF = os.path.join(ROOT, "baseline", "_ref")
-
-
 @pytest.mark.parametrize("bid,share", [("sigmoid", True), ("sigmoid", "exclusive"), ("softmax", "exclusive"),
-                                       ("softmax", False), ("sigshift", True), ("expshift", True)])
+                                       ("softmax", False), ("sigshift", True), ("expshift", True),
+                                       ("relu", True), ("softplus", True), ("relu2", False)])
 def test_reference_model_with_a_variant_configuration(bid, share):
     """The unmodified DilutionLM configured with an ablation binds dilution.kernels_bid
     (model.py:145-156): after install() its kernel path runs here and must reproduce the eager
-    logits, in the full forward and in prefill + cached steps."""
+    logits, in the full forward and in prefill + cached steps.  (minshift is left to the
+    operator-level tests: the key at a row's minimum gets no mass at all, so in a row of three
+    keys a near-tie that the model's "tf32" products resolve the other way moves the output by
+    O(1) — in the reference's kernels as much as here; under "ieee" the same tensors agree to 1e-7.)"""
     if not os.path.isdir(os.path.join(REF, "dilution")):
         pytest.skip("no installed copy of the reference under baseline/_ref")
     if REF not in sys.path:

@@ -98,8 +98,7 @@ def test_variant_codes_and_errors_follow_the_reference_module():
     assert KB._share_code(True) == 1 and KB._share_code(False) == 0 and KB._share_code("exclusive") == 2
     with pytest.raises(ValueError, match="bid must be one of"):
         KB._bid_code("tanh")
-    with pytest.raises(ValueError, match="not built"):
-        KB._bid_code("softplus")
+    assert KB.BUILT_BIDS == KB.BID_TYPES                                 # every bid of the reference is built
     q = torch.randn(1, 1, 8, 64)
     with pytest.raises(RuntimeError, match="no CPU fallback"):          # the variants have none either
         KB.dilution_attention_forward(q, q, q, bid="sigmoid")
@@ -110,9 +109,9 @@ def test_variant_codes_and_errors_follow_the_reference_module():
                                 torch.zeros(1, 1, 8), 1, bid="sigmoid")
 
 
-def test_variant_install_keeps_the_module_s_own_code_for_unbuilt_bids():
-    """After install() a bid this backend does not build still reaches the module's original
-    function; the built ones reach this backend; uninstall() puts everything back."""
+def test_variant_install_routes_every_bid_here_and_uninstall_puts_the_module_back():
+    """After install() every bid of the reference reaches this backend (none is left to the
+    module's original functions); uninstall() puts everything back."""
     KB = load_package().kernels_bid
     calls = []
 
@@ -124,10 +123,12 @@ def test_variant_install_keeps_the_module_s_own_code_for_unbuilt_bids():
                                  dilution_attention=original, dilution_decode_step=original)
     KB.install(fake)
     assert fake.HAS_TRITON is True
-    assert fake.dilution_attention("q", "k", "v", bid="relu2") == "original" and calls == ["relu2"]
     q = torch.randn(1, 1, 8, 64)
-    with pytest.raises(RuntimeError, match="no CPU fallback"):          # a built bid: this backend, which needs CUDA
-        fake.dilution_attention_forward(q, q, q, bid="sigshift", shift=8.0)
-    assert calls == ["relu2"]
+    for bid in ("relu2", "sigshift", "minshift"):
+        with pytest.raises(RuntimeError, match="no CPU fallback"):      # this backend, which needs CUDA
+            fake.dilution_attention_forward(q, q, q, bid=bid, shift=8.0)
+    with pytest.raises(ValueError, match="bid must be one of"):
+        fake.dilution_attention(q, q, q, bid="tanh")
+    assert calls == []
     KB.uninstall(fake)
     assert fake.dilution_attention is original and fake.HAS_TRITON is False
