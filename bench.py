@@ -367,7 +367,7 @@ def time_shapes(op, dev, shapes, iters=10):
 
 # The bid / share ablations at the shape the reference's ablation configurations train at
 # (configs/bid_8192: context 8192, 8 heads of 64, bf16): (bid, share_cumsum).
-VARIANTS = (("sigmoid", True), ("softmax", "exclusive"), ("softmax", False), ("sigmoid", False))
+VARIANTS = (("sigmoid", True), ("softmax", "exclusive"), ("softmax", False), ("sigmoid", False), ("softplus", True))
 VARIANT_SHAPE = (4, 8, 8192, 64, torch.bfloat16, "bf16")
 
 

@@ -275,19 +275,8 @@ __device__ __forceinline__ float bid_value(float score, const Geom& g, float m, 
   return g.bid == kBidSigmoid ? recip<MMA>(1.f + pow2<MMA>(m - z)) : pow2<MMA>(z - m) * rinv;
 }
 
-// jac, the diagonal factor of dp/da (da = jac * (dp - ghat)), from the raw score
-// (kernels_bid.py:187-225) ...
-template <bool MMA>
-__device__ __forceinline__ float bid_jac_of_score(float score, const Geom& g, float m, float rinv) {
-  const float a = score * g.scale;
-  if (g.bid == kBidRelu) return a > 0.f ? rinv : 0.f;
-  if (g.bid == kBidRelu2) return 2.f * fmaxf(a, 0.f) * rinv;
-  if (g.bid == kBidSoftplus) return rinv / (1.f + expf(-a));
-  if (g.bid == kBidMinshift) return rinv;
-  const float p = bid_value<MMA>(score, g, m, rinv, 0.f);
-  return g.bid == kBidSigmoid ? p * (1.f - p) : p;
-}
-// ... and from the bid itself, where the score is gone: relu p > 0 <=> a > 0; relu2 p = f^2 r so
+// jac, the diagonal factor of dp/da (da = jac * (dp - ghat), kernels_bid.py:187-225), from the bid
+// itself (the tile no longer holds the score): relu p > 0 <=> a > 0; relu2 p = f^2 r so
 // 2 f r = 2 sqrt(p r); softplus f = p / r and sigmoid(a) = 1 - e^-f; minshift r inside the causal
 // window (`inside`).  A row without mass has rinv = 0 and with it a zero Jacobian.
 __device__ __forceinline__ float bid_jac_of_bid(float p, const Geom& g, float rinv, bool inside) {
@@ -767,8 +756,8 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
   }
 }
 
-// Jacobian correction of a row-normalised bid for dk (the reference's BC, kernels.py:777-809):
-// dk = dk_main - scale * jac^T (ghat q), jac = p for the softmax.  grid = n * ceil(t/64).
+// Softmax-Jacobian correction for dk (the reference's BC, kernels.py:777-809):
+// dk = dk_main - scale * p^T (ghat q).  grid = n * ceil(t/64).
 template <typename T, int D, bool MMA>
 __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     const T* __restrict__ q, const T* __restrict__ k, Geom g, const float* __restrict__ rmax,
@@ -807,7 +796,8 @@ __global__ void __launch_bounds__(NT) backward_dk_correction_kernel(
     for (int idx = threadIdx.x; idx < TS * TS; idx += NT) {
       const int i = idx >> 6, j = idx & 63;
       const int ja = jb * TS + j, ia = g.q_off + ib * TS + i;
-      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? op_round<MMA>(bid_jac_of_score<MMA>(sP[i * SL + j], g, sM[i], sRinv[i]) * sG[i]) : 0.f;
+      // (softmax only: jac = p; the f(a) / rowsum(f) bids subtract ghat inside their second sweep)
+      sP[i * SL + j] = (ja <= ia && ja < g.tk) ? op_round<MMA>(bid_value<MMA>(sP[i * SL + j], g, sM[i], sRinv[i], 0.f) * sG[i]) : 0.f;
     }
     __syncthreads();
     accum_tile<D, true, MMA>(sP, sQ, acc);
