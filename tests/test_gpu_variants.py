@@ -248,6 +248,31 @@ def test_bid_model_kernel_matches_eager(bid):
         pkg.uninstall()
 
 
+@pytest.mark.parametrize("dtype,d,length", [(torch.bfloat16, 64, 5000), (torch.float32, 32, 2100), (torch.float32, 128, 1)])
+@pytest.mark.parametrize("bid,share", [("relu", True), ("relu2", "exclusive"), ("softplus", True), ("minshift", True),
+                                       ("minshift", False), ("sigshift", True)])
+def test_decode_long_rows_many_chunks(KB, bid, share, dtype, d, length):
+    """Rows split over many key chunks: the chunk statistics of an f(a) / rowsum(f) bid — (minimum,
+    mass) — are combined across chunks, random demand, spare rows untouched, caches read-only.
+    A single-key row has no mass under minshift: the uniform fall-back (kernels_bid.py:944)."""
+    b, h, cap = 2, 3, length + 5
+    g = torch.Generator().manual_seed(length + d)
+    kc = torch.randn(b, h, cap, d, generator=g).mul(0.5).to(dtype)
+    vc = torch.randn(b, h, cap, d, generator=g).to(dtype)
+    q1 = torch.randn(b, h, 1, d, generator=g).mul(0.5).to(dtype)
+    committed = torch.rand(b, h, cap, generator=g)
+    committed[:, :, length - 1:] = 0
+    want_c = committed.clone()
+    want = O.variant_decode_step(q1, kc, vc, want_c, length, bid, share, SHIFT)
+    dk, dv, dc = kc.to(DEV), vc.to(DEV), committed.to(DEV)
+    got = KB.dilution_decode_step(q1.to(DEV), dk, dv, dc, length, bid=bid, share_cumsum=share, shift=SHIFT)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert rel_err(got.float().cpu(), want) < tol
+    assert rel_err(dc.cpu(), want_c) < 1e-5
+    assert torch.equal(dc[:, :, length:].cpu(), committed[:, :, length:])
+    assert torch.equal(dk.cpu(), kc) and torch.equal(dv.cpu(), vc)
+
+
 def test_variant_decode_appends_through_the_c_abi():
     """k1 / v1 given: the call writes the new token's rows and treats its demand as zero."""
     pkg = load_package()
