@@ -312,6 +312,8 @@ def shard_lm_heads(model, group=None):
         attn = block.attn
         if not hasattr(attn, "c_attn"):
             raise ValueError(f"cannot shard a {type(attn).__name__} layer by heads")
+        if isinstance(attn.c_attn, HeadParallelInput):
+            raise ValueError("this model's heads are split already")
         heads, width = attn.n_heads, attn.d_model
         if heads % world:
             raise ValueError(f"{heads} heads do not divide over {world} ranks")
