@@ -139,12 +139,15 @@ __host__ __device__ constexpr int bid_form(int bid) {
 constexpr int kShareNone = 0, kShareInclusive = 1, kShareExclusive = 2;
 
 // f of the scaled score a for the f(a) / rowsum(f) bids (minshift: the caller subtracts the row minimum).
+// FAST: the special-function unit's exponential and logarithm (next to tf32 products; the absolute
+// error of log(1 + e^-|a|), ~1e-7, is far below what the rounded products already carry).
+template <bool FAST = false>
 __device__ __forceinline__ float bid_mass(float a, int bid) {
   if (bid == kBidMinshift) return a;
   const float f = fmaxf(a, 0.f);
   if (bid == kBidRelu) return f;
   if (bid == kBidRelu2) return f * f;
-  return f + log1pf(expf(-fabsf(a)));                     // stable softplus
+  return f + (FAST ? __logf(1.f + __expf(-fabsf(a))) : log1pf(expf(-fabsf(a))));   // stable softplus
 }
 
 }  // namespace dil

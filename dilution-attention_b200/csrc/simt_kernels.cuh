@@ -268,7 +268,7 @@ template <bool MMA>
 __device__ __forceinline__ float bid_value(float score, const Geom& g, float m, float rinv, float unif) {
   if (row_sum_bid(g.bid)) {
     const float a = score * g.scale;
-    const float f = g.bid == kBidMinshift ? fmaxf(a - m, 0.f) : bid_mass(a, g.bid);
+    const float f = g.bid == kBidMinshift ? fmaxf(a - m, 0.f) : bid_mass<MMA>(a, g.bid);
     return fmaf(f, rinv, unif);
   }
   const float z = score * g.zscale;
@@ -279,12 +279,16 @@ __device__ __forceinline__ float bid_value(float score, const Geom& g, float m, 
 // itself (the tile no longer holds the score): relu p > 0 <=> a > 0; relu2 p = f^2 r so
 // 2 f r = 2 sqrt(p r); softplus f = p / r and sigmoid(a) = 1 - e^-f; minshift r inside the causal
 // window (`inside`).  A row without mass has rinv = 0 and with it a zero Jacobian.
+template <bool MMA>
 __device__ __forceinline__ float bid_jac_of_bid(float p, const Geom& g, float rinv, bool inside) {
   if (g.bid == kBidSoftmax) return p;
   if (g.bid == kBidSigmoid) return p * (1.f - p);
   if (g.bid == kBidRelu) return p > 0.f ? rinv : 0.f;
   if (g.bid == kBidRelu2) return 2.f * sqrtf(p * rinv);
-  if (g.bid == kBidSoftplus) return rinv > 0.f ? -expm1f(-p / rinv) * rinv : 0.f;
+  if (g.bid == kBidSoftplus) {
+    if (!(rinv > 0.f)) return 0.f;
+    return MMA ? (1.f - __expf(-p * fast_rcp(rinv))) * rinv : -expm1f(-p / rinv) * rinv;
+  }
   return inside ? rinv : 0.f;
 }
 
@@ -328,7 +332,7 @@ __global__ void __launch_bounds__(NT) rowstats_kernel(const T* __restrict__ q,
         const int ja = jb * TS + part * 16 + c;
         if (ja > ia || ja >= g.tk) continue;
         const float a = sS[r * SL + part * 16 + c] * g.scale;
-        s += bid_mass(a, g.bid);
+        s += bid_mass<MMA>(a, g.bid);
         m = fminf(m, a);
       }
       continue;
@@ -698,7 +702,7 @@ __global__ void __launch_bounds__(NT) backward_main_kernel(
           direct = ds * inv;
         }
         const int il = ib * TS + i;
-        const float jac = bid_jac_of_bid(p, g, sRinv[i], ja <= g.q_off + il && ja < g.tk && il < g.tq);
+        const float jac = bid_jac_of_bid<MMA>(p, g, sRinv[i], ja <= g.q_off + il && ja < g.tk && il < g.tq);
         float dp = direct + r;
         if (g.ghat_pass == 1) {
           // ghat_i = sum_j p_ij dp_ij (not the row sum of the tile below: jac != p): the 32 columns
